@@ -1,0 +1,161 @@
+/*
+ * mor_b200 -- C ABI of the B200 (sm_100a) fake-quantization library.
+ *
+ * Every entry point takes raw DEVICE pointers, plain sizes and a CUDA stream
+ * (cudaStream_t passed as void*), enqueues its kernels on that stream and returns
+ * without synchronising.  Nothing here allocates: the operators that need scratch
+ * memory take a caller-owned workspace whose size mor_b200_workspace_bytes()
+ * reports.  The return value is a status code; no entry point throws or traps.
+ *
+ * Tensors are contiguous row-major [rows, cols], 16-byte aligned at the base.
+ * dtype MOR_B200_BF16: bf16 in, bf16 out (the reference's only data type).
+ * dtype MOR_B200_FP32: binary32 in, binary32 out with the same arithmetic minus the
+ * bf16 widening/rounding steps (an extension; the reference has no such path).
+ *
+ * Each declaration cites the interface of the reference (boryiings/mor) that it
+ * replaces: the operator schema in mor/csrc/fake_quantize.cpp and the host launcher
+ * in mor/csrc/cuda/fake_quantize.cu.
+ */
+#ifndef MOR_B200_H_
+#define MOR_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* every entry point below is exported from libmor_b200.so; nothing else is */
+#if defined(__GNUC__)
+#define MOR_B200_API __attribute__((visibility("default")))
+#else
+#define MOR_B200_API
+#endif
+
+#define MOR_B200_OK 0
+#define MOR_B200_ERR_INVALID_ARGUMENT (-1) /* bad pointer, size, mode or dtype               */
+#define MOR_B200_ERR_UNSUPPORTED_SHAPE (-2) /* shape/alignment the kernels do not cover       */
+#define MOR_B200_ERR_WORKSPACE (-3)        /* workspace missing or too small                 */
+#define MOR_B200_ERR_LAUNCH (-4)           /* the CUDA runtime refused a launch              */
+#define MOR_B200_ERR_TOO_LARGE (-5)        /* more blocks than a grid can index              */
+
+#define MOR_B200_BF16 0
+#define MOR_B200_FP32 1
+
+/* narrow formats (quant_dequant, fake_quantize_group) */
+#define MOR_B200_E4M3 0
+#define MOR_B200_E5M2 1
+#define MOR_B200_E3M2 2
+#define MOR_B200_E2M3 3
+
+/* operators that need a workspace */
+#define MOR_B200_OP_BLOCK_SCALING 1
+#define MOR_B200_OP_CHANNEL_SCALING 2
+#define MOR_B200_OP_E8MX 3
+#define MOR_B200_OP_AMAX_NNZ 4
+
+MOR_B200_API int mor_b200_version(void);
+MOR_B200_API const char* mor_b200_status_string(int status);
+
+/* Bytes of device workspace for one call of `op` on a [rows, cols] tensor with the
+ * given block shape (0 for operators that need none).  Replaces the torch::empty
+ * temporaries of the reference launchers (fake_quantize.cu:2070-2078, 2272-2277,
+ * 2489-2497). */
+MOR_B200_API size_t mor_b200_workspace_bytes(int op, int64_t rows, int64_t cols, int block_rows, int block_cols);
+
+/* mor::fake_quantize / mor::fake_quantize_no_alloc
+ * (fake_quantize.cpp:12-13; fake_quantize.cu:1763-1907, kernel 684-852).
+ * mode % 10: 1 MoR, 2 block E4M3, 3 block E5M2, 4 current-scaling E4M3, 5 current-
+ * scaling E5M2 (clamp_threshold is then the scale), anything else BF16 pass-through;
+ * mode / 100 > 0 selects MoR's dynamic-range criterion instead of the relative-error
+ * one.  sf_type 1: binary32 scale, 2: power-of-two (E8) scale.
+ * meta: int32 [ceil(rows/block_rows), ceil((cols/2)/(block_cols/2))].
+ * output may alias input. */
+MOR_B200_API int mor_b200_fake_quantize(const void* input, void* output, int32_t* meta, int dtype, int64_t rows, int64_t cols,
+                           int block_rows, int block_cols, double clamp_threshold, int mode, int sf_type,
+                           void* stream);
+
+/* mor::quant_dequant_e4m3 / _e5m2 / _e3m2 / _e2m3 (fake_quantize.cpp:14-17;
+ * fake_quantize.cu:1909-1964, kernel 854-863): binary32 -> format -> binary32, no
+ * scaling, the reference's own cast (NaN on E4M3/E5M2 overflow, clamp for E3M2/E2M3). */
+MOR_B200_API int mor_b200_quant_dequant(const float* input, float* output, int64_t rows, int64_t cols, int format, void* stream);
+
+/* mor::e4m3_with_e8_scale_rne / _rz (fake_quantize.cpp:18-19; fake_quantize.cu:1966-2011,
+ * kernel 865-875): per-element power-of-two scale from 448/x. */
+MOR_B200_API int mor_b200_e4m3_with_e8_scale(const float* input, float* output, int64_t rows, int64_t cols, int rne,
+                                void* stream);
+
+/* mor::fake_quantize_block_scaling[_inplace] (fake_quantize.cpp:20-21;
+ * fake_quantize.cu:2013-2230, kernels 951-1241).  ss_mode 1 global-mantissa, 2 block
+ * amax with power-of-two scale, 3 block amax with binary32 scale, 4 tensor scale
+ * (2 and 3 are that way round in the reference, and here).  block_rows % 32 == 0,
+ * block_cols % 64 == 0.  Scalar outputs are device pointers: meta (1 = E4M3 kept,
+ * 3 = tensor left in BF16), global_amax, global_nnz (int32, or int64 when
+ * nnz_is_int64), global_error.  output == input gives the _inplace operator. */
+MOR_B200_API int mor_b200_block_scaling(const void* input, void* output, int dtype, int64_t rows, int64_t cols, int block_rows,
+                           int block_cols, double e4m3_threshold, int ss_mode, int32_t* meta, float* global_amax,
+                           void* global_nnz, int nnz_is_int64, float* global_error, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
+/* mor::fake_quantize_channel_scaling[_inplace] (fake_quantize.cpp:24-25;
+ * fake_quantize.cu:2399-2660, kernels 1430-1752).  block_rows == 1 (1 x k row groups,
+ * k a multiple of 128, or k in {8,16,32,64} with cols % 128 == 0) or block_cols == 1
+ * (k x 1 column groups, k % 16 == 0, cols % 64 == 0).  Launch geometry is that of the
+ * reference's e2m3 fork (e2m3/fake_quantize_e2m3.cu:2518), under which every group is
+ * visited once. */
+MOR_B200_API int mor_b200_channel_scaling(const void* input, void* output, int dtype, int64_t rows, int64_t cols, int block_rows,
+                             int block_cols, double e4m3_threshold, int ss_mode, int32_t* meta, float* global_amax,
+                             void* global_nnz, int nnz_is_int64, float* global_error, void* workspace,
+                             size_t workspace_bytes, void* stream);
+
+/* mor::fake_quantize_e8mx / _inplace (fake_quantize.cpp:22-23; fake_quantize.cu:2232-2397,
+ * kernels 1243-1428).  quantize_type 1..3 = mantissa bits kept; scaling_strategy 1 =
+ * scale by the tensor amax, anything else = unscaled.  bf16 only. */
+MOR_B200_API int mor_b200_e8mx(const void* input, void* output, int64_t rows, int64_t cols, int quantize_type,
+                  int scaling_strategy, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Extension (no reference operator; element semantics of quantize_kernel's
+ * BLOCK_SCALING modes, fake_quantize.cu:801-823, with the SQDD wrappers :356-379):
+ * single-pass fake-quantize with one scale per 1 x block_cols group, formats E4M3,
+ * E5M2, E2M3, scale binary32 (sf_type 1) or power of two / E8M0 (sf_type 2).
+ * scales (optional, device, one float per group) receives the scale applied. */
+MOR_B200_API int mor_b200_fake_quantize_group(const void* input, void* output, float* scales, int dtype, int64_t rows,
+                                 int64_t cols, int block_cols, int format, int sf_type, void* stream);
+
+/* ---- row-sharded pipeline (extension): the phases of block/channel scaling as separate
+ * calls, so that a caller holding one row slab per GPU can all-reduce the amax (max)
+ * and the non-zero count (sum) and all-gather the block errors between them. ---- */
+
+/* Phase 1 (kernels 951-1049 / 1459-1631): per-block amax into the workspace, slab amax
+ * and non-zero count to amax_out / nnz_out (device). kind = MOR_B200_OP_BLOCK_SCALING or
+ * MOR_B200_OP_CHANNEL_SCALING. */
+MOR_B200_API int mor_b200_scaling_amax(int kind, const void* input, int dtype, int64_t rows, int64_t cols, int block_rows,
+                          int block_cols, float* amax_out, int64_t* nnz_out, void* workspace, size_t workspace_bytes,
+                          void* stream);
+/* Phase 2 (kernels 1095-1176 / 1633-1752): scale, cast, store, per-CTA error sums.
+ * global_amax: device pointer to the amax of the WHOLE tensor.  block_err_out: device
+ * array of mor_b200_scaling_num_errors() floats.  Uses the block amax left in the
+ * workspace by phase 1. */
+MOR_B200_API int mor_b200_scaling_cast(int kind, const void* input, void* output, int dtype, int64_t rows, int64_t cols,
+                          int block_rows, int block_cols, int ss_mode, const float* global_amax, float* block_err_out,
+                          void* workspace, size_t workspace_bytes, void* stream);
+MOR_B200_API int64_t mor_b200_scaling_num_errors(int kind, int64_t rows, int64_t cols, int block_rows, int block_cols);
+/* slots of the reference's error array per stored sum (1, or blocks per CTA) */
+MOR_B200_API int mor_b200_scaling_error_stride(int kind, int block_rows, int block_cols);
+/* Phase 3 (kernels 1178-1241): ordered sum of ALL slabs' errors (concatenated in row
+ * order), error / nnz against the threshold.  Writes meta (1 or 3) and global_error. */
+MOR_B200_API int mor_b200_scaling_finalize(const float* block_err, int64_t n_err, int error_stride, const int64_t* global_nnz,
+                              double e4m3_threshold, int32_t* meta, float* global_error, void* workspace,
+                              size_t workspace_bytes, void* stream);
+/* Phase 4: if *meta == 3, copy the slab's input over its output. */
+MOR_B200_API int mor_b200_scaling_fallback(const void* input, void* output, int64_t n_bytes, const int32_t* meta, void* stream);
+
+/* amax and non-zero count of a flat tensor (kernels 951-1049 without the block array). */
+MOR_B200_API int mor_b200_amax_nnz(const void* input, int dtype, int64_t n_elems, float* amax_out, int64_t* nnz_out,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOR_B200_H_ */

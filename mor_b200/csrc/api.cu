@@ -1,0 +1,330 @@
+// extern "C" surface of libmor_b200 (include/mor_b200.h): argument validation,
+// workspace carving and the fixed kernel sequence of each operator.
+#include "../../include/mor_b200.h"
+
+#include "kernels.cuh"
+
+using namespace morb;
+
+namespace {
+
+constexpr size_t kHead = 256;  // ScalarsWs lives in the first 256 bytes of a workspace
+
+inline size_t round256(size_t n) { return (n + 255) & ~size_t(255); }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+struct Geometry {
+    int64_t n_amax;   // per-block amax entries kept in the workspace
+    int64_t n_err;    // per-CTA error sums
+    int stride;       // slots of the reference's error array per stored sum
+    int status;
+};
+
+// Shapes accepted by the block pipeline: the reference's 32 x 32-thread CTA strides a
+// block in steps of 32 rows x 32 words with no bounds check (ref: 979-987, 1117-1126).
+Geometry block_geometry(int64_t rows, int64_t cols, int br, int bc) {
+    Geometry g{0, 0, 1, kOk};
+    if (rows <= 0 || cols <= 0 || br <= 0 || bc <= 0) { g.status = kErrInvalidArgument; return g; }
+    if (rows % br || cols % bc) { g.status = kErrInvalidArgument; return g; }  // ref: 2019-2020
+    if (br % 32 || bc % 64) { g.status = kErrUnsupportedShape; return g; }
+    g.n_amax = g.n_err = (rows / br) * (cols / bc);
+    return g;
+}
+
+// ref: 2399-2416, 2499-2511 with grid.y = row blocks (e2m3 fork :2518)
+Geometry channel_geometry(int64_t rows, int64_t cols, int br, int bc, int dtype) {
+    Geometry g{0, 0, 1, kOk};
+    if (rows <= 0 || cols <= 0 || br <= 0 || bc <= 0) { g.status = kErrInvalidArgument; return g; }
+    if (!(br == 1 || bc == 1)) { g.status = kErrInvalidArgument; return g; }  // ref: 2501
+    if (rows % br || cols % bc || cols % 2) { g.status = kErrInvalidArgument; return g; }
+    const int epv = dtype == MOR_B200_FP32 ? 4 : 8;
+    if (br == 1) {
+        if (bc < 128) {
+            if (128 % bc || bc > 64 || bc < epv || cols % 128) { g.status = kErrUnsupportedShape; return g; }
+            g.stride = 128 / bc;
+            g.n_amax = 0;  // recomputed from the data inside the cast kernel
+            g.n_err = rows * (cols / 128);
+        } else {
+            if (bc % 128) { g.status = kErrUnsupportedShape; return g; }
+            g.n_amax = g.n_err = rows * (cols / bc);
+        }
+    } else {
+        if (cols % 64 || br % 16) { g.status = kErrUnsupportedShape; return g; }
+        g.stride = 64;
+        g.n_amax = (rows / br) * cols;
+        g.n_err = (rows / br) * (cols / 64);
+    }
+    return g;
+}
+
+Geometry geometry(int kind, int64_t rows, int64_t cols, int br, int bc, int dtype) {
+    if (kind == MOR_B200_OP_BLOCK_SCALING) return block_geometry(rows, cols, br, bc);
+    if (kind == MOR_B200_OP_CHANNEL_SCALING) return channel_geometry(rows, cols, br, bc, dtype);
+    return Geometry{0, 0, 1, kErrInvalidArgument};
+}
+
+size_t ws_bytes_for(const Geometry& g) { return kHead + round256(4 * (size_t)g.n_amax) + round256(4 * (size_t)g.n_err); }
+
+__global__ void export_scalars_kernel(const ScalarsWs* ws, float* amax_out, long long* nnz_out) {
+    if (amax_out) *amax_out = u2f(ws->gamax_bits);
+    if (nnz_out) *nnz_out = (long long)ws->gnnz;
+}
+
+__global__ void __launch_bounds__(256) copy_if_meta3_kernel(const uint4* __restrict__ in, uint4* __restrict__ out,
+                                                            int64_t nvec, int64_t tail_bytes,
+                                                            const int32_t* __restrict__ meta) {
+    if (*meta != 3) return;
+    const int64_t stride = (int64_t)gridDim.x * 256;
+    const int64_t gtid = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    for (int64_t i = gtid; i < nvec; i += stride) out[i] = in[i];
+    if (gtid < tail_bytes) reinterpret_cast<uint8_t*>(out + nvec)[gtid] = reinterpret_cast<const uint8_t*>(in + nvec)[gtid];
+}
+
+int phase_amax(int kind, const void* in, int dtype, int64_t rows, int64_t cols, int br, int bc, const Geometry& g,
+               ScalarsWs* ws, float* block_amax, cudaStream_t st) {
+    int rc = launch_zero_scalars(ws, st);
+    if (rc) return rc;
+    const int is_f32 = dtype == MOR_B200_FP32;
+    if (kind == MOR_B200_OP_CHANNEL_SCALING && g.n_amax == 0) return launch_amax_nnz_flat(in, is_f32, rows * cols, ws, st);
+    return launch_amax_nnz_blocks(in, is_f32, rows, cols, br, bc, block_amax, ws, st);
+}
+
+int phase_cast(int kind, const ScalingArgs& a, bool store, bool skip_if_fallback, cudaStream_t st) {
+    if (kind == MOR_B200_OP_BLOCK_SCALING) return launch_block_err_cast(a, store, skip_if_fallback, st);
+    if (a.brows == 1) return launch_rowgroup_err_cast(a, store, skip_if_fallback, st);
+    return launch_colgroup_err_cast(a, store, skip_if_fallback, st);
+}
+
+int scaling_op(int kind, const void* in, void* out, int dtype, int64_t rows, int64_t cols, int br, int bc, double thr,
+               int ss, int32_t* meta, float* gamax, void* gnnz, int nnz64, float* gerr, void* wsp, size_t wsb,
+               void* stream) {
+    if (!in || !out || (dtype != MOR_B200_BF16 && dtype != MOR_B200_FP32)) return kErrInvalidArgument;
+    if (ss < 1 || ss > 4) return kErrInvalidArgument;  // the reference falls off a switch here (ref: 2120)
+    const Geometry g = geometry(kind, rows, cols, br, bc, dtype);
+    if (g.status) return g.status;
+    if (!aligned16(in) || !aligned16(out)) return kErrUnsupportedShape;
+    if (!wsp || wsb < ws_bytes_for(g) || !aligned16(wsp)) return kErrWorkspace;
+    auto st = static_cast<cudaStream_t>(stream);
+    auto* ws = static_cast<ScalarsWs*>(wsp);
+    ScalingArgs a{};
+    a.in = in; a.out = out; a.is_fp32 = dtype == MOR_B200_FP32; a.rows = rows; a.cols = cols;
+    a.brows = br; a.bcols = bc; a.threshold = (float)thr; a.ss_mode = ss;
+    a.block_amax = reinterpret_cast<float*>(static_cast<char*>(wsp) + kHead);
+    a.block_err = reinterpret_cast<float*>(static_cast<char*>(wsp) + kHead + round256(4 * (size_t)g.n_amax));
+    a.n_err = g.n_err; a.err_slot_stride = g.stride; a.ws = ws; a.ext_gamax = nullptr;
+    int rc = phase_amax(kind, in, dtype, rows, cols, br, bc, g, ws, a.block_amax, st);
+    if (rc) return rc;
+    const bool inplace = in == out;
+    // In place the input must survive until the tensor-level decision is known: sum the
+    // errors without storing, decide, then cast only if the tensor is kept in E4M3.
+    rc = phase_cast(kind, a, /*store=*/!inplace, false, st);
+    if (rc) return rc;
+    rc = launch_finalize(a, nullptr, meta, gamax, gnnz, nnz64, gerr, st);
+    if (rc) return rc;
+    if (inplace) {
+        ScalingArgs b = a;
+        b.block_err = a.block_err;  // rewritten with identical values
+        return phase_cast(kind, b, /*store=*/true, /*skip_if_fallback=*/true, st);
+    }
+    return launch_fallback_copy(a, st);
+}
+
+}  // namespace
+
+extern "C" {
+
+int mor_b200_version(void) { return 100; }
+
+const char* mor_b200_status_string(int status) {
+    switch (status) {
+        case kOk: return "ok";
+        case kErrInvalidArgument: return "invalid argument";
+        case kErrUnsupportedShape: return "unsupported shape or alignment";
+        case kErrWorkspace: return "workspace missing, misaligned or too small";
+        case kErrLaunch: return "CUDA launch failed";
+        case kErrTooLarge: return "too many blocks for one grid";
+        default: return "unknown status";
+    }
+}
+
+size_t mor_b200_workspace_bytes(int op, int64_t rows, int64_t cols, int br, int bc) {
+    if (op == MOR_B200_OP_E8MX || op == MOR_B200_OP_AMAX_NNZ) return kHead;
+    // sized for the wider of the two dtypes' geometries (they only differ in which small groups are accepted)
+    Geometry g = geometry(op, rows, cols, br, bc, MOR_B200_BF16);
+    if (g.status) g = geometry(op, rows, cols, br, bc, MOR_B200_FP32);
+    if (g.status) return 0;
+    return ws_bytes_for(g);
+}
+
+int mor_b200_fake_quantize(const void* in, void* out, int32_t* meta, int dtype, int64_t rows, int64_t cols, int br,
+                           int bc, double clamp, int mode, int sf_type, void* stream) {
+    if (!in || !out || !meta) return kErrInvalidArgument;
+    if (dtype != MOR_B200_BF16 && dtype != MOR_B200_FP32) return kErrInvalidArgument;
+    if (rows <= 0 || cols <= 0 || br <= 0 || bc < 2 || mode < 0) return kErrInvalidArgument;
+    if (cols % 2 || bc % 2) return kErrInvalidArgument;  // ref: 1767; odd block widths split a packed word
+    if (sf_type != kSfFp32 && sf_type != kSfE8) return kErrInvalidArgument;
+    const int esz = dtype == MOR_B200_FP32 ? 4 : 2;
+    if ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & (2 * esz - 1)) return kErrUnsupportedShape;
+    auto st = static_cast<cudaStream_t>(stream);
+    const int qm = mode % 10;
+    const int dyn = mode / 100 > 0;
+    const int64_t gx = (cols / 2 - 1) / (bc / 2) + 1, gy = (rows - 1) / br + 1, n_meta = gx * gy;
+    if (qm == 4 || qm == 5) {
+        if (dtype != MOR_B200_BF16 || !aligned16(in) || !aligned16(out)) return kErrUnsupportedShape;
+        return launch_cast_uniform(in, out, rows * cols, qm == 4 ? kE4M3 : kE5M2, sf_type, (float)clamp, meta, n_meta,
+                                   qm == 4 ? 1 : 2, st);
+    }
+    if (qm != 1 && qm != 2 && qm != 3) {  // ref: 1831: every other code is the BF16 pass-through
+        if (!aligned16(in) || !aligned16(out)) return kErrUnsupportedShape;
+        return launch_copy(in, out, rows * cols * esz, meta, n_meta, 3, st);
+    }
+    if (qm == 1 && (int64_t)br * bc > 1024 && (br < 32 || bc < 32)) return kErrUnsupportedShape;  // ref: 1781-1784
+    // per-row groups in the fixed-format modes take the single-pass group kernels
+    static const bool force_generic = getenv("MOR_B200_FORCE_GENERIC") != nullptr;
+    if (qm != 1 && br == 1 && cols % bc == 0 && aligned16(in) && aligned16(out) && !force_generic) {
+        const int rc = launch_fq_group(in, out, dtype == MOR_B200_FP32, nullptr, meta, qm == 2 ? 1 : 2, rows, cols, bc,
+                                       qm == 2 ? kE4M3 : kE5M2, sf_type, st);
+        if (rc != kErrUnsupportedShape) return rc;
+    }
+    return launch_fq_block(in, out, dtype == MOR_B200_FP32, meta, rows, cols, br, bc, (float)clamp, qm, dyn, sf_type, st);
+}
+
+int mor_b200_quant_dequant(const float* in, float* out, int64_t rows, int64_t cols, int format, void* stream) {
+    if (!in || !out || rows <= 0 || cols <= 0) return kErrInvalidArgument;
+    return launch_quant_dequant(in, out, rows * cols, format, static_cast<cudaStream_t>(stream));
+}
+
+int mor_b200_e4m3_with_e8_scale(const float* in, float* out, int64_t rows, int64_t cols, int rne, void* stream) {
+    if (!in || !out || rows <= 0 || cols <= 0) return kErrInvalidArgument;
+    return launch_e4m3_e8_scale(in, out, rows * cols, rne, static_cast<cudaStream_t>(stream));
+}
+
+int mor_b200_block_scaling(const void* in, void* out, int dtype, int64_t rows, int64_t cols, int br, int bc,
+                           double thr, int ss, int32_t* meta, float* gamax, void* gnnz, int nnz64, float* gerr,
+                           void* ws, size_t wsb, void* stream) {
+    return scaling_op(MOR_B200_OP_BLOCK_SCALING, in, out, dtype, rows, cols, br, bc, thr, ss, meta, gamax, gnnz, nnz64,
+                      gerr, ws, wsb, stream);
+}
+
+int mor_b200_channel_scaling(const void* in, void* out, int dtype, int64_t rows, int64_t cols, int br, int bc,
+                             double thr, int ss, int32_t* meta, float* gamax, void* gnnz, int nnz64, float* gerr,
+                             void* ws, size_t wsb, void* stream) {
+    return scaling_op(MOR_B200_OP_CHANNEL_SCALING, in, out, dtype, rows, cols, br, bc, thr, ss, meta, gamax, gnnz,
+                      nnz64, gerr, ws, wsb, stream);
+}
+
+int mor_b200_e8mx(const void* in, void* out, int64_t rows, int64_t cols, int qtype, int strategy, void* wsp,
+                  size_t wsb, void* stream) {
+    if (!in || !out || rows <= 0 || cols <= 0 || cols % 2) return kErrInvalidArgument;
+    if (qtype < 1 || qtype > 3) return kErrInvalidArgument;
+    if (!aligned16(in) || !aligned16(out)) return kErrUnsupportedShape;
+    if (!wsp || wsb < kHead || !aligned16(wsp)) return kErrWorkspace;
+    auto st = static_cast<cudaStream_t>(stream);
+    auto* ws = static_cast<ScalarsWs*>(wsp);
+    int rc = launch_zero_scalars(ws, st);
+    if (rc) return rc;
+    rc = launch_amax_nnz_flat(in, 0, rows * cols, ws, st);
+    if (rc) return rc;
+    return launch_e8mx_cast(in, out, rows * cols, qtype, strategy, &ws->gamax_bits, st);
+}
+
+int mor_b200_fake_quantize_group(const void* in, void* out, float* scales, int dtype, int64_t rows, int64_t cols,
+                                 int bc, int format, int sf_type, void* stream) {
+    if (!in || !out || rows <= 0 || cols <= 0 || bc <= 0) return kErrInvalidArgument;
+    if (dtype != MOR_B200_BF16 && dtype != MOR_B200_FP32) return kErrInvalidArgument;
+    if (sf_type != kSfFp32 && sf_type != kSfE8) return kErrInvalidArgument;
+    if (cols % bc) return kErrInvalidArgument;
+    if (!aligned16(in) || !aligned16(out)) return kErrUnsupportedShape;
+    return launch_fq_group(in, out, dtype == MOR_B200_FP32, scales, nullptr, 0, rows, cols, bc, format, sf_type,
+                           static_cast<cudaStream_t>(stream));
+}
+
+int mor_b200_scaling_amax(int kind, const void* in, int dtype, int64_t rows, int64_t cols, int br, int bc,
+                          float* amax_out, int64_t* nnz_out, void* wsp, size_t wsb, void* stream) {
+    if (!in || (dtype != MOR_B200_BF16 && dtype != MOR_B200_FP32)) return kErrInvalidArgument;
+    const Geometry g = geometry(kind, rows, cols, br, bc, dtype);
+    if (g.status) return g.status;
+    if (!aligned16(in)) return kErrUnsupportedShape;
+    if (!wsp || wsb < ws_bytes_for(g) || !aligned16(wsp)) return kErrWorkspace;
+    auto st = static_cast<cudaStream_t>(stream);
+    auto* ws = static_cast<ScalarsWs*>(wsp);
+    const int rc = phase_amax(kind, in, dtype, rows, cols, br, bc, g, ws, reinterpret_cast<float*>(static_cast<char*>(wsp) + kHead), st);
+    if (rc) return rc;
+    export_scalars_kernel<<<1, 1, 0, st>>>(ws, amax_out, reinterpret_cast<long long*>(nnz_out));
+    return check_launch();
+}
+
+int mor_b200_scaling_cast(int kind, const void* in, void* out, int dtype, int64_t rows, int64_t cols, int br, int bc,
+                          int ss, const float* global_amax, float* block_err_out, void* wsp, size_t wsb,
+                          void* stream) {
+    if (!in || !out || !global_amax || !block_err_out) return kErrInvalidArgument;
+    if (dtype != MOR_B200_BF16 && dtype != MOR_B200_FP32) return kErrInvalidArgument;
+    if (ss < 1 || ss > 4) return kErrInvalidArgument;
+    const Geometry g = geometry(kind, rows, cols, br, bc, dtype);
+    if (g.status) return g.status;
+    if (!aligned16(in) || !aligned16(out)) return kErrUnsupportedShape;
+    if (!wsp || wsb < ws_bytes_for(g) || !aligned16(wsp)) return kErrWorkspace;
+    ScalingArgs a{};
+    a.in = in; a.out = out; a.is_fp32 = dtype == MOR_B200_FP32; a.rows = rows; a.cols = cols;
+    a.brows = br; a.bcols = bc; a.threshold = 0.0f; a.ss_mode = ss;
+    a.block_amax = reinterpret_cast<float*>(static_cast<char*>(wsp) + kHead);
+    a.block_err = block_err_out;
+    a.n_err = g.n_err; a.err_slot_stride = g.stride; a.ws = static_cast<ScalarsWs*>(wsp); a.ext_gamax = global_amax;
+    return phase_cast(kind, a, /*store=*/true, false, static_cast<cudaStream_t>(stream));
+}
+
+int64_t mor_b200_scaling_num_errors(int kind, int64_t rows, int64_t cols, int br, int bc) {
+    Geometry g = geometry(kind, rows, cols, br, bc, MOR_B200_BF16);
+    if (g.status) g = geometry(kind, rows, cols, br, bc, MOR_B200_FP32);
+    return g.status ? -1 : g.n_err;
+}
+
+int mor_b200_scaling_error_stride(int kind, int br, int bc) {
+    if (kind == MOR_B200_OP_BLOCK_SCALING) return 1;
+    if (kind != MOR_B200_OP_CHANNEL_SCALING) return -1;
+    if (br == 1) return (bc < 128 && bc > 0 && 128 % bc == 0) ? 128 / bc : 1;
+    return 64;
+}
+
+int mor_b200_scaling_finalize(const float* block_err, int64_t n_err, int stride, const int64_t* global_nnz, double thr,
+                              int32_t* meta, float* global_error, void* wsp, size_t wsb, void* stream) {
+    if (!block_err || n_err <= 0 || !global_nnz || !meta) return kErrInvalidArgument;
+    if (stride < 1 || stride > 64 || (stride & (stride - 1))) return kErrInvalidArgument;
+    if (!wsp || wsb < kHead || !aligned16(wsp)) return kErrWorkspace;
+    ScalingArgs a{};
+    a.block_err = const_cast<float*>(block_err);
+    a.n_err = n_err; a.err_slot_stride = stride; a.threshold = (float)thr; a.ws = static_cast<ScalarsWs*>(wsp);
+    return launch_finalize(a, reinterpret_cast<const long long*>(global_nnz), meta, nullptr, nullptr, 0, global_error,
+                           static_cast<cudaStream_t>(stream));
+}
+
+int mor_b200_scaling_fallback(const void* in, void* out, int64_t n_bytes, const int32_t* meta, void* stream) {
+    if (!in || !out || !meta || n_bytes < 0) return kErrInvalidArgument;
+    if (in == out || n_bytes == 0) return kOk;
+    if (!aligned16(in) || !aligned16(out)) return kErrUnsupportedShape;
+    const int64_t nvec = n_bytes / 16;
+    int64_t grid = (nvec + 255) / 256;
+    const int64_t cap = (int64_t)sm_count() * 8;
+    if (grid > cap) grid = cap;
+    if (grid < 1) grid = 1;
+    copy_if_meta3_kernel<<<(unsigned)grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(in), static_cast<uint4*>(out), nvec, n_bytes % 16, meta);
+    return check_launch();
+}
+
+int mor_b200_amax_nnz(const void* in, int dtype, int64_t n, float* amax_out, int64_t* nnz_out, void* wsp, size_t wsb,
+                      void* stream) {
+    if (!in || n <= 0 || (dtype != MOR_B200_BF16 && dtype != MOR_B200_FP32)) return kErrInvalidArgument;
+    if (!aligned16(in)) return kErrUnsupportedShape;
+    if (!wsp || wsb < kHead || !aligned16(wsp)) return kErrWorkspace;
+    auto st = static_cast<cudaStream_t>(stream);
+    auto* ws = static_cast<ScalarsWs*>(wsp);
+    int rc = launch_zero_scalars(ws, st);
+    if (rc) return rc;
+    rc = launch_amax_nnz_flat(in, dtype == MOR_B200_FP32, n, ws, st);
+    if (rc) return rc;
+    export_scalars_kernel<<<1, 1, 0, st>>>(ws, amax_out, reinterpret_cast<long long*>(nnz_out));
+    return check_launch();
+}
+
+}  // extern "C"

@@ -1,0 +1,284 @@
+// Kernels whose scale is the same for the whole tensor (or absent): the
+// CURRENT_SCALING modes of fake_quantize, the BF16 pass-through, the E8Mx cast and
+// the binary32 test operators.  One HBM read and one HBM write per element,
+// 16-byte accesses, persistent grid-stride loops sized to the SM count.
+#include "kernels.cuh"
+
+namespace morb {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;
+
+// Output of scale-cast-descale for a FIXED binary32 scale is a pure function of the
+// narrow-float code, so each CTA tabulates it once with the exact IEEE division of
+// the reference (ref: 310-316, 46-60) and the hot loop is multiply, cvt, table look-up.
+template <int FMT>
+__device__ __forceinline__ void build_lut_bf16(uint16_t* lut, float s) {
+    for (int c = threadIdx.x; c < 256; c += blockDim.x) {
+        const float q = h_lo_to_f32(codes_to_h2<FMT>((uint32_t)c));
+        lut[c] = (uint16_t)f32_to_bf16_bits(__fdiv_rn(q, s));
+    }
+    __syncthreads();
+}
+
+template <int FMT, int SF>
+__global__ void __launch_bounds__(kThreads) cast_uniform_bf16_kernel(const uint4* __restrict__ in,
+                                                                     uint4* __restrict__ out, int64_t nvec,
+                                                                     int64_t n_tail_words, float s,
+                                                                     int32_t* __restrict__ meta, int64_t n_meta,
+                                                                     int32_t meta_code) {
+    __shared__ uint16_t lut[256];
+    if constexpr (SF == kSfFp32) build_lut_bf16<FMT>(lut, s);
+    const int e8 = e8_of_scale(s);
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    const int64_t gtid = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    for (int64_t m = gtid; m < n_meta; m += stride) meta[m] = meta_code;
+
+    auto word = [&](uint32_t w) -> uint32_t {
+        if constexpr (SF == kSfFp32) {
+            const uint32_t c = cvt_codes<FMT>(__fmul_rn(bf16_hi(w), s), __fmul_rn(bf16_lo(w), s));
+            return ((uint32_t)lut[c >> 8] << 16) | lut[c & 0xFFu];
+        } else {
+            float rh, rl;
+            sqdd_e8_pair<FMT>(bf16_hi(w), bf16_lo(w), e8, rh, rl);
+            return pack_bf16(rh, rl);
+        }
+    };
+
+    for (int64_t i = gtid; i < nvec; i += stride * kUnroll) {
+        uint4 v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+            if (i + u * stride < nvec) v[u] = ld_stream(in + i + u * stride);
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+            if (i + u * stride < nvec) {
+                uint4 r;
+                r.x = word(v[u].x); r.y = word(v[u].y); r.z = word(v[u].z); r.w = word(v[u].w);
+                st_stream(out + i + u * stride, r);
+            }
+    }
+    if (gtid < n_tail_words) {
+        const uint32_t* tin = reinterpret_cast<const uint32_t*>(in + nvec);
+        uint32_t* tout = reinterpret_cast<uint32_t*>(out + nvec);
+        tout[gtid] = word(tin[gtid]);
+    }
+}
+
+__global__ void __launch_bounds__(kThreads) copy_kernel(const uint4* __restrict__ in, uint4* __restrict__ out,
+                                                        int64_t nvec, int64_t n_tail_bytes,
+                                                        int32_t* __restrict__ meta, int64_t n_meta,
+                                                        int32_t meta_code) {
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    const int64_t gtid = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    for (int64_t m = gtid; m < n_meta; m += stride) meta[m] = meta_code;
+    if (in == out) return;
+    for (int64_t i = gtid; i < nvec; i += stride * kUnroll) {
+        uint4 v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+            if (i + u * stride < nvec) v[u] = ld_stream(in + i + u * stride);
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+            if (i + u * stride < nvec) st_stream(out + i + u * stride, v[u]);
+    }
+    if (gtid < n_tail_bytes) {
+        reinterpret_cast<uint8_t*>(out + nvec)[gtid] = reinterpret_cast<const uint8_t*>(in + nvec)[gtid];
+    }
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(kThreads) quant_dequant_kernel(const float* __restrict__ in,
+                                                                 float* __restrict__ out, int64_t n) {
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride)
+        out[i] = narrow_custom_fmt<FMT>(in[i]);
+}
+
+// ref: 865-875 + 248-306 with the custom E4M3 cast.  The per-element scale is
+// 448.0 / x evaluated in double (the literal is a double) and narrowed to binary32.
+template <bool RNE>
+__global__ void __launch_bounds__(kThreads) e4m3_e8_scale_kernel(const float* __restrict__ in,
+                                                                 float* __restrict__ out, int64_t n) {
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
+        const float x = in[i];
+        const float s = (float)__ddiv_rn(448.0, (double)x);
+        const uint32_t sb = f2u(s), xb = f2u(x);
+        int e8 = (int)((sb >> 23) & 0xFFu) - 127;
+        const int xexp = (int)((xb >> 23) & 0xFFu);
+        const uint32_t xman = xb & 0x7FFFFFu;
+        if constexpr (RNE) {
+            const uint32_t sman = sb & 0x7FFFFFu;
+            const uint32_t guard = (sman >> 22) & 1u;
+            const uint32_t sticky = (sman & ((1u << 22) - 1u)) != 0;
+            // 6815744 = 0b1101 << 19: the largest mantissa that still rounds down to 1.75
+            if (guard && xman <= 6815744u && xexp + e8 < 135 && (sticky | ((uint32_t)e8 & 1u))) e8 += 1;
+        }
+        const float q = narrow_custom_fmt<kE4M3>(e8_shift_field(x, e8));
+        out[i] = e8_shift_field(q, -e8);
+    }
+}
+
+// ref: 1243-1327: keep the exponent, round the mantissa to M bits.  The reference's
+// threshold ladder is round-to-nearest-even on the top seven mantissa bits: index j
+// is kept while man <= j*step + step/2 (even j) or that minus 65536 (odd j).
+template <int M>
+__device__ __forceinline__ float e8m_round(float v) {
+    const uint32_t b = f2u(v);
+    uint32_t e = (b >> 23) & 0xFFu, man = b & 0x7FFFFFu;
+    if (e == 0) man = 0;
+    else if (e != 255) {
+        constexpr uint32_t step = 0x800000u >> M;
+        constexpr uint32_t steps = 1u << M;
+        uint32_t k = steps;
+#pragma unroll
+        for (int j = (int)steps - 1; j >= 0; --j) {
+            const uint32_t lim = (uint32_t)j * step + step / 2 - ((j & 1) ? 65536u : 0u);
+            if (man <= lim) k = (uint32_t)j;
+        }
+        if (k < steps) man = k * step;
+        else {
+            man = 0;
+            e += 1;
+            if (e == 255) { e = 254; man = (steps - 1) * step; }
+        }
+    }
+    return u2f((b & 0x80000000u) | (e << 23) | man);
+}
+
+// ref: 1335-1359
+template <int M>
+__device__ __forceinline__ float e8mx_scale(float gamax, int strategy) {
+    if (strategy != 1) return 1.0f;
+    const uint32_t e = (f2u(gamax) >> 23) + 1;
+    const float fp_max = u2f((e << 23) | (((1u << M) - 1u) << (23 - M)));
+    float s = __fdiv_rn(fp_max, gamax);
+    if (s >= 2.0f) s = __fdiv_rn(s, 2.0f);
+    return s;
+}
+
+template <int M>
+__global__ void __launch_bounds__(kThreads) e8mx_cast_kernel(const uint4* __restrict__ in, uint4* __restrict__ out,
+                                                             int64_t nvec, int64_t n_tail_words, int strategy,
+                                                             const uint32_t* __restrict__ gamax_bits) {
+    const float s = e8mx_scale<M>(u2f(*gamax_bits), strategy);
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    const int64_t gtid = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    auto one = [&](float x) -> float {
+        const float v = __fmul_rn(x, s);
+        float d = 0.0f;
+        if (v != 0.0f) d = e8m_round<M>(v);
+        return __fdiv_rn(d, s);
+    };
+    auto word = [&](uint32_t w) -> uint32_t { return pack_bf16(one(bf16_hi(w)), one(bf16_lo(w))); };
+    for (int64_t i = gtid; i < nvec; i += stride * kUnroll) {
+        uint4 v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+            if (i + u * stride < nvec) v[u] = ld_stream(in + i + u * stride);
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+            if (i + u * stride < nvec) {
+                uint4 r;
+                r.x = word(v[u].x); r.y = word(v[u].y); r.z = word(v[u].z); r.w = word(v[u].w);
+                st_stream(out + i + u * stride, r);
+            }
+    }
+    if (gtid < n_tail_words) {
+        const uint32_t* tin = reinterpret_cast<const uint32_t*>(in + nvec);
+        uint32_t* tout = reinterpret_cast<uint32_t*>(out + nvec);
+        tout[gtid] = word(tin[gtid]);
+    }
+}
+
+int grid_for(int64_t work_items_per_thread_unit) {
+    // work_items = number of per-thread loop slots; at most 8 CTAs of 256 threads per SM
+    const int64_t want = (work_items_per_thread_unit + kThreads - 1) / kThreads;
+    const int64_t cap = (int64_t)sm_count() * 8;
+    int64_t g = want < cap ? want : cap;
+    if (g < 1) g = 1;
+    return (int)g;
+}
+
+}  // namespace
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (cached[dev] == 0) {
+        int n = 0;
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        cached[dev] = n > 0 ? n : 148;
+    }
+    return cached[dev];
+}
+
+int check_launch() { return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch; }
+
+int launch_cast_uniform(const void* in, void* out, int64_t n_elems, int fmt, int sf_type, float scale,
+                        int32_t* meta, int64_t n_meta, int32_t meta_code, cudaStream_t st) {
+    const int64_t nvec = n_elems / 8;
+    const int64_t tail_words = (n_elems % 8) / 2;
+    const int g = grid_for(nvec > n_meta ? nvec : n_meta);
+    auto* i4 = static_cast<const uint4*>(in);
+    auto* o4 = static_cast<uint4*>(out);
+#define MORB_GO(F, S) cast_uniform_bf16_kernel<F, S><<<g, kThreads, 0, st>>>(i4, o4, nvec, tail_words, scale, meta, n_meta, meta_code)
+    if (fmt == kE4M3 && sf_type == kSfFp32) MORB_GO(kE4M3, kSfFp32);
+    else if (fmt == kE4M3 && sf_type == kSfE8) MORB_GO(kE4M3, kSfE8);
+    else if (fmt == kE5M2 && sf_type == kSfFp32) MORB_GO(kE5M2, kSfFp32);
+    else if (fmt == kE5M2 && sf_type == kSfE8) MORB_GO(kE5M2, kSfE8);
+    else return kErrInvalidArgument;
+#undef MORB_GO
+    return check_launch();
+}
+
+int launch_copy(const void* in, void* out, int64_t n_bytes, int32_t* meta, int64_t n_meta, int32_t meta_code,
+                cudaStream_t st) {
+    const int64_t nvec = n_bytes / 16;
+    const int g = grid_for(nvec > n_meta ? nvec : n_meta);
+    copy_kernel<<<g, kThreads, 0, st>>>(static_cast<const uint4*>(in), static_cast<uint4*>(out), nvec, n_bytes % 16,
+                                        meta, n_meta, meta_code);
+    return check_launch();
+}
+
+int launch_quant_dequant(const float* in, float* out, int64_t n, int fmt, cudaStream_t st) {
+    const int g = grid_for(n);
+    switch (fmt) {
+        case kE4M3: quant_dequant_kernel<kE4M3><<<g, kThreads, 0, st>>>(in, out, n); break;
+        case kE5M2: quant_dequant_kernel<kE5M2><<<g, kThreads, 0, st>>>(in, out, n); break;
+        case kE3M2: quant_dequant_kernel<kE3M2><<<g, kThreads, 0, st>>>(in, out, n); break;
+        case kE2M3: quant_dequant_kernel<kE2M3><<<g, kThreads, 0, st>>>(in, out, n); break;
+        default: return kErrInvalidArgument;
+    }
+    return check_launch();
+}
+
+int launch_e4m3_e8_scale(const float* in, float* out, int64_t n, int rne, cudaStream_t st) {
+    const int g = grid_for(n);
+    if (rne) e4m3_e8_scale_kernel<true><<<g, kThreads, 0, st>>>(in, out, n);
+    else e4m3_e8_scale_kernel<false><<<g, kThreads, 0, st>>>(in, out, n);
+    return check_launch();
+}
+
+int launch_e8mx_cast(const void* in, void* out, int64_t n_elems, int qtype, int strategy,
+                     const uint32_t* gamax_bits, cudaStream_t st) {
+    const int64_t nvec = n_elems / 8;
+    const int64_t tail_words = (n_elems % 8) / 2;
+    const int g = grid_for(nvec);
+    auto* i4 = static_cast<const uint4*>(in);
+    auto* o4 = static_cast<uint4*>(out);
+    switch (qtype) {
+        case 1: e8mx_cast_kernel<1><<<g, kThreads, 0, st>>>(i4, o4, nvec, tail_words, strategy, gamax_bits); break;
+        case 2: e8mx_cast_kernel<2><<<g, kThreads, 0, st>>>(i4, o4, nvec, tail_words, strategy, gamax_bits); break;
+        case 3: e8mx_cast_kernel<3><<<g, kThreads, 0, st>>>(i4, o4, nvec, tail_words, strategy, gamax_bits); break;
+        default: return kErrInvalidArgument;
+    }
+    return check_launch();
+}
+
+}  // namespace morb

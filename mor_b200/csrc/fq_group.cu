@@ -1,0 +1,189 @@
+// Single-pass fake-quantize with one scale per 1 x k group of a row: MX-style 1 x 32
+// groups with power-of-two (E8M0) scales, per-row (per-channel) scaling, and anything
+// between.  Semantics are those of quantize_kernel<BLOCK_SCALING_*> (ref: 801-823)
+// with the element wrappers SQDD_{fp32,e8}_{e4m3,e5m2,e2m3} (ref: 356-379): group
+// amax, scale = format max / amax (truncated to a power of two for E8 scaling),
+// multiply, RNE cast, exact division, bf16 rounding.  An all-zero group is copied.
+// One HBM read and one HBM write per element:
+//   k <= 32 vectors : a group is a power-of-two set of lanes, amax by xor shuffles;
+//   larger k        : one CTA per group, the group cached in registers between the
+//                     amax pass and the cast, per-group look-up table for the
+//                     division when the scale is a binary32 number.
+#include "kernels.cuh"
+
+namespace morb {
+
+namespace {
+
+template <typename T>
+__device__ __forceinline__ float vec_amax(const typename T::vec_t& v) {
+    float a = 0.0f;
+#pragma unroll
+    for (int k = 0; k < T::kWordsPerVec; ++k) {
+        float hi, lo;
+        T::unpack(v, k, hi, lo);
+        a = fmaxf(a, fmaxf(fabsf(hi), fabsf(lo)));
+    }
+    return a;
+}
+
+template <typename T, int FMT, int SF>
+__device__ __forceinline__ typename T::vec_t vec_cast(const typename T::vec_t& v, float s) {
+    typename T::vec_t o;
+#pragma unroll
+    for (int k = 0; k < T::kWordsPerVec; ++k) {
+        float hi, lo, rh, rl;
+        T::unpack(v, k, hi, lo);
+        sqdd_pair<FMT, SF>(hi, lo, s, rh, rl);
+        T::pack(o, k, rh, rl);
+    }
+    return o;
+}
+
+template <typename T, int FMT, int SF>
+__global__ void __launch_bounds__(256)
+group_small_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_t* __restrict__ out,
+                   float* __restrict__ scales, int64_t nvec, int lanes_per_group, int32_t* __restrict__ meta,
+                   int64_t n_meta, int32_t meta_code) {
+    const int64_t stride = (int64_t)gridDim.x * 256;
+    const int64_t gtid = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    for (int64_t m = gtid; m < n_meta; m += stride) meta[m] = meta_code;
+    // nvec is a multiple of 32, so whole warps enter or leave the loop together
+    for (int64_t i = gtid; i < nvec; i += stride * 2) {
+        const bool second = i + stride < nvec;
+        typename T::vec_t v0 = ld_stream(in + i), v1;
+        if (second) v1 = ld_stream(in + i + stride);
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            if (u == 1 && !second) break;
+            typename T::vec_t& v = u ? v1 : v0;
+            float a = vec_amax<T>(v);
+            for (int o = lanes_per_group >> 1; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+            float s = 1.0f;
+            if (a > 0.0f) {
+                s = __fdiv_rn(fmt_max<FMT>(), a);
+                v = vec_cast<T, FMT, SF>(v, s);
+            }
+            const int64_t idx = i + u * stride;
+            st_stream(out + idx, v);
+            if (scales && (threadIdx.x & (lanes_per_group - 1)) == 0)
+                scales[idx / lanes_per_group] = (SF == kSfE8 && a > 0.0f) ? u2f(f2u(s) & 0x7F800000u) : s;
+        }
+    }
+}
+
+constexpr int kRowThreads = 256;
+constexpr int kRowMaxVec = 8;
+
+template <typename T, int FMT, int SF>
+__global__ void __launch_bounds__(kRowThreads)
+group_row_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_t* __restrict__ out,
+                 float* __restrict__ scales, int group_vec, int32_t* __restrict__ meta, int32_t meta_code) {
+    __shared__ float s_red[kRowThreads / 32];
+    __shared__ uint32_t s_lut[256];  // bf16 bits (bf16 output) or binary32 bits (binary32 output)
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int64_t base = (int64_t)blockIdx.x * group_vec;
+    typename T::vec_t v[kRowMaxVec];
+    float a = 0.0f;
+#pragma unroll
+    for (int u = 0; u < kRowMaxVec; ++u)
+        if (tid + u * kRowThreads < group_vec) v[u] = ld_stream(in + base + tid + u * kRowThreads);
+#pragma unroll
+    for (int u = 0; u < kRowMaxVec; ++u)
+        if (tid + u * kRowThreads < group_vec) a = fmaxf(a, vec_amax<T>(v[u]));
+    a = warp_max(a);
+    if (lane == 0) s_red[wid] = a;
+    __syncthreads();
+#pragma unroll
+    for (int w = 0; w < kRowThreads / 32; ++w) a = fmaxf(a, s_red[w]);
+    float s = 1.0f;
+    if (a > 0.0f) s = __fdiv_rn(fmt_max<FMT>(), a);
+    if (tid == 0) {
+        if (meta) meta[blockIdx.x] = meta_code;
+        if (scales) scales[blockIdx.x] = (SF == kSfE8 && a > 0.0f) ? u2f(f2u(s) & 0x7F800000u) : s;
+    }
+    if (a > 0.0f) {
+        if constexpr (SF == kSfFp32) {
+            // result = f(code) for a fixed scale: tabulate with the exact division once
+            constexpr int NCODES = (FMT == kE2M3) ? 64 : 256;
+            for (int c = tid; c < NCODES; c += kRowThreads) {
+                float q = h_lo_to_f32(codes_to_h2<FMT>((uint32_t)c));
+                if (FMT == kE2M3 && q == 0.0f) q = 0.0f;
+                const float r = __fdiv_rn(q, s);
+                s_lut[c] = (T::kBytesPerElem == 2) ? f32_to_bf16_bits(r) : f2u(r);
+            }
+            __syncthreads();
+#pragma unroll
+            for (int u = 0; u < kRowMaxVec; ++u)
+                if (tid + u * kRowThreads < group_vec) {
+#pragma unroll
+                    for (int k = 0; k < T::kWordsPerVec; ++k) {
+                        float hi, lo;
+                        T::unpack(v[u], k, hi, lo);
+                        const uint32_t c = cvt_codes<FMT>(__fmul_rn(hi, s), __fmul_rn(lo, s));
+                        if constexpr (T::kBytesPerElem == 2) {
+                            const uint32_t w = (s_lut[c >> 8] << 16) | s_lut[c & 0xFFu];
+                            if (k == 0) v[u].x = w; else if (k == 1) v[u].y = w; else if (k == 2) v[u].z = w; else v[u].w = w;
+                        } else {
+                            T::pack(v[u], k, u2f(s_lut[c >> 8]), u2f(s_lut[c & 0xFFu]));
+                        }
+                    }
+                }
+        } else {
+#pragma unroll
+            for (int u = 0; u < kRowMaxVec; ++u)
+                if (tid + u * kRowThreads < group_vec) v[u] = vec_cast<T, FMT, SF>(v[u], s);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < kRowMaxVec; ++u)
+        if (tid + u * kRowThreads < group_vec) st_stream(out + base + tid + u * kRowThreads, v[u]);
+}
+
+template <typename T, int FMT, int SF>
+int launch_t(const void* in, void* out, float* scales, int32_t* meta, int32_t meta_code, int64_t rows, int64_t cols,
+             int bcols, cudaStream_t st) {
+    constexpr int EPV = 16 / T::kBytesPerElem;
+    if (bcols % EPV || cols % bcols) return kErrUnsupportedShape;
+    const int gvec = bcols / EPV;
+    const int64_t nvec = rows * cols / EPV;
+    const int64_t n_groups = rows * (cols / bcols);
+    auto* i4 = static_cast<const typename T::vec_t*>(in);
+    auto* o4 = static_cast<typename T::vec_t*>(out);
+    if (gvec <= 32 && (gvec & (gvec - 1)) == 0 && nvec % 32 == 0) {
+        int64_t grid = (nvec + 511) / 512;
+        const int64_t cap = (int64_t)sm_count() * 8;
+        if (grid > cap) grid = cap;
+        if (grid < 1) grid = 1;
+        group_small_kernel<T, FMT, SF><<<(unsigned)grid, 256, 0, st>>>(i4, o4, scales, nvec, gvec, meta, meta ? n_groups : 0, meta_code);
+        return check_launch();
+    }
+    if (gvec <= kRowThreads * kRowMaxVec) {
+        if (n_groups > 0x7FFFFFFF) return kErrTooLarge;
+        group_row_kernel<T, FMT, SF><<<(unsigned)n_groups, kRowThreads, 0, st>>>(i4, o4, scales, gvec, meta, meta_code);
+        return check_launch();
+    }
+    return kErrUnsupportedShape;
+}
+
+template <typename T>
+int launch_fmt(const void* in, void* out, float* scales, int32_t* meta, int32_t meta_code, int64_t rows,
+               int64_t cols, int bcols, int fmt, int sf, cudaStream_t st) {
+#define MORB_GO(F) (sf == kSfE8 ? launch_t<T, F, kSfE8>(in, out, scales, meta, meta_code, rows, cols, bcols, st) \
+                                : launch_t<T, F, kSfFp32>(in, out, scales, meta, meta_code, rows, cols, bcols, st))
+    if (fmt == kE4M3) return MORB_GO(kE4M3);
+    if (fmt == kE5M2) return MORB_GO(kE5M2);
+    if (fmt == kE2M3) return MORB_GO(kE2M3);
+#undef MORB_GO
+    return kErrInvalidArgument;
+}
+
+}  // namespace
+
+int launch_fq_group(const void* in, void* out, int is_fp32, float* scales, int32_t* meta, int32_t meta_code,
+                    int64_t rows, int64_t cols, int bcols, int fmt, int sf_type, cudaStream_t st) {
+    return is_fp32 ? launch_fmt<Fp32>(in, out, scales, meta, meta_code, rows, cols, bcols, fmt, sf_type, st)
+                   : launch_fmt<Bf16>(in, out, scales, meta, meta_code, rows, cols, bcols, fmt, sf_type, st);
+}
+
+}  // namespace morb

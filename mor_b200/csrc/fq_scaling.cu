@@ -1,0 +1,362 @@
+// Phase 2..4 of the tensor-scaled pipelines (fake_quantize_block_scaling and
+// fake_quantize_channel_scaling; ref: 1059-1241, 1633-1752, 2013-2102, 2431-2526):
+//   error+cast : per block scale, E4M3 cast, output store and the per-CTA sum of
+//                |(q - x) / x| in the reference's order of additions;
+//   finalize   : ordered sum of those per-CTA errors (one 1024-thread CTA in the
+//                reference), error / nnz against the threshold, meta;
+//   fallback   : copy of the input over the output when the tensor stays BF16.
+//
+// The reference walks a block with a CTA of one thread per 32-bit word and adds the
+// errors of a thread's words one after another, then folds threads with shfl_down
+// trees.  Float addition does not associate, so the sums here are built from the
+// same additions in the same order: each physical lane owns VW consecutive "logical
+// threads" of the reference's CTA (the words of one 16-byte vector), keeps one
+// running sum per logical thread, and logical_warp_sum() folds them exactly as the
+// reference's tree folds real lanes.
+#include "kernels.cuh"
+
+namespace morb {
+
+namespace {
+
+// ref: 1059-1093.  All four strategies; the block amax is floored at 1e-35.
+__device__ __forceinline__ float scaling_factor(int ss, float gamax, float bamax) {
+    if (bamax < 1e-35f) bamax = 1e-35f;
+    if (ss == 1) {
+        const uint32_t gman = f2u(__fdiv_rn(448.0f, gamax)) & 0x007FFFFFu;
+        const uint32_t bb = f2u(__fdiv_rn(448.0f, bamax));
+        const float adj = u2f((bb & 0xFF800000u) | gman);
+        return (gman <= (bb & 0x007FFFFFu)) ? adj : __fdiv_rn(adj, 2.0f);
+    }
+    if (ss == 2 || ss == 3) return __fdiv_rn(448.0f, bamax);
+    if (ss == 4 && gamax > 0.0f) return __fdiv_rn(448.0f, gamax);
+    return 1.0f;
+}
+
+__device__ __forceinline__ float read_gamax(const ScalarsWs* ws, const float* ext) {
+    return ext ? *ext : u2f(ws->gamax_bits);
+}
+
+// One element pair of block_e4m3_relative_error (ref: 1133-1162).  ss_mode 2 is the
+// one that takes the power-of-two path: the reference tests `T_SCALING_STRATEGY ==
+// SF_E8` and SF_E8 is the enumerator 2 of another enum.
+template <bool E8>
+__device__ __forceinline__ void err_pair(float hi, float lo, float sf, int e8, float& dh, float& dl, float& eh,
+                                         float& el) {
+    if constexpr (E8) sqdd_e8_pair<kE4M3>(hi, lo, e8, dh, dl);
+    else sqdd_fp32_pair<kE4M3>(hi, lo, sf, dh, dl);
+    eh = 0.0f;
+    el = 0.0f;
+    if (hi != 0.0f) eh = fabsf(__fdiv_rn(__fsub_rn(dh, hi), hi)); else dh = 0.0f;
+    if (lo != 0.0f) el = fabsf(__fdiv_rn(__fsub_rn(dl, lo), lo)); else dl = 0.0f;
+}
+
+// ---------------------------------------------------------------------------------
+// blocks of brows x bcols (multiples of 32 rows x 32 words); reference CTA 32 x 32
+// ---------------------------------------------------------------------------------
+template <typename T, bool E8, bool STORE>
+__global__ void __launch_bounds__(1024 / T::kWordsPerVec)
+block_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_t* __restrict__ out,
+                      int64_t cols_vec, int brows, int bcols_vec, int64_t blocks_x, int ss,
+                      const float* __restrict__ block_amax, float* __restrict__ block_err,
+                      const ScalarsWs* __restrict__ ws, const float* __restrict__ ext_gamax, int skip_if_fallback) {
+    constexpr int VW = T::kWordsPerVec;
+    constexpr int LPW = 32 / VW;  // physical lanes per logical warp (= per logical row of 32 threads)
+    if (skip_if_fallback && ws->fallback) return;
+    __shared__ float wsum[32];
+    const int64_t b = blockIdx.x;
+    const int64_t r0 = (b / blocks_x) * brows, c0 = (b % blocks_x) * bcols_vec;
+    const float sf = scaling_factor(ss, read_gamax(ws, ext_gamax), block_amax[b]);
+    const int e8 = e8_of_scale(sf);
+    const int p = threadIdx.x % LPW, ty = threadIdx.x / LPW;
+    float acc[VW];
+#pragma unroll
+    for (int k = 0; k < VW; ++k) acc[k] = 0.0f;
+
+    for (int r = ty; r < brows; r += 32) {
+        const int64_t row_off = (r0 + r) * cols_vec + c0;
+        for (int cv = p; cv < bcols_vec; cv += LPW) {  // 32 words = LPW vectors per step
+            const typename T::vec_t v = STORE ? ld_stream(in + row_off + cv) : ld_keep(in + row_off + cv);
+            typename T::vec_t o;
+#pragma unroll
+            for (int k = 0; k < VW; ++k) {
+                float hi, lo, dh, dl, eh, el;
+                T::unpack(v, k, hi, lo);
+                err_pair<E8>(hi, lo, sf, e8, dh, dl, eh, el);
+                acc[k] = __fadd_rn(acc[k], eh);
+                acc[k] = __fadd_rn(acc[k], el);
+                if constexpr (STORE) T::pack(o, k, dh, dl);
+            }
+            if constexpr (STORE) st_stream(out + row_off + cv, o);
+        }
+    }
+    const float s = logical_warp_sum<VW>(acc);
+    if (p == 0) wsum[ty] = s;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const float t = warp_sum_ordered(wsum[threadIdx.x]);
+        if (threadIdx.x == 0) block_err[b] = t;
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// 1 x k row groups; reference CTA = 64 threads over max(k, 128) columns of one row
+// ---------------------------------------------------------------------------------
+template <typename T, bool E8, bool STORE>
+__global__ void __launch_bounds__(256)
+rowgroup_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_t* __restrict__ out,
+                         int64_t n_units, int span_vec, int group_lanes, int ss,
+                         const float* __restrict__ block_amax, float* __restrict__ block_err,
+                         const ScalarsWs* __restrict__ ws, const float* __restrict__ ext_gamax,
+                         int skip_if_fallback) {
+    constexpr int VW = T::kWordsPerVec;
+    constexpr int LPU = 64 / VW;       // physical lanes per unit (one reference CTA)
+    constexpr int UPW = 32 / LPU;      // units per physical warp
+    if (skip_if_fallback && ws->fallback) return;
+    const float gamax = read_gamax(ws, ext_gamax);
+    const int lane = threadIdx.x & 31;
+    const int p = lane % LPU;
+    const int64_t warps_total = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int64_t warp0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t n_iter = (n_units + UPW - 1) / UPW;
+    for (int64_t it = warp0; it < n_iter; it += warps_total) {
+        const int64_t u = it * UPW + lane / LPU;
+        const bool live = u < n_units;
+        const int64_t base = (live ? u : 0) * span_vec;
+        float sf = 1.0f;
+        if (group_lanes == 0 && live) sf = scaling_factor(ss, gamax, block_amax[u]);  // one block per unit
+        float eh[VW], el[VW];
+#pragma unroll
+        for (int k = 0; k < VW; ++k) eh[k] = el[k] = 0.0f;
+        for (int cv = p; cv < span_vec; cv += LPU) {
+            typename T::vec_t v = ld_stream(in + base + cv);
+            if (group_lanes > 0) {
+                // several 1 x k blocks inside the unit: amax of the lanes of this block
+                float a = 0.0f;
+#pragma unroll
+                for (int k = 0; k < VW; ++k) {
+                    float hi, lo;
+                    T::unpack(v, k, hi, lo);
+                    a = fmaxf(a, fmaxf(fabsf(hi), fabsf(lo)));
+                }
+                for (int o = group_lanes >> 1; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+                sf = scaling_factor(ss, gamax, a);
+            }
+            const int e8 = e8_of_scale(sf);
+            typename T::vec_t o4;
+#pragma unroll
+            for (int k = 0; k < VW; ++k) {
+                float hi, lo, dh, dl, e_h, e_l;
+                T::unpack(v, k, hi, lo);
+                err_pair<E8>(hi, lo, sf, e8, dh, dl, e_h, e_l);
+                eh[k] = __fadd_rn(eh[k], e_h);
+                el[k] = __fadd_rn(el[k], e_l);
+                if constexpr (STORE) T::pack(o4, k, dh, dl);
+            }
+            if constexpr (STORE) { if (live) st_stream(out + base + cv, o4); }
+        }
+        float acc[VW];
+#pragma unroll
+        for (int k = 0; k < VW; ++k) acc[k] = __fadd_rn(eh[k], el[k]);
+        float s = logical_warp_sum<VW>(acc);                       // valid at p == 0 and p == LPU / 2
+        const float s1 = __shfl_down_sync(0xFFFFFFFFu, s, LPU / 2);
+        s = __fadd_rn(s, s1);                                      // second-level tree: s0 + s1 (rest are +0)
+        if (p == 0 && live) block_err[u] = s;
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// k x 1 column groups; reference CTA = 32 x 16 threads over 64 columns x k rows
+// ---------------------------------------------------------------------------------
+template <typename T, bool E8, bool STORE>
+__global__ void __launch_bounds__(512 / T::kWordsPerVec)
+colgroup_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_t* __restrict__ out,
+                         int64_t cols, int brows, int ss, const float* __restrict__ block_amax,
+                         float* __restrict__ block_err, const ScalarsWs* __restrict__ ws,
+                         const float* __restrict__ ext_gamax, int skip_if_fallback) {
+    constexpr int VW = T::kWordsPerVec;
+    constexpr int LPW = 32 / VW;
+    constexpr int EPV = 2 * VW;
+    if (skip_if_fallback && ws->fallback) return;
+    __shared__ float wsum[32];
+    const float gamax = read_gamax(ws, ext_gamax);
+    const int64_t ctas_x = cols / 64;
+    const int64_t rb = blockIdx.x / ctas_x, cx = blockIdx.x % ctas_x;
+    const int p = threadIdx.x % LPW, ty = threadIdx.x / LPW;
+    const int64_t cols_vec = cols / EPV;
+    const int64_t cv = cx * (64 / EPV) + p;
+    float sfh[VW], sfl[VW], eh[VW], el[VW];
+#pragma unroll
+    for (int k = 0; k < VW; ++k) {
+        const int64_t col = cv * EPV + 2 * k;
+        sfl[k] = scaling_factor(ss, gamax, block_amax[rb * cols + col]);
+        sfh[k] = scaling_factor(ss, gamax, block_amax[rb * cols + col + 1]);
+        eh[k] = el[k] = 0.0f;
+    }
+    for (int64_t r = rb * brows + ty; r < (rb + 1) * (int64_t)brows; r += 16) {
+        const typename T::vec_t v = ld_stream(in + r * cols_vec + cv);
+        typename T::vec_t o;
+#pragma unroll
+        for (int k = 0; k < VW; ++k) {
+            float hi, lo, dh, dl, e_h, e_l, unused_d, unused_e;
+            T::unpack(v, k, hi, lo);
+            // the two halves of a word belong to different columns, hence different scales
+            err_pair<E8>(hi, hi, sfh[k], e8_of_scale(sfh[k]), dh, unused_d, e_h, unused_e);
+            err_pair<E8>(lo, lo, sfl[k], e8_of_scale(sfl[k]), dl, unused_d, e_l, unused_e);
+            eh[k] = __fadd_rn(eh[k], e_h);
+            el[k] = __fadd_rn(el[k], e_l);
+            if constexpr (STORE) T::pack(o, k, dh, dl);
+        }
+        if constexpr (STORE) st_stream(out + r * cols_vec + cv, o);
+    }
+    float acc[VW];
+#pragma unroll
+    for (int k = 0; k < VW; ++k) acc[k] = __fadd_rn(eh[k], el[k]);
+    const float s = logical_warp_sum<VW>(acc);
+    if (threadIdx.x < 32) wsum[threadIdx.x] = 0.0f;
+    __syncthreads();
+    if (p == 0) wsum[ty] = s;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const float t = warp_sum_ordered(wsum[threadIdx.x]);
+        if (threadIdx.x == 0) block_err[blockIdx.x] = t;
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// ordered tensor-level error sum + decision (ref: 1178-1241)
+// ---------------------------------------------------------------------------------
+// The reference array has an entry per block; a CTA that covers `stride` blocks writes
+// its sum to the first of them and zeros to the rest.  Thread t of 1024 adds slots t,
+// t+1024, ... in order; adding +0.0 to a non-negative sum does not change it, so only
+// the slots that hold a sum are visited, in the same order.
+__global__ void __launch_bounds__(1024)
+finalize_kernel(const float* __restrict__ block_err, int64_t n_err, int stride, float threshold, ScalarsWs* ws,
+                const float* __restrict__ ext_gamax, const long long* __restrict__ ext_nnz, int32_t* meta_out,
+                float* gamax_out, void* gnnz_out, int nnz_is_i64, float* gerr_out) {
+    __shared__ float wsum[32];
+    const int t = threadIdx.x;
+    float acc = 0.0f;
+    if (t % stride == 0)
+        for (int64_t e = t / stride; e < n_err; e += 1024 / stride) acc = __fadd_rn(acc, block_err[e]);
+    acc = warp_sum_ordered(acc);
+    if ((t & 31) == 0) wsum[t >> 5] = acc;
+    __syncthreads();
+    if (t < 32) {
+        const float total = warp_sum_ordered(wsum[t]);
+        if (t == 0) {
+            const long long nnz = ext_nnz ? *ext_nnz : (long long)ws->gnnz;
+            const float gamax = ext_gamax ? *ext_gamax : u2f(ws->gamax_bits);
+            const float avg = __fdiv_rn(total, (float)nnz);
+            const int fb = avg > threshold;
+            ws->fallback = fb;
+            ws->gerr = total;
+            ws->meta = fb ? 3 : 1;
+            if (meta_out) *meta_out = fb ? 3 : 1;
+            if (gamax_out) *gamax_out = gamax;
+            if (gerr_out) *gerr_out = total;
+            if (gnnz_out) {
+                if (nnz_is_i64) *static_cast<long long*>(gnnz_out) = nnz;
+                else *static_cast<int32_t*>(gnnz_out) = (int32_t)nnz;
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) fallback_copy_kernel(const uint4* __restrict__ in, uint4* __restrict__ out,
+                                                            int64_t nvec, const ScalarsWs* __restrict__ ws) {
+    if (!ws->fallback) return;
+    const int64_t stride = (int64_t)gridDim.x * 256;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < nvec; i += stride) st_stream(out + i, ld_stream(in + i));
+}
+
+template <typename T>
+int launch_block_t(const ScalingArgs& a, bool store, bool skip, cudaStream_t st) {
+    constexpr int EPV = 16 / T::kBytesPerElem;
+    const int64_t cols_vec = a.cols / EPV, bx = a.cols / a.bcols, nb = bx * (a.rows / a.brows);
+    if (nb > 0x7FFFFFFF) return kErrTooLarge;
+    const bool e8 = a.ss_mode == 2;
+    auto* in = static_cast<const typename T::vec_t*>(a.in);
+    auto* out = static_cast<typename T::vec_t*>(a.out);
+    constexpr int TH = 1024 / T::kWordsPerVec;
+#define MORB_GO(E, S) block_err_cast_kernel<T, E, S><<<(unsigned)nb, TH, 0, st>>>(in, out, cols_vec, a.brows, a.bcols / EPV, bx, a.ss_mode, a.block_amax, a.block_err, a.ws, a.ext_gamax, skip ? 1 : 0)
+    if (e8 && store) MORB_GO(true, true);
+    else if (e8) MORB_GO(true, false);
+    else if (store) MORB_GO(false, true);
+    else MORB_GO(false, false);
+#undef MORB_GO
+    return check_launch();
+}
+
+template <typename T>
+int launch_rowgroup_t(const ScalingArgs& a, bool store, bool skip, cudaStream_t st) {
+    constexpr int EPV = 16 / T::kBytesPerElem;
+    const int span = a.bcols < 128 ? 128 : a.bcols;
+    const int64_t n_units = a.rows * (a.cols / span);
+    const int group_lanes = a.bcols < 128 ? a.bcols / EPV : 0;
+    if (a.bcols < 128 && (a.bcols % EPV || group_lanes < 1)) return kErrUnsupportedShape;
+    constexpr int UPW = 32 / (64 / T::kWordsPerVec);
+    const int64_t n_warps = (n_units + UPW - 1) / UPW;
+    int64_t grid = (n_warps + 7) / 8;
+    const int64_t cap = (int64_t)sm_count() * 8;
+    if (grid > cap) grid = cap;
+    if (grid < 1) grid = 1;
+    const bool e8 = a.ss_mode == 2;
+    auto* in = static_cast<const typename T::vec_t*>(a.in);
+    auto* out = static_cast<typename T::vec_t*>(a.out);
+#define MORB_GO(E, S) rowgroup_err_cast_kernel<T, E, S><<<(unsigned)grid, 256, 0, st>>>(in, out, n_units, span / EPV, group_lanes, a.ss_mode, a.block_amax, a.block_err, a.ws, a.ext_gamax, skip ? 1 : 0)
+    if (e8 && store) MORB_GO(true, true);
+    else if (e8) MORB_GO(true, false);
+    else if (store) MORB_GO(false, true);
+    else MORB_GO(false, false);
+#undef MORB_GO
+    return check_launch();
+}
+
+template <typename T>
+int launch_colgroup_t(const ScalingArgs& a, bool store, bool skip, cudaStream_t st) {
+    const int64_t n_cta = (a.rows / a.brows) * (a.cols / 64);
+    if (n_cta > 0x7FFFFFFF) return kErrTooLarge;
+    const bool e8 = a.ss_mode == 2;
+    auto* in = static_cast<const typename T::vec_t*>(a.in);
+    auto* out = static_cast<typename T::vec_t*>(a.out);
+    constexpr int TH = 512 / T::kWordsPerVec;
+#define MORB_GO(E, S) colgroup_err_cast_kernel<T, E, S><<<(unsigned)n_cta, TH, 0, st>>>(in, out, a.cols, a.brows, a.ss_mode, a.block_amax, a.block_err, a.ws, a.ext_gamax, skip ? 1 : 0)
+    if (e8 && store) MORB_GO(true, true);
+    else if (e8) MORB_GO(true, false);
+    else if (store) MORB_GO(false, true);
+    else MORB_GO(false, false);
+#undef MORB_GO
+    return check_launch();
+}
+
+}  // namespace
+
+int launch_block_err_cast(const ScalingArgs& a, bool store, bool skip, cudaStream_t st) {
+    return a.is_fp32 ? launch_block_t<Fp32>(a, store, skip, st) : launch_block_t<Bf16>(a, store, skip, st);
+}
+int launch_rowgroup_err_cast(const ScalingArgs& a, bool store, bool skip, cudaStream_t st) {
+    return a.is_fp32 ? launch_rowgroup_t<Fp32>(a, store, skip, st) : launch_rowgroup_t<Bf16>(a, store, skip, st);
+}
+int launch_colgroup_err_cast(const ScalingArgs& a, bool store, bool skip, cudaStream_t st) {
+    return a.is_fp32 ? launch_colgroup_t<Fp32>(a, store, skip, st) : launch_colgroup_t<Bf16>(a, store, skip, st);
+}
+
+int launch_finalize(const ScalingArgs& a, const long long* ext_nnz, int32_t* meta, float* gamax, void* gnnz,
+                    int nnz_is_i64, float* gerr, cudaStream_t st) {
+    finalize_kernel<<<1, 1024, 0, st>>>(a.block_err, a.n_err, a.err_slot_stride, a.threshold, a.ws, a.ext_gamax,
+                                        ext_nnz, meta, gamax, gnnz, nnz_is_i64, gerr);
+    return check_launch();
+}
+
+int launch_fallback_copy(const ScalingArgs& a, cudaStream_t st) {
+    if (a.in == a.out) return kOk;
+    const int64_t nvec = a.rows * a.cols * (a.is_fp32 ? 4 : 2) / 16;
+    int64_t grid = (nvec + 255) / 256;
+    const int64_t cap = (int64_t)sm_count() * 8;
+    if (grid > cap) grid = cap;
+    fallback_copy_kernel<<<(unsigned)grid, 256, 0, st>>>(static_cast<const uint4*>(a.in), static_cast<uint4*>(a.out), nvec, a.ws);
+    return check_launch();
+}
+
+}  // namespace morb

@@ -1,0 +1,75 @@
+// Host-side launch functions of libmor_b200, one per kernel family.  Each returns a
+// status code (common.cuh) and never synchronises, allocates or throws.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace morb {
+
+int sm_count();                 // SMs of the current device (cached per device)
+int check_launch();             // cudaGetLastError() -> status code
+
+// ---- fq_elementwise.cu: one scale for the whole tensor, or none ------------------
+// fake_quantize CURRENT_SCALING modes and the BF16 pass-through (ref: 825-844).
+int launch_cast_uniform(const void* in, void* out, int64_t n_elems, int fmt, int sf_type, float scale,
+                        int32_t* meta, int64_t n_meta, int32_t meta_code, cudaStream_t st);
+int launch_copy(const void* in, void* out, int64_t n_bytes, int32_t* meta, int64_t n_meta, int32_t meta_code,
+                cudaStream_t st);
+// test operators (ref: 854-875), binary32 in/out
+int launch_quant_dequant(const float* in, float* out, int64_t n, int fmt, cudaStream_t st);
+int launch_e4m3_e8_scale(const float* in, float* out, int64_t n, int rne, cudaStream_t st);
+// E8Mx cast with the scale derived from a device-resident amax (ref: 1335-1428)
+int launch_e8mx_cast(const void* in, void* out, int64_t n_elems, int qtype, int strategy,
+                     const uint32_t* gamax_bits, cudaStream_t st);
+
+// ---- fq_reduce.cu: amax / non-zero reductions ------------------------------------
+struct ScalarsWs {              // head of every workspace, 32 bytes, zeroed by launch_zero_scalars
+    uint32_t gamax_bits;        // max |x| as the bit pattern of a non-negative float
+    int32_t fallback;           // 1 when the tensor-level BF16 fallback fired
+    unsigned long long gnnz;    // count of non-zero elements
+    float gerr;                 // ordered sum of the block errors
+    int32_t meta;
+    uint32_t pad[2];
+};
+int launch_zero_scalars(ScalarsWs* ws, cudaStream_t st);
+// amax and nnz of a flat tensor (phase 1 of e8mx and of the row-sharded pipeline)
+int launch_amax_nnz_flat(const void* in, int is_fp32, int64_t n_elems, ScalarsWs* ws, cudaStream_t st);
+// per-block amax (brows x bcols blocks, natural row-major block index) + tensor amax/nnz
+int launch_amax_nnz_blocks(const void* in, int is_fp32, int64_t rows, int64_t cols, int brows, int bcols,
+                           float* block_amax, ScalarsWs* ws, cudaStream_t st);
+
+// ---- fq_scaling.cu: the amax -> error+cast -> ordered error sum -> fallback pipeline
+struct ScalingArgs {
+    const void* in;
+    void* out;
+    int is_fp32;
+    int64_t rows, cols;
+    int brows, bcols;
+    float threshold;
+    int ss_mode;
+    float* block_amax;          // workspace, one per block
+    float* block_err;           // workspace, one per virtual CTA of the reference
+    int64_t n_err;              // entries of block_err
+    int err_slot_stride;        // the reference stores entry i at slot i * stride of its array
+    ScalarsWs* ws;
+    const float* ext_gamax;     // optional device pointer: amax of the whole (sharded) tensor
+};
+int launch_block_err_cast(const ScalingArgs& a, bool store, bool only_if_not_fallback, cudaStream_t st);
+int launch_rowgroup_err_cast(const ScalingArgs& a, bool store, bool only_if_not_fallback, cudaStream_t st);
+int launch_colgroup_err_cast(const ScalingArgs& a, bool store, bool only_if_not_fallback, cudaStream_t st);
+int launch_finalize(const ScalingArgs& a, const long long* ext_nnz, int32_t* meta, float* gamax, void* gnnz,
+                    int nnz_is_i64, float* gerr, cudaStream_t st);
+int launch_fallback_copy(const ScalingArgs& a, cudaStream_t st);
+
+// ---- fq_block.cu: fake_quantize per-block modes (MoR, block E4M3 / E5M2) ----------
+int launch_fq_block(const void* in, void* out, int is_fp32, int32_t* meta, int64_t rows, int64_t cols, int brows,
+                    int bcols, float clamp, int quant_mode, int dynamic_range_mode, int sf_type, cudaStream_t st);
+
+// ---- fq_group.cu: single-pass per-group scaling (1 x k groups, MX style) ----------
+int launch_fq_group(const void* in, void* out, int is_fp32, float* scales, int32_t* meta, int32_t meta_code,
+                    int64_t rows, int64_t cols, int bcols, int fmt, int sf_type, cudaStream_t st);
+
+}  // namespace morb
