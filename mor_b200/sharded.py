@@ -1,0 +1,142 @@
+"""Row-sharded tensor-scaled fake-quantize: one process per GPU, each holding a
+contiguous slab of rows whose height is a multiple of the block height, so that no
+block, row or group straddles two GPUs.
+
+The reference (boryiings/mor) is single-GPU; this is the multi-GPU form of its
+``fake_quantize_block_scaling`` / ``fake_quantize_channel_scaling`` pipeline
+(mor/csrc/cuda/fake_quantize.cu:2013-2102, 2431-2526).  Per call:
+
+    phase 1  slab amax + non-zero count                     (kernel, local)
+             all-reduce amax (MAX, float32, exact), non-zero count (SUM, int64)
+    phase 2  scale, cast, store, per-CTA error sums          (kernel, local)
+             all-gather the per-CTA error sums (rank order = row order)
+    phase 3  ordered sum of ALL error sums, error / nnz vs threshold -> meta
+             (every rank repeats the reference's single-CTA summation order on the
+             gathered array, so meta and global_error are bit-identical on every
+             rank and equal to the single-GPU result; a float all-reduce would not be)
+    phase 4  if meta == 3 copy the slab's input over its output
+
+The collectives are two scalars and a few hundred KiB: latency-bound over NVLink.
+Operators without a tensor-wide quantity (per-block MoR, per-row, 1 x 32 MX) need no
+communication at all: call them on the slab.
+
+``backend`` supplies the four phases.  The product backend is :class:`CudaBackend`
+(C ABI of libmor_b200 on the current CUDA stream).  Tests of the host logic pass a CPU
+stand-in over gloo; nothing in this module falls back to one on its own.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from . import cabi
+
+KIND_BLOCK = cabi.OP_BLOCK_SCALING
+KIND_CHANNEL = cabi.OP_CHANNEL_SCALING
+
+
+def shard_rows(rows: int, world_size: int, rank: int, multiple: int):
+    """Contiguous row range of `rank`: slabs are multiples of `multiple` rows, sizes differ by at most one unit."""
+    if rows % multiple:
+        raise ValueError(f"rows ({rows}) must be a multiple of the block height ({multiple})")
+    units = rows // multiple
+    base, extra = divmod(units, world_size)
+    start = rank * base + min(rank, extra)
+    n = base + (1 if rank < extra else 0)
+    return start * multiple, (start + n) * multiple
+
+
+@dataclass
+class ScalingResult:
+    meta: torch.Tensor          # int32[1]: 1 = E4M3 kept, 3 = tensor left as it was
+    global_amax: torch.Tensor   # float32[1]
+    global_nnz: torch.Tensor    # int64[1]
+    global_error: torch.Tensor  # float32[1]
+
+
+class CudaBackend:
+    """The four phases on the GPU through the C ABI (include/mor_b200.h)."""
+
+    def __init__(self, kind: int, rows: int, cols: int, brows: int, bcols: int, dtype: torch.dtype,
+                 device: torch.device):
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise TypeError("bfloat16 or float32 tensors only")
+        self.kind, self.rows, self.cols, self.brows, self.bcols = kind, rows, cols, brows, bcols
+        self.dt = cabi.FP32 if dtype == torch.float32 else cabi.BF16
+        self.device = device
+        self.ws_bytes = cabi.workspace_bytes(kind, rows, cols, brows, bcols)
+        if self.ws_bytes == 0:
+            raise ValueError(f"unsupported slab/block shape {rows}x{cols} / {brows}x{bcols}")
+        self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=device)
+        self.n_err = int(cabi.lib().mor_b200_scaling_num_errors(kind, rows, cols, brows, bcols))
+        self.stride = int(cabi.lib().mor_b200_scaling_error_stride(kind, brows, bcols))
+        self.launches = 0
+
+    def _stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def amax_nnz(self, x, amax_out, nnz_out):
+        cabi.call("mor_b200_scaling_amax", self.kind, x.data_ptr(), self.dt, self.rows, self.cols, self.brows,
+                  self.bcols, amax_out.data_ptr(), nnz_out.data_ptr(), self.ws.data_ptr(), self.ws_bytes,
+                  self._stream())
+        self.launches += 3
+
+    def cast(self, x, out, ss_mode, global_amax, block_err):
+        cabi.call("mor_b200_scaling_cast", self.kind, x.data_ptr(), out.data_ptr(), self.dt, self.rows, self.cols,
+                  self.brows, self.bcols, ss_mode, global_amax.data_ptr(), block_err.data_ptr(), self.ws.data_ptr(),
+                  self.ws_bytes, self._stream())
+        self.launches += 1
+
+    def finalize(self, all_err, global_nnz, threshold, meta, global_error):
+        cabi.call("mor_b200_scaling_finalize", all_err.data_ptr(), all_err.numel(), self.stride,
+                  global_nnz.data_ptr(), float(threshold), meta.data_ptr(), global_error.data_ptr(),
+                  self.ws.data_ptr(), self.ws_bytes, self._stream())
+        self.launches += 1
+
+    def fallback(self, x, out, meta):
+        cabi.call("mor_b200_scaling_fallback", x.data_ptr(), out.data_ptr(), x.numel() * x.element_size(),
+                  meta.data_ptr(), self._stream())
+        self.launches += 1
+
+
+class ShardedScaling:
+    """Row-sharded ``fake_quantize_block_scaling`` / ``fake_quantize_channel_scaling``.
+
+    All ranks must call with slabs of the SAME height (the all-gather is fixed-size);
+    :func:`shard_rows` gives such a partition when the row count divides evenly.
+    """
+
+    def __init__(self, rows_local: int, cols: int, brows: int, bcols: int, dtype: torch.dtype,
+                 device: torch.device, kind: int = KIND_BLOCK, group: Optional[dist.ProcessGroup] = None,
+                 backend=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.device = device
+        self.backend = backend if backend is not None else CudaBackend(kind, rows_local, cols, brows, bcols, dtype, device)
+        n_err = self.backend.n_err
+        self.amax = torch.zeros(1, dtype=torch.float32, device=device)
+        self.nnz = torch.zeros(1, dtype=torch.int64, device=device)
+        self.meta = torch.zeros(1, dtype=torch.int32, device=device)
+        self.gerr = torch.zeros(1, dtype=torch.float32, device=device)
+        self.all_err = torch.zeros(n_err * self.world, dtype=torch.float32, device=device)
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.local_err = self.all_err[self.rank * n_err:(self.rank + 1) * n_err]
+        self.collectives = 0
+
+    def __call__(self, x: torch.Tensor, out: torch.Tensor, ss_mode: int, threshold: float) -> ScalingResult:
+        b = self.backend
+        b.amax_nnz(x, self.amax, self.nnz)
+        if self.world > 1:
+            dist.all_reduce(self.amax, op=dist.ReduceOp.MAX, group=self.group)
+            dist.all_reduce(self.nnz, op=dist.ReduceOp.SUM, group=self.group)
+            self.collectives += 2
+        b.cast(x, out, ss_mode, self.amax, self.local_err)
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.all_err, self.local_err.clone(), group=self.group)
+            self.collectives += 1
+        b.finalize(self.all_err, self.nnz, threshold, self.meta, self.gerr)
+        b.fallback(x, out, self.meta)
+        return ScalingResult(self.meta, self.amax, self.nnz, self.gerr)

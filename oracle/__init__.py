@@ -67,6 +67,8 @@ def lib() -> C.CDLL:
         L.mor_o_e4m3_with_e8_scale.argtypes = [vp, vp, i64, i32]
         L.mor_o_fake_quantize_group.argtypes = [vp, vp, i32, vp, i64, i64, i32, i32, i32, i32]
         L.mor_o_amax_nnz.argtypes = [vp, i32, i64, vp, vp]
+        L.mor_o_finalize.restype = f32
+        L.mor_o_finalize.argtypes = [vp, i64, i32, i64, dbl, vp]
         L.mor_o_num_threads.restype = i32
         L.mor_o_set_num_threads.argtypes = [i32]
         _lib = L
@@ -203,6 +205,14 @@ def amax_nnz(x):
     n = np.zeros(1, np.int64)
     lib().mor_o_amax_nnz(_p(x), is_f32, x.size, _p(a), _p(n))
     return a[0], int(n[0])
+
+
+def finalize(block_err, stride, nnz, thr):
+    """Ordered tensor-level error sum over gathered per-CTA errors: (meta, global_error)."""
+    be = np.ascontiguousarray(block_err, dtype=np.float32)
+    meta = np.zeros(1, np.int32)
+    total = lib().mor_o_finalize(_p(be), be.size, int(stride), int(nnz), float(thr), _p(meta))
+    return int(meta[0]), np.float32(total)
 
 
 # ----------------------------------------------------------------- torch helpers

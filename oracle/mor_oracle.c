@@ -870,6 +870,24 @@ MOR_O_API int mor_o_amax_nnz(const void *in, int is_fp32, int64_t n, float *amax
     return 0;
 }
 
+/* ref: 1178-1241 on an error array gathered from several row slabs: entry i sits at
+ * slot i * stride of the reference's array.  Returns the ordered sum; *meta_out gets 3
+ * when sum / nnz exceeds the threshold, else 1. */
+MOR_O_API float mor_o_finalize(const float *block_err, int64_t n_err, int stride, int64_t nnz, double thr,
+                               int32_t *meta_out) {
+    float part[1024];
+    for (int t = 0; t < 1024; ++t) {
+        float acc = 0.0f;
+        if (t % stride == 0)
+            for (int64_t e = t / stride; e < n_err; e += 1024 / stride) acc += block_err[e];
+        part[t] = acc;
+    }
+    const float total = cta_tree_sum(part, 1024);
+    volatile float avg = total / (float)nnz;
+    if (meta_out) *meta_out = (avg > (float)thr) ? 3 : 1;
+    return total;
+}
+
 MOR_O_API int mor_o_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

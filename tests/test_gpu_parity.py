@@ -1,0 +1,307 @@
+"""Bit-exact parity of the CUDA kernels (through the C ABI) with the CPU oracle.
+
+bf16 outputs, meta matrices, amax, non-zero counts and error sums must be identical
+bit for bit; float32 outputs likewise except that NaNs compare by position (payloads of
+NaNs are not defined by the reference).  No tolerance is used anywhere in this file.
+"""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from cases import cases
+from replay import run_oracle
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def canon(a):
+    a = np.asarray(a)
+    if a.dtype == np.float32:
+        b = a.copy()
+        b[np.isnan(b)] = np.float32(np.nan)
+        return b.view(np.uint32)
+    return a
+
+
+def f32_bits(v):
+    return int(np.array([v], np.float32).view(np.uint32)[0])
+
+
+def assert_same(got: dict, exp: dict, what: str):
+    a, b = canon(got["out"]).reshape(-1), canon(exp["out"]).reshape(-1)
+    bad = np.nonzero(a != b)[0]
+    assert bad.size == 0, f"{what}: {bad.size}/{a.size} outputs differ, first at {bad[:8].tolist()}: cuda {a[bad[:8]].tolist()} oracle {b[bad[:8]].tolist()}"
+    if "meta" in exp:
+        assert np.array_equal(np.asarray(got["meta"]).reshape(-1), np.asarray(exp["meta"]).reshape(-1)), \
+            f"{what}: meta cuda {np.asarray(got['meta']).reshape(-1)[:32]} oracle {np.asarray(exp['meta']).reshape(-1)[:32]}"
+    for k in ("gamax", "gerr"):
+        if k in exp:
+            assert f32_bits(got[k]) == f32_bits(exp[k]), f"{what}: {k} cuda {got[k]!r} oracle {float(exp[k])!r}"
+    if "gnnz" in exp:
+        assert got["gnnz"] == exp["gnnz"], f"{what}: nnz cuda {got['gnnz']} oracle {exp['gnnz']}"
+
+
+ALL_CASES = cases()
+
+
+@pytest.mark.parametrize("case", ALL_CASES, ids=[c[0] for c in ALL_CASES])
+def test_golden_case_matches_oracle(case):
+    import gpu_harness as H
+    name, op, fn, kw = case
+    x = fn()
+    assert_same(H.run_case(op, x, kw), run_oracle(op, x, kw), name)
+
+
+# ------------------------------------------------------------------ exhaustive element sweeps
+def all_bf16_patterns(finite_only: bool) -> np.ndarray:
+    p = np.arange(65536, dtype=np.uint32).astype(np.uint16)
+    if finite_only:
+        p = p.copy()
+        p[(p & 0x7F80) == 0x7F80] = 0
+    return p.reshape(256, 256)
+
+
+SWEEP_SCALES = [1.0, 448.0 / 240.0, 0.37, 3.0e-3, 7.0e4, 2.0 ** -20, 1.0e-30, 5.1e27, 0.99999994, 57344.0 / 3.0]
+
+
+@pytest.mark.parametrize("mode,sf", [(4, 1), (5, 1), (4, 2), (5, 2)])
+def test_every_bf16_pattern_uniform_scale(mode, sf):
+    import gpu_harness as H
+    x = all_bf16_patterns(finite_only=(sf == 2))
+    for s in SWEEP_SCALES:
+        if sf == 2 and not (1e-20 < s < 1e20):
+            continue  # exponent-field arithmetic leaves the reference's asserted domain
+        oracle.clear_assert_flags()
+        exp = dict(zip(("out", "meta"), oracle.fake_quantize(x, 128, 128, s, mode, sf)))
+        if oracle.assert_flags():
+            continue
+        assert_same(H.fake_quantize(x, 128, 128, s, mode, sf), exp, f"mode {mode} sf {sf} scale {s}")
+
+
+@pytest.mark.parametrize("fmt", [oracle.FMT_E4M3, oracle.FMT_E5M2, oracle.FMT_E2M3])
+@pytest.mark.parametrize("sf", [1, 2])
+def test_every_bf16_pattern_group_scaled(fmt, sf):
+    """65536 patterns shuffled into 1 x 32 groups and into full rows: every pattern meets many scales."""
+    import gpu_harness as H
+    rng = np.random.default_rng(123)
+    pats = all_bf16_patterns(finite_only=True).reshape(-1)
+    for rep in range(3):
+        x = rng.permutation(pats).reshape(256, 256)
+        if sf == 2:
+            # keep each group's dynamic range inside the exponent field: sort so neighbours are similar
+            x = np.sort(x.reshape(-1) & 0x7FFF).astype(np.uint16).reshape(256, 256) | (x & 0x8000)
+        for by in (32, 256):
+            oracle.clear_assert_flags()
+            out, scales = oracle.fake_quantize_group(x, 1, by, fmt, sf, want_scales=True)
+            if oracle.assert_flags():
+                continue
+            got = H.fake_quantize_group(x, by, fmt, sf)
+            assert_same(got, {"out": out}, f"group fmt {fmt} sf {sf} by {by} rep {rep}")
+            assert np.array_equal(got["scales"].view(np.uint32), scales.view(np.uint32))
+
+
+def test_unscaled_casts_every_bf16_pattern_and_neighbours():
+    """quant_dequant_*: all bf16 patterns widened to float32, plus values just off the rounding ties."""
+    import gpu_harness as H
+    base = (all_bf16_patterns(False).astype(np.uint32) << 16)
+    for delta in (0, 1, 0x7FFF, 0x8000, 0x8001, 0xFFFF):
+        x = (base + np.uint32(delta)).view(np.float32)
+        for fmt in (oracle.FMT_E4M3, oracle.FMT_E5M2, oracle.FMT_E3M2, oracle.FMT_E2M3):
+            exp = oracle.quant_dequant(x, fmt).reshape(x.shape)
+            # the custom cast has no defined result for NaN inputs of E4M3/E5M2 beyond "NaN"
+            assert_same(H.quant_dequant(x, fmt), {"out": exp}, f"quant_dequant fmt {fmt} delta {delta:#x}")
+
+
+def test_exact_division_building_blocks():
+    """Hardware fp8/fp6 conversions agree with the oracle's casts on a dense float32 sweep."""
+    import gpu_harness as H
+    rng = np.random.default_rng(5)
+    # dense around every binade boundary and tie of the formats, both signs
+    mant = rng.integers(0, 1 << 23, size=1 << 18, dtype=np.uint32)
+    expo = rng.integers(127 - 20, 127 + 18, size=1 << 18, dtype=np.uint32)
+    sign = rng.integers(0, 2, size=1 << 18, dtype=np.uint32)
+    x = ((sign << 31) | (expo << 23) | mant).view(np.float32).reshape(512, 512)
+    xb = (x.view(np.uint32) >> 16).astype(np.uint16)  # as bf16
+    for fmt in (oracle.FMT_E4M3, oracle.FMT_E5M2, oracle.FMT_E2M3):
+        for sf in (1, 2):
+            exp = oracle.fake_quantize_group(xb, 1, 512, fmt, sf)
+            got = H.fake_quantize_group(xb, 512, fmt, sf, want_scales=False)
+            assert_same(got, {"out": exp}, f"row-group fmt {fmt} sf {sf}")
+
+
+# ------------------------------------------------------------------ shapes, aliasing, dtypes
+def rand_bits(seed, rows, cols, kind="normal"):
+    g = torch.Generator().manual_seed(seed)
+    if kind == "normal":
+        t = torch.randn(rows, cols, generator=g)
+    elif kind == "wide":
+        t = 10.0 ** (torch.rand(rows, cols, generator=g) * 8 - 4) * torch.where(torch.rand(rows, cols, generator=g) < 0.5, -1.0, 1.0)
+    else:
+        t = torch.rand(rows, cols, generator=g) * 2 - 1
+    z = torch.rand(rows, cols, generator=g) < 0.05
+    t = torch.where(z, 0.0, t)
+    return t.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+
+
+@pytest.mark.parametrize("rows,cols,bx,by", [(200, 136, 128, 128), (250, 130, 96, 64), (64, 66, 32, 32),
+                                              (33, 64, 32, 64), (256, 256, 4, 16), (128, 128, 2, 32),
+                                              (384, 640, 128, 128), (96, 192, 32, 64)])
+@pytest.mark.parametrize("mode", [1, 101, 2, 3])
+def test_fake_quantize_ragged_and_odd_blocks(rows, cols, bx, by, mode):
+    import gpu_harness as H
+    x = rand_bits(rows * 7 + cols + mode, rows, cols, "wide" if mode in (1, 101) else "normal")
+    for sf in (1, 2):
+        oracle.clear_assert_flags()
+        try:
+            exp = dict(zip(("out", "meta"), oracle.fake_quantize(x, bx, by, 1e-15, mode, sf)))
+        except oracle.OracleError:
+            from mor_b200 import cabi
+            with pytest.raises(cabi.MorB200Error):
+                H.fake_quantize(x, bx, by, 1e-15, mode, sf)
+            continue
+        if oracle.assert_flags():
+            continue
+        assert_same(H.fake_quantize(x, bx, by, 1e-15, mode, sf), exp, f"{rows}x{cols} block {bx}x{by} mode {mode} sf {sf}")
+
+
+@pytest.mark.parametrize("by", [8, 16, 32, 64, 128, 256, 1024, 4096])
+@pytest.mark.parametrize("mode", [2, 3])
+def test_fake_quantize_row_groups(by, mode):
+    """fixed-format modes with 1 x k blocks run on the single-pass group kernels"""
+    import gpu_harness as H
+    x = rand_bits(by + mode, 64, 4096, "wide")
+    for sf in (1, 2):
+        oracle.clear_assert_flags()
+        exp = dict(zip(("out", "meta"), oracle.fake_quantize(x, 1, by, 1e-15, mode, sf)))
+        if oracle.assert_flags():
+            continue
+        assert_same(H.fake_quantize(x, 1, by, 1e-15, mode, sf), exp, f"1x{by} mode {mode} sf {sf}")
+
+
+@pytest.mark.parametrize("mode,sf", [(1, 1), (101, 2), (2, 1), (4, 1), (7, 1)])
+def test_fake_quantize_in_place(mode, sf):
+    import gpu_harness as H
+    from cases import mixed_blocks_bf16
+    x = mixed_blocks_bf16(77)
+    clamp = 0.5 if mode == 4 else 1e-15
+    exp = dict(zip(("out", "meta"), oracle.fake_quantize(x, 128, 128, clamp, mode, sf)))
+    assert_same(H.fake_quantize(x, 128, 128, clamp, mode, sf, inplace=True), exp, f"in place mode {mode}")
+
+
+@pytest.mark.parametrize("by", [8, 16, 32, 64, 128, 256, 512])
+@pytest.mark.parametrize("ss", [1, 2, 3, 4])
+def test_channel_scaling_row_groups(by, ss):
+    import gpu_harness as H
+    x = rand_bits(by * 10 + ss, 96, 512, "wide" if ss != 2 else "normal")
+    for thr in (0.045, 3e38):
+        oracle.clear_assert_flags()
+        exp = dict(zip(("out", "meta", "gamax", "gnnz", "gerr"), oracle.channel_scaling(x, 1, by, thr, ss)))
+        if oracle.assert_flags():
+            continue
+        exp["meta"] = np.array([exp["meta"]])
+        assert_same(H.channel_scaling(x, 1, by, thr, ss), exp, f"1x{by} ss {ss} thr {thr}")
+
+
+@pytest.mark.parametrize("bx,rows", [(256, 256), (64, 256), (16, 64), (128, 384)])
+@pytest.mark.parametrize("ss", [1, 2, 3, 4])
+def test_channel_scaling_column_groups(bx, rows, ss):
+    import gpu_harness as H
+    x = rand_bits(bx + rows + ss, rows, 192, "normal")
+    for thr in (0.045, 3e38):
+        oracle.clear_assert_flags()
+        exp = dict(zip(("out", "meta", "gamax", "gnnz", "gerr"), oracle.channel_scaling(x, bx, 1, thr, ss)))
+        if oracle.assert_flags():
+            continue
+        exp["meta"] = np.array([exp["meta"]])
+        assert_same(H.channel_scaling(x, bx, 1, thr, ss), exp, f"{bx}x1 ss {ss} thr {thr}")
+
+
+@pytest.mark.parametrize("kind", ["block", "row", "col"])
+@pytest.mark.parametrize("thr", [0.045, 1e-6])
+def test_scaling_in_place(kind, thr):
+    """in place: the input must survive until the tensor-level BF16 decision (thr=1e-6 forces it)"""
+    import gpu_harness as H
+    x = rand_bits(91, 256, 256, "normal")
+    if kind == "block":
+        exp = oracle.block_scaling(x, 128, 128, thr, 1)
+        got = H.block_scaling(x, 128, 128, thr, 1, inplace=True)
+    elif kind == "row":
+        exp = oracle.channel_scaling(x, 1, 256, thr, 1)
+        got = H.channel_scaling(x, 1, 256, thr, 1, inplace=True)
+    else:
+        exp = oracle.channel_scaling(x, 256, 1, thr, 1)
+        got = H.channel_scaling(x, 256, 1, thr, 1, inplace=True)
+    e = dict(zip(("out", "meta", "gamax", "gnnz", "gerr"), exp))
+    e["meta"] = np.array([e["meta"]])
+    assert e["meta"][0] == (3 if thr < 1e-3 else 1)
+    assert_same(got, e, f"in place {kind} thr {thr}")
+
+
+@pytest.mark.parametrize("ss", [1, 2, 3, 4])
+def test_block_scaling_float32(ss):
+    import gpu_harness as H
+    g = torch.Generator().manual_seed(50 + ss)
+    x = torch.randn(256, 512, generator=g).numpy()
+    x[5, 7] = 0.0
+    for bx, by in ((128, 128), (32, 64)):
+        e = dict(zip(("out", "meta", "gamax", "gnnz", "gerr"), oracle.block_scaling(x, bx, by, 0.045, ss)))
+        e["meta"] = np.array([e["meta"]])
+        assert_same(H.block_scaling(x, bx, by, 0.045, ss), e, f"float32 block scaling ss {ss} {bx}x{by}")
+
+
+def test_group_and_generic_float32():
+    import gpu_harness as H
+    g = torch.Generator().manual_seed(60)
+    x = (torch.randn(64, 1024, generator=g) * 3).numpy()
+    for fmt in (oracle.FMT_E4M3, oracle.FMT_E5M2, oracle.FMT_E2M3):
+        for sf in (1, 2):
+            for by in (32, 1024):
+                out, sc = oracle.fake_quantize_group(x, 1, by, fmt, sf, want_scales=True)
+                got = H.fake_quantize_group(x, by, fmt, sf)
+                assert_same(got, {"out": out}, f"float32 group fmt {fmt} sf {sf} by {by}")
+                assert np.array_equal(got["scales"].view(np.uint32), sc.view(np.uint32))
+    for mode in (1, 101, 2, 3):
+        exp = dict(zip(("out", "meta"), oracle.fake_quantize(x, 32, 64, 1e-15, mode, 1)))
+        assert_same(H.fake_quantize(x, 32, 64, 1e-15, mode, 1), exp, f"float32 generic mode {mode}")
+
+
+def test_generic_block_kernel_matches_tile_kernel():
+    """MOR_B200_FORCE_GENERIC routes 128x128 blocks through the generic kernel; same bits expected."""
+    code = (
+        "import sys; sys.path[:0]=[%r, %r, %r]\n"
+        "import numpy as np, oracle, gpu_harness as H\n"
+        "from cases import mixed_blocks_bf16\n"
+        "x = mixed_blocks_bf16(7)\n"
+        "for mode, sf in ((1,1),(101,1),(1,2),(2,1),(3,2)):\n"
+        "    out, meta = oracle.fake_quantize(x,128,128,1e-15,mode,sf)\n"
+        "    g = H.fake_quantize(x,128,128,1e-15,mode,sf)\n"
+        "    assert np.array_equal(g['out'], out) and np.array_equal(g['meta'], meta), (mode, sf)\n"
+        "print('generic ok')\n" % (ROOT, os.path.join(ROOT, "tests"), os.path.join(ROOT, "tests", "golden")))
+    env = dict(os.environ, MOR_B200_FORCE_GENERIC="1")
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "generic ok" in r.stdout, r.stdout + r.stderr
+
+
+def test_invalid_arguments_are_status_codes_not_faults():
+    import gpu_harness as H
+    from mor_b200 import cabi
+    x = rand_bits(1, 64, 64)
+    with pytest.raises(cabi.MorB200Error):
+        H.fake_quantize(x, 32, 33, 1.0, 1, 1)          # odd block width
+    with pytest.raises(cabi.MorB200Error):
+        H.fake_quantize(x, 32, 32, 1.0, 1, 3)          # unknown sf_type
+    with pytest.raises(cabi.MorB200Error):
+        H.block_scaling(x, 32, 64, 0.045, 5)           # ss_mode out of range
+    with pytest.raises(AssertionError):
+        H.block_scaling(x, 16, 16, 0.045, 1)           # block shape the pipeline does not cover
+    with pytest.raises(cabi.MorB200Error):
+        H.e8mx(x, 4, 1)                                # quantize_type out of range
+    # the context is still healthy
+    assert torch.zeros(1, device="cuda").item() == 0.0
