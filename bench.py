@@ -152,6 +152,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--suite", action="store_true", help="also time configurations 1-4 (single GPU)")
     ap.add_argument("--scale", type=int, default=1, help="divide the row count (development only; reported)")
+    ap.add_argument("--no-main", action="store_true", help="skip the configuration-5 workload (profiling the suite)")
+    ap.add_argument("--suite-only", default="", help="substring filter on suite entry names")
+    ap.add_argument("--suite-iters", type=int, default=10)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -177,6 +180,11 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     n_gpus = world
+
+    if args.no_main:
+        peak, _ = measured_peak()
+        run_suite(torch, dev, peak, args.suite_only, args.suite_iters)
+        return 0
 
     rows = ROWS // args.scale
     r0, r1 = shard_rows(rows, world, rank, BLOCK)
@@ -281,7 +289,7 @@ def main():
     suite = None
     if args.suite and rank == 0 and world == 1:
         del out
-        suite = run_suite(torch, dev, peak)
+        suite = run_suite(torch, dev, peak, args.suite_only, args.suite_iters)
 
     if rank == 0:
         line = {
@@ -317,7 +325,7 @@ def main():
     return 0
 
 
-def run_suite(torch, dev, peak):
+def run_suite(torch, dev, peak, only="", iters=10):
     """Times every kernel family on configurations 1-4 (bf16, one GPU).  Each launch is
     timed alone with CUDA events on the launching stream; configuration 1 (32 MiB) fits
     in L2, so a 512 MiB buffer is rewritten between launches to evict it."""
@@ -326,7 +334,7 @@ def run_suite(torch, dev, peak):
     results = []
     flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
 
-    def time_call(fn, n=10, warm=3):
+    def time_call(fn, n=iters, warm=min(3, iters)):
         for _ in range(warm):
             fn()
         ms = []
@@ -339,6 +347,8 @@ def run_suite(torch, dev, peak):
         return statistics.median(ms)
 
     def add(name, x, bytes_per_elem, fn):
+        if only and only not in name:
+            return
         ms = time_call(fn)
         n = x.numel()
         gbs = n * bytes_per_elem / (ms * 1e-3) / 1e9
@@ -370,6 +380,11 @@ def run_suite(torch, dev, peak):
     add("c4 MoR 128x128 relative-error criterion (mode 1)", x, 4, lambda: mor.ops.fake_quantize(x, r, c, 128, 128, 1e-15, 1, 1))
     add("c4 MoR 128x128 dynamic-range criterion (mode 101)", x, 4, lambda: mor.ops.fake_quantize(x, r, c, 128, 128, 1e-15, 101, 1))
     add("c4 block scaling 128x128 pipeline (ss 1)", x, 6, lambda: mor.ops.fake_quantize_block_scaling(x, r, c, 128, 128, 3e38, 1))
+    del x
+    x = workloads.config5_slab(0, device=dev)
+    r, c = x.shape
+    add("c5 float32 1 GiB slab block scaling 128x128 pipeline (ss 1)", x, 12, lambda: mor.ops.fake_quantize_block_scaling(x, r, c, 128, 128, THRESHOLD, 1))
+    add("c5 float32 1 GiB slab per-tensor pipeline (ss 4)", x, 12, lambda: mor.ops.fake_quantize_block_scaling(x, r, c, 128, 128, THRESHOLD, 4))
     del x
     os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
     with open(os.path.join(ROOT, "gpurun_out", "suite.json"), "w") as f:

@@ -188,6 +188,108 @@ __device__ __forceinline__ void sqdd_pair(float hi, float lo, float s, float& rh
     else sqdd_fp32_pair<FMT>(hi, lo, s, rhi, rlo);
 }
 
+// ----------------------------------------------------------------------------
+// fast forms, bit-identical to the ones above on their stated domains
+// ----------------------------------------------------------------------------
+// 2^e as a float, -126 <= e <= 127
+__device__ __forceinline__ float pow2f(int e) { return u2f((uint32_t)(e + 127) << 23); }
+
+// Two floats -> packed bf16 word with the reference's round-half-away rule.  Exact
+// for every input except a NEGATIVE NaN whose top eight mantissa bits are ones (the
+// reference maps that to 0x8000, the plain add wraps to 0); callers canonicalise NaNs
+// to +0x7fffffff, for which the add gives 0x8000 as required.
+__device__ __forceinline__ uint32_t pack_bf16_round(float hi, float lo) {
+    return __byte_perm(f2u(lo) + 0x8000u, f2u(hi) + 0x8000u, 0x7632);
+}
+// Two floats whose low 16 bits are zero (results of the power-of-two path) -> packed word
+__device__ __forceinline__ uint32_t pack_bf16_trunc(float hi, float lo) {
+    return __byte_perm(f2u(lo), f2u(hi), 0x7632);
+}
+__device__ __forceinline__ float canon_nan(float v) { return (v != v) ? u2f(0x7FFFFFFFu) : v; }
+
+// Power-of-two (E8) scaling as two float multiplies instead of exponent-field
+// arithmetic.  For -119 <= e8 <= 100 and finite x the field arithmetic of the
+// reference (ref: 283-305) and x * 2^e8 give the same narrow-float code: both scale a
+// normal value exactly, and whatever lands below 2^-126 casts to a signed zero either
+// way; on the way back q * 2^-e8 is exact for every non-zero code.  The one
+// difference is a code of zero with e8 < 0: the field arithmetic returns
+// +-2^(-e8-127), restored here with a select.  e8 outside the range takes the literal
+// path.
+__device__ __forceinline__ bool e8_fast_ok(int e8) { return e8 >= -119 && e8 <= 100; }
+
+template <int FMT>
+__device__ __forceinline__ void sqdd_e8_pair_fast(float hi, float lo, float up, float down, uint32_t zero_bits,
+                                                  float& rhi, float& rlo) {
+    float qhi, qlo;
+    quant_dequant_pair<FMT>(__fmul_rn(hi, up), __fmul_rn(lo, up), qhi, qlo);
+    rhi = __fmul_rn(qhi, down);
+    rlo = __fmul_rn(qlo, down);
+    if (zero_bits) {  // e8 < 0: a zero code comes back as 2^(-e8-127) with the sign of the code
+        if (qhi == 0.0f) rhi = u2f((f2u(qhi) & 0x80000000u) | zero_bits);
+        if (qlo == 0.0f) rlo = u2f((f2u(qlo) & 0x80000000u) | zero_bits);
+    }
+}
+struct E8Consts {
+    float up, down;        // 2^e8, 2^-e8
+    uint32_t zero_bits;    // (-e8) << 23 when e8 < 0, else 0
+    int e8;
+    bool fast;
+};
+__device__ __forceinline__ E8Consts e8_consts(float scale) {
+    E8Consts c;
+    c.e8 = e8_of_scale(scale);
+    c.fast = e8_fast_ok(c.e8);
+    const int e = c.fast ? c.e8 : 0;
+    c.up = pow2f(e);
+    c.down = pow2f(-e);
+    c.zero_bits = e < 0 ? ((uint32_t)(-e) << 23) : 0u;
+    return c;
+}
+template <int FMT>
+__device__ __forceinline__ void sqdd_e8_pair_auto(float hi, float lo, const E8Consts& c, float& rhi, float& rlo) {
+    if (c.fast) sqdd_e8_pair_fast<FMT>(hi, lo, c.up, c.down, c.zero_bits, rhi, rlo);
+    else sqdd_e8_pair<FMT>(hi, lo, c.e8, rhi, rlo);
+}
+
+// exponent of RN(fmax / amax) for fmax = 1.75 * 2^k (448, 57344) or 1.875 * 2^2 (7.5)
+// without the division: amax = m * 2^ea gives (c / m) * 2^(k - ea), and c / m < 1
+// exactly when m > c (no float of either input type rounds c / m up to 1).  Valid for
+// a normal, finite, non-zero amax; `bits` is its binary32 pattern.
+template <int FMT>
+__device__ __forceinline__ int e8_of_amax(uint32_t bits) {
+    constexpr int k = (FMT == kE4M3) ? 8 : (FMT == kE5M2 ? 15 : (FMT == kE3M2 ? 4 : 2));
+    constexpr uint32_t cman = (FMT == kE2M3) ? 0x700000u : 0x600000u;  // 1.875 / 1.75
+    const int ea = (int)(bits >> 23) - 127;
+    return k - ea - ((bits & 0x7FFFFFu) > cman ? 1 : 0);
+}
+
+// q / x for a float q of about the magnitude of x (or zero) and a bf16-valued x,
+// 2^-64 <= |x| < 2^64 (so that the residual below stays a normal number): exactly RN(q / x).
+// With r within one ulp of 1/x, q0 = q * r is within a few ulps of the quotient; x has
+// 8 significant bits, so the residual q - x*q0 is exact in the fma, and q0 + rem * r
+// differs from the true quotient by less than 2^-20 ulp, while a quotient by an 8-bit
+// divisor is never closer than 2^-10 ulp to a rounding boundary: one correction step
+// rounds correctly.
+__device__ __forceinline__ float rcp_fast(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ float div_by_bf16(float q, float x, float r) {
+    const float q0 = __fmul_rn(q, r);
+    const float rem = __fmaf_rn(-x, q0, q);
+    return __fmaf_rn(rem, r, q0);
+}
+__device__ __forceinline__ bool bf16_div_safe(float x) { return (f2u(x) & 0x7FFFFFFFu) - 0x1F800000u < 0x40000000u; }
+
+// packed bf16 magnitude helpers: both halves of a word at once
+__device__ __forceinline__ uint32_t mag2(uint32_t w) { return w & 0x7FFF7FFFu; }
+// number of non-zero halves of a magnitude word (each half <= 0x7FFF, so adding 0x7FFF
+// sets bit 15 exactly when the half is non-zero and never carries across)
+__device__ __forceinline__ int nnz2(uint32_t m) { return __popc((m + 0x7FFF7FFFu) & 0x80008000u); }
+__device__ __forceinline__ uint32_t umax16x2(uint32_t a, uint32_t b) { return __vmaxu2(a, b); }
+__device__ __forceinline__ uint32_t hmax_halves(uint32_t m) { return max(m & 0xFFFFu, m >> 16); }
+
 template <int FMT>
 __device__ __forceinline__ float fmt_max() {
     if constexpr (FMT == kE4M3) return 448.0f;

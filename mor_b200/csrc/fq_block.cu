@@ -1,8 +1,8 @@
 // fake_quantize with a scale per (brows x bcols) block: MoR's per-block choice of
 // representation and the fixed E4M3 / E5M2 block modes (ref: 407-852).
 //
-//   fq_tile128_kernel  128 x 128 bf16 blocks: the 32 KiB tile is read from HBM once
-//                      with 16-byte loads and lives in registers through the
+//   fq_tile128_kernel  128 x 128 bf16 blocks: the 32 KiB tile is read from HBM once,
+//                      by TMA into shared memory, and stays there through the
 //                      amax/amin pass, the optional two-format error pass and the
 //                      cast; one HBM read + one HBM write per element.
 //   fq_block_generic_kernel  any block shape, ragged edges, bf16 or binary32; rereads
@@ -11,6 +11,10 @@
 // The error pass compares two float sums, so both kernels add in the order of the
 // reference's CTA of 16 x 32 threads (one thread per 32-bit word, rows outer, words
 // inner, (e_high + e_low) per word, shfl_down trees); see logical_warp_sum().
+#include <cuda.h>
+
+#include <type_traits>
+
 #include "kernels.cuh"
 
 namespace morb {
@@ -68,41 +72,150 @@ __device__ __forceinline__ void cast_pair(int fmt, float hi, float lo, float s, 
 }
 
 // ---------------------------------------------------------------------------------
-// 128 x 128 bf16 tile in registers
+// 128 x 128 bf16 tile staged in shared memory by TMA
 // ---------------------------------------------------------------------------------
+// One CTA of 128 threads per tile.  Thread 0 issues four cp.async.bulk.tensor.2d loads
+// (column strips of 32 elements = 64 bytes x 128 rows) that land as strip-major
+// [4][128][64 B] in shared memory and signal an mbarrier; several CTAs per SM overlap
+// one tile's load with another's arithmetic.  Lane (a, ty) owns the reference's
+// logical threads tx = 4a..4a+3 of row ty: its 16-byte chunk of strip i, row ty + 32 j
+// holds words tx + 16 i, and a warp's eight rows x four chunks are 512 contiguous
+// bytes, so every shared-memory access is conflict-free.  The passes (amax/amin, the
+// optional two-format error sums, the cast) walk the tile with rolled loops; results
+// go from registers straight to global memory with 16-byte stores.
+
+constexpr int kTileBytes = 128 * 128 * 2;
+constexpr uint32_t kSpinLimit = 1u << 22;  // bounded mbarrier wait; a tile that never arrives is reported, not awaited
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// returns false if the barrier did not complete within the spin limit
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+
+template <int SF>
+struct ErrCtx {
+    const float* lut4;  // SF_FP32: RN(dequant(code) / s) tables
+    const float* lut5;
+    float s4, s5;
+    E8Consts c4, c5;    // SF_E8
+};
+
+// |q4/x - 1| and |q5/x - 1| for one element (ref: 504-541); zero elements add nothing
+template <int SF, bool SAFE>
+__device__ __forceinline__ void word_errors_fast(const ErrCtx<SF>& e, float hi, float lo, float& e4, float& e5) {
+    float q4h, q4l, q5h, q5l;
+    if constexpr (SF == kSfFp32) {
+        const uint32_t c4 = cvt_codes<kE4M3>(__fmul_rn(hi, e.s4), __fmul_rn(lo, e.s4));
+        const uint32_t c5 = cvt_codes<kE5M2>(__fmul_rn(hi, e.s5), __fmul_rn(lo, e.s5));
+        q4h = e.lut4[c4 >> 8]; q4l = e.lut4[c4 & 0xFFu];
+        q5h = e.lut5[c5 >> 8]; q5l = e.lut5[c5 & 0xFFu];
+    } else {
+        sqdd_e8_pair_auto<kE4M3>(hi, lo, e.c4, q4h, q4l);
+        sqdd_e8_pair_auto<kE5M2>(hi, lo, e.c5, q5h, q5l);
+    }
+    float e4h = 0.0f, e4l = 0.0f, e5h = 0.0f, e5l = 0.0f;
+    if constexpr (SAFE) {
+        if (hi != 0.0f) {
+            const float r = rcp_fast(hi);
+            e4h = fabsf(__fsub_rn(div_by_bf16(q4h, hi, r), 1.0f));
+            e5h = fabsf(__fsub_rn(div_by_bf16(q5h, hi, r), 1.0f));
+        }
+        if (lo != 0.0f) {
+            const float r = rcp_fast(lo);
+            e4l = fabsf(__fsub_rn(div_by_bf16(q4l, lo, r), 1.0f));
+            e5l = fabsf(__fsub_rn(div_by_bf16(q5l, lo, r), 1.0f));
+        }
+    } else {
+        if (hi != 0.0f) {
+            e4h = fabsf(__fsub_rn(__fdiv_rn(q4h, hi), 1.0f));
+            e5h = fabsf(__fsub_rn(__fdiv_rn(q5h, hi), 1.0f));
+        }
+        if (lo != 0.0f) {
+            e4l = fabsf(__fsub_rn(__fdiv_rn(q4l, lo), 1.0f));
+            e5l = fabsf(__fsub_rn(__fdiv_rn(q5l, lo), 1.0f));
+        }
+    }
+    e4 = __fadd_rn(e4h, e4l);
+    e5 = __fadd_rn(e5h, e5l);
+}
+
 template <int FMT>
-__device__ __forceinline__ void fill_lut(uint16_t* lut, float s) {
+__device__ __forceinline__ void fill_lut16(uint16_t* lut, float s, int tid) {
     constexpr int NCODES = (FMT == kE2M3) ? 64 : 256;
-    for (int c = threadIdx.x; c < NCODES; c += blockDim.x) {
+    for (int c = tid; c < NCODES; c += 128) {
         float q = h_lo_to_f32(codes_to_h2<FMT>((uint32_t)c));
         if (FMT == kE2M3 && q == 0.0f) q = 0.0f;  // the custom cast returns +0
         lut[c] = (uint16_t)f32_to_bf16_bits(__fdiv_rn(q, s));
     }
 }
 template <int FMT>
+__device__ __forceinline__ void fill_lut32t(float* lut, float s, int tid) {
+    for (int c = tid; c < 256; c += 128) lut[c] = __fdiv_rn(h_lo_to_f32(codes_to_h2<FMT>((uint32_t)c)), s);
+}
+template <int FMT>
 __device__ __forceinline__ uint32_t lut_word(const uint16_t* lut, uint32_t w, float s) {
     const uint32_t c = cvt_codes<FMT>(__fmul_rn(bf16_hi(w), s), __fmul_rn(bf16_lo(w), s));
-    return ((uint32_t)lut[c >> 8] << 16) | lut[c & 0xFFu];
+    return __byte_perm((uint32_t)lut[c & 0xFFu], (uint32_t)lut[c >> 8], 0x5410);
+}
+template <int FMT>
+__device__ __forceinline__ uint32_t e8_word(uint32_t w, const E8Consts& c) {
+    float rh, rl;
+    sqdd_e8_pair_auto<FMT>(bf16_hi(w), bf16_lo(w), c, rh, rl);
+    return c.fast ? pack_bf16_trunc(rh, rl) : pack_bf16(rh, rl);
 }
 
 template <int SF>
 __global__ void __launch_bounds__(128)
-fq_tile128_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, int32_t* __restrict__ meta,
+fq_tile128_kernel(const __grid_constant__ CUtensorMap tmap, uint4* __restrict__ out, int32_t* __restrict__ meta,
                   int64_t cols_vec, int blocks_x, float clamp, int qmode, int dyn_mode) {
+    extern __shared__ __align__(128) uint8_t s_tile[];  // [4 strips][128 rows][64 B]
+    __shared__ __align__(8) uint64_t s_bar;
     __shared__ float s_red[2][4];
     __shared__ float s_w4[16], s_w5[16];
     __shared__ float s_tot[2];
-    __shared__ uint16_t s_lut[256];
+    __shared__ __align__(16) float s_lut4[256];
+    __shared__ __align__(16) float s_lut5[256];
+    uint16_t* s_lut16 = reinterpret_cast<uint16_t*>(s_lut4);  // the cast table reuses the error tables' space
     const int tid = threadIdx.x, a = tid & 3, ty = tid >> 2, lane = tid & 31, wid = tid >> 5;
     const int64_t b = blockIdx.x;
-    const int64_t r0 = (b / blocks_x) * 128, c0v = (int64_t)(b % blocks_x) * 16;
+    const int bx = (int)(b % blocks_x), by = (int)(b / blocks_x);
 
-    // the lane that owns logical threads tx = 4a..4a+3 of row ty holds words 4a+16i+k
-    uint4 v[4][4];
+    if (tid == 0) mbar_init(&s_bar, 1);
+    __syncthreads();
+    if (tid == 0) {
+        mbar_expect_tx(&s_bar, kTileBytes);
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) v[j][i] = ld_stream(in + (r0 + ty + 32 * j) * cols_vec + c0v + 4 * i + a);
+        for (int sidx = 0; sidx < 4; ++sidx) tma_load_2d(s_tile + sidx * 8192, &tmap, bx * 128 + sidx * 32, by * 128, &s_bar);
+    }
+    if (!mbar_wait_bounded(&s_bar, 0)) {
+        // the load did not complete: report it in meta, give the copy one more bounded
+        // chance to land before this CTA's shared memory is handed to the next one
+        if (tid == 0) meta[b] = -1;
+        mbar_wait_bounded(&s_bar, 0);
+        return;
+    }
+    const uint4* tile = reinterpret_cast<const uint4*>(s_tile);
+    auto chunk = [&](int j, int i) -> uint4 { return tile[i * 512 + (ty + 32 * j) * 4 + a]; };
 
     // amax and smallest non-zero magnitude (ref: 407-485); bf16 magnitudes order like
     // their 15-bit patterns, and "pattern - 1" as unsigned sends zero to the top.
@@ -114,10 +227,11 @@ fq_tile128_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, int32_t
         mx = max(mx, max(lo_v, hi_v));
         mn = min(mn, min(lo_v - 1u, hi_v - 1u));
     };
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) { scan(v[j][i].x); scan(v[j][i].y); scan(v[j][i].z); scan(v[j][i].w); }
+#pragma unroll 4
+    for (int n = 0; n < 16; ++n) {
+        const uint4 v = chunk(n >> 2, n & 3);
+        scan(v.x); scan(v.y); scan(v.z); scan(v.w);
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         mx = max(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
@@ -132,21 +246,34 @@ fq_tile128_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, int32_t
     if (qmode == QM_MOR) {
         repr = choose_by_range(amax, amin, clamp, dyn_mode != 0);
         if (repr == NEED_ERRORS) {
-            const float s4 = __fdiv_rn(448.0f, amax), s5 = __fdiv_rn(57344.0f, amax);
+            ErrCtx<SF> e;
+            e.s4 = __fdiv_rn(448.0f, amax);
+            e.s5 = __fdiv_rn(57344.0f, amax);
+            e.lut4 = s_lut4; e.lut5 = s_lut5;
+            if constexpr (SF == kSfFp32) {
+                fill_lut32t<kE4M3>(s_lut4, e.s4, tid);
+                fill_lut32t<kE5M2>(s_lut5, e.s5, tid);
+                __syncthreads();
+            } else {
+                e.c4 = e8_consts(e.s4);
+                e.c5 = e8_consts(e.s5);
+            }
+            // every non-zero magnitude of the block lies in [amin, amax]
+            const bool safe = bf16_div_safe(amin) && bf16_div_safe(amax);
             float a4[4] = {0.f, 0.f, 0.f, 0.f}, a5[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+            for (int n = 0; n < 16; ++n) {  // rows outer (j = n / 4), words inner (i = n % 4)
+                const uint4 v = chunk(n >> 2, n & 3);
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const uint32_t w[4] = {v[j][i].x, v[j][i].y, v[j][i].z, v[j][i].w};
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        float e4, e5;
-                        word_errors<SF>(bf16_hi(w[k]), bf16_lo(w[k]), s4, s5, e4, e5);
-                        a4[k] = __fadd_rn(a4[k], e4);
-                        a5[k] = __fadd_rn(a5[k], e5);
-                    }
+                for (int k = 0; k < 4; ++k) {
+                    float e4, e5;
+                    if (safe) word_errors_fast<SF, true>(e, bf16_hi(w[k]), bf16_lo(w[k]), e4, e5);
+                    else word_errors_fast<SF, false>(e, bf16_hi(w[k]), bf16_lo(w[k]), e4, e5);
+                    a4[k] = __fadd_rn(a4[k], e4);
+                    a5[k] = __fadd_rn(a5[k], e5);
                 }
+            }
             const float w4 = logical_warp_sum<4>(a4), w5 = logical_warp_sum<4>(a5);
             if ((tid & 7) == 0) { s_w4[tid >> 3] = w4; s_w5[tid >> 3] = w5; }
             __syncthreads();
@@ -165,38 +292,75 @@ fq_tile128_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, int32_t
     if (tid == 0) meta[b] = code;
     if (!(amax > 0.0f)) fmt = -1;  // all-zero block: copied through (ref: 759, 773, 787, 802, 814)
 
-    if (fmt >= 0) {
-        const float s = __fdiv_rn(fmt == kE2M3 ? 7.5f : (fmt == kE4M3 ? 448.0f : 57344.0f), amax);
-        if constexpr (SF == kSfFp32) {
-            if (fmt == kE4M3) fill_lut<kE4M3>(s_lut, s);
-            else if (fmt == kE5M2) fill_lut<kE5M2>(s_lut, s);
-            else fill_lut<kE2M3>(s_lut, s);
-            __syncthreads();
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                uint32_t w[4] = {v[j][i].x, v[j][i].y, v[j][i].z, v[j][i].w};
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    if constexpr (SF == kSfFp32) {
-                        if (fmt == kE4M3) w[k] = lut_word<kE4M3>(s_lut, w[k], s);
-                        else if (fmt == kE5M2) w[k] = lut_word<kE5M2>(s_lut, w[k], s);
-                        else w[k] = lut_word<kE2M3>(s_lut, w[k], s);
-                    } else {
-                        float rh, rl;
-                        cast_pair<SF>(fmt, bf16_hi(w[k]), bf16_lo(w[k]), s, rh, rl);
-                        w[k] = pack_bf16(rh, rl);
-                    }
-                }
-                v[j][i] = make_uint4(w[0], w[1], w[2], w[3]);
-            }
+    uint4* dst = out + ((int64_t)by * 128) * cols_vec + (int64_t)bx * 16;
+    auto store = [&](int n, const uint4& v) { st_stream(dst + (int64_t)(ty + 32 * (n >> 2)) * cols_vec + 4 * (n & 3) + a, v); };
+    if (fmt < 0) {
+#pragma unroll 4
+        for (int n = 0; n < 16; ++n) store(n, chunk(n >> 2, n & 3));
+        return;
     }
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) st_stream(out + (r0 + ty + 32 * j) * cols_vec + c0v + 4 * i + a, v[j][i]);
+    const float s = __fdiv_rn(fmt == kE2M3 ? 7.5f : (fmt == kE4M3 ? 448.0f : 57344.0f), amax);
+    if constexpr (SF == kSfFp32) {
+        if (fmt == kE4M3) fill_lut16<kE4M3>(s_lut16, s, tid);
+        else if (fmt == kE5M2) fill_lut16<kE5M2>(s_lut16, s, tid);
+        else fill_lut16<kE2M3>(s_lut16, s, tid);
+        __syncthreads();
+        auto cast_all = [&](auto fmt_tag) {
+            constexpr int F = decltype(fmt_tag)::value;
+#pragma unroll 2
+            for (int n = 0; n < 16; ++n) {
+                uint4 v = chunk(n >> 2, n & 3);
+                v.x = lut_word<F>(s_lut16, v.x, s); v.y = lut_word<F>(s_lut16, v.y, s);
+                v.z = lut_word<F>(s_lut16, v.z, s); v.w = lut_word<F>(s_lut16, v.w, s);
+                store(n, v);
+            }
+        };
+        if (fmt == kE4M3) cast_all(std::integral_constant<int, kE4M3>{});
+        else if (fmt == kE5M2) cast_all(std::integral_constant<int, kE5M2>{});
+        else cast_all(std::integral_constant<int, kE2M3>{});
+    } else {
+        const E8Consts c = e8_consts(s);
+        auto cast_all = [&](auto fmt_tag) {
+            constexpr int F = decltype(fmt_tag)::value;
+#pragma unroll 2
+            for (int n = 0; n < 16; ++n) {
+                uint4 v = chunk(n >> 2, n & 3);
+                v.x = e8_word<F>(v.x, c); v.y = e8_word<F>(v.y, c); v.z = e8_word<F>(v.z, c); v.w = e8_word<F>(v.w, c);
+                store(n, v);
+            }
+        };
+        if (fmt == kE4M3) cast_all(std::integral_constant<int, kE4M3>{});
+        else if (fmt == kE5M2) cast_all(std::integral_constant<int, kE5M2>{});
+        else cast_all(std::integral_constant<int, kE2M3>{});
+    }
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess) return nullptr;
+        if (qres != cudaDriverEntryPointSuccess) return nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// bf16 [rows, cols] tensor, boxes of 32 elements (64 bytes) x 128 rows, no swizzle
+bool make_strip_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {32, 128};
+    const cuuint32_t estride[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride, box, estride,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // ---------------------------------------------------------------------------------
@@ -314,12 +478,15 @@ int launch_fq_block(const void* in, void* out, int is_fp32, int32_t* meta, int64
     if (nb > 0x7FFFFFFF) return kErrTooLarge;
     const bool aligned = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
     static const bool force_generic = getenv("MOR_B200_FORCE_GENERIC") != nullptr;
-    if (!is_fp32 && brows == 128 && bcols == 128 && rows % 128 == 0 && cols % 128 == 0 && aligned && !force_generic) {
-        auto* i4 = static_cast<const uint4*>(in);
-        auto* o4 = static_cast<uint4*>(out);
-        if (sf_type == kSfE8) fq_tile128_kernel<kSfE8><<<(unsigned)nb, 128, 0, st>>>(i4, o4, meta, cols / 8, (int)bx, clamp, quant_mode, dynamic_range_mode);
-        else fq_tile128_kernel<kSfFp32><<<(unsigned)nb, 128, 0, st>>>(i4, o4, meta, cols / 8, (int)bx, clamp, quant_mode, dynamic_range_mode);
-        return check_launch();
+    if (!is_fp32 && brows == 128 && bcols == 128 && rows % 128 == 0 && cols % 128 == 0 && aligned && !force_generic &&
+        rows < (int64_t(1) << 31) && cols < (int64_t(1) << 31)) {
+        CUtensorMap map;
+        if (make_strip_map(&map, in, rows, cols)) {
+            auto* o4 = static_cast<uint4*>(out);
+            if (sf_type == kSfE8) fq_tile128_kernel<kSfE8><<<(unsigned)nb, 128, kTileBytes, st>>>(map, o4, meta, cols / 8, (int)bx, clamp, quant_mode, dynamic_range_mode);
+            else fq_tile128_kernel<kSfFp32><<<(unsigned)nb, 128, kTileBytes, st>>>(map, o4, meta, cols / 8, (int)bx, clamp, quant_mode, dynamic_range_mode);
+            return check_launch();
+        }
     }
     // logical CTA of the reference (ref: 1770-1790), needed for the order of the error sums
     int ltx = 16, lty = 32;

@@ -4,19 +4,27 @@
 // with the element wrappers SQDD_{fp32,e8}_{e4m3,e5m2,e2m3} (ref: 356-379): group
 // amax, scale = format max / amax (truncated to a power of two for E8 scaling),
 // multiply, RNE cast, exact division, bf16 rounding.  An all-zero group is copied.
-// One HBM read and one HBM write per element:
+// One HBM read and one HBM write per element (4 bytes per bf16 element):
 //   k <= 32 vectors : a group is a power-of-two set of lanes, amax by xor shuffles;
 //   larger k        : one CTA per group, the group cached in registers between the
 //                     amax pass and the cast, per-group look-up table for the
 //                     division when the scale is a binary32 number.
+// Instruction budget: at the HBM roofline a bf16 element has about 22 issue slots, so
+// amax works on packed bf16 magnitudes (both halves of a word per instruction), the
+// power-of-two scale is two float multiplies with its exponent taken from the amax
+// bits (no division), and results of that path are packed without rounding (they are
+// exact in bf16).
 #include "kernels.cuh"
 
 namespace morb {
 
 namespace {
 
+// amax of a vector as a float; bf16 vectors go through packed integer maxima.  A NaN
+// element makes the packed maximum exceed 0x7F80; the reference ignores NaNs (fmaxf),
+// so that rare case is redone with float compares.
 template <typename T>
-__device__ __forceinline__ float vec_amax(const typename T::vec_t& v) {
+__device__ __forceinline__ float vec_amax_float(const typename T::vec_t& v) {
     float a = 0.0f;
 #pragma unroll
     for (int k = 0; k < T::kWordsPerVec; ++k) {
@@ -26,18 +34,60 @@ __device__ __forceinline__ float vec_amax(const typename T::vec_t& v) {
     }
     return a;
 }
+__device__ __forceinline__ uint32_t vec_amax_pattern(const uint4& v) {
+    return hmax_halves(umax16x2(umax16x2(mag2(v.x), mag2(v.y)), umax16x2(mag2(v.z), mag2(v.w))));
+}
 
 template <typename T, int FMT, int SF>
-__device__ __forceinline__ typename T::vec_t vec_cast(const typename T::vec_t& v, float s) {
+__device__ __forceinline__ typename T::vec_t vec_cast_fp32scale(const typename T::vec_t& v, float s) {
     typename T::vec_t o;
 #pragma unroll
     for (int k = 0; k < T::kWordsPerVec; ++k) {
         float hi, lo, rh, rl;
         T::unpack(v, k, hi, lo);
-        sqdd_pair<FMT, SF>(hi, lo, s, rh, rl);
+        sqdd_fp32_pair<FMT>(hi, lo, s, rh, rl);
         T::pack(o, k, rh, rl);
     }
     return o;
+}
+
+template <typename T, int FMT>
+__device__ __forceinline__ typename T::vec_t vec_cast_e8(const typename T::vec_t& v, const E8Consts& c) {
+    typename T::vec_t o;
+#pragma unroll
+    for (int k = 0; k < T::kWordsPerVec; ++k) {
+        float hi, lo, rh, rl;
+        T::unpack(v, k, hi, lo);
+        sqdd_e8_pair_auto<FMT>(hi, lo, c, rh, rl);
+        if constexpr (T::kBytesPerElem == 2) {
+            // exact in bf16 (at most four significant bits) unless the literal path met a non-finite value
+            const uint32_t w = c.fast ? pack_bf16_trunc(rh, rl) : pack_bf16(rh, rl);
+            if (k == 0) o.x = w; else if (k == 1) o.y = w; else if (k == 2) o.z = w; else o.w = w;
+        } else {
+            T::pack(o, k, rh, rl);
+        }
+    }
+    return o;
+}
+
+// scale constants of a group from its amax: the exponent comes from the amax bits when
+// the quotient is a normal number, from the division itself otherwise
+template <int FMT>
+__device__ __forceinline__ E8Consts e8_from_amax(float a, float& scale_out) {
+    const uint32_t ab = f2u(a);
+    E8Consts c;
+    int e8 = 1000;
+    if ((ab >> 23) != 0u && (ab >> 23) != 0xFFu) e8 = e8_of_amax<FMT>(ab);
+    if (e8_fast_ok(e8)) {
+        c.e8 = e8; c.fast = true; c.up = pow2f(e8); c.down = pow2f(-e8);
+        c.zero_bits = e8 < 0 ? ((uint32_t)(-e8) << 23) : 0u;
+        scale_out = c.up;  // the E8M0 scale that is applied
+    } else {
+        const float s = __fdiv_rn(fmt_max<FMT>(), a);
+        c = e8_consts(s);
+        scale_out = u2f(f2u(s) & 0x7F800000u);
+    }
+    return c;
 }
 
 template <typename T, int FMT, int SF>
@@ -48,26 +98,42 @@ group_small_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_t* 
     const int64_t stride = (int64_t)gridDim.x * 256;
     const int64_t gtid = (int64_t)blockIdx.x * 256 + threadIdx.x;
     for (int64_t m = gtid; m < n_meta; m += stride) meta[m] = meta_code;
+    constexpr int U = 4;
     // nvec is a multiple of 32, so whole warps enter or leave the loop together
-    for (int64_t i = gtid; i < nvec; i += stride * 2) {
-        const bool second = i + stride < nvec;
-        typename T::vec_t v0 = ld_stream(in + i), v1;
-        if (second) v1 = ld_stream(in + i + stride);
+    for (int64_t i = gtid; i < nvec; i += stride * U) {
+        typename T::vec_t v[U];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            if (u == 1 && !second) break;
-            typename T::vec_t& v = u ? v1 : v0;
-            float a = vec_amax<T>(v);
-            for (int o = lanes_per_group >> 1; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+        for (int u = 0; u < U; ++u)
+            if (i + u * stride < nvec) v[u] = ld_stream(in + i + u * stride);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (i + u * stride >= nvec) break;
+            float a;
+            if constexpr (T::kBytesPerElem == 2) {
+                uint32_t p = vec_amax_pattern(v[u]);
+                for (int o = lanes_per_group >> 1; o > 0; o >>= 1) p = max(p, __shfl_xor_sync(0xFFFFFFFFu, p, o));
+                a = u2f(p << 16);
+                if (p > 0x7F80u) {  // a NaN in the group: the reference's fmaxf skips it
+                    a = vec_amax_float<T>(v[u]);
+                    for (int o = lanes_per_group >> 1; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+                }
+            } else {
+                a = vec_amax_float<T>(v[u]);
+                for (int o = lanes_per_group >> 1; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+            }
             float s = 1.0f;
             if (a > 0.0f) {
-                s = __fdiv_rn(fmt_max<FMT>(), a);
-                v = vec_cast<T, FMT, SF>(v, s);
+                if constexpr (SF == kSfE8) {
+                    const E8Consts c = e8_from_amax<FMT>(a, s);
+                    v[u] = vec_cast_e8<T, FMT>(v[u], c);
+                } else {
+                    s = __fdiv_rn(fmt_max<FMT>(), a);
+                    v[u] = vec_cast_fp32scale<T, FMT, SF>(v[u], s);
+                }
             }
             const int64_t idx = i + u * stride;
-            st_stream(out + idx, v);
-            if (scales && (threadIdx.x & (lanes_per_group - 1)) == 0)
-                scales[idx / lanes_per_group] = (SF == kSfE8 && a > 0.0f) ? u2f(f2u(s) & 0x7F800000u) : s;
+            st_stream(out + idx, v[u]);
+            if (scales && (threadIdx.x & (lanes_per_group - 1)) == 0) scales[idx / lanes_per_group] = s;
         }
     }
 }
@@ -76,7 +142,7 @@ constexpr int kRowThreads = 256;
 constexpr int kRowMaxVec = 8;
 
 template <typename T, int FMT, int SF>
-__global__ void __launch_bounds__(kRowThreads)
+__global__ void __launch_bounds__(kRowThreads, 4)
 group_row_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_t* __restrict__ out,
                  float* __restrict__ scales, int group_vec, int32_t* __restrict__ meta, int32_t meta_code) {
     __shared__ float s_red[kRowThreads / 32];
@@ -84,26 +150,36 @@ group_row_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_t* __
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int64_t base = (int64_t)blockIdx.x * group_vec;
     typename T::vec_t v[kRowMaxVec];
-    float a = 0.0f;
 #pragma unroll
     for (int u = 0; u < kRowMaxVec; ++u)
         if (tid + u * kRowThreads < group_vec) v[u] = ld_stream(in + base + tid + u * kRowThreads);
+    float a = 0.0f;
+    if constexpr (T::kBytesPerElem == 2) {
+        uint32_t p = 0u;
 #pragma unroll
-    for (int u = 0; u < kRowMaxVec; ++u)
-        if (tid + u * kRowThreads < group_vec) a = fmaxf(a, vec_amax<T>(v[u]));
+        for (int u = 0; u < kRowMaxVec; ++u)
+            if (tid + u * kRowThreads < group_vec) p = max(p, vec_amax_pattern(v[u]));
+        a = u2f(p << 16);
+        if (p > 0x7F80u) {
+            a = 0.0f;
+#pragma unroll
+            for (int u = 0; u < kRowMaxVec; ++u)
+                if (tid + u * kRowThreads < group_vec) a = fmaxf(a, vec_amax_float<T>(v[u]));
+        }
+    } else {
+#pragma unroll
+        for (int u = 0; u < kRowMaxVec; ++u)
+            if (tid + u * kRowThreads < group_vec) a = fmaxf(a, vec_amax_float<T>(v[u]));
+    }
     a = warp_max(a);
     if (lane == 0) s_red[wid] = a;
     __syncthreads();
 #pragma unroll
     for (int w = 0; w < kRowThreads / 32; ++w) a = fmaxf(a, s_red[w]);
     float s = 1.0f;
-    if (a > 0.0f) s = __fdiv_rn(fmt_max<FMT>(), a);
-    if (tid == 0) {
-        if (meta) meta[blockIdx.x] = meta_code;
-        if (scales) scales[blockIdx.x] = (SF == kSfE8 && a > 0.0f) ? u2f(f2u(s) & 0x7F800000u) : s;
-    }
     if (a > 0.0f) {
         if constexpr (SF == kSfFp32) {
+            s = __fdiv_rn(fmt_max<FMT>(), a);
             // result = f(code) for a fixed scale: tabulate with the exact division once
             constexpr int NCODES = (FMT == kE2M3) ? 64 : 256;
             for (int c = tid; c < NCODES; c += kRowThreads) {
@@ -122,7 +198,7 @@ group_row_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_t* __
                         T::unpack(v[u], k, hi, lo);
                         const uint32_t c = cvt_codes<FMT>(__fmul_rn(hi, s), __fmul_rn(lo, s));
                         if constexpr (T::kBytesPerElem == 2) {
-                            const uint32_t w = (s_lut[c >> 8] << 16) | s_lut[c & 0xFFu];
+                            const uint32_t w = __byte_perm(s_lut[c & 0xFFu], s_lut[c >> 8], 0x5410);
                             if (k == 0) v[u].x = w; else if (k == 1) v[u].y = w; else if (k == 2) v[u].z = w; else v[u].w = w;
                         } else {
                             T::pack(v[u], k, u2f(s_lut[c >> 8]), u2f(s_lut[c & 0xFFu]));
@@ -130,10 +206,15 @@ group_row_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_t* __
                     }
                 }
         } else {
+            const E8Consts c = e8_from_amax<FMT>(a, s);
 #pragma unroll
             for (int u = 0; u < kRowMaxVec; ++u)
-                if (tid + u * kRowThreads < group_vec) v[u] = vec_cast<T, FMT, SF>(v[u], s);
+                if (tid + u * kRowThreads < group_vec) v[u] = vec_cast_e8<T, FMT>(v[u], c);
         }
+    }
+    if (tid == 0) {
+        if (meta) meta[blockIdx.x] = meta_code;
+        if (scales) scales[blockIdx.x] = s;
     }
 #pragma unroll
     for (int u = 0; u < kRowMaxVec; ++u)
@@ -151,7 +232,7 @@ int launch_t(const void* in, void* out, float* scales, int32_t* meta, int32_t me
     auto* i4 = static_cast<const typename T::vec_t*>(in);
     auto* o4 = static_cast<typename T::vec_t*>(out);
     if (gvec <= 32 && (gvec & (gvec - 1)) == 0 && nvec % 32 == 0) {
-        int64_t grid = (nvec + 511) / 512;
+        int64_t grid = (nvec + 1023) / 1024;
         const int64_t cap = (int64_t)sm_count() * 8;
         if (grid > cap) grid = cap;
         if (grid < 1) grid = 1;

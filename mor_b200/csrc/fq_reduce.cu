@@ -2,7 +2,14 @@
 // order-independent, so these kernels are free to use any traversal: 16-byte loads,
 // warp shuffles, one shared-memory step per CTA, and one atomicMax / atomicAdd per CTA
 // into the workspace scalars (the bit pattern of a non-negative float orders like an
-// unsigned integer).  NaNs are ignored by fmaxf and never counted, as in the reference.
+// unsigned integer).
+//
+// These kernels read 2 bytes per bf16 element, i.e. they have about 11 issue slots per
+// element at the HBM roofline, so bf16 data is reduced in packed form: a magnitude
+// word (w & 0x7FFF7FFF) feeds one packed 16-bit maximum for both halves, and the
+// non-zero count is a popcount of (m + 0x7FFF7FFF) & 0x80008000.  NaNs, which the
+// reference's fmaxf ignores and never counts, show up as a packed maximum above
+// 0x7F80; a CTA that sees one redoes its part with float compares.
 #include "kernels.cuh"
 
 namespace morb {
@@ -11,8 +18,26 @@ namespace {
 
 constexpr int kThreads = 256;
 
+struct Acc {
+    uint32_t packed_max;  // bf16 path: two 15-bit maxima
+    float fmax_;          // float path
+    int nnz;
+};
+
 template <typename T>
-__device__ __forceinline__ void vec_amax_nnz(const typename T::vec_t& v, float& amax, int& nnz) {
+__device__ __forceinline__ void vec_acc_fast(const typename T::vec_t& v, Acc& a) {
+    if constexpr (T::kBytesPerElem == 2) {
+        const uint32_t m0 = mag2(v.x), m1 = mag2(v.y), m2 = mag2(v.z), m3 = mag2(v.w);
+        a.packed_max = umax16x2(umax16x2(a.packed_max, m0), umax16x2(umax16x2(m1, m2), m3));
+        a.nnz += nnz2(m0) + nnz2(m1) + nnz2(m2) + nnz2(m3);
+    } else {
+        const float a0 = fabsf(v.x), a1 = fabsf(v.y), a2 = fabsf(v.z), a3 = fabsf(v.w);
+        a.fmax_ = fmaxf(fmaxf(a.fmax_, a0), fmaxf(fmaxf(a1, a2), a3));
+        a.nnz += (a0 > 0.0f) + (a1 > 0.0f) + (a2 > 0.0f) + (a3 > 0.0f);
+    }
+}
+template <typename T>
+__device__ __forceinline__ void vec_acc_exact(const typename T::vec_t& v, float& amax, int& nnz) {
 #pragma unroll
     for (int k = 0; k < T::kWordsPerVec; ++k) {
         float hi, lo;
@@ -23,23 +48,38 @@ __device__ __forceinline__ void vec_amax_nnz(const typename T::vec_t& v, float& 
     }
 }
 
-// CTA-wide combine; returns the totals in thread 0.
-__device__ __forceinline__ void cta_amax_nnz(float& amax, int& nnz) {
+// CTA-wide combine; totals valid in thread 0 (and in all of warp 0's lanes).
+__device__ __forceinline__ void cta_combine(float& amax, int& nnz) {
     __shared__ float s_a[32];
     __shared__ int s_n[32];
+    __syncthreads();
     amax = warp_max(amax);
     nnz = warp_sum_int(nnz);
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     if (lane == 0) { s_a[wid] = amax; s_n[wid] = nnz; }
     __syncthreads();
-    if (wid == 0) {
-        const int nw = (blockDim.x + 31) >> 5;
-        amax = lane < nw ? s_a[lane] : 0.0f;
-        nnz = lane < nw ? s_n[lane] : 0;
-        amax = warp_max(amax);
-        nnz = warp_sum_int(nnz);
-    }
-    __syncthreads();
+    const int nw = (blockDim.x + 31) >> 5;
+    amax = lane < nw ? s_a[lane] : 0.0f;
+    nnz = lane < nw ? s_n[lane] : 0;
+    amax = warp_max(amax);
+    nnz = warp_sum_int(nnz);
+}
+
+template <typename T>
+__device__ __forceinline__ float acc_amax(const Acc& a) {
+    if constexpr (T::kBytesPerElem == 2) return u2f(hmax_halves(a.packed_max) << 16);
+    else return a.fmax_;
+}
+// true when the fast bf16 accumulation may have met a NaN anywhere in the CTA
+template <typename T>
+__device__ __forceinline__ bool cta_saw_nan(float amax) {
+    if constexpr (T::kBytesPerElem == 2) return __syncthreads_or(f2u(amax) > 0x7F800000u);
+    else return false;
+}
+
+__device__ __forceinline__ void publish(ScalarsWs* ws, float amax, int nnz) {
+    atomicMax(&ws->gamax_bits, f2u(amax));
+    if (nnz) atomicAdd(&ws->gnnz, (unsigned long long)nnz);
 }
 
 __global__ void zero_scalars_kernel(ScalarsWs* ws) {
@@ -51,8 +91,7 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads) amax_nnz_flat_kernel(const typename T::vec_t* __restrict__ in,
                                                                  int64_t nvec, int64_t n_tail_elems,
                                                                  ScalarsWs* __restrict__ ws) {
-    float amax = 0.0f;
-    int nnz = 0;
+    Acc acc{0u, 0.0f, 0};
     const int64_t stride = (int64_t)gridDim.x * kThreads;
     const int64_t gtid = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     for (int64_t i = gtid; i < nvec; i += stride * 4) {
@@ -62,7 +101,13 @@ __global__ void __launch_bounds__(kThreads) amax_nnz_flat_kernel(const typename 
             if (i + u * stride < nvec) v[u] = ld_keep(in + i + u * stride);
 #pragma unroll
         for (int u = 0; u < 4; ++u)
-            if (i + u * stride < nvec) vec_amax_nnz<T>(v[u], amax, nnz);
+            if (i + u * stride < nvec) vec_acc_fast<T>(v[u], acc);
+    }
+    float amax = acc_amax<T>(acc);
+    int nnz = acc.nnz;
+    if (cta_saw_nan<T>(amax)) {
+        amax = 0.0f; nnz = 0;
+        for (int64_t i = gtid; i < nvec; i += stride) vec_acc_exact<T>(ld_keep(in + i), amax, nnz);
     }
     if (gtid < n_tail_elems) {
         float a;
@@ -71,68 +116,61 @@ __global__ void __launch_bounds__(kThreads) amax_nnz_flat_kernel(const typename 
         amax = fmaxf(amax, a);
         nnz += a > 0.0f;
     }
-    cta_amax_nnz(amax, nnz);
-    if (threadIdx.x == 0) {
-        atomicMax(&ws->gamax_bits, f2u(amax));
-        if (nnz) atomicAdd(&ws->gnnz, (unsigned long long)nnz);
-    }
+    cta_combine(amax, nnz);
+    if (threadIdx.x == 0) publish(ws, amax, nnz);
 }
 
-// One CTA per (brows x bcols) block; bcols is a multiple of the 16-byte vector width
-// and rows are 16-byte aligned (checked by the caller).
+// One CTA per (brows x bcols) block.  W lanes (a power of two) span a block row in
+// 16-byte vectors, 256 / W rows are in flight per step; no division in the loops.
 template <typename T>
 __global__ void __launch_bounds__(kThreads) amax_nnz_blocks_kernel(const typename T::vec_t* __restrict__ in,
                                                                    int64_t cols_vec, int brows, int bcols_vec,
-                                                                   int64_t blocks_x, float* __restrict__ block_amax,
+                                                                   int64_t blocks_x, int w_shift,
+                                                                   float* __restrict__ block_amax,
                                                                    ScalarsWs* __restrict__ ws) {
     const int64_t b = blockIdx.x;
     const int64_t r0 = (b / blocks_x) * brows, c0 = (b % blocks_x) * bcols_vec;
-    float amax = 0.0f;
-    int nnz = 0;
-    const int n = brows * bcols_vec;
-    for (int i = threadIdx.x; i < n; i += kThreads * 4) {
-        typename T::vec_t v[4];
+    const int W = 1 << w_shift, RPS = kThreads >> w_shift;
+    const int tx = threadIdx.x & (W - 1), ty = threadIdx.x >> w_shift;
+    const typename T::vec_t* base = in + r0 * cols_vec + c0;
+    Acc acc{0u, 0.0f, 0};
+    if (brows >= 4 * RPS) {  // tall blocks: four rows in flight per lane
+        for (int cv = tx; cv < bcols_vec; cv += W) {
+            int r = ty;
+            for (; r + 3 * RPS < brows; r += 4 * RPS) {
+                typename T::vec_t v[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int j = i + u * kThreads;
-            if (j < n) v[u] = ld_keep(in + (r0 + j / bcols_vec) * cols_vec + c0 + j % bcols_vec);
+                for (int u = 0; u < 4; ++u) v[u] = ld_keep(base + (int64_t)(r + u * RPS) * cols_vec + cv);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) vec_acc_fast<T>(v[u], acc);
+            }
+            for (; r < brows; r += RPS) vec_acc_fast<T>(ld_keep(base + (int64_t)r * cols_vec + cv), acc);
         }
+    } else {                 // wide blocks (rows of a matrix): four vectors of a row in flight per lane
+        for (int r = ty; r < brows; r += RPS) {
+            const typename T::vec_t* row = base + (int64_t)r * cols_vec;
+            int cv = tx;
+            for (; cv + 3 * W < bcols_vec; cv += 4 * W) {
+                typename T::vec_t v[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-            if (i + u * kThreads < n) vec_amax_nnz<T>(v[u], amax, nnz);
+                for (int u = 0; u < 4; ++u) v[u] = ld_keep(row + cv + u * W);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) vec_acc_fast<T>(v[u], acc);
+            }
+            for (; cv < bcols_vec; cv += W) vec_acc_fast<T>(ld_keep(row + cv), acc);
+        }
     }
-    cta_amax_nnz(amax, nnz);
+    float amax = acc_amax<T>(acc);
+    int nnz = acc.nnz;
+    if (cta_saw_nan<T>(amax)) {
+        amax = 0.0f; nnz = 0;
+        for (int cv = tx; cv < bcols_vec; cv += W)
+            for (int r = ty; r < brows; r += RPS) vec_acc_exact<T>(ld_keep(base + (int64_t)r * cols_vec + cv), amax, nnz);
+    }
+    cta_combine(amax, nnz);
     if (threadIdx.x == 0) {
         block_amax[b] = amax;
-        atomicMax(&ws->gamax_bits, f2u(amax));
-        if (nnz) atomicAdd(&ws->gnnz, (unsigned long long)nnz);
-    }
-}
-
-// Row groups (1 x k) with k smaller than a CTA's worth: grid-stride over vectors, a
-// group is k / elems-per-vector consecutive lanes (a power of two <= 32), combined with
-// xor shuffles.  Lane 0 of each group writes the group's amax.
-template <typename T>
-__global__ void __launch_bounds__(kThreads) amax_nnz_rowgroups_kernel(const typename T::vec_t* __restrict__ in,
-                                                                      int64_t nvec, int lanes_per_group,
-                                                                      float* __restrict__ block_amax,
-                                                                      ScalarsWs* __restrict__ ws) {
-    float amax = 0.0f;
-    int nnz = 0;
-    const int64_t stride = (int64_t)gridDim.x * kThreads;
-    // nvec is a multiple of 32 (cols is a multiple of 128 elements per row at least)
-    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < nvec; i += stride) {
-        const typename T::vec_t v = ld_keep(in + i);
-        float a = 0.0f;
-        vec_amax_nnz<T>(v, a, nnz);
-        amax = fmaxf(amax, a);
-        for (int o = lanes_per_group >> 1; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
-        if ((threadIdx.x & (lanes_per_group - 1)) == 0) block_amax[i / lanes_per_group] = a;
-    }
-    cta_amax_nnz(amax, nnz);
-    if (threadIdx.x == 0) {
-        atomicMax(&ws->gamax_bits, f2u(amax));
-        if (nnz) atomicAdd(&ws->gnnz, (unsigned long long)nnz);
+        publish(ws, amax, nnz);
     }
 }
 
@@ -174,11 +212,8 @@ __global__ void __launch_bounds__(kThreads) amax_nnz_colgroups_kernel(const type
             atomicMax(reinterpret_cast<uint32_t*>(block_amax) + rb * cols_vec * EPV + cv * EPV + e, f2u(cmax[e]));
         }
     }
-    cta_amax_nnz(amax, nnz);
-    if (threadIdx.x == 0) {
-        atomicMax(&ws->gamax_bits, f2u(amax));
-        if (nnz) atomicAdd(&ws->gnnz, (unsigned long long)nnz);
-    }
+    cta_combine(amax, nnz);
+    if (threadIdx.x == 0) publish(ws, amax, nnz);
 }
 
 __global__ void zero_floats_kernel(float* p, int64_t n) {
@@ -209,20 +244,6 @@ int launch_amax_nnz_blocks(const void* in, int is_fp32, int64_t rows, int64_t co
     const int epv = is_fp32 ? 4 : 8;
     if (cols % epv) return kErrUnsupportedShape;
     const int64_t cols_vec = cols / epv;
-    if (brows == 1 && bcols < 32 * epv) {
-        // small row groups: a group is a power-of-two number of lanes
-        if (bcols % epv) return kErrUnsupportedShape;
-        const int lpg = bcols / epv;
-        if (lpg & (lpg - 1)) return kErrUnsupportedShape;
-        const int64_t nvec = rows * cols_vec;
-        if (nvec % 32) return kErrUnsupportedShape;
-        int64_t want = (nvec + kThreads - 1) / kThreads;
-        const int64_t cap = (int64_t)sm_count() * 8;
-        if (want > cap) want = cap;
-        if (is_fp32) amax_nnz_rowgroups_kernel<Fp32><<<(int)want, kThreads, 0, st>>>(static_cast<const float4*>(in), nvec, lpg, block_amax, ws);
-        else amax_nnz_rowgroups_kernel<Bf16><<<(int)want, kThreads, 0, st>>>(static_cast<const uint4*>(in), nvec, lpg, block_amax, ws);
-        return check_launch();
-    }
     if (bcols == 1) {
         // column groups: block index = row_block * cols + column
         const int64_t n_amax = (rows / brows) * cols;
@@ -236,10 +257,13 @@ int launch_amax_nnz_blocks(const void* in, int is_fp32, int64_t rows, int64_t co
         return check_launch();
     }
     if (bcols % epv) return kErrUnsupportedShape;
+    const int bcols_vec = bcols / epv;
     const int64_t bx = cols / bcols, nb = bx * (rows / brows);
     if (nb > 0x7FFFFFFF) return kErrTooLarge;
-    if (is_fp32) amax_nnz_blocks_kernel<Fp32><<<(unsigned)nb, kThreads, 0, st>>>(static_cast<const float4*>(in), cols_vec, brows, bcols / epv, bx, block_amax, ws);
-    else amax_nnz_blocks_kernel<Bf16><<<(unsigned)nb, kThreads, 0, st>>>(static_cast<const uint4*>(in), cols_vec, brows, bcols / epv, bx, block_amax, ws);
+    int w_shift = 0;
+    while ((2 << w_shift) <= bcols_vec && (2 << w_shift) <= kThreads) ++w_shift;  // largest power of two <= min(bcols_vec, 256)
+    if (is_fp32) amax_nnz_blocks_kernel<Fp32><<<(unsigned)nb, kThreads, 0, st>>>(static_cast<const float4*>(in), cols_vec, brows, bcols_vec, bx, w_shift, block_amax, ws);
+    else amax_nnz_blocks_kernel<Bf16><<<(unsigned)nb, kThreads, 0, st>>>(static_cast<const uint4*>(in), cols_vec, brows, bcols_vec, bx, w_shift, block_amax, ws);
     return check_launch();
 }
 

@@ -13,6 +13,8 @@
 // threads" of the reference's CTA (the words of one 16-byte vector), keeps one
 // running sum per logical thread, and logical_warp_sum() folds them exactly as the
 // reference's tree folds real lanes.
+#include <type_traits>
+
 #include "kernels.cuh"
 
 namespace morb {
@@ -39,16 +41,106 @@ __device__ __forceinline__ float read_gamax(const ScalarsWs* ws, const float* ex
 
 // One element pair of block_e4m3_relative_error (ref: 1133-1162).  ss_mode 2 is the
 // one that takes the power-of-two path: the reference tests `T_SCALING_STRATEGY ==
-// SF_E8` and SF_E8 is the enumerator 2 of another enum.
-template <bool E8>
-__device__ __forceinline__ void err_pair(float hi, float lo, float sf, int e8, float& dh, float& dl, float& eh,
+// SF_E8` and SF_E8 is the enumerator 2 of another enum.  Zeros are skipped by the
+// reference: they are written back as +0 and add no error.
+//
+// Three ways to the same bits:
+//   Lut   scale is a binary32 number shared by many elements: dequantised value =
+//         table[code], the table filled once with the exact division q / scale;
+//   Div   same scale kind, too few elements per scale to pay for a table;
+//   E8    power-of-two scale: two multiplies (or the literal exponent-field form
+//         outside the range where they are provably identical).
+struct PathLut { const float* lut; float sf; };
+struct PathDiv { float sf; };
+struct PathE8 { E8Consts c; };
+
+__device__ __forceinline__ void dequant_pair(const PathLut& p, float hi, float lo, float& dh, float& dl) {
+    const uint32_t c = cvt_codes<kE4M3>(__fmul_rn(hi, p.sf), __fmul_rn(lo, p.sf));
+    dh = p.lut[c >> 8];
+    dl = p.lut[c & 0xFFu];
+}
+__device__ __forceinline__ void dequant_pair(const PathDiv& p, float hi, float lo, float& dh, float& dl) {
+    sqdd_fp32_pair<kE4M3>(hi, lo, p.sf, dh, dl);
+    dh = canon_nan(dh);
+    dl = canon_nan(dl);
+}
+__device__ __forceinline__ void dequant_pair(const PathE8& p, float hi, float lo, float& dh, float& dl) {
+    sqdd_e8_pair_auto<kE4M3>(hi, lo, p.c, dh, dl);
+}
+template <typename P> struct PathTraits { static constexpr bool kExactBf16 = false; };
+template <> struct PathTraits<PathE8> { static constexpr bool kExactBf16 = true; };
+
+// table[code] = RN(dequant(code) / sf), NaNs canonicalised so that the add-and-shift
+// bf16 rounding reproduces the reference's result for them
+__device__ __forceinline__ void fill_lut32(float* lut, float sf, int tid, int nthreads) {
+    for (int c = tid; c < 256; c += nthreads)
+        lut[c] = canon_nan(__fdiv_rn(h_lo_to_f32(codes_to_h2<kE4M3>((uint32_t)c)), sf));
+}
+
+// |(d - x) / x| for x != 0 (ref: 1143, 1154).  BF16X: x carries a bf16 value, for which
+// the quotient has a four-instruction exact form on all but extreme exponents.
+template <bool BF16X>
+__device__ __forceinline__ float rel_err(float d, float x) {
+    if constexpr (BF16X) {
+        if (bf16_div_safe(x)) return fabsf(div_by_bf16(__fsub_rn(d, x), x, rcp_fast(x)));
+    }
+    return fabsf(__fdiv_rn(__fsub_rn(d, x), x));
+}
+template <bool BF16X, typename P>
+__device__ __forceinline__ void err_pair(const P& path, float hi, float lo, float& dh, float& dl, float& eh,
                                          float& el) {
-    if constexpr (E8) sqdd_e8_pair<kE4M3>(hi, lo, e8, dh, dl);
-    else sqdd_fp32_pair<kE4M3>(hi, lo, sf, dh, dl);
+    dequant_pair(path, hi, lo, dh, dl);
     eh = 0.0f;
     el = 0.0f;
-    if (hi != 0.0f) eh = fabsf(__fdiv_rn(__fsub_rn(dh, hi), hi)); else dh = 0.0f;
-    if (lo != 0.0f) el = fabsf(__fdiv_rn(__fsub_rn(dl, lo), lo)); else dl = 0.0f;
+    if (hi != 0.0f) eh = rel_err<BF16X>(dh, hi); else dh = 0.0f;
+    if (lo != 0.0f) el = rel_err<BF16X>(dl, lo); else dl = 0.0f;
+}
+
+// process one 16-byte vector: VW logical threads, errors added high half first
+template <typename T, typename P, bool STORE>
+__device__ __forceinline__ void err_vec(const P& path, const typename T::vec_t& v, typename T::vec_t& o,
+                                        float (&acc)[T::kWordsPerVec]) {
+#pragma unroll
+    for (int k = 0; k < T::kWordsPerVec; ++k) {
+        float hi, lo, dh, dl, eh, el;
+        T::unpack(v, k, hi, lo);
+        err_pair<T::kBytesPerElem == 2>(path, hi, lo, dh, dl, eh, el);
+        acc[k] = __fadd_rn(acc[k], eh);
+        acc[k] = __fadd_rn(acc[k], el);
+        if constexpr (STORE) {
+            if constexpr (T::kBytesPerElem == 2) {
+                uint32_t w;
+                if constexpr (PathTraits<P>::kExactBf16) w = path.c.fast ? pack_bf16_trunc(dh, dl) : pack_bf16(dh, dl);
+                else w = pack_bf16_round(dh, dl);
+                if (k == 0) o.x = w; else if (k == 1) o.y = w; else if (k == 2) o.z = w; else o.w = w;
+            } else {
+                T::pack(o, k, dh, dl);
+            }
+        }
+    }
+}
+// same, separate sums for the high and the low halves (channel kernels, ref: 1694-1748)
+template <typename T, typename P, bool STORE>
+__device__ __forceinline__ void err_vec_split(const P& path, const typename T::vec_t& v, typename T::vec_t& o,
+                                              float (&eh)[T::kWordsPerVec], float (&el)[T::kWordsPerVec]) {
+#pragma unroll
+    for (int k = 0; k < T::kWordsPerVec; ++k) {
+        float hi, lo, dh, dl, e_h, e_l;
+        T::unpack(v, k, hi, lo);
+        err_pair<T::kBytesPerElem == 2>(path, hi, lo, dh, dl, e_h, e_l);
+        eh[k] = __fadd_rn(eh[k], e_h);
+        el[k] = __fadd_rn(el[k], e_l);
+        if constexpr (STORE) {
+            if constexpr (T::kBytesPerElem == 2) {
+                uint32_t w;
+                if constexpr (PathTraits<P>::kExactBf16) w = path.c.fast ? pack_bf16_trunc(dh, dl) : pack_bf16(dh, dl);
+                else w = pack_bf16_round(dh, dl);
+                if (k == 0) o.x = w; else if (k == 1) o.y = w; else if (k == 2) o.z = w; else o.w = w;
+            } else {
+                T::pack(o, k, dh, dl);
+            }
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------------
@@ -62,33 +154,54 @@ block_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_
                       const ScalarsWs* __restrict__ ws, const float* __restrict__ ext_gamax, int skip_if_fallback) {
     constexpr int VW = T::kWordsPerVec;
     constexpr int LPW = 32 / VW;  // physical lanes per logical warp (= per logical row of 32 threads)
+    constexpr int NT = 1024 / VW;
     if (skip_if_fallback && ws->fallback) return;
     __shared__ float wsum[32];
+    __shared__ float s_lut[E8 ? 1 : 256];
     const int64_t b = blockIdx.x;
     const int64_t r0 = (b / blocks_x) * brows, c0 = (b % blocks_x) * bcols_vec;
     const float sf = scaling_factor(ss, read_gamax(ws, ext_gamax), block_amax[b]);
-    const int e8 = e8_of_scale(sf);
     const int p = threadIdx.x % LPW, ty = threadIdx.x / LPW;
     float acc[VW];
 #pragma unroll
     for (int k = 0; k < VW; ++k) acc[k] = 0.0f;
+    const typename T::vec_t* src = in + r0 * cols_vec + c0;
+    typename T::vec_t* dst = out + r0 * cols_vec + c0;
 
-    for (int r = ty; r < brows; r += 32) {
-        const int64_t row_off = (r0 + r) * cols_vec + c0;
-        for (int cv = p; cv < bcols_vec; cv += LPW) {  // 32 words = LPW vectors per step
-            const typename T::vec_t v = STORE ? ld_stream(in + row_off + cv) : ld_keep(in + row_off + cv);
-            typename T::vec_t o;
+    auto run = [&](const auto& path) {
+        // items (row j, vector i) in the reference's order: rows outer, words inner;
+        // four loads are kept in flight per lane, then consumed in that order
+        const int CI = bcols_vec / LPW, RJ = brows / 32, total = CI * RJ;
+        int j = 0, i = 0;
+        for (int done = 0; done < total; done += 4) {
+            typename T::vec_t v[4];
+            int off[4];
+            int jj = j, ii = i;
 #pragma unroll
-            for (int k = 0; k < VW; ++k) {
-                float hi, lo, dh, dl, eh, el;
-                T::unpack(v, k, hi, lo);
-                err_pair<E8>(hi, lo, sf, e8, dh, dl, eh, el);
-                acc[k] = __fadd_rn(acc[k], eh);
-                acc[k] = __fadd_rn(acc[k], el);
-                if constexpr (STORE) T::pack(o, k, dh, dl);
+            for (int u = 0; u < 4; ++u) {
+                off[u] = -1;
+                if (done + u < total) {
+                    off[u] = (ty + 32 * jj) * (int)cols_vec + p + LPW * ii;
+                    v[u] = STORE ? ld_stream(src + off[u]) : ld_keep(src + off[u]);
+                    if (++ii == CI) { ii = 0; ++jj; }
+                }
             }
-            if constexpr (STORE) st_stream(out + row_off + cv, o);
+            j = jj; i = ii;
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (off[u] >= 0) {
+                    typename T::vec_t o;
+                    err_vec<T, std::decay_t<decltype(path)>, STORE>(path, v[u], o, acc);
+                    if constexpr (STORE) st_stream(dst + off[u], o);
+                }
         }
+    };
+    if constexpr (E8) {
+        run(PathE8{e8_consts(sf)});
+    } else {
+        fill_lut32(s_lut, sf, threadIdx.x, NT);
+        __syncthreads();
+        run(PathLut{s_lut, sf});
     }
     const float s = logical_warp_sum<VW>(acc);
     if (p == 0) wsum[ty] = s;
@@ -102,7 +215,9 @@ block_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_
 // ---------------------------------------------------------------------------------
 // 1 x k row groups; reference CTA = 64 threads over max(k, 128) columns of one row
 // ---------------------------------------------------------------------------------
-template <typename T, bool E8, bool STORE>
+// MODE 0: binary32 scale, division per element (short groups); 1: binary32 scale with a
+// per-unit table in shared memory (long rows); 2: power-of-two scale.
+template <typename T, int MODE, bool STORE>
 __global__ void __launch_bounds__(256)
 rowgroup_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_t* __restrict__ out,
                          int64_t n_units, int span_vec, int group_lanes, int ss,
@@ -112,48 +227,58 @@ rowgroup_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::v
     constexpr int VW = T::kWordsPerVec;
     constexpr int LPU = 64 / VW;       // physical lanes per unit (one reference CTA)
     constexpr int UPW = 32 / LPU;      // units per physical warp
+    constexpr int UPC = 8 * UPW;       // units per CTA of 8 warps
     if (skip_if_fallback && ws->fallback) return;
+    __shared__ float s_lut[MODE == 1 ? UPC * 256 : 1];
     const float gamax = read_gamax(ws, ext_gamax);
     const int lane = threadIdx.x & 31;
     const int p = lane % LPU;
+    const int unit_in_cta = (threadIdx.x >> 5) * UPW + lane / LPU;
     const int64_t warps_total = ((int64_t)gridDim.x * blockDim.x) >> 5;
     const int64_t warp0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int64_t n_iter = (n_units + UPW - 1) / UPW;
     for (int64_t it = warp0; it < n_iter; it += warps_total) {
         const int64_t u = it * UPW + lane / LPU;
         const bool live = u < n_units;
-        const int64_t base = (live ? u : 0) * span_vec;
+        const typename T::vec_t* src = in + (live ? u : 0) * span_vec;
+        typename T::vec_t* dst = out + (live ? u : 0) * span_vec;
         float sf = 1.0f;
         if (group_lanes == 0 && live) sf = scaling_factor(ss, gamax, block_amax[u]);  // one block per unit
+        float* lut = s_lut + (MODE == 1 ? unit_in_cta * 256 : 0);
+        if constexpr (MODE == 1) {
+            __syncwarp();
+            fill_lut32(lut, sf, p, LPU);
+            __syncwarp();
+        }
         float eh[VW], el[VW];
 #pragma unroll
         for (int k = 0; k < VW; ++k) eh[k] = el[k] = 0.0f;
-        for (int cv = p; cv < span_vec; cv += LPU) {
-            typename T::vec_t v = ld_stream(in + base + cv);
-            if (group_lanes > 0) {
-                // several 1 x k blocks inside the unit: amax of the lanes of this block
-                float a = 0.0f;
+        for (int cv = p; cv < span_vec; cv += 4 * LPU) {
+            typename T::vec_t v[4];
 #pragma unroll
-                for (int k = 0; k < VW; ++k) {
-                    float hi, lo;
-                    T::unpack(v, k, hi, lo);
-                    a = fmaxf(a, fmaxf(fabsf(hi), fabsf(lo)));
+            for (int q = 0; q < 4; ++q)
+                if (cv + q * LPU < span_vec) v[q] = ld_stream(src + cv + q * LPU);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                if (cv + q * LPU >= span_vec) break;
+                if (group_lanes > 0) {
+                    // several 1 x k blocks inside the unit: amax of the lanes of this block
+                    float a = 0.0f;
+#pragma unroll
+                    for (int k = 0; k < VW; ++k) {
+                        float hi, lo;
+                        T::unpack(v[q], k, hi, lo);
+                        a = fmaxf(a, fmaxf(fabsf(hi), fabsf(lo)));
+                    }
+                    for (int o = group_lanes >> 1; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+                    sf = scaling_factor(ss, gamax, a);
                 }
-                for (int o = group_lanes >> 1; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
-                sf = scaling_factor(ss, gamax, a);
+                typename T::vec_t o4;
+                if constexpr (MODE == 2) err_vec_split<T, PathE8, STORE>(PathE8{e8_consts(sf)}, v[q], o4, eh, el);
+                else if constexpr (MODE == 1) err_vec_split<T, PathLut, STORE>(PathLut{lut, sf}, v[q], o4, eh, el);
+                else err_vec_split<T, PathDiv, STORE>(PathDiv{sf}, v[q], o4, eh, el);
+                if constexpr (STORE) { if (live) st_stream(dst + cv + q * LPU, o4); }
             }
-            const int e8 = e8_of_scale(sf);
-            typename T::vec_t o4;
-#pragma unroll
-            for (int k = 0; k < VW; ++k) {
-                float hi, lo, dh, dl, e_h, e_l;
-                T::unpack(v, k, hi, lo);
-                err_pair<E8>(hi, lo, sf, e8, dh, dl, e_h, e_l);
-                eh[k] = __fadd_rn(eh[k], e_h);
-                el[k] = __fadd_rn(el[k], e_l);
-                if constexpr (STORE) T::pack(o4, k, dh, dl);
-            }
-            if constexpr (STORE) { if (live) st_stream(out + base + cv, o4); }
         }
         float acc[VW];
 #pragma unroll
@@ -201,8 +326,13 @@ colgroup_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::v
             float hi, lo, dh, dl, e_h, e_l, unused_d, unused_e;
             T::unpack(v, k, hi, lo);
             // the two halves of a word belong to different columns, hence different scales
-            err_pair<E8>(hi, hi, sfh[k], e8_of_scale(sfh[k]), dh, unused_d, e_h, unused_e);
-            err_pair<E8>(lo, lo, sfl[k], e8_of_scale(sfl[k]), dl, unused_d, e_l, unused_e);
+            if constexpr (E8) {
+                err_pair<T::kBytesPerElem == 2>(PathE8{e8_consts(sfh[k])}, hi, hi, dh, unused_d, e_h, unused_e);
+                err_pair<T::kBytesPerElem == 2>(PathE8{e8_consts(sfl[k])}, lo, lo, dl, unused_d, e_l, unused_e);
+            } else {
+                err_pair<T::kBytesPerElem == 2>(PathDiv{sfh[k]}, hi, hi, dh, unused_d, e_h, unused_e);
+                err_pair<T::kBytesPerElem == 2>(PathDiv{sfl[k]}, lo, lo, dl, unused_d, e_l, unused_e);
+            }
             eh[k] = __fadd_rn(eh[k], e_h);
             el[k] = __fadd_rn(el[k], e_l);
             if constexpr (STORE) T::pack(o, k, dh, dl);
@@ -301,14 +431,14 @@ int launch_rowgroup_t(const ScalingArgs& a, bool store, bool skip, cudaStream_t 
     const int64_t cap = (int64_t)sm_count() * 8;
     if (grid > cap) grid = cap;
     if (grid < 1) grid = 1;
-    const bool e8 = a.ss_mode == 2;
+    // a table of 256 quotients per unit pays off from about 2048 elements per scale
+    const int mode = a.ss_mode == 2 ? 2 : ((group_lanes == 0 && span >= 2048) ? 1 : 0);
     auto* in = static_cast<const typename T::vec_t*>(a.in);
     auto* out = static_cast<typename T::vec_t*>(a.out);
-#define MORB_GO(E, S) rowgroup_err_cast_kernel<T, E, S><<<(unsigned)grid, 256, 0, st>>>(in, out, n_units, span / EPV, group_lanes, a.ss_mode, a.block_amax, a.block_err, a.ws, a.ext_gamax, skip ? 1 : 0)
-    if (e8 && store) MORB_GO(true, true);
-    else if (e8) MORB_GO(true, false);
-    else if (store) MORB_GO(false, true);
-    else MORB_GO(false, false);
+#define MORB_GO(M, S) rowgroup_err_cast_kernel<T, M, S><<<(unsigned)grid, 256, 0, st>>>(in, out, n_units, span / EPV, group_lanes, a.ss_mode, a.block_amax, a.block_err, a.ws, a.ext_gamax, skip ? 1 : 0)
+    if (mode == 2) { if (store) MORB_GO(2, true); else MORB_GO(2, false); }
+    else if (mode == 1) { if (store) MORB_GO(1, true); else MORB_GO(1, false); }
+    else { if (store) MORB_GO(0, true); else MORB_GO(0, false); }
 #undef MORB_GO
     return check_launch();
 }
