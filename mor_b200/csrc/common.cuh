@@ -78,14 +78,17 @@ __device__ __forceinline__ float h_hi_to_f32(uint32_t h2) { return __half2float(
 // ref: 218-245 with T_USE_CUDA_CAST = true for E4M3/E5M2 (static_cast through
 // __nv_fp8_e4m3/e5m2: RNE, saturate-to-finite, zero keeps its sign) and the custom
 // cast for E2M3 (ref: 125-215: same grid and rounding, but a zero result is +0).
-template <int FMT>
+template <int FMT, bool FINITE = false>
 __device__ __forceinline__ void quant_dequant_pair(float hi, float lo, float& qhi, float& qlo) {
-    const uint32_t h2 = codes_to_h2<FMT>(cvt_codes<FMT>(hi, lo));
+    uint32_t h2 = codes_to_h2<FMT>(cvt_codes<FMT>(hi, lo));
+    if constexpr (FMT == kE2M3 || FMT == kE3M2) {
+        // -0 -> +0 on both halves at once: bit 15 of (|h| + 0x7FFF) is set iff the half is non-zero
+        const uint32_t nz = ((h2 & 0x7FFF7FFFu) + 0x7FFF7FFFu) & 0x80008000u;
+        h2 &= nz | 0x7FFF7FFFu;
+    }
     qhi = h_hi_to_f32(h2);
     qlo = h_lo_to_f32(h2);
-    if constexpr (FMT == kE2M3 || FMT == kE3M2) {
-        if (qhi == 0.0f) qhi = 0.0f;  // -0 -> +0
-        if (qlo == 0.0f) qlo = 0.0f;
+    if constexpr ((FMT == kE2M3 || FMT == kE3M2) && !FINITE) {
         // no NaN encoding: the custom cast clamps NaN/Inf to the signed maximum,
         // the hardware returns +max for NaN.
         if (hi != hi) qhi = copysignf(qhi, hi);

@@ -138,6 +138,81 @@ group_small_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_t* 
     }
 }
 
+// ---------------------------------------------------------------------------------
+// bf16, power-of-two scale, groups of 1..32 vectors: the MX hot path
+// ---------------------------------------------------------------------------------
+// Everything a lane needs is derived from the packed amax pattern with integer
+// operations; one warp-uniform test selects the branch-free body (normal finite amax,
+// scale exponent inside the range where multiplying equals exponent-field
+// arithmetic) and anything else (zero or non-finite group, extreme exponents) goes to
+// the general code.
+template <int FMT>
+__device__ __forceinline__ uint4 mx_cast_vec(const uint4& v, float up, float down, uint32_t zero_bits, bool any_neg) {
+    uint4 o;
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t r[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        float qh, ql;
+        quant_dequant_pair<FMT, true>(__fmul_rn(bf16_hi(w[k]), up), __fmul_rn(bf16_lo(w[k]), up), qh, ql);
+        float rh = __fmul_rn(qh, down), rl = __fmul_rn(ql, down);
+        if (any_neg) {  // a zero code under a scale below one comes back as +-2^(-e8-127)
+            if (qh == 0.0f) rh = u2f((f2u(qh) & 0x80000000u) | zero_bits);
+            if (ql == 0.0f) rl = u2f((f2u(ql) & 0x80000000u) | zero_bits);
+        }
+        r[k] = pack_bf16_trunc(rh, rl);
+    }
+    o.x = r[0]; o.y = r[1]; o.z = r[2]; o.w = r[3];
+    return o;
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(256)
+mx_bf16_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, float* __restrict__ scales, int64_t nvec,
+               int group_shift, int32_t* __restrict__ meta, int64_t n_meta, int32_t meta_code) {
+    constexpr int K127 = ((FMT == kE4M3) ? 8 : (FMT == kE5M2 ? 15 : 2)) + 127;
+    constexpr uint32_t CMAN7 = (FMT == kE2M3) ? 0x70u : 0x60u;  // 1.875 / 1.75 as a 7-bit mantissa
+    const int lanes_per_group = 1 << group_shift;
+    const int64_t stride = (int64_t)gridDim.x * 256;
+    const int64_t gtid = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    for (int64_t m = gtid; m < n_meta; m += stride) meta[m] = meta_code;
+    constexpr int U = 4;
+    auto one = [&](uint4 v, int64_t idx) {
+        uint32_t p = vec_amax_pattern(v);
+        for (int o = lanes_per_group >> 1; o > 0; o >>= 1) p = max(p, __shfl_xor_sync(0xFFFFFFFFu, p, o));
+        const int ea = (int)(p >> 7);                               // exponent field of the group amax
+        const int e8 = K127 - ea - ((p & 0x7Fu) > CMAN7 ? 1 : 0);   // exponent of RN(fmax / amax)
+        const bool fast = (uint32_t)(ea - 1) < 254u && (uint32_t)(e8 + 119) <= 219u;
+        float s;
+        if (__all_sync(0xFFFFFFFFu, fast)) {
+            const float up = u2f((uint32_t)(e8 + 127) << 23), down = u2f((uint32_t)(127 - e8) << 23);
+            const uint32_t zero_bits = e8 < 0 ? ((uint32_t)(-e8) << 23) : 0u;
+            v = mx_cast_vec<FMT>(v, up, down, zero_bits, __any_sync(0xFFFFFFFFu, e8 < 0));
+            s = up;
+        } else {
+            float a = u2f(p << 16);
+            if (p > 0x7F80u) {  // a NaN in the group: the reference's fmaxf skips it
+                a = vec_amax_float<Bf16>(v);
+                for (int o = lanes_per_group >> 1; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+            }
+            s = 1.0f;
+            if (a > 0.0f) v = vec_cast_e8<Bf16, FMT>(v, e8_from_amax<FMT>(a, s));
+        }
+        st_stream(out + idx, v);
+        if (scales && (threadIdx.x & (lanes_per_group - 1)) == 0) scales[idx >> group_shift] = s;
+    };
+    int64_t i = gtid;
+    // nvec is a multiple of 32, so whole warps enter or leave the loops together
+    for (; i + (U - 1) * stride < nvec; i += stride * U) {
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) v[u] = ld_stream(in + i + u * stride);
+#pragma unroll
+        for (int u = 0; u < U; ++u) one(v[u], i + u * stride);
+    }
+    for (; i < nvec; i += stride) one(ld_stream(in + i), i);
+}
+
 constexpr int kRowThreads = 256;
 constexpr int kRowMaxVec = 8;
 
@@ -236,6 +311,12 @@ int launch_t(const void* in, void* out, float* scales, int32_t* meta, int32_t me
         const int64_t cap = (int64_t)sm_count() * 8;
         if (grid > cap) grid = cap;
         if (grid < 1) grid = 1;
+        if constexpr (T::kBytesPerElem == 2 && SF == kSfE8) {
+            int shift = 0;
+            while ((1 << shift) < gvec) ++shift;
+            mx_bf16_kernel<FMT><<<(unsigned)grid, 256, 0, st>>>(i4, o4, scales, nvec, shift, meta, meta ? n_groups : 0, meta_code);
+            return check_launch();
+        }
         group_small_kernel<T, FMT, SF><<<(unsigned)grid, 256, 0, st>>>(i4, o4, scales, nvec, gvec, meta, meta ? n_groups : 0, meta_code);
         return check_launch();
     }

@@ -22,14 +22,27 @@ struct Acc {
     uint32_t packed_max;  // bf16 path: two 15-bit maxima
     float fmax_;          // float path
     int nnz;
+    uint32_t tiny;        // bf16 path: bit 15 / 31 set once a non-zero magnitude below 2^-90 was seen
 };
+
+// halves of a magnitude word that are non-zero (bit 15 of the half set)
+__device__ __forceinline__ uint32_t nz_flags(uint32_t m) { return (m + 0x7FFF7FFFu) & 0x80008000u; }
+// acc |= flags of the halves that are non-zero and below 2^-90 (bf16 pattern 0x1280):
+// with bit 15 forced on, subtracting the threshold never borrows across halves and
+// leaves bit 15 clear exactly when the half is below it
+__device__ __forceinline__ uint32_t tiny_or(uint32_t acc, uint32_t m, uint32_t nz) {
+    const uint32_t r = (m | 0x80008000u) - 0x12801280u;
+    return acc | (~r & nz);
+}
 
 template <typename T>
 __device__ __forceinline__ void vec_acc_fast(const typename T::vec_t& v, Acc& a) {
     if constexpr (T::kBytesPerElem == 2) {
         const uint32_t m0 = mag2(v.x), m1 = mag2(v.y), m2 = mag2(v.z), m3 = mag2(v.w);
         a.packed_max = umax16x2(umax16x2(a.packed_max, m0), umax16x2(umax16x2(m1, m2), m3));
-        a.nnz += nnz2(m0) + nnz2(m1) + nnz2(m2) + nnz2(m3);
+        const uint32_t z0 = nz_flags(m0), z1 = nz_flags(m1), z2 = nz_flags(m2), z3 = nz_flags(m3);
+        a.nnz += __popc(z0) + __popc(z1) + __popc(z2) + __popc(z3);
+        a.tiny = tiny_or(tiny_or(tiny_or(tiny_or(a.tiny, m0, z0), m1, z1), m2, z2), m3, z3);
     } else {
         const float a0 = fabsf(v.x), a1 = fabsf(v.y), a2 = fabsf(v.z), a3 = fabsf(v.w);
         a.fmax_ = fmaxf(fmaxf(a.fmax_, a0), fmaxf(fmaxf(a1, a2), a3));
@@ -81,17 +94,21 @@ __device__ __forceinline__ void publish(ScalarsWs* ws, float amax, int nnz) {
     atomicMax(&ws->gamax_bits, f2u(amax));
     if (nnz) atomicAdd(&ws->gnnz, (unsigned long long)nnz);
 }
+// CTA-wide OR of the "tiny non-zero value seen" flags (and of "a NaN was seen"); one atomic if set
+__device__ __forceinline__ void publish_unsafe(ScalarsWs* ws, bool mine) {
+    if (__syncthreads_or(mine) && threadIdx.x == 0) atomicOr(&ws->div_unsafe, 1u);
+}
 
 __global__ void zero_scalars_kernel(ScalarsWs* ws) {
     ws->gamax_bits = 0u; ws->fallback = 0; ws->gnnz = 0ull; ws->gerr = 0.0f; ws->meta = 0;
-    ws->pad[0] = ws->pad[1] = 0u;
+    ws->div_unsafe = 0u; ws->pad = 0u;
 }
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads) amax_nnz_flat_kernel(const typename T::vec_t* __restrict__ in,
                                                                  int64_t nvec, int64_t n_tail_elems,
                                                                  ScalarsWs* __restrict__ ws) {
-    Acc acc{0u, 0.0f, 0};
+    Acc acc{0u, 0.0f, 0, 0u};
     const int64_t stride = (int64_t)gridDim.x * kThreads;
     const int64_t gtid = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     for (int64_t i = gtid; i < nvec; i += stride * 4) {
@@ -105,10 +122,12 @@ __global__ void __launch_bounds__(kThreads) amax_nnz_flat_kernel(const typename 
     }
     float amax = acc_amax<T>(acc);
     int nnz = acc.nnz;
-    if (cta_saw_nan<T>(amax)) {
+    const bool saw_nan = cta_saw_nan<T>(amax);
+    if (saw_nan) {
         amax = 0.0f; nnz = 0;
         for (int64_t i = gtid; i < nvec; i += stride) vec_acc_exact<T>(ld_keep(in + i), amax, nnz);
     }
+    publish_unsafe(ws, saw_nan || acc.tiny != 0u);
     if (gtid < n_tail_elems) {
         float a;
         if constexpr (T::kBytesPerElem == 2) a = fabsf(u2f((uint32_t)reinterpret_cast<const uint16_t*>(in + nvec)[gtid] << 16));
@@ -133,7 +152,7 @@ __global__ void __launch_bounds__(kThreads) amax_nnz_blocks_kernel(const typenam
     const int W = 1 << w_shift, RPS = kThreads >> w_shift;
     const int tx = threadIdx.x & (W - 1), ty = threadIdx.x >> w_shift;
     const typename T::vec_t* base = in + r0 * cols_vec + c0;
-    Acc acc{0u, 0.0f, 0};
+    Acc acc{0u, 0.0f, 0, 0u};
     if (brows >= 4 * RPS) {  // tall blocks: four rows in flight per lane
         for (int cv = tx; cv < bcols_vec; cv += W) {
             int r = ty;
@@ -162,11 +181,13 @@ __global__ void __launch_bounds__(kThreads) amax_nnz_blocks_kernel(const typenam
     }
     float amax = acc_amax<T>(acc);
     int nnz = acc.nnz;
-    if (cta_saw_nan<T>(amax)) {
+    const bool saw_nan = cta_saw_nan<T>(amax);
+    if (saw_nan) {
         amax = 0.0f; nnz = 0;
         for (int cv = tx; cv < bcols_vec; cv += W)
             for (int r = ty; r < brows; r += RPS) vec_acc_exact<T>(ld_keep(base + (int64_t)r * cols_vec + cv), amax, nnz);
     }
+    publish_unsafe(ws, saw_nan || acc.tiny != 0u);
     cta_combine(amax, nnz);
     if (threadIdx.x == 0) {
         block_amax[b] = amax;
@@ -213,7 +234,10 @@ __global__ void __launch_bounds__(kThreads) amax_nnz_colgroups_kernel(const type
         }
     }
     cta_combine(amax, nnz);
-    if (threadIdx.x == 0) publish(ws, amax, nnz);
+    if (threadIdx.x == 0) {
+        publish(ws, amax, nnz);
+        atomicOr(&ws->div_unsafe, 1u);  // this traversal does not screen magnitudes: keep the IEEE division
+    }
 }
 
 __global__ void zero_floats_kernel(float* p, int64_t n) {

@@ -38,6 +38,13 @@ __device__ __forceinline__ float scaling_factor(int ss, float gamax, float bamax
 __device__ __forceinline__ float read_gamax(const ScalarsWs* ws, const float* ext) {
     return ext ? *ext : u2f(ws->gamax_bits);
 }
+// may the four-instruction quotient by a bf16 value be used for the whole tensor?  (amax
+// pass: no non-zero magnitude below 2^-90 and no NaN; here: nothing at or above 2^90)
+template <typename T>
+__device__ __forceinline__ bool fast_div_ok(const ScalarsWs* ws) {
+    if constexpr (T::kBytesPerElem != 2) return false;
+    else return ws->div_unsafe == 0u && ws->gamax_bits < 0x6C800000u;
+}
 
 // One element pair of block_e4m3_relative_error (ref: 1133-1162).  ss_mode 2 is the
 // one that takes the power-of-two path: the reference tests `T_SCALING_STRATEGY ==
@@ -77,34 +84,37 @@ __device__ __forceinline__ void fill_lut32(float* lut, float sf, int tid, int nt
         lut[c] = canon_nan(__fdiv_rn(h_lo_to_f32(codes_to_h2<kE4M3>((uint32_t)c)), sf));
 }
 
-// |(d - x) / x| for x != 0 (ref: 1143, 1154).  BF16X: x carries a bf16 value, for which
-// the quotient has a four-instruction exact form on all but extreme exponents.
-template <bool BF16X>
-__device__ __forceinline__ float rel_err(float d, float x) {
-    if constexpr (BF16X) {
-        if (bf16_div_safe(x)) return fabsf(div_by_bf16(__fsub_rn(d, x), x, rcp_fast(x)));
-    }
-    return fabsf(__fdiv_rn(__fsub_rn(d, x), x));
-}
-template <bool BF16X, typename P>
+// |(d - x) / x| for x != 0 (ref: 1143, 1154).  FASTDIV: x carries a bf16 value and the
+// amax pass found every non-zero magnitude of the tensor inside [2^-90, 2^90), where
+// the quotient has a four-instruction exact form (div_by_bf16).  Zero elements are
+// skipped by the reference: no error, written back as +0; selects, not branches.
+template <bool FASTDIV, typename P>
 __device__ __forceinline__ void err_pair(const P& path, float hi, float lo, float& dh, float& dl, float& eh,
                                          float& el) {
     dequant_pair(path, hi, lo, dh, dl);
-    eh = 0.0f;
-    el = 0.0f;
-    if (hi != 0.0f) eh = rel_err<BF16X>(dh, hi); else dh = 0.0f;
-    if (lo != 0.0f) el = rel_err<BF16X>(dl, lo); else dl = 0.0f;
+    const bool zh = hi == 0.0f, zl = lo == 0.0f;
+    if constexpr (FASTDIV) {
+        eh = fabsf(div_by_bf16(__fsub_rn(dh, hi), hi, rcp_fast(hi)));
+        el = fabsf(div_by_bf16(__fsub_rn(dl, lo), lo, rcp_fast(lo)));
+    } else {
+        eh = fabsf(__fdiv_rn(__fsub_rn(dh, hi), zh ? 1.0f : hi));
+        el = fabsf(__fdiv_rn(__fsub_rn(dl, lo), zl ? 1.0f : lo));
+    }
+    eh = zh ? 0.0f : eh;
+    el = zl ? 0.0f : el;
+    dh = zh ? 0.0f : dh;
+    dl = zl ? 0.0f : dl;
 }
 
 // process one 16-byte vector: VW logical threads, errors added high half first
-template <typename T, typename P, bool STORE>
+template <typename T, typename P, bool STORE, bool FASTDIV>
 __device__ __forceinline__ void err_vec(const P& path, const typename T::vec_t& v, typename T::vec_t& o,
                                         float (&acc)[T::kWordsPerVec]) {
 #pragma unroll
     for (int k = 0; k < T::kWordsPerVec; ++k) {
         float hi, lo, dh, dl, eh, el;
         T::unpack(v, k, hi, lo);
-        err_pair<T::kBytesPerElem == 2>(path, hi, lo, dh, dl, eh, el);
+        err_pair<FASTDIV>(path, hi, lo, dh, dl, eh, el);
         acc[k] = __fadd_rn(acc[k], eh);
         acc[k] = __fadd_rn(acc[k], el);
         if constexpr (STORE) {
@@ -120,14 +130,14 @@ __device__ __forceinline__ void err_vec(const P& path, const typename T::vec_t& 
     }
 }
 // same, separate sums for the high and the low halves (channel kernels, ref: 1694-1748)
-template <typename T, typename P, bool STORE>
+template <typename T, typename P, bool STORE, bool FASTDIV>
 __device__ __forceinline__ void err_vec_split(const P& path, const typename T::vec_t& v, typename T::vec_t& o,
                                               float (&eh)[T::kWordsPerVec], float (&el)[T::kWordsPerVec]) {
 #pragma unroll
     for (int k = 0; k < T::kWordsPerVec; ++k) {
         float hi, lo, dh, dl, e_h, e_l;
         T::unpack(v, k, hi, lo);
-        err_pair<T::kBytesPerElem == 2>(path, hi, lo, dh, dl, e_h, e_l);
+        err_pair<FASTDIV>(path, hi, lo, dh, dl, e_h, e_l);
         eh[k] = __fadd_rn(eh[k], e_h);
         el[k] = __fadd_rn(el[k], e_l);
         if constexpr (STORE) {
@@ -168,7 +178,9 @@ block_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_
     const typename T::vec_t* src = in + r0 * cols_vec + c0;
     typename T::vec_t* dst = out + r0 * cols_vec + c0;
 
-    auto run = [&](const auto& path) {
+    const bool fastdiv = fast_div_ok<T>(ws);
+    auto run = [&](const auto& path, auto fd_tag) {
+        constexpr bool FD = decltype(fd_tag)::value;
         // items (row j, vector i) in the reference's order: rows outer, words inner;
         // four loads are kept in flight per lane, then consumed in that order
         const int CI = bcols_vec / LPW, RJ = brows / 32, total = CI * RJ;
@@ -191,17 +203,19 @@ block_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_
             for (int u = 0; u < 4; ++u)
                 if (off[u] >= 0) {
                     typename T::vec_t o;
-                    err_vec<T, std::decay_t<decltype(path)>, STORE>(path, v[u], o, acc);
+                    err_vec<T, std::decay_t<decltype(path)>, STORE, FD>(path, v[u], o, acc);
                     if constexpr (STORE) st_stream(dst + off[u], o);
                 }
         }
     };
     if constexpr (E8) {
-        run(PathE8{e8_consts(sf)});
+        const PathE8 path{e8_consts(sf)};
+        if (fastdiv) run(path, std::true_type{}); else run(path, std::false_type{});
     } else {
         fill_lut32(s_lut, sf, threadIdx.x, NT);
         __syncthreads();
-        run(PathLut{s_lut, sf});
+        const PathLut path{s_lut, sf};
+        if (fastdiv) run(path, std::true_type{}); else run(path, std::false_type{});
     }
     const float s = logical_warp_sum<VW>(acc);
     if (p == 0) wsum[ty] = s;
@@ -231,6 +245,7 @@ rowgroup_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::v
     if (skip_if_fallback && ws->fallback) return;
     __shared__ float s_lut[MODE == 1 ? UPC * 256 : 1];
     const float gamax = read_gamax(ws, ext_gamax);
+    const bool fastdiv = fast_div_ok<T>(ws);
     const int lane = threadIdx.x & 31;
     const int p = lane % LPU;
     const int unit_in_cta = (threadIdx.x >> 5) * UPW + lane / LPU;
@@ -274,9 +289,15 @@ rowgroup_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::v
                     sf = scaling_factor(ss, gamax, a);
                 }
                 typename T::vec_t o4;
-                if constexpr (MODE == 2) err_vec_split<T, PathE8, STORE>(PathE8{e8_consts(sf)}, v[q], o4, eh, el);
-                else if constexpr (MODE == 1) err_vec_split<T, PathLut, STORE>(PathLut{lut, sf}, v[q], o4, eh, el);
-                else err_vec_split<T, PathDiv, STORE>(PathDiv{sf}, v[q], o4, eh, el);
+                if (fastdiv) {
+                    if constexpr (MODE == 2) err_vec_split<T, PathE8, STORE, true>(PathE8{e8_consts(sf)}, v[q], o4, eh, el);
+                    else if constexpr (MODE == 1) err_vec_split<T, PathLut, STORE, true>(PathLut{lut, sf}, v[q], o4, eh, el);
+                    else err_vec_split<T, PathDiv, STORE, true>(PathDiv{sf}, v[q], o4, eh, el);
+                } else {
+                    if constexpr (MODE == 2) err_vec_split<T, PathE8, STORE, false>(PathE8{e8_consts(sf)}, v[q], o4, eh, el);
+                    else if constexpr (MODE == 1) err_vec_split<T, PathLut, STORE, false>(PathLut{lut, sf}, v[q], o4, eh, el);
+                    else err_vec_split<T, PathDiv, STORE, false>(PathDiv{sf}, v[q], o4, eh, el);
+                }
                 if constexpr (STORE) { if (live) st_stream(dst + cv + q * LPU, o4); }
             }
         }
@@ -327,11 +348,11 @@ colgroup_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::v
             T::unpack(v, k, hi, lo);
             // the two halves of a word belong to different columns, hence different scales
             if constexpr (E8) {
-                err_pair<T::kBytesPerElem == 2>(PathE8{e8_consts(sfh[k])}, hi, hi, dh, unused_d, e_h, unused_e);
-                err_pair<T::kBytesPerElem == 2>(PathE8{e8_consts(sfl[k])}, lo, lo, dl, unused_d, e_l, unused_e);
+                err_pair<false>(PathE8{e8_consts(sfh[k])}, hi, hi, dh, unused_d, e_h, unused_e);
+                err_pair<false>(PathE8{e8_consts(sfl[k])}, lo, lo, dl, unused_d, e_l, unused_e);
             } else {
-                err_pair<T::kBytesPerElem == 2>(PathDiv{sfh[k]}, hi, hi, dh, unused_d, e_h, unused_e);
-                err_pair<T::kBytesPerElem == 2>(PathDiv{sfl[k]}, lo, lo, dl, unused_d, e_l, unused_e);
+                err_pair<false>(PathDiv{sfh[k]}, hi, hi, dh, unused_d, e_h, unused_e);
+                err_pair<false>(PathDiv{sfl[k]}, lo, lo, dl, unused_d, e_l, unused_e);
             }
             eh[k] = __fadd_rn(eh[k], e_h);
             el[k] = __fadd_rn(el[k], e_l);

@@ -32,7 +32,8 @@ struct ScalarsWs {              // head of every workspace, 32 bytes, zeroed by 
     unsigned long long gnnz;    // count of non-zero elements
     float gerr;                 // ordered sum of the block errors
     int32_t meta;
-    uint32_t pad[2];
+    uint32_t div_unsafe;        // a non-zero bf16 magnitude below 2^-90 was seen: take the IEEE division
+    uint32_t pad;
 };
 int launch_zero_scalars(ScalarsWs* ws, cudaStream_t st);
 // amax and nnz of a flat tensor (phase 1 of e8mx and of the row-sharded pipeline)
