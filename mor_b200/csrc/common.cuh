@@ -283,6 +283,17 @@ __device__ __forceinline__ float div_by_bf16(float q, float x, float r) {
     const float rem = __fmaf_rn(-x, q0, q);
     return __fmaf_rn(rem, r, q0);
 }
+// The same quotient for a bf16-valued x of ANY magnitude (subnormal to 2^127) and a
+// numerator of comparable or smaller magnitude: both are first multiplied by the power
+// of two that brings x into [2^-6, 2], which changes neither operand's significand nor
+// the quotient, and keeps every intermediate a normal number.
+__device__ __forceinline__ float div_by_bf16_any(float num, float x) {
+    int k = 127 - (int)((f2u(x) >> 23) & 0xFFu);
+    k = max(k, -126);
+    const float s = u2f((uint32_t)(k + 127) << 23);
+    const float xs = __fmul_rn(x, s);
+    return div_by_bf16(__fmul_rn(num, s), xs, rcp_fast(xs));
+}
 __device__ __forceinline__ bool bf16_div_safe(float x) { return (f2u(x) & 0x7FFFFFFFu) - 0x1F800000u < 0x40000000u; }
 
 // packed bf16 magnitude helpers: both halves of a word at once

@@ -135,25 +135,24 @@ __device__ __forceinline__ void word_errors_fast(const ErrCtx<SF>& e, float hi, 
     }
     float e4h = 0.0f, e4l = 0.0f, e5h = 0.0f, e5l = 0.0f;
     if constexpr (SAFE) {
-        if (hi != 0.0f) {
-            const float r = rcp_fast(hi);
-            e4h = fabsf(__fsub_rn(div_by_bf16(q4h, hi, r), 1.0f));
-            e5h = fabsf(__fsub_rn(div_by_bf16(q5h, hi, r), 1.0f));
-        }
-        if (lo != 0.0f) {
-            const float r = rcp_fast(lo);
-            e4l = fabsf(__fsub_rn(div_by_bf16(q4l, lo, r), 1.0f));
-            e5l = fabsf(__fsub_rn(div_by_bf16(q5l, lo, r), 1.0f));
-        }
+        // branch-free: a zero element yields NaN garbage that the selects discard
+        const float rh = rcp_fast(hi), rl = rcp_fast(lo);
+        const bool zh = hi == 0.0f, zl = lo == 0.0f;
+        e4h = fabsf(__fsub_rn(div_by_bf16(q4h, hi, rh), 1.0f));
+        e5h = fabsf(__fsub_rn(div_by_bf16(q5h, hi, rh), 1.0f));
+        e4l = fabsf(__fsub_rn(div_by_bf16(q4l, lo, rl), 1.0f));
+        e5l = fabsf(__fsub_rn(div_by_bf16(q5l, lo, rl), 1.0f));
+        e4h = zh ? 0.0f : e4h; e5h = zh ? 0.0f : e5h;
+        e4l = zl ? 0.0f : e4l; e5l = zl ? 0.0f : e5l;
     } else {
-        if (hi != 0.0f) {
-            e4h = fabsf(__fsub_rn(__fdiv_rn(q4h, hi), 1.0f));
-            e5h = fabsf(__fsub_rn(__fdiv_rn(q5h, hi), 1.0f));
-        }
-        if (lo != 0.0f) {
-            e4l = fabsf(__fsub_rn(__fdiv_rn(q4l, lo), 1.0f));
-            e5l = fabsf(__fsub_rn(__fdiv_rn(q5l, lo), 1.0f));
-        }
+        // magnitudes outside the short form's range: same quotient after a power-of-two pre-scale
+        const bool zh = hi == 0.0f, zl = lo == 0.0f;
+        e4h = fabsf(__fsub_rn(div_by_bf16_any(q4h, hi), 1.0f));
+        e5h = fabsf(__fsub_rn(div_by_bf16_any(q5h, hi), 1.0f));
+        e4l = fabsf(__fsub_rn(div_by_bf16_any(q4l, lo), 1.0f));
+        e5l = fabsf(__fsub_rn(div_by_bf16_any(q5l, lo), 1.0f));
+        e4h = zh ? 0.0f : e4h; e5h = zh ? 0.0f : e5h;
+        e4l = zl ? 0.0f : e4l; e5l = zl ? 0.0f : e5l;
     }
     e4 = __fadd_rn(e4h, e4l);
     e5 = __fadd_rn(e5h, e5l);

@@ -113,7 +113,7 @@ group_small_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_t* 
                 uint32_t p = vec_amax_pattern(v[u]);
                 for (int o = lanes_per_group >> 1; o > 0; o >>= 1) p = max(p, __shfl_xor_sync(0xFFFFFFFFu, p, o));
                 a = u2f(p << 16);
-                if (p > 0x7F80u) {  // a NaN in the group: the reference's fmaxf skips it
+                if (__any_sync(0xFFFFFFFFu, p > 0x7F80u)) {  // a NaN in the warp: the reference's fmaxf skips it
                     a = vec_amax_float<T>(v[u]);
                     for (int o = lanes_per_group >> 1; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
                 }
@@ -191,7 +191,7 @@ mx_bf16_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, float* __r
             s = up;
         } else {
             float a = u2f(p << 16);
-            if (p > 0x7F80u) {  // a NaN in the group: the reference's fmaxf skips it
+            if (__any_sync(0xFFFFFFFFu, p > 0x7F80u)) {  // a NaN in the warp: the reference's fmaxf skips it
                 a = vec_amax_float<Bf16>(v);
                 for (int o = lanes_per_group >> 1; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
             }
@@ -216,84 +216,100 @@ mx_bf16_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, float* __r
 constexpr int kRowThreads = 256;
 constexpr int kRowMaxVec = 8;
 
-template <typename T, int FMT, int SF>
-__global__ void __launch_bounds__(kRowThreads, 4)
+// One CTA per group at a time, persistent over groups: while a group is reduced, cast
+// and stored out of one register buffer, the loads of the CTA's next group are already
+// in flight into the other, so every resident CTA always has HBM reads outstanding.
+template <typename T, int FMT, int SF, int NV>
+__global__ void __launch_bounds__(kRowThreads)
 group_row_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_t* __restrict__ out,
-                 float* __restrict__ scales, int group_vec, int32_t* __restrict__ meta, int32_t meta_code) {
-    __shared__ float s_red[kRowThreads / 32];
+                 float* __restrict__ scales, int group_vec, int64_t n_groups, int32_t* __restrict__ meta,
+                 int32_t meta_code) {
+    __shared__ float s_red[2][kRowThreads / 32];
     __shared__ uint32_t s_lut[256];  // bf16 bits (bf16 output) or binary32 bits (binary32 output)
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-    const int64_t base = (int64_t)blockIdx.x * group_vec;
-    typename T::vec_t v[kRowMaxVec];
+    typename T::vec_t v[NV], nx[NV];
+    auto load = [&](typename T::vec_t (&dst)[NV], int64_t g) {
+        const typename T::vec_t* src = in + g * group_vec;
 #pragma unroll
-    for (int u = 0; u < kRowMaxVec; ++u)
-        if (tid + u * kRowThreads < group_vec) v[u] = ld_stream(in + base + tid + u * kRowThreads);
-    float a = 0.0f;
-    if constexpr (T::kBytesPerElem == 2) {
-        uint32_t p = 0u;
+        for (int u = 0; u < NV; ++u)
+            if (tid + u * kRowThreads < group_vec) dst[u] = ld_stream(src + tid + u * kRowThreads);
+    };
+    int64_t g = blockIdx.x;
+    if (g < n_groups) load(v, g);
+    for (int it = 0; g < n_groups; g += gridDim.x, ++it) {
+        const int64_t gn = g + gridDim.x;
+        if (gn < n_groups) load(nx, gn);
+        float a = 0.0f;
+        if constexpr (T::kBytesPerElem == 2) {
+            uint32_t p = 0u;
 #pragma unroll
-        for (int u = 0; u < kRowMaxVec; ++u)
-            if (tid + u * kRowThreads < group_vec) p = max(p, vec_amax_pattern(v[u]));
-        a = u2f(p << 16);
-        if (p > 0x7F80u) {
-            a = 0.0f;
+            for (int u = 0; u < NV; ++u)
+                if (tid + u * kRowThreads < group_vec) p = max(p, vec_amax_pattern(v[u]));
+            a = u2f(p << 16);
+            if (p > 0x7F80u) {
+                a = 0.0f;
 #pragma unroll
-            for (int u = 0; u < kRowMaxVec; ++u)
+                for (int u = 0; u < NV; ++u)
+                    if (tid + u * kRowThreads < group_vec) a = fmaxf(a, vec_amax_float<T>(v[u]));
+            }
+        } else {
+#pragma unroll
+            for (int u = 0; u < NV; ++u)
                 if (tid + u * kRowThreads < group_vec) a = fmaxf(a, vec_amax_float<T>(v[u]));
         }
-    } else {
+        a = warp_max(a);
+        if (lane == 0) s_red[it & 1][wid] = a;
+        __syncthreads();
 #pragma unroll
-        for (int u = 0; u < kRowMaxVec; ++u)
-            if (tid + u * kRowThreads < group_vec) a = fmaxf(a, vec_amax_float<T>(v[u]));
-    }
-    a = warp_max(a);
-    if (lane == 0) s_red[wid] = a;
-    __syncthreads();
+        for (int w = 0; w < kRowThreads / 32; ++w) a = fmaxf(a, s_red[it & 1][w]);
+        float s = 1.0f;
+        if (a > 0.0f) {
+            if constexpr (SF == kSfFp32) {
+                s = __fdiv_rn(fmt_max<FMT>(), a);
+                // result = f(code) for a fixed scale: tabulate with the exact division once
+                constexpr int NCODES = (FMT == kE2M3) ? 64 : 256;
+                for (int c = tid; c < NCODES; c += kRowThreads) {
+                    float q = h_lo_to_f32(codes_to_h2<FMT>((uint32_t)c));
+                    if (FMT == kE2M3 && q == 0.0f) q = 0.0f;
+                    const float r = __fdiv_rn(q, s);
+                    s_lut[c] = (T::kBytesPerElem == 2) ? f32_to_bf16_bits(r) : f2u(r);
+                }
+                __syncthreads();
 #pragma unroll
-    for (int w = 0; w < kRowThreads / 32; ++w) a = fmaxf(a, s_red[w]);
-    float s = 1.0f;
-    if (a > 0.0f) {
-        if constexpr (SF == kSfFp32) {
-            s = __fdiv_rn(fmt_max<FMT>(), a);
-            // result = f(code) for a fixed scale: tabulate with the exact division once
-            constexpr int NCODES = (FMT == kE2M3) ? 64 : 256;
-            for (int c = tid; c < NCODES; c += kRowThreads) {
-                float q = h_lo_to_f32(codes_to_h2<FMT>((uint32_t)c));
-                if (FMT == kE2M3 && q == 0.0f) q = 0.0f;
-                const float r = __fdiv_rn(q, s);
-                s_lut[c] = (T::kBytesPerElem == 2) ? f32_to_bf16_bits(r) : f2u(r);
-            }
-            __syncthreads();
+                for (int u = 0; u < NV; ++u)
+                    if (tid + u * kRowThreads < group_vec) {
 #pragma unroll
-            for (int u = 0; u < kRowMaxVec; ++u)
-                if (tid + u * kRowThreads < group_vec) {
-#pragma unroll
-                    for (int k = 0; k < T::kWordsPerVec; ++k) {
-                        float hi, lo;
-                        T::unpack(v[u], k, hi, lo);
-                        const uint32_t c = cvt_codes<FMT>(__fmul_rn(hi, s), __fmul_rn(lo, s));
-                        if constexpr (T::kBytesPerElem == 2) {
-                            const uint32_t w = __byte_perm(s_lut[c & 0xFFu], s_lut[c >> 8], 0x5410);
-                            if (k == 0) v[u].x = w; else if (k == 1) v[u].y = w; else if (k == 2) v[u].z = w; else v[u].w = w;
-                        } else {
-                            T::pack(v[u], k, u2f(s_lut[c >> 8]), u2f(s_lut[c & 0xFFu]));
+                        for (int k = 0; k < T::kWordsPerVec; ++k) {
+                            float hi, lo;
+                            T::unpack(v[u], k, hi, lo);
+                            const uint32_t c = cvt_codes<FMT>(__fmul_rn(hi, s), __fmul_rn(lo, s));
+                            if constexpr (T::kBytesPerElem == 2) {
+                                const uint32_t w = __byte_perm(s_lut[c & 0xFFu], s_lut[c >> 8], 0x5410);
+                                if (k == 0) v[u].x = w; else if (k == 1) v[u].y = w; else if (k == 2) v[u].z = w; else v[u].w = w;
+                            } else {
+                                T::pack(v[u], k, u2f(s_lut[c >> 8]), u2f(s_lut[c & 0xFFu]));
+                            }
                         }
                     }
-                }
-        } else {
-            const E8Consts c = e8_from_amax<FMT>(a, s);
+            } else {
+                const E8Consts c = e8_from_amax<FMT>(a, s);
 #pragma unroll
-            for (int u = 0; u < kRowMaxVec; ++u)
-                if (tid + u * kRowThreads < group_vec) v[u] = vec_cast_e8<T, FMT>(v[u], c);
+                for (int u = 0; u < NV; ++u)
+                    if (tid + u * kRowThreads < group_vec) v[u] = vec_cast_e8<T, FMT>(v[u], c);
+            }
         }
-    }
-    if (tid == 0) {
-        if (meta) meta[blockIdx.x] = meta_code;
-        if (scales) scales[blockIdx.x] = s;
-    }
+        if (tid == 0) {
+            if (meta) meta[g] = meta_code;
+            if (scales) scales[g] = s;
+        }
+        typename T::vec_t* dst = out + g * group_vec;
 #pragma unroll
-    for (int u = 0; u < kRowMaxVec; ++u)
-        if (tid + u * kRowThreads < group_vec) st_stream(out + base + tid + u * kRowThreads, v[u]);
+        for (int u = 0; u < NV; ++u)
+            if (tid + u * kRowThreads < group_vec) st_stream(dst + tid + u * kRowThreads, v[u]);
+#pragma unroll
+        for (int u = 0; u < NV; ++u) v[u] = nx[u];
+        if constexpr (SF == kSfFp32) __syncthreads();  // the table is rewritten by the next group
+    }
 }
 
 template <typename T, int FMT, int SF>
@@ -321,8 +337,12 @@ int launch_t(const void* in, void* out, float* scales, int32_t* meta, int32_t me
         return check_launch();
     }
     if (gvec <= kRowThreads * kRowMaxVec) {
-        if (n_groups > 0x7FFFFFFF) return kErrTooLarge;
-        group_row_kernel<T, FMT, SF><<<(unsigned)n_groups, kRowThreads, 0, st>>>(i4, o4, scales, gvec, meta, meta_code);
+        int64_t grid = (int64_t)sm_count() * 4;
+        if (grid > n_groups) grid = n_groups;
+        const int nv = (gvec + kRowThreads - 1) / kRowThreads;
+#define MORB_ROW(NV) group_row_kernel<T, FMT, SF, NV><<<(unsigned)grid, kRowThreads, 0, st>>>(i4, o4, scales, gvec, n_groups, meta, meta_code)
+        if (nv <= 1) MORB_ROW(1); else if (nv <= 2) MORB_ROW(2); else if (nv <= 4) MORB_ROW(4); else MORB_ROW(8);
+#undef MORB_ROW
         return check_launch();
     }
     return kErrUnsupportedShape;

@@ -84,18 +84,27 @@ __device__ __forceinline__ void fill_lut32(float* lut, float sf, int tid, int nt
         lut[c] = canon_nan(__fdiv_rn(h_lo_to_f32(codes_to_h2<kE4M3>((uint32_t)c)), sf));
 }
 
-// |(d - x) / x| for x != 0 (ref: 1143, 1154).  FASTDIV: x carries a bf16 value and the
-// amax pass found every non-zero magnitude of the tensor inside [2^-90, 2^90), where
-// the quotient has a four-instruction exact form (div_by_bf16).  Zero elements are
-// skipped by the reference: no error, written back as +0; selects, not branches.
-template <bool FASTDIV, typename P>
+// |(d - x) / x| for x != 0 (ref: 1143, 1154).  Zero elements are skipped by the
+// reference: no error, written back as +0; handled with selects, not branches.
+// DIV selects how the exact quotient is formed:
+//   kDivIeee     x is a binary32 value: the IEEE division;
+//   kDivBf16     x carries a bf16 value and the amax pass found every non-zero magnitude
+//                of the tensor inside [2^-90, 2^90): four instructions (div_by_bf16);
+//   kDivBf16Any  x carries a bf16 value of any magnitude: operands pre-scaled by a power
+//                of two, then the same four instructions.
+enum { kDivIeee = 0, kDivBf16 = 1, kDivBf16Any = 2 };
+
+template <int DIV, typename P>
 __device__ __forceinline__ void err_pair(const P& path, float hi, float lo, float& dh, float& dl, float& eh,
                                          float& el) {
     dequant_pair(path, hi, lo, dh, dl);
     const bool zh = hi == 0.0f, zl = lo == 0.0f;
-    if constexpr (FASTDIV) {
+    if constexpr (DIV == kDivBf16) {
         eh = fabsf(div_by_bf16(__fsub_rn(dh, hi), hi, rcp_fast(hi)));
         el = fabsf(div_by_bf16(__fsub_rn(dl, lo), lo, rcp_fast(lo)));
+    } else if constexpr (DIV == kDivBf16Any) {
+        eh = fabsf(div_by_bf16_any(__fsub_rn(dh, hi), hi));
+        el = fabsf(div_by_bf16_any(__fsub_rn(dl, lo), lo));
     } else {
         eh = fabsf(__fdiv_rn(__fsub_rn(dh, hi), zh ? 1.0f : hi));
         el = fabsf(__fdiv_rn(__fsub_rn(dl, lo), zl ? 1.0f : lo));
@@ -107,14 +116,14 @@ __device__ __forceinline__ void err_pair(const P& path, float hi, float lo, floa
 }
 
 // process one 16-byte vector: VW logical threads, errors added high half first
-template <typename T, typename P, bool STORE, bool FASTDIV>
+template <typename T, typename P, bool STORE, int DIV>
 __device__ __forceinline__ void err_vec(const P& path, const typename T::vec_t& v, typename T::vec_t& o,
                                         float (&acc)[T::kWordsPerVec]) {
 #pragma unroll
     for (int k = 0; k < T::kWordsPerVec; ++k) {
         float hi, lo, dh, dl, eh, el;
         T::unpack(v, k, hi, lo);
-        err_pair<FASTDIV>(path, hi, lo, dh, dl, eh, el);
+        err_pair<DIV>(path, hi, lo, dh, dl, eh, el);
         acc[k] = __fadd_rn(acc[k], eh);
         acc[k] = __fadd_rn(acc[k], el);
         if constexpr (STORE) {
@@ -130,14 +139,14 @@ __device__ __forceinline__ void err_vec(const P& path, const typename T::vec_t& 
     }
 }
 // same, separate sums for the high and the low halves (channel kernels, ref: 1694-1748)
-template <typename T, typename P, bool STORE, bool FASTDIV>
+template <typename T, typename P, bool STORE, int DIV>
 __device__ __forceinline__ void err_vec_split(const P& path, const typename T::vec_t& v, typename T::vec_t& o,
                                               float (&eh)[T::kWordsPerVec], float (&el)[T::kWordsPerVec]) {
 #pragma unroll
     for (int k = 0; k < T::kWordsPerVec; ++k) {
         float hi, lo, dh, dl, e_h, e_l;
         T::unpack(v, k, hi, lo);
-        err_pair<FASTDIV>(path, hi, lo, dh, dl, e_h, e_l);
+        err_pair<DIV>(path, hi, lo, dh, dl, e_h, e_l);
         eh[k] = __fadd_rn(eh[k], e_h);
         el[k] = __fadd_rn(el[k], e_l);
         if constexpr (STORE) {
@@ -180,7 +189,7 @@ block_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_
 
     const bool fastdiv = fast_div_ok<T>(ws);
     auto run = [&](const auto& path, auto fd_tag) {
-        constexpr bool FD = decltype(fd_tag)::value;
+        constexpr int FD = (T::kBytesPerElem != 2) ? kDivIeee : (decltype(fd_tag)::value ? kDivBf16 : kDivBf16Any);
         // items (row j, vector i) in the reference's order: rows outer, words inner;
         // four loads are kept in flight per lane, then consumed in that order
         const int CI = bcols_vec / LPW, RJ = brows / 32, total = CI * RJ;
@@ -242,6 +251,7 @@ rowgroup_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::v
     constexpr int LPU = 64 / VW;       // physical lanes per unit (one reference CTA)
     constexpr int UPW = 32 / LPU;      // units per physical warp
     constexpr int UPC = 8 * UPW;       // units per CTA of 8 warps
+    constexpr int kSlowDiv = (T::kBytesPerElem == 2) ? kDivBf16Any : kDivIeee;
     if (skip_if_fallback && ws->fallback) return;
     __shared__ float s_lut[MODE == 1 ? UPC * 256 : 1];
     const float gamax = read_gamax(ws, ext_gamax);
@@ -276,27 +286,57 @@ rowgroup_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::v
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 if (cv + q * LPU >= span_vec) break;
+                typename T::vec_t o4;
                 if (group_lanes > 0) {
                     // several 1 x k blocks inside the unit: amax of the lanes of this block
                     float a = 0.0f;
-#pragma unroll
-                    for (int k = 0; k < VW; ++k) {
-                        float hi, lo;
-                        T::unpack(v[q], k, hi, lo);
-                        a = fmaxf(a, fmaxf(fabsf(hi), fabsf(lo)));
+                    if constexpr (T::kBytesPerElem == 2) {
+                        uint32_t pm = hmax_halves(umax16x2(umax16x2(mag2(v[q].x), mag2(v[q].y)), umax16x2(mag2(v[q].z), mag2(v[q].w))));
+                        for (int o = group_lanes >> 1; o > 0; o >>= 1) pm = max(pm, __shfl_xor_sync(0xFFFFFFFFu, pm, o));
+                        if constexpr (MODE == 2) {
+                            // power-of-two scale of 448 / amax straight from the amax pattern (amax >= 1e-35,
+                            // normal, finite) when every lane of the warp can and the fast quotient is allowed
+                            const int ea = (int)(pm >> 7);
+                            const int e8 = 135 - ea - ((pm & 0x7Fu) > 0x60u ? 1 : 0);
+                            const bool ok = fastdiv && (uint32_t)(ea - 12) < 243u && (uint32_t)(e8 + 119) <= 219u;
+                            if (__all_sync(0xFFFFFFFFu, ok)) {
+                                PathE8 pe;
+                                pe.c.e8 = e8; pe.c.fast = true;
+                                pe.c.up = u2f((uint32_t)(e8 + 127) << 23);
+                                pe.c.down = u2f((uint32_t)(127 - e8) << 23);
+                                pe.c.zero_bits = e8 < 0 ? ((uint32_t)(-e8) << 23) : 0u;
+                                err_vec_split<T, PathE8, STORE, kDivBf16>(pe, v[q], o4, eh, el);
+                                if constexpr (STORE) { if (live) st_stream(dst + cv + q * LPU, o4); }
+                                continue;
+                            }
+                        }
+                        a = u2f(pm << 16);
+                        // a NaN somewhere in the warp: every lane redoes its group with the NaN-ignoring
+                        // float maximum (the shuffles below need the whole warp)
+                        if (__any_sync(0xFFFFFFFFu, pm > 0x7F80u)) a = -1.0f;
+                    } else {
+                        a = -1.0f;
                     }
-                    for (int o = group_lanes >> 1; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+                    if (a < 0.0f) {
+                        a = 0.0f;
+#pragma unroll
+                        for (int k = 0; k < VW; ++k) {
+                            float hi, lo;
+                            T::unpack(v[q], k, hi, lo);
+                            a = fmaxf(a, fmaxf(fabsf(hi), fabsf(lo)));
+                        }
+                        for (int o = group_lanes >> 1; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+                    }
                     sf = scaling_factor(ss, gamax, a);
                 }
-                typename T::vec_t o4;
                 if (fastdiv) {
-                    if constexpr (MODE == 2) err_vec_split<T, PathE8, STORE, true>(PathE8{e8_consts(sf)}, v[q], o4, eh, el);
-                    else if constexpr (MODE == 1) err_vec_split<T, PathLut, STORE, true>(PathLut{lut, sf}, v[q], o4, eh, el);
-                    else err_vec_split<T, PathDiv, STORE, true>(PathDiv{sf}, v[q], o4, eh, el);
+                    if constexpr (MODE == 2) err_vec_split<T, PathE8, STORE, kDivBf16>(PathE8{e8_consts(sf)}, v[q], o4, eh, el);
+                    else if constexpr (MODE == 1) err_vec_split<T, PathLut, STORE, kDivBf16>(PathLut{lut, sf}, v[q], o4, eh, el);
+                    else err_vec_split<T, PathDiv, STORE, kDivBf16>(PathDiv{sf}, v[q], o4, eh, el);
                 } else {
-                    if constexpr (MODE == 2) err_vec_split<T, PathE8, STORE, false>(PathE8{e8_consts(sf)}, v[q], o4, eh, el);
-                    else if constexpr (MODE == 1) err_vec_split<T, PathLut, STORE, false>(PathLut{lut, sf}, v[q], o4, eh, el);
-                    else err_vec_split<T, PathDiv, STORE, false>(PathDiv{sf}, v[q], o4, eh, el);
+                    if constexpr (MODE == 2) err_vec_split<T, PathE8, STORE, kSlowDiv>(PathE8{e8_consts(sf)}, v[q], o4, eh, el);
+                    else if constexpr (MODE == 1) err_vec_split<T, PathLut, STORE, kSlowDiv>(PathLut{lut, sf}, v[q], o4, eh, el);
+                    else err_vec_split<T, PathDiv, STORE, kSlowDiv>(PathDiv{sf}, v[q], o4, eh, el);
                 }
                 if constexpr (STORE) { if (live) st_stream(dst + cv + q * LPU, o4); }
             }
@@ -348,11 +388,11 @@ colgroup_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::v
             T::unpack(v, k, hi, lo);
             // the two halves of a word belong to different columns, hence different scales
             if constexpr (E8) {
-                err_pair<false>(PathE8{e8_consts(sfh[k])}, hi, hi, dh, unused_d, e_h, unused_e);
-                err_pair<false>(PathE8{e8_consts(sfl[k])}, lo, lo, dl, unused_d, e_l, unused_e);
+                err_pair<(T::kBytesPerElem == 2) ? kDivBf16Any : kDivIeee>(PathE8{e8_consts(sfh[k])}, hi, hi, dh, unused_d, e_h, unused_e);
+                err_pair<(T::kBytesPerElem == 2) ? kDivBf16Any : kDivIeee>(PathE8{e8_consts(sfl[k])}, lo, lo, dl, unused_d, e_l, unused_e);
             } else {
-                err_pair<false>(PathDiv{sfh[k]}, hi, hi, dh, unused_d, e_h, unused_e);
-                err_pair<false>(PathDiv{sfl[k]}, lo, lo, dl, unused_d, e_l, unused_e);
+                err_pair<(T::kBytesPerElem == 2) ? kDivBf16Any : kDivIeee>(PathDiv{sfh[k]}, hi, hi, dh, unused_d, e_h, unused_e);
+                err_pair<(T::kBytesPerElem == 2) ? kDivBf16Any : kDivIeee>(PathDiv{sfl[k]}, lo, lo, dl, unused_d, e_l, unused_e);
             }
             eh[k] = __fadd_rn(eh[k], e_h);
             el[k] = __fadd_rn(el[k], e_l);

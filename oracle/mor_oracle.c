@@ -186,6 +186,9 @@ static float sqdd_fp32_scale(float x, float s, int fmt, int cuda_cast) {
     volatile float scaled = x * s;
     float q = quant_dequant(scaled, fmt, cuda_cast);
     volatile float out = q / s;
+    /* a NaN that arithmetic produces on the GPU is the canonical 0x7fffffff (x86 would
+     * give 0xffc00000 for 0/0); it matters because fp32_to_bf16 maps the former to 0x8000 */
+    if (out != out) return u2f(NAN_ALL_ONES);
     return out;
 }
 

@@ -107,6 +107,30 @@ def test_every_bf16_pattern_group_scaled(fmt, sf):
             assert np.array_equal(got["scales"].view(np.uint32), scales.view(np.uint32))
 
 
+@pytest.mark.parametrize("by", [32, 256, 1024])
+def test_group_scaled_with_nan_and_inf_elements(by):
+    """a NaN is skipped by the group amax (fmaxf) and comes out as 0x8000; the other elements are unaffected"""
+    import gpu_harness as H
+    x = rand_bits(700 + by, 64, 2048, "normal")
+    x[3, 5] = 0x7FC0
+    x[3, 700] = 0xFFC1
+    x[40, 100] = 0x7F80   # +inf: the group's scale becomes 0
+    for fmt in (oracle.FMT_E4M3, oracle.FMT_E5M2):
+        out, scales = oracle.fake_quantize_group(x, 1, by, fmt, 1, want_scales=True)
+        got = H.fake_quantize_group(x, by, fmt, 1)
+        assert_same(got, {"out": out}, f"group with NaN fmt {fmt} by {by}")
+    # power-of-two scales: non-finite values are outside the reference's domain (it asserts);
+    # here they must not fault, and groups without them must still be exact
+    clean = np.ones(x.shape, bool)
+    for r, c in ((3, 5), (3, 700), (40, 100)):
+        clean[r, (c // by) * by:(c // by + 1) * by] = False
+    for fmt in (oracle.FMT_E4M3, oracle.FMT_E2M3):
+        out = oracle.fake_quantize_group(x, 1, by, fmt, 2)
+        got = H.fake_quantize_group(x, by, fmt, 2, want_scales=False)["out"]
+        assert np.array_equal(got[clean], out[clean])
+    assert torch.zeros(1, device="cuda").item() == 0.0
+
+
 def test_unscaled_casts_every_bf16_pattern_and_neighbours():
     """quant_dequant_*: all bf16 patterns widened to float32, plus values just off the rounding ties."""
     import gpu_harness as H
@@ -169,6 +193,22 @@ def test_fake_quantize_ragged_and_odd_blocks(rows, cols, bx, by, mode):
         if oracle.assert_flags():
             continue
         assert_same(H.fake_quantize(x, bx, by, 1e-15, mode, sf), exp, f"{rows}x{cols} block {bx}x{by} mode {mode} sf {sf}")
+
+
+@pytest.mark.parametrize("shift", [-96, 90])
+@pytest.mark.parametrize("sf", [1, 2])
+def test_mor_error_pass_with_extreme_magnitudes(shift, sf):
+    """blocks scaled by 2^-96 / 2^90 leave the range of the short exact quotient: the IEEE division takes over"""
+    import gpu_harness as H
+    from cases import mixed_blocks_bf16
+    from ref_fixtures import bits_to_bf16, bf16_bits
+    t = bits_to_bf16(mixed_blocks_bf16(7)).float() * (2.0 ** shift)
+    x = bf16_bits(t.to(torch.bfloat16))
+    oracle.clear_assert_flags()
+    exp = dict(zip(("out", "meta"), oracle.fake_quantize(x, 128, 128, 1e-38, 1, sf)))
+    if oracle.assert_flags():
+        pytest.skip("outside the reference's asserted domain")
+    assert_same(H.fake_quantize(x, 128, 128, 1e-38, 1, sf), exp, f"MoR shift {shift} sf {sf}")
 
 
 @pytest.mark.parametrize("by", [8, 16, 32, 64, 128, 256, 1024, 4096])
@@ -242,6 +282,35 @@ def test_scaling_in_place(kind, thr):
     e["meta"] = np.array([e["meta"]])
     assert e["meta"][0] == (3 if thr < 1e-3 else 1)
     assert_same(got, e, f"in place {kind} thr {thr}")
+
+
+@pytest.mark.parametrize("kind", ["tiny", "huge", "nan"])
+@pytest.mark.parametrize("ss", [1, 2, 3, 4])
+def test_scaling_with_extreme_magnitudes(kind, ss):
+    """values outside [2^-90, 2^90) (or a NaN) switch the error quotient to the IEEE division: same bits"""
+    import gpu_harness as H
+    x = rand_bits(300 + ss, 256, 256, "normal")
+    if kind == "tiny":
+        x[7, 9] = 0x0081      # 1.2e-38
+        x[130, 200] = 0x8F00  # -6.3e-30
+    elif kind == "huge":
+        x[:128, :128] = rand_bits(301, 128, 128, "normal") + np.uint16(0x3000)  # times 2^96
+    else:
+        if ss == 2:
+            pytest.skip("non-finite inputs are outside the reference's domain for power-of-two scales")
+        x[3, 3] = 0x7FC0
+    for (op, h, bx, by) in ((oracle.block_scaling, H.block_scaling, 128, 128), (oracle.channel_scaling, H.channel_scaling, 1, 256),
+                            (oracle.channel_scaling, H.channel_scaling, 1, 32)):
+        oracle.clear_assert_flags()
+        e = dict(zip(("out", "meta", "gamax", "gnnz", "gerr"), op(x, bx, by, 3e38, ss)))
+        if oracle.assert_flags():
+            continue
+        e["meta"] = np.array([e["meta"]])
+        got = h(x, bx, by, 3e38, ss)
+        if kind == "nan":   # the error sum is NaN on both sides; compare everything else exactly
+            assert np.isnan(got["gerr"]) and np.isnan(e["gerr"])
+            got["gerr"] = e["gerr"] = 0.0
+        assert_same(got, e, f"{kind} ss {ss} {bx}x{by}")
 
 
 @pytest.mark.parametrize("ss", [1, 2, 3, 4])
