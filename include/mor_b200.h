@@ -39,6 +39,7 @@ extern "C" {
 #define MOR_B200_ERR_WORKSPACE (-3)        /* workspace missing or too small                 */
 #define MOR_B200_ERR_LAUNCH (-4)           /* the CUDA runtime refused a launch              */
 #define MOR_B200_ERR_TOO_LARGE (-5)        /* more blocks than a grid can index              */
+#define MOR_B200_ERR_STATIC_SCRATCH (-6)   /* more blocks than the built-in scratch holds    */
 
 #define MOR_B200_BF16 0
 #define MOR_B200_FP32 1
@@ -97,6 +98,30 @@ MOR_B200_API int mor_b200_block_scaling(const void* input, void* output, int dty
                            int block_cols, double e4m3_threshold, int ss_mode, int32_t* meta, float* global_amax,
                            void* global_nnz, int nnz_is_int64, float* global_error, void* workspace,
                            size_t workspace_bytes, void* stream);
+
+/* mor_b200_block_scaling without a workspace argument.  No counterpart in the reference.
+ *
+ * For hosts that may not allocate device memory at the point of the call: code running
+ * inside a CUDA-graph capture or another runtime's stream callback, plugins handed a
+ * fixed set of buffers by their framework, services whose memory is carved up front by
+ * an arena they do not own.  The scratch the pipeline needs (scalar head, one amax and
+ * one error sum per block) lives in an array built into the library instead:
+ * 256 B + 8 B x 65536 blocks = 512.25 KiB of device memory on every GPU that loads the
+ * library, held until the process exits.  Tensors with more than 65536 blocks (e.g. more
+ * than 32768 x 32768 elements at 128 x 128) get MOR_B200_ERR_STATIC_SCRATCH; use
+ * mor_b200_block_scaling for those.
+ *
+ * This call performs no cudaMalloc / cudaFree and calls no allocating library routine.
+ * Its FIRST call on a device looks up the device address of the built-in array (once per
+ * device, that device current); make that first call outside any stream capture.
+ * All calls on a device share the one array: it keeps the previous call's contents (the
+ * call clears or overwrites everything it later reads), and two calls whose kernels
+ * overlap on the GPU -- different streams, or different host threads -- race on it.
+ * Same arguments and results as mor_b200_block_scaling otherwise. */
+MOR_B200_API int mor_b200_block_scaling_static(const void* input, void* output, int dtype, int64_t rows, int64_t cols,
+                                  int block_rows, int block_cols, double e4m3_threshold, int ss_mode, int32_t* meta,
+                                  float* global_amax, void* global_nnz, int nnz_is_int64, float* global_error,
+                                  void* stream);
 
 /* mor::fake_quantize_channel_scaling[_inplace] (fake_quantize.cpp:24-25;
  * fake_quantize.cu:2399-2660, kernels 1430-1752).  block_rows == 1 (1 x k row groups,

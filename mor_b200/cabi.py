@@ -28,6 +28,7 @@ SIGNATURES = {
     "mor_b200_quant_dequant": (_i, [_vp, _vp, _i64, _i64, _i, _vp]),
     "mor_b200_e4m3_with_e8_scale": (_i, [_vp, _vp, _i64, _i64, _i, _vp]),
     "mor_b200_block_scaling": (_i, [_vp, _vp, _i, _i64, _i64, _i, _i, _d, _i, _vp, _vp, _vp, _i, _vp, _vp, _sz, _vp]),
+    "mor_b200_block_scaling_static": (_i, [_vp, _vp, _i, _i64, _i64, _i, _i, _d, _i, _vp, _vp, _vp, _i, _vp, _vp]),
     "mor_b200_channel_scaling": (_i, [_vp, _vp, _i, _i64, _i64, _i, _i, _d, _i, _vp, _vp, _vp, _i, _vp, _vp, _sz, _vp]),
     "mor_b200_e8mx": (_i, [_vp, _vp, _i64, _i64, _i, _i, _vp, _sz, _vp]),
     "mor_b200_fake_quantize_group": (_i, [_vp, _vp, _vp, _i, _i64, _i64, _i, _i, _i, _vp]),

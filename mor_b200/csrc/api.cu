@@ -2,6 +2,8 @@
 // workspace carving and the fixed kernel sequence of each operator.
 #include "../../include/mor_b200.h"
 
+#include <mutex>
+
 #include "kernels.cuh"
 
 using namespace morb;
@@ -129,6 +131,31 @@ int scaling_op(int kind, const void* in, void* out, int dtype, int64_t rows, int
     return launch_fallback_copy(a, st);
 }
 
+// ---- scratch for mor_b200_block_scaling_static ------------------------------------
+// Sized for kStaticMaxBlocks blocks: scalar head + one amax and one error sum per block.
+// Device memory that every GPU loading this library holds until the process exits.
+constexpr int64_t kStaticMaxBlocks = 65536;
+constexpr size_t kStaticScratchBytes = kHead + 2 * 4 * (size_t)kStaticMaxBlocks;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code the name g_static_scratch is only a handle for the runtime, not a device
+// address; the address each device gave the array is looked up once per device (with
+// that device current) and cached.
+void* static_scratch_ptr(int* status) {
+    static std::mutex mu;
+    static void* ptrs[64] = {nullptr};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { *status = kErrLaunch; return nullptr; }
+    std::lock_guard<std::mutex> lock(mu);
+    if (!ptrs[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) { *status = kErrLaunch; return nullptr; }
+        ptrs[dev] = p;
+    }
+    *status = kOk;
+    return ptrs[dev];
+}
+
 }  // namespace
 
 extern "C" {
@@ -143,6 +170,7 @@ const char* mor_b200_status_string(int status) {
         case kErrWorkspace: return "workspace missing, misaligned or too small";
         case kErrLaunch: return "CUDA launch failed";
         case kErrTooLarge: return "too many blocks for one grid";
+        case -6: return "tensor has more blocks than the built-in scratch holds (65536); use the workspace form";
         default: return "unknown status";
     }
 }
@@ -204,6 +232,21 @@ int mor_b200_block_scaling(const void* in, void* out, int dtype, int64_t rows, i
                            void* ws, size_t wsb, void* stream) {
     return scaling_op(MOR_B200_OP_BLOCK_SCALING, in, out, dtype, rows, cols, br, bc, thr, ss, meta, gamax, gnnz, nnz64,
                       gerr, ws, wsb, stream);
+}
+
+int mor_b200_block_scaling_static(const void* in, void* out, int dtype, int64_t rows, int64_t cols, int br, int bc,
+                                  double thr, int ss, int32_t* meta, float* gamax, void* gnnz, int nnz64,
+                                  float* gerr, void* stream) {
+    const Geometry g = block_geometry(rows, cols, br, bc);
+    if (g.status) return g.status;
+    if (g.n_amax > kStaticMaxBlocks) return -6;
+    int rc = kOk;
+    void* ws = static_scratch_ptr(&rc);
+    if (rc) return rc;
+    // the scalar head is zeroed by the first kernel of every call; the per-block arrays are
+    // fully rewritten before they are read, so nothing of the previous call survives
+    return scaling_op(MOR_B200_OP_BLOCK_SCALING, in, out, dtype, rows, cols, br, bc, thr, ss, meta, gamax, gnnz, nnz64,
+                      gerr, ws, kStaticScratchBytes, stream);
 }
 
 int mor_b200_channel_scaling(const void* in, void* out, int dtype, int64_t rows, int64_t cols, int br, int bc,
