@@ -38,6 +38,10 @@ BYTES_PER_ELEM_TWO_PASS = 12   # 2 x 4-byte reads + 1 x 4-byte write
 THRESHOLD = 0.045              # the reference tests' e4m3_threshold
 SS_MODE = 1
 FALLBACK_HBM_GBS = 6650.0      # used only when MEASURED_PEAKS.json is absent
+# dram read + write bytes of the dominant kernel per algorithmic byte, from one ncu capture of a
+# 1 GiB slab (profiles/block_err_cast_fp32_config5.md: 2.0993 GB moved for 2.1475 GB algorithmic);
+# one CTA per block and no reuse across blocks, so traffic grows in proportion to the elements
+TRAFFIC_PER_ALGORITHMIC_BYTE = 2.0993 / 2.1475
 
 
 def measured_peak():
@@ -306,7 +310,8 @@ def main():
             "roofline": {"bound": "hbm", "kernel": "block_err_cast_kernel<Fp32> (scale + E4M3 cast + error sums)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind, "ms_per_launch": cast_ms, "bytes_per_launch": cast_bytes,
-                         "traffic": None,
+                         "traffic": cast_bytes * TRAFFIC_PER_ALGORITHMIC_BYTE,
+                         "traffic_source": "ncu dram__bytes_read+write on a 1 GiB slab, scaled by elements",
                          "amax_kernel": {"ms_per_launch": amax_ms,
                                          "achieved": rows_local * COLS * 4 / (amax_ms * 1e-3) / 1e9}},
             "clocks": clocks.summary(),
