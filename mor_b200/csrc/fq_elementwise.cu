@@ -31,7 +31,7 @@ __global__ void __launch_bounds__(kThreads) cast_uniform_bf16_kernel(const uint4
                                                                      int32_t meta_code) {
     __shared__ uint16_t lut[256];
     if constexpr (SF == kSfFp32) build_lut_bf16<FMT>(lut, s);
-    const int e8 = e8_of_scale(s);
+    const E8Consts e8c = e8_consts(s);
     const int64_t stride = (int64_t)gridDim.x * kThreads;
     const int64_t gtid = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     for (int64_t m = gtid; m < n_meta; m += stride) meta[m] = meta_code;
@@ -39,10 +39,17 @@ __global__ void __launch_bounds__(kThreads) cast_uniform_bf16_kernel(const uint4
     auto word = [&](uint32_t w) -> uint32_t {
         if constexpr (SF == kSfFp32) {
             const uint32_t c = cvt_codes<FMT>(__fmul_rn(bf16_hi(w), s), __fmul_rn(bf16_lo(w), s));
-            return ((uint32_t)lut[c >> 8] << 16) | lut[c & 0xFFu];
+            return __byte_perm((uint32_t)lut[c & 0xFFu], (uint32_t)lut[c >> 8], 0x5410);
         } else {
+            // the multiply form needs finite inputs; a caller-supplied scale comes with no amax
+            // to vouch for them, so non-finite halves of the word take the literal form
+            const bool finite = ((w & 0x7F80u) != 0x7F80u) && ((w & 0x7F800000u) != 0x7F800000u);
             float rh, rl;
-            sqdd_e8_pair<FMT>(bf16_hi(w), bf16_lo(w), e8, rh, rl);
+            if (e8c.fast && finite) {
+                sqdd_e8_pair_fast<FMT>(bf16_hi(w), bf16_lo(w), e8c.up, e8c.down, e8c.zero_bits, rh, rl);
+                return pack_bf16_trunc(rh, rl);
+            }
+            sqdd_e8_pair<FMT>(bf16_hi(w), bf16_lo(w), e8c.e8, rh, rl);
             return pack_bf16(rh, rl);
         }
     };

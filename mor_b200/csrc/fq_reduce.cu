@@ -153,9 +153,16 @@ __global__ void __launch_bounds__(kThreads) amax_nnz_blocks_kernel(const typenam
     const int tx = threadIdx.x & (W - 1), ty = threadIdx.x >> w_shift;
     const typename T::vec_t* base = in + r0 * cols_vec + c0;
     Acc acc{0u, 0.0f, 0, 0u};
-    if (brows >= 4 * RPS) {  // tall blocks: four rows in flight per lane
+    if (brows >= 4 * RPS) {  // tall blocks: eight, then four rows in flight per lane
         for (int cv = tx; cv < bcols_vec; cv += W) {
             int r = ty;
+            for (; r + 7 * RPS < brows; r += 8 * RPS) {
+                typename T::vec_t v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) v[u] = ld_keep(base + (int64_t)(r + u * RPS) * cols_vec + cv);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) vec_acc_fast<T>(v[u], acc);
+            }
             for (; r + 3 * RPS < brows; r += 4 * RPS) {
                 typename T::vec_t v[4];
 #pragma unroll

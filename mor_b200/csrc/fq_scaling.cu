@@ -352,6 +352,95 @@ rowgroup_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::v
 }
 
 // ---------------------------------------------------------------------------------
+// 1 x k row groups with k < 128: flat traversal
+// ---------------------------------------------------------------------------------
+// A reference CTA covers 128 columns here, i.e. exactly one 16-byte vector per physical
+// lane, so the tensor is walked as a flat array of vectors (four in flight per lane, as
+// in the MX kernel); vector i belongs to unit i / LPU and to the group of `group_lanes`
+// lanes around it.  E8: power-of-two scale (ss_mode 2), else a binary32 scale per group.
+template <typename T, bool E8, bool STORE>
+__global__ void __launch_bounds__(256)
+rowgroup_small_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_t* __restrict__ out, int64_t nvec,
+                      int group_lanes, int ss, float* __restrict__ block_err, const ScalarsWs* __restrict__ ws,
+                      const float* __restrict__ ext_gamax, int skip_if_fallback) {
+    constexpr int VW = T::kWordsPerVec;
+    constexpr int LPU = 64 / VW;
+    constexpr int kSlowDiv = (T::kBytesPerElem == 2) ? kDivBf16Any : kDivIeee;
+    if (skip_if_fallback && ws->fallback) return;
+    const float gamax = read_gamax(ws, ext_gamax);
+    const bool fastdiv = fast_div_ok<T>(ws);
+    const int p = threadIdx.x % LPU;
+    const int64_t stride = (int64_t)gridDim.x * 256;
+    auto one = [&](const typename T::vec_t& v, int64_t idx) {
+        float eh[VW], el[VW];
+#pragma unroll
+        for (int k = 0; k < VW; ++k) eh[k] = el[k] = 0.0f;
+        typename T::vec_t o4;
+        bool done = false;
+        float a = -1.0f;
+        if constexpr (T::kBytesPerElem == 2) {
+            uint32_t pm = hmax_halves(umax16x2(umax16x2(mag2(v.x), mag2(v.y)), umax16x2(mag2(v.z), mag2(v.w))));
+            for (int o = group_lanes >> 1; o > 0; o >>= 1) pm = max(pm, __shfl_xor_sync(0xFFFFFFFFu, pm, o));
+            if constexpr (E8) {
+                // 448 / amax as a power of two straight from the amax pattern (amax >= 1e-35, normal, finite)
+                const int ea = (int)(pm >> 7);
+                const int e8 = 135 - ea - ((pm & 0x7Fu) > 0x60u ? 1 : 0);
+                const bool ok = fastdiv && (uint32_t)(ea - 12) < 243u && (uint32_t)(e8 + 119) <= 219u;
+                if (__all_sync(0xFFFFFFFFu, ok)) {
+                    PathE8 pe;
+                    pe.c.e8 = e8; pe.c.fast = true;
+                    pe.c.up = u2f((uint32_t)(e8 + 127) << 23);
+                    pe.c.down = u2f((uint32_t)(127 - e8) << 23);
+                    pe.c.zero_bits = e8 < 0 ? ((uint32_t)(-e8) << 23) : 0u;
+                    err_vec_split<T, PathE8, STORE, kDivBf16>(pe, v, o4, eh, el);
+                    done = true;
+                }
+            }
+            // a NaN somewhere in the warp: every lane redoes its group with the NaN-ignoring float maximum
+            if (!done && !__any_sync(0xFFFFFFFFu, pm > 0x7F80u)) a = u2f(pm << 16);
+        }
+        if (!done) {
+            if (a < 0.0f) {
+                a = 0.0f;
+#pragma unroll
+                for (int k = 0; k < VW; ++k) {
+                    float hi, lo;
+                    T::unpack(v, k, hi, lo);
+                    a = fmaxf(a, fmaxf(fabsf(hi), fabsf(lo)));
+                }
+                for (int o = group_lanes >> 1; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+            }
+            const float sf = scaling_factor(ss, gamax, a);
+            if (fastdiv) {
+                if constexpr (E8) err_vec_split<T, PathE8, STORE, kDivBf16>(PathE8{e8_consts(sf)}, v, o4, eh, el);
+                else err_vec_split<T, PathDiv, STORE, kDivBf16>(PathDiv{sf}, v, o4, eh, el);
+            } else {
+                if constexpr (E8) err_vec_split<T, PathE8, STORE, kSlowDiv>(PathE8{e8_consts(sf)}, v, o4, eh, el);
+                else err_vec_split<T, PathDiv, STORE, kSlowDiv>(PathDiv{sf}, v, o4, eh, el);
+            }
+        }
+        if constexpr (STORE) st_stream(out + idx, o4);
+        float acc[VW];
+#pragma unroll
+        for (int k = 0; k < VW; ++k) acc[k] = __fadd_rn(eh[k], el[k]);
+        float s = logical_warp_sum<VW>(acc);                       // valid at p == 0 and p == LPU / 2
+        const float s1 = __shfl_down_sync(0xFFFFFFFFu, s, LPU / 2);
+        s = __fadd_rn(s, s1);
+        if (p == 0) block_err[idx / LPU] = s;
+    };
+    int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    // nvec is a multiple of 32 (rows of 128-column units), so whole warps enter or leave together
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+        typename T::vec_t v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = ld_stream(in + i + u * stride);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) one(v[u], i + u * stride);
+    }
+    for (; i < nvec; i += stride) one(ld_stream(in + i), i);
+}
+
+// ---------------------------------------------------------------------------------
 // k x 1 column groups; reference CTA = 32 x 16 threads over 64 columns x k rows
 // ---------------------------------------------------------------------------------
 template <typename T, bool E8, bool STORE>
@@ -422,14 +511,49 @@ colgroup_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::v
 // t+1024, ... in order; adding +0.0 to a non-negative sum does not change it, so only
 // the slots that hold a sum are visited, in the same order.
 __global__ void __launch_bounds__(1024)
-finalize_kernel(const float* __restrict__ block_err, int64_t n_err, int stride, float threshold, ScalarsWs* ws,
+finalize_kernel(const float* __restrict__ block_err, int64_t n_err, int stride, int chunk_elems, float threshold,
+                ScalarsWs* ws,
                 const float* __restrict__ ext_gamax, const long long* __restrict__ ext_nnz, int32_t* meta_out,
                 float* gamax_out, void* gnnz_out, int nnz_is_i64, float* gerr_out) {
     __shared__ float wsum[32];
+    extern __shared__ float s_chunk[];  // chunk_elems floats
     const int t = threadIdx.x;
     float acc = 0.0f;
-    if (t % stride == 0)
-        for (int64_t e = t / stride; e < n_err; e += 1024 / stride) acc = __fadd_rn(acc, block_err[e]);
+    // The additions of a thread are sequential by definition; what can be hidden is the
+    // latency of the loads: the array is staged through shared memory in large chunks
+    // with all 1024 threads loading (coalesced, many loads in flight), then each summing
+    // thread walks its own entries of the chunk in order.  chunk_elems is a multiple of
+    // 1024, hence of the period 1024 / stride, so a thread's entries keep their phase.
+    const int period = 1024 / stride;
+    for (int64_t c0 = 0; c0 < n_err; c0 += chunk_elems) {
+        const int n = (int)((n_err - c0 < chunk_elems) ? (n_err - c0) : chunk_elems);
+        if (n == chunk_elems && (chunk_elems & 32767) == 0 && (reinterpret_cast<uintptr_t>(block_err) & 15u) == 0) {
+            // full chunk of 32768 floats: eight 16-byte loads per thread, all in flight (c0 is a
+            // multiple of the chunk, the array is 16-byte aligned)
+            const float4* src = reinterpret_cast<const float4*>(block_err + c0);
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = __ldg(src + t + u * 1024);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) reinterpret_cast<float4*>(s_chunk)[t + u * 1024] = v[u];
+        } else {
+#pragma unroll 8
+            for (int i = t; i < n; i += 1024) s_chunk[i] = block_err[c0 + i];
+        }
+        __syncthreads();
+        if (t % stride == 0) {
+            int e = t / stride;
+            for (; e + 7 * period < n; e += 8 * period) {  // loads first, then the ordered additions
+                float x[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) x[u] = s_chunk[e + u * period];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) acc = __fadd_rn(acc, x[u]);
+            }
+            for (; e < n; e += period) acc = __fadd_rn(acc, s_chunk[e]);
+        }
+        __syncthreads();
+    }
     acc = warp_sum_ordered(acc);
     if ((t & 31) == 0) wsum[t >> 5] = acc;
     __syncthreads();
@@ -496,6 +620,17 @@ int launch_rowgroup_t(const ScalingArgs& a, bool store, bool skip, cudaStream_t 
     const int mode = a.ss_mode == 2 ? 2 : ((group_lanes == 0 && span >= 2048) ? 1 : 0);
     auto* in = static_cast<const typename T::vec_t*>(a.in);
     auto* out = static_cast<typename T::vec_t*>(a.out);
+    if (group_lanes > 0) {
+        const int64_t nvec = a.rows * a.cols / EPV;
+        int64_t g2 = (nvec + 1023) / 1024;
+        if (g2 > cap) g2 = cap;
+        if (g2 < 1) g2 = 1;
+#define MORB_SMALL(E, S) rowgroup_small_kernel<T, E, S><<<(unsigned)g2, 256, 0, st>>>(in, out, nvec, group_lanes, a.ss_mode, a.block_err, a.ws, a.ext_gamax, skip ? 1 : 0)
+        if (mode == 2) { if (store) MORB_SMALL(true, true); else MORB_SMALL(true, false); }
+        else { if (store) MORB_SMALL(false, true); else MORB_SMALL(false, false); }
+#undef MORB_SMALL
+        return check_launch();
+    }
 #define MORB_GO(M, S) rowgroup_err_cast_kernel<T, M, S><<<(unsigned)grid, 256, 0, st>>>(in, out, n_units, span / EPV, group_lanes, a.ss_mode, a.block_amax, a.block_err, a.ws, a.ext_gamax, skip ? 1 : 0)
     if (mode == 2) { if (store) MORB_GO(2, true); else MORB_GO(2, false); }
     else if (mode == 1) { if (store) MORB_GO(1, true); else MORB_GO(1, false); }
@@ -535,8 +670,15 @@ int launch_colgroup_err_cast(const ScalingArgs& a, bool store, bool skip, cudaSt
 
 int launch_finalize(const ScalingArgs& a, const long long* ext_nnz, int32_t* meta, float* gamax, void* gnnz,
                     int nnz_is_i64, float* gerr, cudaStream_t st) {
-    finalize_kernel<<<1, 1024, 0, st>>>(a.block_err, a.n_err, a.err_slot_stride, a.threshold, a.ws, a.ext_gamax,
-                                        ext_nnz, meta, gamax, gnnz, nnz_is_i64, gerr);
+    constexpr int kMaxChunk = 32768;  // floats: 128 KiB of shared memory for the one CTA
+    int chunk = (int)((a.n_err + 1023) / 1024 * 1024);
+    if (chunk > kMaxChunk || a.n_err > kMaxChunk) chunk = kMaxChunk;
+    const size_t smem = (size_t)chunk * sizeof(float);
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(finalize_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxChunk * (int)sizeof(float)) != cudaSuccess)
+        return kErrLaunch;
+    finalize_kernel<<<1, 1024, smem, st>>>(a.block_err, a.n_err, a.err_slot_stride, chunk, a.threshold, a.ws,
+                                           a.ext_gamax, ext_nnz, meta, gamax, gnnz, nnz_is_i64, gerr);
     return check_launch();
 }
 
