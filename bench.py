@@ -159,6 +159,7 @@ def main():
     ap.add_argument("--no-main", action="store_true", help="skip the configuration-5 workload (profiling the suite)")
     ap.add_argument("--suite-only", default="", help="substring filter on suite entry names")
     ap.add_argument("--suite-iters", type=int, default=10)
+    ap.add_argument("--suite-out", default=None, help="where --suite writes its table (default gpurun_out/suite.json)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -187,7 +188,7 @@ def main():
 
     if args.no_main:
         peak, _ = measured_peak()
-        run_suite(torch, dev, peak, args.suite_only, args.suite_iters)
+        run_suite(torch, dev, peak, args.suite_only, args.suite_iters, args.suite_out)
         return 0
 
     rows = ROWS // args.scale
@@ -293,7 +294,7 @@ def main():
     suite = None
     if args.suite and rank == 0 and world == 1:
         del out
-        suite = run_suite(torch, dev, peak, args.suite_only, args.suite_iters)
+        suite = run_suite(torch, dev, peak, args.suite_only, args.suite_iters, args.suite_out)
 
     if rank == 0:
         line = {
@@ -330,69 +331,75 @@ def main():
     return 0
 
 
-def run_suite(torch, dev, peak, only="", iters=10):
-    """Times every kernel family on configurations 1-4 (bf16, one GPU).  Each launch is
-    timed alone with CUDA events on the launching stream; configuration 1 (32 MiB) fits
-    in L2, so a 512 MiB buffer is rewritten between launches to evict it."""
+def run_suite(torch, dev, peak, only="", iters=10, out_path=None):
+    """Times every kernel family on configurations 1-5 (one GPU).  Every operator runs
+    `iters` times back to back between one pair of CUDA events on the launching stream;
+    successive calls take their input from, and leave their outputs in, a ring of distinct
+    buffers whose total size is at least four times the L2, so that no call finds its
+    input or the lines of its output in cache.  The time per call is the total divided
+    by `iters`: launch gaps between the kernels of a pipeline are part of it."""
     import mor
     from mor_b200 import workloads
     results = []
-    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    ring_bytes = 512 << 20
 
-    def time_call(fn, n=iters, warm=min(3, iters)):
-        for _ in range(warm):
-            fn()
-        ms = []
-        for _ in range(n):
-            flush.zero_()
-            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s.record(); fn(); e.record()
-            torch.cuda.synchronize()
-            ms.append(s.elapsed_time(e))
-        return statistics.median(ms)
+    def time_call(fn, x, n=iters, warm=3):
+        k = max(2, -(-ring_bytes // (x.numel() * x.element_size())))
+        xs = [x] + [x.clone() for _ in range(k - 1)]
+        outs = [None] * k
+        for i in range(max(warm, k + 1)):  # also fills the ring, so that no allocation is left for the timed loop
+            outs[i % k] = fn(xs[i % k])
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for i in range(n):
+            outs[i % k] = fn(xs[i % k])
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) / n, k
 
     def add(name, x, bytes_per_elem, fn):
         if only and only not in name:
             return
-        ms = time_call(fn)
+        ms, k = time_call(fn, x)
         n = x.numel()
         gbs = n * bytes_per_elem / (ms * 1e-3) / 1e9
         results.append({"name": name, "rows": x.shape[0], "cols": x.shape[1], "ms": ms, "GB/s": gbs,
                         "elements_per_s": n / (ms * 1e-3), "bytes_per_element": bytes_per_elem,
-                        "frac_of_peak": gbs / peak})
-        print(f"[suite] {name}: {ms:.3f} ms  {gbs:.0f} GB/s  {100 * gbs / peak:.1f}% of peak", file=sys.stderr)
+                        "frac_of_peak": gbs / peak, "buffers_in_ring": k})
+        print(f"[suite] {name}: {ms:.4f} ms  {gbs:.0f} GB/s  {100 * gbs / peak:.1f}% of peak", file=sys.stderr)
 
     x = workloads.config1(device=dev)
     r, c = x.shape
     scale = (448.0 / x.float().abs().max()).item()
-    add("c1 per-tensor E4M3, scale given (fake_quantize mode 4)", x, 4, lambda: mor.ops.fake_quantize(x, r, c, 128, 128, scale, 4, 1))
-    add("c1 per-tensor E4M3, self-contained (block_scaling ss 4)", x, 6, lambda: mor.ops.fake_quantize_block_scaling(x, r, c, 128, 128, 3e38, 4))
+    add("c1 per-tensor E4M3, scale given (fake_quantize mode 4)", x, 4, lambda x: mor.ops.fake_quantize(x, r, c, 128, 128, scale, 4, 1))
+    add("c1 per-tensor E4M3, self-contained (block_scaling ss 4)", x, 6, lambda x: mor.ops.fake_quantize_block_scaling(x, r, c, 128, 128, 3e38, 4))
     del x
     x = workloads.config2(device=dev)
     r, c = x.shape
-    add("c2 per-row E4M3 single pass (fake_quantize mode 2, 1x8192)", x, 4, lambda: mor.ops.fake_quantize(x, r, c, 1, c, 0.0, 2, 1))
-    add("c2 per-row E5M2 single pass (fake_quantize mode 3, 1x8192)", x, 4, lambda: mor.ops.fake_quantize(x, r, c, 1, c, 0.0, 3, 1))
-    add("c2 per-row E4M3 pipeline (channel_scaling ss 3)", x, 6, lambda: mor.ops.fake_quantize_channel_scaling(x, r, c, 1, c, 3e38, 3))
+    add("c2 per-row E4M3 single pass (fake_quantize mode 2, 1x8192)", x, 4, lambda x: mor.ops.fake_quantize(x, r, c, 1, c, 0.0, 2, 1))
+    add("c2 per-row E5M2 single pass (fake_quantize mode 3, 1x8192)", x, 4, lambda x: mor.ops.fake_quantize(x, r, c, 1, c, 0.0, 3, 1))
+    add("c2 per-row E4M3 pipeline (channel_scaling ss 3)", x, 6, lambda x: mor.ops.fake_quantize_channel_scaling(x, r, c, 1, c, 3e38, 3))
     del x
     x = workloads.config3(device=dev)
     r, c = x.shape
-    add("c3 MX 1x32 E8M0 E4M3 single pass (fake_quantize_mx)", x, 4, lambda: mor.ops.fake_quantize_mx(x, r, c, 32, 0, 2))
-    add("c3 MX 1x32 E8M0 E2M3 single pass (fake_quantize_mx)", x, 4, lambda: mor.ops.fake_quantize_mx(x, r, c, 32, 3, 2))
-    add("c3 MX 1x32 E4M3 pipeline (channel_scaling ss 2)", x, 6, lambda: mor.ops.fake_quantize_channel_scaling(x, r, c, 1, 32, 3e38, 2))
+    add("c3 MX 1x32 E8M0 E4M3 single pass (fake_quantize_mx)", x, 4, lambda x: mor.ops.fake_quantize_mx(x, r, c, 32, 0, 2))
+    add("c3 MX 1x32 E8M0 E2M3 single pass (fake_quantize_mx)", x, 4, lambda x: mor.ops.fake_quantize_mx(x, r, c, 32, 3, 2))
+    add("c3 MX 1x32 E4M3 pipeline (channel_scaling ss 2)", x, 6, lambda x: mor.ops.fake_quantize_channel_scaling(x, r, c, 1, 32, 3e38, 2))
     del x
     x = workloads.config4(device=dev)
     r, c = x.shape
-    add("c4 MoR 128x128 relative-error criterion (mode 1)", x, 4, lambda: mor.ops.fake_quantize(x, r, c, 128, 128, 1e-15, 1, 1))
-    add("c4 MoR 128x128 dynamic-range criterion (mode 101)", x, 4, lambda: mor.ops.fake_quantize(x, r, c, 128, 128, 1e-15, 101, 1))
-    add("c4 block scaling 128x128 pipeline (ss 1)", x, 6, lambda: mor.ops.fake_quantize_block_scaling(x, r, c, 128, 128, 3e38, 1))
+    add("c4 MoR 128x128 relative-error criterion (mode 1)", x, 4, lambda x: mor.ops.fake_quantize(x, r, c, 128, 128, 1e-15, 1, 1))
+    add("c4 MoR 128x128 dynamic-range criterion (mode 101)", x, 4, lambda x: mor.ops.fake_quantize(x, r, c, 128, 128, 1e-15, 101, 1))
+    add("c4 block scaling 128x128 pipeline (ss 1)", x, 6, lambda x: mor.ops.fake_quantize_block_scaling(x, r, c, 128, 128, 3e38, 1))
     del x
     x = workloads.config5_slab(0, device=dev)
     r, c = x.shape
-    add("c5 float32 1 GiB slab block scaling 128x128 pipeline (ss 1)", x, 12, lambda: mor.ops.fake_quantize_block_scaling(x, r, c, 128, 128, THRESHOLD, 1))
-    add("c5 float32 1 GiB slab per-tensor pipeline (ss 4)", x, 12, lambda: mor.ops.fake_quantize_block_scaling(x, r, c, 128, 128, THRESHOLD, 4))
+    add("c5 float32 1 GiB slab block scaling 128x128 pipeline (ss 1)", x, 12, lambda x: mor.ops.fake_quantize_block_scaling(x, r, c, 128, 128, THRESHOLD, 1))
+    add("c5 float32 1 GiB slab per-tensor pipeline (ss 4)", x, 12, lambda x: mor.ops.fake_quantize_block_scaling(x, r, c, 128, 128, THRESHOLD, 4))
     del x
     os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
-    with open(os.path.join(ROOT, "gpurun_out", "suite.json"), "w") as f:
+    with open(out_path or os.path.join(ROOT, "gpurun_out", "suite.json"), "w") as f:
         json.dump({"peak_GB/s": peak, "results": results}, f, indent=1)
     return results
 

@@ -106,7 +106,7 @@ MOR_B200_API int mor_b200_block_scaling(const void* input, void* output, int dty
  * fixed set of buffers by their framework, services whose memory is carved up front by
  * an arena they do not own.  The scratch the pipeline needs (scalar head, one amax and
  * one error sum per block) lives in an array built into the library instead:
- * 256 B + 8 B x 65536 blocks = 512.25 KiB of device memory on every GPU that loads the
+ * 4352 B + 8 B x 65536 blocks = 516.25 KiB of device memory on every GPU that loads the
  * library, held until the process exits.  Tensors with more than 65536 blocks (e.g. more
  * than 32768 x 32768 elements at 128 x 128) get MOR_B200_ERR_STATIC_SCRATCH; use
  * mor_b200_block_scaling for those.

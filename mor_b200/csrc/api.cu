@@ -10,7 +10,7 @@ using namespace morb;
 
 namespace {
 
-constexpr size_t kHead = 256;  // ScalarsWs lives in the first 256 bytes of a workspace
+constexpr size_t kHead = kWsHeadBytes;  // scalars and partial error sums, ahead of the per-block arrays
 
 inline size_t round256(size_t n) { return (n + 255) & ~size_t(255); }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

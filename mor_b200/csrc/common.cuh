@@ -301,7 +301,18 @@ __device__ __forceinline__ uint32_t mag2(uint32_t w) { return w & 0x7FFF7FFFu; }
 // number of non-zero halves of a magnitude word (each half <= 0x7FFF, so adding 0x7FFF
 // sets bit 15 exactly when the half is non-zero and never carries across)
 __device__ __forceinline__ int nnz2(uint32_t m) { return __popc((m + 0x7FFF7FFFu) & 0x80008000u); }
-__device__ __forceinline__ uint32_t umax16x2(uint32_t a, uint32_t b) { return __vmaxu2(a, b); }
+// packed 16-bit integer min / max: single instructions on this architecture
+__device__ __forceinline__ uint32_t umax16x2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("max.u16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t umax16x2_3(uint32_t a, uint32_t b, uint32_t c) { return __vimax3_u16x2(a, b, c); }
+__device__ __forceinline__ uint32_t smin16x2_3(uint32_t a, uint32_t b, uint32_t c) { return __vimin3_s16x2(a, b, c); }
+// packed maximum of the four magnitude words of a 16-byte vector of bf16
+__device__ __forceinline__ uint32_t umax16x2_vec(uint32_t m0, uint32_t m1, uint32_t m2, uint32_t m3) {
+    return umax16x2(umax16x2_3(m0, m1, m2), m3);
+}
 __device__ __forceinline__ uint32_t hmax_halves(uint32_t m) { return max(m & 0xFFFFu, m >> 16); }
 
 template <int FMT>

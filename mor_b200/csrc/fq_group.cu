@@ -35,7 +35,7 @@ __device__ __forceinline__ float vec_amax_float(const typename T::vec_t& v) {
     return a;
 }
 __device__ __forceinline__ uint32_t vec_amax_pattern(const uint4& v) {
-    return hmax_halves(umax16x2(umax16x2(mag2(v.x), mag2(v.y)), umax16x2(mag2(v.z), mag2(v.w))));
+    return hmax_halves(umax16x2_vec(mag2(v.x), mag2(v.y), mag2(v.z), mag2(v.w)));
 }
 
 template <typename T, int FMT, int SF>

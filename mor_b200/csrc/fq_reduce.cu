@@ -7,7 +7,7 @@
 // These kernels read 2 bytes per bf16 element, i.e. they have about 11 issue slots per
 // element at the HBM roofline, so bf16 data is reduced in packed form: a magnitude
 // word (w & 0x7FFF7FFF) feeds one packed 16-bit maximum for both halves, and the
-// non-zero count is a popcount of (m + 0x7FFF7FFF) & 0x80008000.  NaNs, which the
+// non-zero count comes from bit 15 of each half of m + 0x7FFF7FFF.  NaNs, which the
 // reference's fmaxf ignores and never counts, show up as a packed maximum above
 // 0x7F80; a CTA that sees one redoes its part with float compares.
 #include "kernels.cuh"
@@ -21,33 +21,51 @@ constexpr int kThreads = 256;
 struct Acc {
     uint32_t packed_max;  // bf16 path: two 15-bit maxima
     float fmax_;          // float path
-    int nnz;
-    uint32_t tiny;        // bf16 path: bit 15 / 31 set once a non-zero magnitude below 2^-90 was seen
+    int nnz;              // bf16 path: four times the count
+    uint32_t tmin;        // bf16 path: packed signed minimum of (magnitude + 0x7FFF) per half, starts at 0x7FFF7FFF
 };
+__device__ __forceinline__ Acc acc_init() { return Acc{0u, 0.0f, 0, 0x7FFF7FFFu}; }
 
-// halves of a magnitude word that are non-zero (bit 15 of the half set)
-__device__ __forceinline__ uint32_t nz_flags(uint32_t m) { return (m + 0x7FFF7FFFu) & 0x80008000u; }
-// acc |= flags of the halves that are non-zero and below 2^-90 (bf16 pattern 0x1280):
-// with bit 15 forced on, subtracting the threshold never borrows across halves and
-// leaves bit 15 clear exactly when the half is below it
-__device__ __forceinline__ uint32_t tiny_or(uint32_t acc, uint32_t m, uint32_t nz) {
-    const uint32_t r = (m | 0x80008000u) - 0x12801280u;
-    return acc | (~r & nz);
+// bytes 1 and 3 of a and of b, each replaced by eight copies of its top bit
+__device__ __forceinline__ uint32_t top_bits_to_bytes(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, 0xFDB9;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+// true when a half of the packed minimum stands for a non-zero magnitude below 2^-90
+// (bf16 pattern 0x1280): a zero leaves 0x7FFF, a magnitude m leaves 0x8000 + m - 1
+__device__ __forceinline__ bool tmin_is_tiny(uint32_t t) {
+    return (t & 0x7FFFu) < 0x127Fu || ((t >> 16) & 0x7FFFu) < 0x127Fu;
 }
 
 template <typename T>
 __device__ __forceinline__ void vec_acc_fast(const typename T::vec_t& v, Acc& a) {
     if constexpr (T::kBytesPerElem == 2) {
+        // s = m + 0x7FFF per half: bit 15 says "non-zero", and as a signed 16-bit number s
+        // orders the non-zero magnitudes below every zero, so one packed minimum tracks the
+        // smallest non-zero magnitude; the eight "non-zero" bits are spread to nibbles and
+        // counted by one popcount
         const uint32_t m0 = mag2(v.x), m1 = mag2(v.y), m2 = mag2(v.z), m3 = mag2(v.w);
-        a.packed_max = umax16x2(umax16x2(a.packed_max, m0), umax16x2(umax16x2(m1, m2), m3));
-        const uint32_t z0 = nz_flags(m0), z1 = nz_flags(m1), z2 = nz_flags(m2), z3 = nz_flags(m3);
-        a.nnz += __popc(z0) + __popc(z1) + __popc(z2) + __popc(z3);
-        a.tiny = tiny_or(tiny_or(tiny_or(tiny_or(a.tiny, m0, z0), m1, z1), m2, z2), m3, z3);
+        a.packed_max = umax16x2_3(umax16x2_3(a.packed_max, m0, m1), m2, m3);
+        const uint32_t s0 = m0 + 0x7FFF7FFFu, s1 = m1 + 0x7FFF7FFFu, s2 = m2 + 0x7FFF7FFFu, s3 = m3 + 0x7FFF7FFFu;
+        a.tmin = smin16x2_3(smin16x2_3(a.tmin, s0, s1), s2, s3);
+        const uint32_t p01 = top_bits_to_bytes(s0, s1), p23 = top_bits_to_bytes(s2, s3);
+        a.nnz += __popc((p01 & 0x0F0F0F0Fu) | (p23 & 0xF0F0F0F0u));
     } else {
         const float a0 = fabsf(v.x), a1 = fabsf(v.y), a2 = fabsf(v.z), a3 = fabsf(v.w);
         a.fmax_ = fmaxf(fmaxf(a.fmax_, a0), fmaxf(fmaxf(a1, a2), a3));
         a.nnz += (a0 > 0.0f) + (a1 > 0.0f) + (a2 > 0.0f) + (a3 > 0.0f);
     }
+}
+template <typename T>
+__device__ __forceinline__ int acc_nnz(const Acc& a) {
+    if constexpr (T::kBytesPerElem == 2) return a.nnz >> 2;
+    else return a.nnz;
+}
+template <typename T>
+__device__ __forceinline__ bool acc_tiny(const Acc& a) {
+    if constexpr (T::kBytesPerElem == 2) return tmin_is_tiny(a.tmin);
+    else return false;
 }
 template <typename T>
 __device__ __forceinline__ void vec_acc_exact(const typename T::vec_t& v, float& amax, int& nnz) {
@@ -78,27 +96,39 @@ __device__ __forceinline__ void cta_combine(float& amax, int& nnz) {
     nnz = warp_sum_int(nnz);
 }
 
+// One-barrier CTA reduction of (amax bits, count, flag bits); every thread gets the totals.
+// amax must be non-negative (or a NaN pattern, which then wins the unsigned maximum).
+__device__ __forceinline__ void cta_reduce_all(float& amax, int& nnz, uint32_t& flags) {
+    __shared__ uint32_t s_a[32], s_f[32];
+    __shared__ int s_n[32];
+    uint32_t ab = __reduce_max_sync(0xFFFFFFFFu, f2u(amax));
+    nnz = __reduce_add_sync(0xFFFFFFFFu, nnz);
+    flags = __reduce_or_sync(0xFFFFFFFFu, flags);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    if (lane == 0) { s_a[wid] = ab; s_n[wid] = nnz; s_f[wid] = flags; }
+    __syncthreads();
+    const int nw = (blockDim.x + 31) >> 5;
+    ab = __reduce_max_sync(0xFFFFFFFFu, lane < nw ? s_a[lane] : 0u);
+    nnz = __reduce_add_sync(0xFFFFFFFFu, lane < nw ? s_n[lane] : 0);
+    flags = __reduce_or_sync(0xFFFFFFFFu, lane < nw ? s_f[lane] : 0u);
+    amax = u2f(ab);
+}
+constexpr uint32_t kFlagTiny = 1u, kFlagNan = 2u;
+template <typename T>
+__device__ __forceinline__ uint32_t acc_flags(const Acc& a, float amax) {
+    if constexpr (T::kBytesPerElem == 2) return (tmin_is_tiny(a.tmin) ? kFlagTiny : 0u) | (f2u(amax) > 0x7F800000u ? kFlagNan : 0u);
+    else return 0u;
+}
+
 template <typename T>
 __device__ __forceinline__ float acc_amax(const Acc& a) {
     if constexpr (T::kBytesPerElem == 2) return u2f(hmax_halves(a.packed_max) << 16);
     else return a.fmax_;
 }
-// true when the fast bf16 accumulation may have met a NaN anywhere in the CTA
-template <typename T>
-__device__ __forceinline__ bool cta_saw_nan(float amax) {
-    if constexpr (T::kBytesPerElem == 2) return __syncthreads_or(f2u(amax) > 0x7F800000u);
-    else return false;
-}
-
 __device__ __forceinline__ void publish(ScalarsWs* ws, float amax, int nnz) {
     atomicMax(&ws->gamax_bits, f2u(amax));
     if (nnz) atomicAdd(&ws->gnnz, (unsigned long long)nnz);
 }
-// CTA-wide OR of the "tiny non-zero value seen" flags (and of "a NaN was seen"); one atomic if set
-__device__ __forceinline__ void publish_unsafe(ScalarsWs* ws, bool mine) {
-    if (__syncthreads_or(mine) && threadIdx.x == 0) atomicOr(&ws->div_unsafe, 1u);
-}
-
 __global__ void zero_scalars_kernel(ScalarsWs* ws) {
     ws->gamax_bits = 0u; ws->fallback = 0; ws->gnnz = 0ull; ws->gerr = 0.0f; ws->meta = 0;
     ws->div_unsafe = 0u; ws->pad = 0u;
@@ -108,7 +138,7 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads) amax_nnz_flat_kernel(const typename T::vec_t* __restrict__ in,
                                                                  int64_t nvec, int64_t n_tail_elems,
                                                                  ScalarsWs* __restrict__ ws) {
-    Acc acc{0u, 0.0f, 0, 0u};
+    Acc acc = acc_init();
     const int64_t stride = (int64_t)gridDim.x * kThreads;
     const int64_t gtid = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     for (int64_t i = gtid; i < nvec; i += stride * 4) {
@@ -121,22 +151,35 @@ __global__ void __launch_bounds__(kThreads) amax_nnz_flat_kernel(const typename 
             if (i + u * stride < nvec) vec_acc_fast<T>(v[u], acc);
     }
     float amax = acc_amax<T>(acc);
-    int nnz = acc.nnz;
-    const bool saw_nan = cta_saw_nan<T>(amax);
-    if (saw_nan) {
-        amax = 0.0f; nnz = 0;
-        for (int64_t i = gtid; i < nvec; i += stride) vec_acc_exact<T>(ld_keep(in + i), amax, nnz);
-    }
-    publish_unsafe(ws, saw_nan || acc.tiny != 0u);
+    int nnz = acc_nnz<T>(acc);
+    uint32_t flags = acc_flags<T>(acc, amax);
     if (gtid < n_tail_elems) {
         float a;
         if constexpr (T::kBytesPerElem == 2) a = fabsf(u2f((uint32_t)reinterpret_cast<const uint16_t*>(in + nvec)[gtid] << 16));
         else a = fabsf(reinterpret_cast<const float*>(in + nvec)[gtid]);
-        amax = fmaxf(amax, a);
-        nnz += a > 0.0f;
+        if (a > 0.0f) {  // false for a NaN, which the maximum has to skip
+            amax = fmaxf(amax, a);
+            nnz += 1;
+            if (a < 8.0779357e-28f) flags |= kFlagTiny;  // 2^-90
+        }
     }
-    cta_combine(amax, nnz);
-    if (threadIdx.x == 0) publish(ws, amax, nnz);
+    cta_reduce_all(amax, nnz, flags);
+    if (flags & kFlagNan) {  // a NaN somewhere in this CTA's part: float compares, as the reference does
+        amax = 0.0f; nnz = 0;
+        for (int64_t i = gtid; i < nvec; i += stride) vec_acc_exact<T>(ld_keep(in + i), amax, nnz);
+        if (gtid < n_tail_elems) {
+            float a;
+            if constexpr (T::kBytesPerElem == 2) a = fabsf(u2f((uint32_t)reinterpret_cast<const uint16_t*>(in + nvec)[gtid] << 16));
+            else a = fabsf(reinterpret_cast<const float*>(in + nvec)[gtid]);
+            amax = fmaxf(amax, a);
+            nnz += a > 0.0f;
+        }
+        cta_combine(amax, nnz);
+    }
+    if (threadIdx.x == 0) {
+        publish(ws, amax, nnz);
+        if (flags) atomicOr(&ws->div_unsafe, 1u);
+    }
 }
 
 // One CTA per (brows x bcols) block.  W lanes (a power of two) span a block row in
@@ -152,7 +195,7 @@ __global__ void __launch_bounds__(kThreads) amax_nnz_blocks_kernel(const typenam
     const int W = 1 << w_shift, RPS = kThreads >> w_shift;
     const int tx = threadIdx.x & (W - 1), ty = threadIdx.x >> w_shift;
     const typename T::vec_t* base = in + r0 * cols_vec + c0;
-    Acc acc{0u, 0.0f, 0, 0u};
+    Acc acc = acc_init();
     if (brows >= 4 * RPS) {  // tall blocks: eight, then four rows in flight per lane
         for (int cv = tx; cv < bcols_vec; cv += W) {
             int r = ty;
@@ -187,18 +230,19 @@ __global__ void __launch_bounds__(kThreads) amax_nnz_blocks_kernel(const typenam
         }
     }
     float amax = acc_amax<T>(acc);
-    int nnz = acc.nnz;
-    const bool saw_nan = cta_saw_nan<T>(amax);
-    if (saw_nan) {
+    int nnz = acc_nnz<T>(acc);
+    uint32_t flags = acc_flags<T>(acc, amax);
+    cta_reduce_all(amax, nnz, flags);
+    if (flags & kFlagNan) {
         amax = 0.0f; nnz = 0;
         for (int cv = tx; cv < bcols_vec; cv += W)
             for (int r = ty; r < brows; r += RPS) vec_acc_exact<T>(ld_keep(base + (int64_t)r * cols_vec + cv), amax, nnz);
+        cta_combine(amax, nnz);
     }
-    publish_unsafe(ws, saw_nan || acc.tiny != 0u);
-    cta_combine(amax, nnz);
     if (threadIdx.x == 0) {
         block_amax[b] = amax;
         publish(ws, amax, nnz);
+        if (flags) atomicOr(&ws->div_unsafe, 1u);
     }
 }
 

@@ -291,7 +291,7 @@ rowgroup_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::v
                     // several 1 x k blocks inside the unit: amax of the lanes of this block
                     float a = 0.0f;
                     if constexpr (T::kBytesPerElem == 2) {
-                        uint32_t pm = hmax_halves(umax16x2(umax16x2(mag2(v[q].x), mag2(v[q].y)), umax16x2(mag2(v[q].z), mag2(v[q].w))));
+                        uint32_t pm = hmax_halves(umax16x2_vec(mag2(v[q].x), mag2(v[q].y), mag2(v[q].z), mag2(v[q].w)));
                         for (int o = group_lanes >> 1; o > 0; o >>= 1) pm = max(pm, __shfl_xor_sync(0xFFFFFFFFu, pm, o));
                         if constexpr (MODE == 2) {
                             // power-of-two scale of 448 / amax straight from the amax pattern (amax >= 1e-35,
@@ -379,7 +379,7 @@ rowgroup_small_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_
         bool done = false;
         float a = -1.0f;
         if constexpr (T::kBytesPerElem == 2) {
-            uint32_t pm = hmax_halves(umax16x2(umax16x2(mag2(v.x), mag2(v.y)), umax16x2(mag2(v.z), mag2(v.w))));
+            uint32_t pm = hmax_halves(umax16x2_vec(mag2(v.x), mag2(v.y), mag2(v.z), mag2(v.w)));
             for (int o = group_lanes >> 1; o > 0; o >>= 1) pm = max(pm, __shfl_xor_sync(0xFFFFFFFFu, pm, o));
             if constexpr (E8) {
                 // 448 / amax as a power of two straight from the amax pattern (amax >= 1e-35, normal, finite)
@@ -578,6 +578,49 @@ finalize_kernel(const float* __restrict__ block_err, int64_t n_err, int stride, 
     }
 }
 
+// Long error arrays: the 1024 / stride sequential sums ("chains": what thread j * stride of
+// the reference's one CTA adds up, entries j, j + period, j + 2 * period, ... in order) do not
+// depend on one another, so they are spread over CTAs, eight chains each.  All 256 threads of
+// a CTA load (32 rows x 8 chains per step, eight steps in flight) and stage 256 rows in shared
+// memory; eight lanes then add their chain's 256 entries in order while the next 256 rows are
+// already on their way.  Rows past the end read as +0.0, which leaves a non-negative sum as it
+// is.  finalize_kernel then runs on the `period` chain sums with the same stride.
+constexpr int kChainsPerCta = 8, kChainRows = 256;
+__global__ void __launch_bounds__(256) chain_sum_kernel(const float* __restrict__ block_err, int64_t n_err, int period,
+                                                        float* __restrict__ chain_sums) {
+    __shared__ float s_rows[kChainRows][kChainsPerCta];
+    const int ch = threadIdx.x & 7, ry = threadIdx.x >> 3;
+    const int j = blockIdx.x * kChainsPerCta + ch;
+    const int64_t rows = (n_err + period - 1) / period;
+    float v[8];
+    auto load = [&](int64_t c0) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int64_t idx = (c0 + ry + 32 * u) * period + j;
+            v[u] = (j < period && idx < n_err) ? __ldg(block_err + idx) : 0.0f;
+        }
+    };
+    load(0);
+    float acc = 0.0f;
+    for (int64_t c0 = 0; c0 < rows; c0 += kChainRows) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) s_rows[ry + 32 * u][ch] = v[u];
+        __syncthreads();
+        if (c0 + kChainRows < rows) load(c0 + kChainRows);
+        if (threadIdx.x < kChainsPerCta) {
+            for (int r = 0; r < kChainRows; r += 8) {
+                float x[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) x[u] = s_rows[r + u][threadIdx.x];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) acc = __fadd_rn(acc, x[u]);
+            }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x < kChainsPerCta && j < period) chain_sums[j] = acc;
+}
+
 __global__ void __launch_bounds__(256) fallback_copy_kernel(const uint4* __restrict__ in, uint4* __restrict__ out,
                                                             int64_t nvec, const ScalarsWs* __restrict__ ws) {
     if (!ws->fallback) return;
@@ -671,13 +714,24 @@ int launch_colgroup_err_cast(const ScalingArgs& a, bool store, bool skip, cudaSt
 int launch_finalize(const ScalingArgs& a, const long long* ext_nnz, int32_t* meta, float* gamax, void* gnnz,
                     int nnz_is_i64, float* gerr, cudaStream_t st) {
     constexpr int kMaxChunk = 32768;  // floats: 128 KiB of shared memory for the one CTA
-    int chunk = (int)((a.n_err + 1023) / 1024 * 1024);
-    if (chunk > kMaxChunk || a.n_err > kMaxChunk) chunk = kMaxChunk;
+    const float* err = a.block_err;
+    int64_t n = a.n_err;
+    if (n > 2 * kMaxChunk) {  // spread the independent sequential sums over CTAs first
+        const int period = 1024 / a.err_slot_stride;
+        float* chains = reinterpret_cast<float*>(reinterpret_cast<char*>(a.ws) + kChainSumsOffset);
+        chain_sum_kernel<<<period / kChainsPerCta, 256, 0, st>>>(err, n, period, chains);
+        const int rc = check_launch();
+        if (rc) return rc;
+        err = chains;
+        n = period;
+    }
+    int chunk = (int)((n + 1023) / 1024 * 1024);
+    if (chunk > kMaxChunk) chunk = kMaxChunk;
     const size_t smem = (size_t)chunk * sizeof(float);
     if (smem > 48 * 1024 &&
         cudaFuncSetAttribute(finalize_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxChunk * (int)sizeof(float)) != cudaSuccess)
         return kErrLaunch;
-    finalize_kernel<<<1, 1024, smem, st>>>(a.block_err, a.n_err, a.err_slot_stride, chunk, a.threshold, a.ws,
+    finalize_kernel<<<1, 1024, smem, st>>>(err, n, a.err_slot_stride, chunk, a.threshold, a.ws,
                                            a.ext_gamax, ext_nnz, meta, gamax, gnnz, nnz_is_i64, gerr);
     return check_launch();
 }

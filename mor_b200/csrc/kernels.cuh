@@ -26,7 +26,11 @@ int launch_e8mx_cast(const void* in, void* out, int64_t n_elems, int qtype, int 
                      const uint32_t* gamax_bits, cudaStream_t st);
 
 // ---- fq_reduce.cu: amax / non-zero reductions ------------------------------------
-struct ScalarsWs {              // head of every workspace, 32 bytes, zeroed by launch_zero_scalars
+// Every workspace starts with a head of kWsHeadBytes: the scalars below in the first 256
+// bytes, then room for the 1024 partial sums of a long error array (launch_finalize).
+constexpr size_t kChainSumsOffset = 256;
+constexpr size_t kWsHeadBytes = kChainSumsOffset + 1024 * sizeof(float);
+struct ScalarsWs {              // 32 bytes, zeroed by launch_zero_scalars
     uint32_t gamax_bits;        // max |x| as the bit pattern of a non-negative float
     int32_t fallback;           // 1 when the tensor-level BF16 fallback fired
     unsigned long long gnnz;    // count of non-zero elements

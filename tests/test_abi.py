@@ -63,15 +63,16 @@ def test_version_and_status_strings():
 
 def test_workspace_sizes():
     wb = cabi.workspace_bytes
-    assert wb(cabi.OP_E8MX, 4096, 4096, 128, 128) == 256
+    head = 256 + 4096  # scalars, then 1024 partial sums of a long error array
+    assert wb(cabi.OP_E8MX, 4096, 4096, 128, 128) == head
     # head + block amax + block errors, each rounded to 256 bytes
-    assert wb(cabi.OP_BLOCK_SCALING, 256, 256, 128, 128) == 256 + 256 + 256
-    assert wb(cabi.OP_BLOCK_SCALING, 4096, 4096, 128, 128) == 256 + 2 * 4096
+    assert wb(cabi.OP_BLOCK_SCALING, 256, 256, 128, 128) == head + 256 + 256
+    assert wb(cabi.OP_BLOCK_SCALING, 4096, 4096, 128, 128) == head + 2 * 4096
     assert wb(cabi.OP_BLOCK_SCALING, 256, 256, 16, 16) == 0          # not a multiple of 32 x 64
     assert wb(cabi.OP_BLOCK_SCALING, 250, 256, 128, 128) == 0        # does not divide
-    assert wb(cabi.OP_CHANNEL_SCALING, 8192, 8192, 1, 8192) == 256 + 2 * 4 * 8192
-    assert wb(cabi.OP_CHANNEL_SCALING, 16384, 8192, 1, 32) == 256 + 4 * 16384 * 64   # one error per 128 columns
-    assert wb(cabi.OP_CHANNEL_SCALING, 256, 256, 256, 1) == 256 + 4 * 256 + 256
+    assert wb(cabi.OP_CHANNEL_SCALING, 8192, 8192, 1, 8192) == head + 2 * 4 * 8192
+    assert wb(cabi.OP_CHANNEL_SCALING, 16384, 8192, 1, 32) == head + 4 * 16384 * 64   # one error per 128 columns
+    assert wb(cabi.OP_CHANNEL_SCALING, 256, 256, 256, 1) == head + 4 * 256 + 256
     assert wb(cabi.OP_CHANNEL_SCALING, 256, 256, 2, 2) == 0
     assert cabi.lib().mor_b200_scaling_error_stride(cabi.OP_CHANNEL_SCALING, 1, 32) == 4
     assert cabi.lib().mor_b200_scaling_error_stride(cabi.OP_CHANNEL_SCALING, 256, 1) == 64

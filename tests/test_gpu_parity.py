@@ -358,6 +358,29 @@ def test_generic_block_kernel_matches_tile_kernel():
     assert r.returncode == 0 and "generic ok" in r.stdout, r.stdout + r.stderr
 
 
+@pytest.mark.parametrize("stride", [1, 4, 64])
+@pytest.mark.parametrize("n", [1, 1000, 32768, 65536, 65537, 200001, 1 << 20])
+def test_ordered_error_sum_of_long_arrays(n, stride):
+    """The tensor-level error sum is order-sensitive (ref: 1178-1241); arrays above 65536 entries
+    take the path that spreads the independent sequential sums over CTAs."""
+    from mor_b200 import cabi
+    rng = np.random.default_rng(n * 7 + stride)
+    err = (rng.random(n, dtype=np.float32) * np.float32(10.0) ** rng.integers(-6, 3, n).astype(np.float32)).astype(np.float32)
+    nnz = int(n) * 100
+    want_meta, want_total = oracle.finalize(err, stride, nnz, 0.045)
+    d_err = torch.from_numpy(err).cuda()
+    d_nnz = torch.tensor([nnz], dtype=torch.int64, device="cuda")
+    meta = torch.zeros(1, dtype=torch.int32, device="cuda")
+    total = torch.zeros(1, dtype=torch.float32, device="cuda")
+    wsb = cabi.workspace_bytes(cabi.OP_AMAX_NNZ, 1, 1, 1, 1)
+    ws = torch.empty(wsb, dtype=torch.uint8, device="cuda")
+    cabi.call("mor_b200_scaling_finalize", d_err.data_ptr(), n, stride, d_nnz.data_ptr(), 0.045, meta.data_ptr(),
+              total.data_ptr(), ws.data_ptr(), wsb, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert total.cpu().numpy().view(np.uint32)[0] == np.float32(want_total).view(np.uint32)
+    assert int(meta.item()) == int(want_meta)
+
+
 def test_invalid_arguments_are_status_codes_not_faults():
     import gpu_harness as H
     from mor_b200 import cabi
