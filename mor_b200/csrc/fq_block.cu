@@ -16,6 +16,7 @@
 #include <type_traits>
 
 #include "kernels.cuh"
+#include "tma.cuh"
 
 namespace morb {
 
@@ -85,33 +86,6 @@ __device__ __forceinline__ void cast_pair(int fmt, float hi, float lo, float s, 
 // go from registers straight to global memory with 16-byte stores.
 
 constexpr int kTileBytes = 128 * 128 * 2;
-constexpr uint32_t kSpinLimit = 1u << 22;  // bounded mbarrier wait; a tile that never arrives is reported, not awaited
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-// returns false if the barrier did not complete within the spin limit
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-    for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
-}
-
 template <int SF>
 struct ErrCtx {
     const float* lut4;  // SF_FP32: RN(dequant(code) / s) tables
@@ -334,34 +308,6 @@ fq_tile128_kernel(const __grid_constant__ CUtensorMap tmap, uint4* __restrict__ 
     }
 }
 
-// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda)
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = []() -> EncodeTiledFn {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess) return nullptr;
-        if (qres != cudaDriverEntryPointSuccess) return nullptr;
-        return reinterpret_cast<EncodeTiledFn>(p);
-    }();
-    return fn;
-}
-
-// bf16 [rows, cols] tensor, boxes of 32 elements (64 bytes) x 128 rows, no swizzle
-bool make_strip_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols) {
-    EncodeTiledFn fn = encode_tiled_fn();
-    if (!fn) return false;
-    const cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
-    const cuuint32_t box[2] = {32, 128};
-    const cuuint32_t estride[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride, box, estride,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 // ---------------------------------------------------------------------------------
 // generic blocks
 // ---------------------------------------------------------------------------------
@@ -480,7 +426,7 @@ int launch_fq_block(const void* in, void* out, int is_fp32, int32_t* meta, int64
     if (!is_fp32 && brows == 128 && bcols == 128 && rows % 128 == 0 && cols % 128 == 0 && aligned && !force_generic &&
         rows < (int64_t(1) << 31) && cols < (int64_t(1) << 31)) {
         CUtensorMap map;
-        if (make_strip_map(&map, in, rows, cols)) {
+        if (make_tile_map(&map, in, rows, cols, 2, 32, 128)) {
             auto* o4 = static_cast<uint4*>(out);
             if (sf_type == kSfE8) fq_tile128_kernel<kSfE8><<<(unsigned)nb, 128, kTileBytes, st>>>(map, o4, meta, cols / 8, (int)bx, clamp, quant_mode, dynamic_range_mode);
             else fq_tile128_kernel<kSfFp32><<<(unsigned)nb, 128, kTileBytes, st>>>(map, o4, meta, cols / 8, (int)bx, clamp, quant_mode, dynamic_range_mode);

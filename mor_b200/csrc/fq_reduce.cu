@@ -131,7 +131,7 @@ __device__ __forceinline__ void publish(ScalarsWs* ws, float amax, int nnz) {
 }
 __global__ void zero_scalars_kernel(ScalarsWs* ws) {
     ws->gamax_bits = 0u; ws->fallback = 0; ws->gnnz = 0ull; ws->gerr = 0.0f; ws->meta = 0;
-    ws->div_unsafe = 0u; ws->pad = 0u;
+    ws->div_unsafe = 0u; ws->load_timeout = 0u;
 }
 
 template <typename T>

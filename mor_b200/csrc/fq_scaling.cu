@@ -13,9 +13,11 @@
 // threads" of the reference's CTA (the words of one 16-byte vector), keeps one
 // running sum per logical thread, and logical_warp_sum() folds them exactly as the
 // reference's tree folds real lanes.
+#include <cstdlib>
 #include <type_traits>
 
 #include "kernels.cuh"
+#include "tma.cuh"
 
 namespace morb {
 
@@ -232,6 +234,104 @@ block_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_
     if (threadIdx.x < 32) {
         const float t = warp_sum_ordered(wsum[threadIdx.x]);
         if (threadIdx.x == 0) block_err[b] = t;
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// 128 x 128 blocks, tile staged by TMA
+// ---------------------------------------------------------------------------------
+// Same arithmetic and the same order of additions as block_err_cast_kernel, but the
+// whole block (64 KiB of binary32, 32 KiB of bf16) is requested from HBM by one thread
+// as the CTA starts: 16 or 8 boxes of 32 rows x 128 bytes, one mbarrier per group of 32
+// rows.  The scale, the quotient table and the barrier that publishes it are computed
+// while the bytes are on their way; rows j*32.. are consumed as soon as their barrier
+// flips.  Shared-memory layout [row group j][strip][32 rows][128 B]: the eight lanes
+// that cover 128 consecutive bytes of a row read eight consecutive 16-byte chunks, so
+// every 16-byte shared load is conflict-free.  No registers hold data in flight, which
+// leaves room for three (binary32) or six (bf16) CTAs per SM.
+template <typename T> struct Tile128 {
+    static constexpr int kStrips = T::kBytesPerElem;          // 128-byte strips per block row
+    static constexpr int kBytes = 128 * 128 * T::kBytesPerElem;
+    static constexpr int kThreads = 1024 / T::kWordsPerVec;
+    static constexpr int kCtasPerSm = T::kBytesPerElem == 4 ? 3 : 6;
+};
+
+template <typename T, bool E8, bool STORE>
+__global__ void __launch_bounds__(Tile128<T>::kThreads, Tile128<T>::kCtasPerSm)
+block_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename T::vec_t* __restrict__ out, int64_t cols_vec,
+                     int blocks_x, int ss, const float* __restrict__ block_amax, float* __restrict__ block_err,
+                     ScalarsWs* __restrict__ ws, const float* __restrict__ ext_gamax, int skip_if_fallback) {
+    constexpr int VW = T::kWordsPerVec, LPW = 32 / VW, NT = Tile128<T>::kThreads, NS = Tile128<T>::kStrips;
+    constexpr int EPS = 128 / T::kBytesPerElem;  // elements per strip
+    constexpr int CI = 2;                        // vectors per lane and row: 128 columns / (LPW lanes x 16 bytes)
+    if (skip_if_fallback && ws->fallback) return;
+    extern __shared__ __align__(128) uint8_t s_tile[];
+    __shared__ __align__(8) uint64_t s_bar[4];
+    __shared__ float wsum[32];
+    __shared__ float s_lut[E8 ? 1 : 256];
+    const int tid = threadIdx.x;
+    const int64_t b = blockIdx.x;
+    const int bx = (int)(b % blocks_x), by = (int)(b / blocks_x);
+    if (tid == 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mbar_init(&s_bar[j], 1);
+    }
+    __syncthreads();
+    if (tid == 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            mbar_expect_tx(&s_bar[j], NS * 4096);
+#pragma unroll
+            for (int sidx = 0; sidx < NS; ++sidx)
+                tma_load_2d(s_tile + (j * NS + sidx) * 4096, &tmap, bx * 128 + sidx * EPS, by * 128 + j * 32, &s_bar[j]);
+        }
+    }
+    const float sf = scaling_factor(ss, read_gamax(ws, ext_gamax), block_amax[b]);
+    const int p = tid % LPW, ty = tid / LPW;
+    float acc[VW];
+#pragma unroll
+    for (int k = 0; k < VW; ++k) acc[k] = 0.0f;
+    const typename T::vec_t* tile = reinterpret_cast<const typename T::vec_t*>(s_tile);
+    typename T::vec_t* dst = out + ((int64_t)by * 128 + ty) * cols_vec + (int64_t)bx * (CI * LPW) + p;
+    const bool fastdiv = fast_div_ok<T>(ws);
+    bool arrived = true;
+    auto run = [&](const auto& path, auto fd_tag) {
+        constexpr int FD = (T::kBytesPerElem != 2) ? kDivIeee : (decltype(fd_tag)::value ? kDivBf16 : kDivBf16Any);
+        for (int j = 0; j < 4; ++j) {
+            if (!mbar_wait_bounded(&s_bar[j], 0)) { arrived = false; return; }
+#pragma unroll
+            for (int i = 0; i < CI; ++i) {
+                const int vc = p + LPW * i;
+                const typename T::vec_t v = tile[((j * NS + (vc >> 3)) * 32 + ty) * 8 + (vc & 7)];
+                typename T::vec_t o;
+                err_vec<T, std::decay_t<decltype(path)>, STORE, FD>(path, v, o, acc);
+                if constexpr (STORE) st_stream(dst + (int64_t)(32 * j) * cols_vec + LPW * i, o);
+            }
+        }
+    };
+    if constexpr (E8) {
+        const PathE8 path{e8_consts(sf)};
+        if (fastdiv) run(path, std::true_type{}); else run(path, std::false_type{});
+    } else {
+        fill_lut32(s_lut, sf, tid, NT);
+        __syncthreads();
+        const PathLut path{s_lut, sf};
+        if (fastdiv) run(path, std::true_type{}); else run(path, std::false_type{});
+    }
+    if (__syncthreads_or(!arrived)) {
+        // a load did not complete within the bounded wait: flag the call (finalize reports
+        // meta = -1) and give the copies one more bounded chance to land before this CTA's
+        // shared memory is handed to the next one
+        if (tid == 0) atomicOr(&ws->load_timeout, 1u);
+        for (int j = 0; j < 4; ++j) mbar_wait_bounded(&s_bar[j], 0);
+        return;
+    }
+    const float s = logical_warp_sum<VW>(acc);
+    if (p == 0) wsum[ty] = s;
+    __syncthreads();
+    if (tid < 32) {
+        const float t = warp_sum_ordered(wsum[tid]);
+        if (tid == 0) block_err[b] = t;
     }
 }
 
@@ -563,11 +663,13 @@ finalize_kernel(const float* __restrict__ block_err, int64_t n_err, int stride, 
             const long long nnz = ext_nnz ? *ext_nnz : (long long)ws->gnnz;
             const float gamax = ext_gamax ? *ext_gamax : u2f(ws->gamax_bits);
             const float avg = __fdiv_rn(total, (float)nnz);
-            const int fb = avg > threshold;
+            const bool timed_out = ws->load_timeout != 0u;  // a tile never arrived: the sums are not valid
+            const int fb = !timed_out && avg > threshold;
+            const int m = timed_out ? -1 : (fb ? 3 : 1);
             ws->fallback = fb;
             ws->gerr = total;
-            ws->meta = fb ? 3 : 1;
-            if (meta_out) *meta_out = fb ? 3 : 1;
+            ws->meta = m;
+            if (meta_out) *meta_out = m;
             if (gamax_out) *gamax_out = gamax;
             if (gerr_out) *gerr_out = total;
             if (gnnz_out) {
@@ -637,6 +739,26 @@ int launch_block_t(const ScalingArgs& a, bool store, bool skip, cudaStream_t st)
     auto* in = static_cast<const typename T::vec_t*>(a.in);
     auto* out = static_cast<typename T::vec_t*>(a.out);
     constexpr int TH = 1024 / T::kWordsPerVec;
+    static const bool force_generic = getenv("MOR_B200_FORCE_GENERIC") != nullptr;
+    CUtensorMap map;
+    if (a.brows == 128 && a.bcols == 128 && !force_generic &&
+        make_tile_map(&map, a.in, a.rows, a.cols, T::kBytesPerElem, 128 / T::kBytesPerElem, 32)) {
+#define MORB_TILE(E, S)                                                                                              \
+    do {                                                                                                             \
+        static const cudaError_t attr = cudaFuncSetAttribute(block_tile128_kernel<T, E, S>,                          \
+                                                             cudaFuncAttributeMaxDynamicSharedMemorySize,            \
+                                                             Tile128<T>::kBytes);                                     \
+        if (attr != cudaSuccess) return kErrLaunch;                                                                  \
+        block_tile128_kernel<T, E, S><<<(unsigned)nb, TH, Tile128<T>::kBytes, st>>>(                                  \
+            map, out, cols_vec, (int)bx, a.ss_mode, a.block_amax, a.block_err, a.ws, a.ext_gamax, skip ? 1 : 0);     \
+    } while (0)
+        if (e8 && store) MORB_TILE(true, true);
+        else if (e8) MORB_TILE(true, false);
+        else if (store) MORB_TILE(false, true);
+        else MORB_TILE(false, false);
+#undef MORB_TILE
+        return check_launch();
+    }
 #define MORB_GO(E, S) block_err_cast_kernel<T, E, S><<<(unsigned)nb, TH, 0, st>>>(in, out, cols_vec, a.brows, a.bcols / EPV, bx, a.ss_mode, a.block_amax, a.block_err, a.ws, a.ext_gamax, skip ? 1 : 0)
     if (e8 && store) MORB_GO(true, true);
     else if (e8) MORB_GO(true, false);

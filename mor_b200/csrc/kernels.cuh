@@ -37,7 +37,7 @@ struct ScalarsWs {              // 32 bytes, zeroed by launch_zero_scalars
     float gerr;                 // ordered sum of the block errors
     int32_t meta;
     uint32_t div_unsafe;        // a non-zero bf16 magnitude below 2^-90 was seen: take the IEEE division
-    uint32_t pad;
+    uint32_t load_timeout;      // a TMA tile load did not complete within its bounded wait
 };
 int launch_zero_scalars(ScalarsWs* ws, cudaStream_t st);
 // amax and nnz of a flat tensor (phase 1 of e8mx and of the row-sharded pipeline)

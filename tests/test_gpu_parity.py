@@ -373,7 +373,7 @@ def test_ordered_error_sum_of_long_arrays(n, stride):
     meta = torch.zeros(1, dtype=torch.int32, device="cuda")
     total = torch.zeros(1, dtype=torch.float32, device="cuda")
     wsb = cabi.workspace_bytes(cabi.OP_AMAX_NNZ, 1, 1, 1, 1)
-    ws = torch.empty(wsb, dtype=torch.uint8, device="cuda")
+    ws = torch.zeros(wsb, dtype=torch.uint8, device="cuda")  # the head carries flags of the earlier phases
     cabi.call("mor_b200_scaling_finalize", d_err.data_ptr(), n, stride, d_nnz.data_ptr(), 0.045, meta.data_ptr(),
               total.data_ptr(), ws.data_ptr(), wsb, torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
