@@ -39,9 +39,9 @@ THRESHOLD = 0.045              # the reference tests' e4m3_threshold
 SS_MODE = 1
 FALLBACK_HBM_GBS = 6650.0      # used only when MEASURED_PEAKS.json is absent
 # dram read + write bytes of the dominant kernel per algorithmic byte, from one ncu capture of a
-# 1 GiB slab (profiles/block_err_cast_fp32_config5.md: 2.0993 GB moved for 2.1475 GB algorithmic);
+# 1 GiB slab (profiles/block_tile128_fp32_config5.md: 2.0914 GB moved for 2.1475 GB algorithmic);
 # one CTA per block and no reuse across blocks, so traffic grows in proportion to the elements
-TRAFFIC_PER_ALGORITHMIC_BYTE = 2.0993 / 2.1475
+TRAFFIC_PER_ALGORITHMIC_BYTE = 2.0914 / 2.1475
 
 
 def measured_peak():
@@ -308,7 +308,7 @@ def main():
             "elements_per_s": total_elems / (step_ms * 1e-3),
             "per_gpu": {"GB/s": value / n_gpus, "elements_per_s": total_elems / (step_ms * 1e-3) / n_gpus,
                         "pct_of_hbm_peak": 100.0 * value / n_gpus / peak, "peak_GB/s": peak, "peak_kind": peak_kind},
-            "roofline": {"bound": "hbm", "kernel": "block_err_cast_kernel<Fp32> (scale + E4M3 cast + error sums)",
+            "roofline": {"bound": "hbm", "kernel": "block_tile128_kernel<Fp32> (TMA-staged tile: scale + E4M3 cast + error sums)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind, "ms_per_launch": cast_ms, "bytes_per_launch": cast_bytes,
                          "traffic": cast_bytes * TRAFFIC_PER_ALGORITHMIC_BYTE,
