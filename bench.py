@@ -159,6 +159,7 @@ def main():
     ap.add_argument("--no-main", action="store_true", help="skip the configuration-5 workload (profiling the suite)")
     ap.add_argument("--suite-only", default="", help="substring filter on suite entry names")
     ap.add_argument("--suite-iters", type=int, default=10)
+    ap.add_argument("--suite-graph", action="store_true", help="also time the suite calls replayed as one CUDA graph")
     ap.add_argument("--suite-out", default=None, help="where --suite writes its table (default gpurun_out/suite.json)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
@@ -188,7 +189,7 @@ def main():
 
     if args.no_main:
         peak, _ = measured_peak()
-        run_suite(torch, dev, peak, args.suite_only, args.suite_iters, args.suite_out)
+        run_suite(torch, dev, peak, args.suite_only, args.suite_iters, args.suite_out, args.suite_graph)
         return 0
 
     rows = ROWS // args.scale
@@ -294,7 +295,7 @@ def main():
     suite = None
     if args.suite and rank == 0 and world == 1:
         del out
-        suite = run_suite(torch, dev, peak, args.suite_only, args.suite_iters, args.suite_out)
+        suite = run_suite(torch, dev, peak, args.suite_only, args.suite_iters, args.suite_out, args.suite_graph)
 
     if rank == 0:
         line = {
@@ -331,7 +332,7 @@ def main():
     return 0
 
 
-def run_suite(torch, dev, peak, only="", iters=10, out_path=None):
+def run_suite(torch, dev, peak, only="", iters=10, out_path=None, use_graph=False):
     """Times every kernel family on configurations 1-5 (one GPU).  Every operator runs
     `iters` times back to back between one pair of CUDA events on the launching stream;
     successive calls take their input from, and leave their outputs in, a ring of distinct
@@ -356,18 +357,41 @@ def run_suite(torch, dev, peak, only="", iters=10, out_path=None):
             outs[i % k] = fn(xs[i % k])
         e.record()
         torch.cuda.synchronize()
-        return s.elapsed_time(e) / n, k
+        eager_ms = s.elapsed_time(e) / n
+        # the same n calls as one CUDA graph: what the device needs when the host is out of the way
+        graph_ms = None
+        if use_graph:
+            try:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    for i in range(n):
+                        outs[i % k] = fn(xs[i % k])
+                g.replay()
+                torch.cuda.synchronize()
+                s.record(); g.replay(); e.record()
+                torch.cuda.synchronize()
+                graph_ms = s.elapsed_time(e) / n
+                del g
+            except Exception as ex:  # an operator that cannot be captured keeps its eager time only
+                print(f"[suite] graph capture failed: {ex}", file=sys.stderr)
+        return eager_ms, graph_ms, k
 
     def add(name, x, bytes_per_elem, fn):
         if only and only not in name:
             return
-        ms, k = time_call(fn, x)
+        ms, graph_ms, k = time_call(fn, x)
         n = x.numel()
         gbs = n * bytes_per_elem / (ms * 1e-3) / 1e9
-        results.append({"name": name, "rows": x.shape[0], "cols": x.shape[1], "ms": ms, "GB/s": gbs,
-                        "elements_per_s": n / (ms * 1e-3), "bytes_per_element": bytes_per_elem,
-                        "frac_of_peak": gbs / peak, "buffers_in_ring": k})
-        print(f"[suite] {name}: {ms:.4f} ms  {gbs:.0f} GB/s  {100 * gbs / peak:.1f}% of peak", file=sys.stderr)
+        rec = {"name": name, "rows": x.shape[0], "cols": x.shape[1], "ms": ms, "GB/s": gbs,
+               "elements_per_s": n / (ms * 1e-3), "bytes_per_element": bytes_per_elem,
+               "frac_of_peak": gbs / peak, "buffers_in_ring": k}
+        line = f"[suite] {name}: {ms:.4f} ms  {gbs:.0f} GB/s  {100 * gbs / peak:.1f}% of peak"
+        if graph_ms:
+            ggbs = n * bytes_per_elem / (graph_ms * 1e-3) / 1e9
+            rec.update({"graph_ms": graph_ms, "graph_GB/s": ggbs, "graph_frac_of_peak": ggbs / peak})
+            line += f"   | as a CUDA graph: {graph_ms:.4f} ms  {ggbs:.0f} GB/s  {100 * ggbs / peak:.1f}%"
+        results.append(rec)
+        print(line, file=sys.stderr)
 
     x = workloads.config1(device=dev)
     r, c = x.shape

@@ -14,7 +14,9 @@
 // power-of-two scale is two float multiplies with its exponent taken from the amax
 // bits (no division), and results of that path are packed without rounding (they are
 // exact in bf16).
+#include <cstdlib>
 #include "kernels.cuh"
+#include "tma.cuh"
 
 namespace morb {
 
@@ -146,8 +148,8 @@ group_small_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_t* 
 // scale exponent inside the range where multiplying equals exponent-field
 // arithmetic) and anything else (zero or non-finite group, extreme exponents) goes to
 // the general code.
-template <int FMT>
-__device__ __forceinline__ uint4 mx_cast_vec(const uint4& v, float up, float down, uint32_t zero_bits, bool any_neg) {
+template <int FMT, bool NEG>
+__device__ __forceinline__ uint4 mx_cast_vec(const uint4& v, float up, float down, uint32_t zero_bits) {
     uint4 o;
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
     uint32_t r[4];
@@ -156,9 +158,9 @@ __device__ __forceinline__ uint4 mx_cast_vec(const uint4& v, float up, float dow
         float qh, ql;
         quant_dequant_pair<FMT, true>(__fmul_rn(bf16_hi(w[k]), up), __fmul_rn(bf16_lo(w[k]), up), qh, ql);
         float rh = __fmul_rn(qh, down), rl = __fmul_rn(ql, down);
-        if (any_neg) {  // a zero code under a scale below one comes back as +-2^(-e8-127)
-            if (qh == 0.0f) rh = u2f((f2u(qh) & 0x80000000u) | zero_bits);
-            if (ql == 0.0f) rl = u2f((f2u(ql) & 0x80000000u) | zero_bits);
+        if constexpr (NEG) {  // a zero code under a scale below one comes back as +-2^(-e8-127)
+            rh = qh == 0.0f ? u2f((f2u(qh) & 0x80000000u) | zero_bits) : rh;
+            rl = ql == 0.0f ? u2f((f2u(ql) & 0x80000000u) | zero_bits) : rl;
         }
         r[k] = pack_bf16_trunc(rh, rl);
     }
@@ -166,51 +168,88 @@ __device__ __forceinline__ uint4 mx_cast_vec(const uint4& v, float up, float dow
     return o;
 }
 
-template <int FMT>
-__global__ void __launch_bounds__(256)
-mx_bf16_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, float* __restrict__ scales, int64_t nvec,
-               int group_shift, int32_t* __restrict__ meta, int64_t n_meta, int32_t meta_code) {
+// One 16-byte vector of a lane: group amax across the 2^GS lanes of the group, cast in
+// place; returns the scale that was applied.  All 32 lanes call together.
+template <int FMT, int GS>
+__device__ __forceinline__ float mx_one(uint4& v) {
     constexpr int K127 = ((FMT == kE4M3) ? 8 : (FMT == kE5M2 ? 15 : 2)) + 127;
     constexpr uint32_t CMAN7 = (FMT == kE2M3) ? 0x70u : 0x60u;  // 1.875 / 1.75 as a 7-bit mantissa
-    const int lanes_per_group = 1 << group_shift;
-    const int64_t stride = (int64_t)gridDim.x * 256;
-    const int64_t gtid = (int64_t)blockIdx.x * 256 + threadIdx.x;
-    for (int64_t m = gtid; m < n_meta; m += stride) meta[m] = meta_code;
-    constexpr int U = 4;
-    auto one = [&](uint4 v, int64_t idx) {
-        uint32_t p = vec_amax_pattern(v);
-        for (int o = lanes_per_group >> 1; o > 0; o >>= 1) p = max(p, __shfl_xor_sync(0xFFFFFFFFu, p, o));
-        const int ea = (int)(p >> 7);                               // exponent field of the group amax
-        const int e8 = K127 - ea - ((p & 0x7Fu) > CMAN7 ? 1 : 0);   // exponent of RN(fmax / amax)
-        const bool fast = (uint32_t)(ea - 1) < 254u && (uint32_t)(e8 + 119) <= 219u;
-        float s;
-        if (__all_sync(0xFFFFFFFFu, fast)) {
-            const float up = u2f((uint32_t)(e8 + 127) << 23), down = u2f((uint32_t)(127 - e8) << 23);
+    uint32_t p = vec_amax_pattern(v);
+#pragma unroll
+    for (int o = (1 << GS) >> 1; o > 0; o >>= 1) p = max(p, __shfl_xor_sync(0xFFFFFFFFu, p, o));
+    const int ea = (int)(p >> 7);                               // exponent field of the group amax
+    const int e8 = K127 - ea - ((p & 0x7Fu) > CMAN7 ? 1 : 0);   // exponent of RN(fmax / amax)
+    const bool fast = (uint32_t)(ea - 1) < 254u && (uint32_t)(e8 + 119) <= 219u;
+    float s;
+    if (__all_sync(0xFFFFFFFFu, fast)) {
+        const float up = u2f((uint32_t)(e8 + 127) << 23), down = u2f((uint32_t)(127 - e8) << 23);
+        if (__any_sync(0xFFFFFFFFu, e8 < 0)) {
             const uint32_t zero_bits = e8 < 0 ? ((uint32_t)(-e8) << 23) : 0u;
-            v = mx_cast_vec<FMT>(v, up, down, zero_bits, __any_sync(0xFFFFFFFFu, e8 < 0));
-            s = up;
+            v = mx_cast_vec<FMT, true>(v, up, down, zero_bits);
         } else {
-            float a = u2f(p << 16);
-            if (__any_sync(0xFFFFFFFFu, p > 0x7F80u)) {  // a NaN in the warp: the reference's fmaxf skips it
-                a = vec_amax_float<Bf16>(v);
-                for (int o = lanes_per_group >> 1; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
-            }
-            s = 1.0f;
-            if (a > 0.0f) v = vec_cast_e8<Bf16, FMT>(v, e8_from_amax<FMT>(a, s));
+            v = mx_cast_vec<FMT, false>(v, up, down, 0u);
         }
-        st_stream(out + idx, v);
-        if (scales && (threadIdx.x & (lanes_per_group - 1)) == 0) scales[idx >> group_shift] = s;
-    };
-    int64_t i = gtid;
-    // nvec is a multiple of 32, so whole warps enter or leave the loops together
-    for (; i + (U - 1) * stride < nvec; i += stride * U) {
-        uint4 v[U];
+        s = up;
+    } else {
+        float a = u2f(p << 16);
+        if (__any_sync(0xFFFFFFFFu, p > 0x7F80u)) {  // a NaN in the warp: the reference's fmaxf skips it
+            a = vec_amax_float<Bf16>(v);
 #pragma unroll
-        for (int u = 0; u < U; ++u) v[u] = ld_stream(in + i + u * stride);
-#pragma unroll
-        for (int u = 0; u < U; ++u) one(v[u], i + u * stride);
+            for (int o = (1 << GS) >> 1; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+        }
+        s = 1.0f;
+        if (a > 0.0f) v = vec_cast_e8<Bf16, FMT>(v, e8_from_amax<FMT>(a, s));
     }
-    for (; i < nvec; i += stride) one(ld_stream(in + i), i);
+    return s;
+}
+
+// Every warp streams its own 2 KiB chunks (four rows of 32 vectors) through a private
+// two-stage shared-memory ring filled by bulk copies, so HBM reads stay in flight while
+// the warp computes and no register holds data that has not arrived yet.  nvec is a
+// multiple of 32: whole warps take every step together.
+constexpr int kMxStages = 2, kMxChunkVec = 128, kMxWarps = 8;
+template <int FMT, int GS>
+__global__ void __launch_bounds__(32 * kMxWarps, 5)
+mx_bf16_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, float* __restrict__ scales, int64_t nvec,
+               int32_t* __restrict__ meta, int64_t n_meta, int32_t meta_code) {
+    extern __shared__ __align__(128) uint8_t s_ring[];  // [warp][stage][2 KiB]
+    __shared__ __align__(8) uint64_t s_bar[kMxWarps][kMxStages];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int64_t n_warps = (int64_t)gridDim.x * kMxWarps, gw = (int64_t)blockIdx.x * kMxWarps + wid;
+    WarpStream<kMxStages, kMxChunkVec * 16> ws;
+    ws.start(s_ring + wid * (kMxStages * kMxChunkVec * 16), s_bar[wid], in, nvec * 16, gw, n_warps);
+    for (int64_t m = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; m < n_meta; m += (int64_t)gridDim.x * blockDim.x)
+        meta[m] = meta_code;
+    const int64_t n_chunks = (nvec + kMxChunkVec - 1) / kMxChunkVec;
+    const bool scale_lane = scales != nullptr && (lane & ((1 << GS) - 1)) == 0;
+    int st = 0;
+    for (int64_t c = gw; c < n_chunks; c += n_warps) {
+        const int64_t v0 = c * kMxChunkVec;
+        uint4* o = out + v0 + lane;
+        float* sc = scales ? scales + ((v0 + lane) >> GS) : nullptr;
+        const bool staged = ws.acquire(st);
+        if (staged && v0 + kMxChunkVec <= nvec) {
+            const uint4* chunk = reinterpret_cast<const uint4*>(ws.stage(st)) + lane;
+#pragma unroll
+            for (int r = 0; r < kMxChunkVec / 32; ++r) {
+                uint4 v = chunk[r * 32];
+                const float s = mx_one<FMT, GS>(v);
+                st_stream(o + r * 32, v);
+                if (scale_lane) sc[r * (32 >> GS)] = s;
+            }
+        } else {  // last, partial chunk, or a copy that did not arrive: ordinary loads
+            const int nv = (int)(nvec - v0 < kMxChunkVec ? nvec - v0 : kMxChunkVec);
+            for (int r = 0; r * 32 < nv; ++r) {
+                uint4 v = ld_stream(in + v0 + r * 32 + lane);
+                const float s = mx_one<FMT, GS>(v);
+                st_stream(o + r * 32, v);
+                if (scale_lane) sc[r * (32 >> GS)] = s;
+            }
+        }
+        ws.release(st, c + kMxStages * n_warps);
+        st = st + 1 == kMxStages ? 0 : st + 1;
+    }
+    ws.drain();
 }
 
 constexpr int kRowThreads = 256;
@@ -330,14 +369,39 @@ int launch_t(const void* in, void* out, float* scales, int32_t* meta, int32_t me
         if constexpr (T::kBytesPerElem == 2 && SF == kSfE8) {
             int shift = 0;
             while ((1 << shift) < gvec) ++shift;
-            mx_bf16_kernel<FMT><<<(unsigned)grid, 256, 0, st>>>(i4, o4, scales, nvec, shift, meta, meta ? n_groups : 0, meta_code);
+            constexpr int kRing = kMxWarps * kMxStages * kMxChunkVec * 16;
+            // The hardware's CTA scheduler evens out the speed differences between SMs only if
+            // it has CTAs left to hand out: two chunks per warp (both requested as the warp
+            // starts) measured best, a persistent grid with a static partition 20 % slower.
+            constexpr int kChunksPerWarp = 2;
+            const int64_t n_chunks = (nvec + kMxChunkVec - 1) / kMxChunkVec;
+            int64_t g2 = (n_chunks + kMxWarps * kChunksPerWarp - 1) / (kMxWarps * kChunksPerWarp);
+            if (g2 > 0x7FFFFFFF) return kErrTooLarge;
+            if (g2 < 1) g2 = 1;
+#define MORB_MX(GS)                                                                                                    \
+    do {                                                                                                               \
+        static const cudaError_t attr =                                                                                \
+            cudaFuncSetAttribute(mx_bf16_kernel<FMT, GS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing);         \
+        if (attr != cudaSuccess) return kErrLaunch;                                                                    \
+        mx_bf16_kernel<FMT, GS><<<(unsigned)g2, 32 * kMxWarps, kRing, st>>>(i4, o4, scales, nvec, meta,               \
+                                                                            meta ? n_groups : 0, meta_code);           \
+    } while (0)
+            switch (shift) {
+                case 0: MORB_MX(0); break;
+                case 1: MORB_MX(1); break;
+                case 2: MORB_MX(2); break;
+                case 3: MORB_MX(3); break;
+                case 4: MORB_MX(4); break;
+                default: MORB_MX(5); break;
+            }
+#undef MORB_MX
             return check_launch();
         }
         group_small_kernel<T, FMT, SF><<<(unsigned)grid, 256, 0, st>>>(i4, o4, scales, nvec, gvec, meta, meta ? n_groups : 0, meta_code);
         return check_launch();
     }
     if (gvec <= kRowThreads * kRowMaxVec) {
-        int64_t grid = (int64_t)sm_count() * 4;
+        int64_t grid = (n_groups + 1) / 2;  // two groups per CTA: the second one's loads overlap the first one's arithmetic
         if (grid > n_groups) grid = n_groups;
         const int nv = (gvec + kRowThreads - 1) / kRowThreads;
 #define MORB_ROW(NV) group_row_kernel<T, FMT, SF, NV><<<(unsigned)grid, kRowThreads, 0, st>>>(i4, o4, scales, gvec, n_groups, meta, meta_code)

@@ -4,6 +4,7 @@
 
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <cstdlib>
 
 #include "common.cuh"
 

@@ -35,6 +35,85 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
 }
 
 
+// untiled bulk copy global -> shared (16-byte aligned addresses, size a multiple of 16)
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+// A warp's private stream of fixed-size chunks of a contiguous global array through
+// shared memory: STAGES buffers, one mbarrier each, bulk copies issued by lane 0.  The
+// warp takes chunks first, first + step, ...; while it works on one, the next STAGES - 1
+// are on their way, whatever the register budget of the kernel.  Every wait is bounded:
+// if a copy does not arrive the stream turns itself off for good (`ok` false) and the
+// caller reads the data with ordinary loads instead; drain() then gives the copies still
+// in flight a last bounded chance to land before the shared memory is handed on.
+template <int STAGES, int CHUNK_BYTES>
+struct WarpStream {
+    uint8_t* buf;        // STAGES * CHUNK_BYTES of shared memory owned by this warp
+    uint64_t* bars;      // STAGES barriers owned by this warp
+    const uint8_t* src;
+    int64_t total_bytes;
+    int64_t step;        // distance between this warp's chunks, in chunks
+    uint32_t pending;    // bit s: a copy into stage s has been issued and not yet seen complete
+    uint32_t phase;      // bit s: parity that copy will flip
+    bool ok;
+
+    __device__ __forceinline__ void issue(int64_t chunk, int s) {  // lane 0
+        const int64_t off = chunk * CHUNK_BYTES;
+        if (off >= total_bytes) return;
+        const int64_t left = total_bytes - off;
+        const uint32_t bytes = left < CHUNK_BYTES ? (uint32_t)left : (uint32_t)CHUNK_BYTES;
+        mbar_expect_tx(&bars[s], bytes);
+        bulk_load(buf + s * CHUNK_BYTES, src + off, bytes, &bars[s]);
+    }
+    __device__ __forceinline__ void start(uint8_t* b, uint64_t* br, const void* s_, int64_t bytes, int64_t first,
+                                          int64_t step_) {
+        buf = b; bars = br; src = static_cast<const uint8_t*>(s_); total_bytes = bytes; step = step_;
+        pending = 0u; phase = 0u; ok = true;
+        const int lane = threadIdx.x & 31;
+        if (lane == 0) {
+#pragma unroll
+            for (int s = 0; s < STAGES; ++s) mbar_init(&bars[s], 1);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int s = 0; s < STAGES; ++s) {
+            const int64_t c = first + s * step;
+            if (c * CHUNK_BYTES < total_bytes) {
+                if (lane == 0) issue(c, s);
+                pending |= 1u << s;
+            }
+        }
+    }
+    // wait for the chunk in stage s; false (warp-uniform, and from then on always) if it did not arrive
+    __device__ __forceinline__ bool acquire(int s) {
+        if (!ok) return false;
+        const bool mine = mbar_wait_bounded(&bars[s], (phase >> s) & 1u);
+        if (__all_sync(0xFFFFFFFFu, mine)) {
+            pending &= ~(1u << s);
+            phase ^= 1u << s;
+            return true;
+        }
+        ok = false;
+        return false;
+    }
+    __device__ __forceinline__ const uint8_t* stage(int s) const { return buf + s * CHUNK_BYTES; }
+    // every lane is done with stage s: refill it with chunk `next`
+    __device__ __forceinline__ void release(int s, int64_t next) {
+        __syncwarp();
+        if (ok && next * CHUNK_BYTES < total_bytes) {
+            if ((threadIdx.x & 31) == 0) issue(next, s);
+            pending |= 1u << s;
+        }
+    }
+    __device__ __forceinline__ void drain() {
+#pragma unroll
+        for (int s = 0; s < STAGES; ++s)
+            if (pending & (1u << s)) mbar_wait_bounded(&bars[s], (phase >> s) & 1u);
+    }
+};
+
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda)
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
