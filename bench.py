@@ -159,6 +159,8 @@ def main():
     ap.add_argument("--no-main", action="store_true", help="skip the configuration-5 workload (profiling the suite)")
     ap.add_argument("--suite-only", default="", help="substring filter on suite entry names")
     ap.add_argument("--suite-iters", type=int, default=10)
+    ap.add_argument("--suite-impl", choices=["ours", "reference"], default="ours",
+                    help="reference: time the unmodified reference CUDA extension (oracle/_ref) on the configurations it supports")
     ap.add_argument("--suite-graph", action="store_true", help="also time the suite calls replayed as one CUDA graph")
     ap.add_argument("--suite-out", default=None, help="where --suite writes its table (default gpurun_out/suite.json)")
     ap.add_argument("--no-e2e", action="store_true")
@@ -171,6 +173,21 @@ def main():
 
     import torch
     import torch.distributed as dist
+
+    if args.no_main and args.suite_impl == "reference":
+        # the reference extension registers the same torch.ops.mor.* names as the repository's shim: this
+        # process loads the workload generators by file and never imports the mor_b200 package
+        import importlib.util
+        spec = importlib.util.spec_from_file_location("_workloads", os.path.join(ROOT, "mor_b200", "workloads.py"))
+        wl = importlib.util.module_from_spec(spec)
+        sys.modules["_workloads"] = wl
+        spec.loader.exec_module(wl)
+        if not torch.cuda.is_available():
+            raise SystemExit("the reference extension needs a CUDA device")
+        peak, _ = measured_peak()
+        run_suite(torch, torch.device("cuda", 0), peak, args.suite_only, args.suite_iters, args.suite_out, False,
+                  "reference", wl)
+        return 0
 
     import mor_b200  # noqa: F401  fails loudly if the CUDA library or the shim is missing
     from mor_b200 import workloads
@@ -189,7 +206,7 @@ def main():
 
     if args.no_main:
         peak, _ = measured_peak()
-        run_suite(torch, dev, peak, args.suite_only, args.suite_iters, args.suite_out, args.suite_graph)
+        run_suite(torch, dev, peak, args.suite_only, args.suite_iters, args.suite_out, args.suite_graph, args.suite_impl)
         return 0
 
     rows = ROWS // args.scale
@@ -295,7 +312,7 @@ def main():
     suite = None
     if args.suite and rank == 0 and world == 1:
         del out
-        suite = run_suite(torch, dev, peak, args.suite_only, args.suite_iters, args.suite_out, args.suite_graph)
+        suite = run_suite(torch, dev, peak, args.suite_only, args.suite_iters, args.suite_out, args.suite_graph, args.suite_impl)
 
     if rank == 0:
         line = {
@@ -332,15 +349,30 @@ def main():
     return 0
 
 
-def run_suite(torch, dev, peak, only="", iters=10, out_path=None, use_graph=False):
+def run_suite(torch, dev, peak, only="", iters=10, out_path=None, use_graph=False, impl="ours", workloads=None):
     """Times every kernel family on configurations 1-5 (one GPU).  Every operator runs
     `iters` times back to back between one pair of CUDA events on the launching stream;
     successive calls take their input from, and leave their outputs in, a ring of distinct
     buffers whose total size is at least four times the L2, so that no call finds its
     input or the lines of its output in cache.  The time per call is the total divided
     by `iters`: launch gaps between the kernels of a pipeline are part of it."""
-    import mor
-    from mor_b200 import workloads
+    if workloads is None:
+        from mor_b200 import workloads
+    if impl == "reference":
+        # the unmodified reference extension, built by oracle/build_ref.sh; it registers torch.ops.mor.*,
+        # so this process must not load the repository's own extension
+        ref_so = os.path.join(ROOT, "oracle", "_ref", "mor_ref_C.so")
+        if not os.path.exists(ref_so):
+            raise SystemExit("oracle/_ref/mor_ref_C.so is missing: run oracle/build_ref.sh where the reference sources are")
+        torch.ops.load_library(ref_so)
+
+        def call(op, x, args):
+            return getattr(torch.ops.mor, op).default(x, *args)
+    else:
+        import mor
+
+        def call(op, x, args):
+            return getattr(mor.ops, op)(x, *args)
     results = []
     ring_bytes = 512 << 20
 
@@ -376,9 +408,12 @@ def run_suite(torch, dev, peak, only="", iters=10, out_path=None, use_graph=Fals
                 print(f"[suite] graph capture failed: {ex}", file=sys.stderr)
         return eager_ms, graph_ms, k
 
-    def add(name, x, bytes_per_elem, fn):
+    def add(name, x, bytes_per_elem, op, args, ref_ok=False):
         if only and only not in name:
             return
+        if impl == "reference" and not ref_ok:   # shapes or operators the reference does not have, or asserts on
+            return
+        fn = lambda t: call(op, t, args)  # noqa: E731
         ms, graph_ms, k = time_call(fn, x)
         n = x.numel()
         gbs = n * bytes_per_elem / (ms * 1e-3) / 1e9
@@ -395,36 +430,39 @@ def run_suite(torch, dev, peak, only="", iters=10, out_path=None, use_graph=Fals
 
     x = workloads.config1(device=dev)
     r, c = x.shape
-    scale = (448.0 / x.float().abs().max()).item()
-    add("c1 per-tensor E4M3, scale given (fake_quantize mode 4)", x, 4, lambda x: mor.ops.fake_quantize(x, r, c, 128, 128, scale, 4, 1))
-    add("c1 per-tensor E4M3, self-contained (block_scaling ss 4)", x, 6, lambda x: mor.ops.fake_quantize_block_scaling(x, r, c, 128, 128, 3e38, 4))
+    scale = (torch.tensor(448.0) / x.float().abs().max().cpu()).item()   # binary32 division, as the cast kernels do
+    add("c1 per-tensor E4M3, scale given (fake_quantize mode 4)", x, 4, "fake_quantize", (r, c, 128, 128, scale, 4, 1), ref_ok=True)
+    add("c1 per-tensor E4M3, self-contained (block_scaling ss 4)", x, 6, "fake_quantize_block_scaling", (r, c, 128, 128, 3e38, 4), ref_ok=True)
     del x
     x = workloads.config2(device=dev)
     r, c = x.shape
-    add("c2 per-row E4M3 single pass (fake_quantize mode 2, 1x8192)", x, 4, lambda x: mor.ops.fake_quantize(x, r, c, 1, c, 0.0, 2, 1))
-    add("c2 per-row E5M2 single pass (fake_quantize mode 3, 1x8192)", x, 4, lambda x: mor.ops.fake_quantize(x, r, c, 1, c, 0.0, 3, 1))
-    add("c2 per-row E4M3 pipeline (channel_scaling ss 3)", x, 6, lambda x: mor.ops.fake_quantize_channel_scaling(x, r, c, 1, c, 3e38, 3))
+    add("c2 per-row E4M3 single pass (fake_quantize mode 2, 1x8192)", x, 4, "fake_quantize", (r, c, 1, c, 0.0, 2, 1))
+    add("c2 per-row E5M2 single pass (fake_quantize mode 3, 1x8192)", x, 4, "fake_quantize", (r, c, 1, c, 0.0, 3, 1))
+    # not for the reference arm: its channel path launches the 1024-thread reductions with the 64-thread
+    # kernels' shared-memory size (fake_quantize.cu:2515-2522) and raised an illegal memory access at this size
+    add("c2 per-row E4M3 pipeline (channel_scaling ss 3)", x, 6, "fake_quantize_channel_scaling", (r, c, 1, c, 3e38, 3))
     del x
     x = workloads.config3(device=dev)
     r, c = x.shape
-    add("c3 MX 1x32 E8M0 E4M3 single pass (fake_quantize_mx)", x, 4, lambda x: mor.ops.fake_quantize_mx(x, r, c, 32, 0, 2))
-    add("c3 MX 1x32 E8M0 E2M3 single pass (fake_quantize_mx)", x, 4, lambda x: mor.ops.fake_quantize_mx(x, r, c, 32, 3, 2))
-    add("c3 MX 1x32 E4M3 pipeline (channel_scaling ss 2)", x, 6, lambda x: mor.ops.fake_quantize_channel_scaling(x, r, c, 1, 32, 3e38, 2))
+    add("c3 MX 1x32 E8M0 E4M3 single pass (fake_quantize_mx)", x, 4, "fake_quantize_mx", (r, c, 32, 0, 2))
+    add("c3 MX 1x32 E8M0 E2M3 single pass (fake_quantize_mx)", x, 4, "fake_quantize_mx", (r, c, 32, 3, 2))
+    add("c3 MX 1x32 E4M3 pipeline (channel_scaling ss 2)", x, 6, "fake_quantize_channel_scaling", (r, c, 1, 32, 3e38, 2))
     del x
     x = workloads.config4(device=dev)
     r, c = x.shape
-    add("c4 MoR 128x128 relative-error criterion (mode 1)", x, 4, lambda x: mor.ops.fake_quantize(x, r, c, 128, 128, 1e-15, 1, 1))
-    add("c4 MoR 128x128 dynamic-range criterion (mode 101)", x, 4, lambda x: mor.ops.fake_quantize(x, r, c, 128, 128, 1e-15, 101, 1))
-    add("c4 block scaling 128x128 pipeline (ss 1)", x, 6, lambda x: mor.ops.fake_quantize_block_scaling(x, r, c, 128, 128, 3e38, 1))
+    add("c4 MoR 128x128 relative-error criterion (mode 1)", x, 4, "fake_quantize", (r, c, 128, 128, 1e-15, 1, 1), ref_ok=True)
+    add("c4 MoR 128x128 dynamic-range criterion (mode 101)", x, 4, "fake_quantize", (r, c, 128, 128, 1e-15, 101, 1), ref_ok=True)
+    add("c4 block scaling 128x128 pipeline (ss 1)", x, 6, "fake_quantize_block_scaling", (r, c, 128, 128, 3e38, 1), ref_ok=True)
     del x
-    x = workloads.config5_slab(0, device=dev)
-    r, c = x.shape
-    add("c5 float32 1 GiB slab block scaling 128x128 pipeline (ss 1)", x, 12, lambda x: mor.ops.fake_quantize_block_scaling(x, r, c, 128, 128, THRESHOLD, 1))
-    add("c5 float32 1 GiB slab per-tensor pipeline (ss 4)", x, 12, lambda x: mor.ops.fake_quantize_block_scaling(x, r, c, 128, 128, THRESHOLD, 4))
-    del x
+    if impl != "reference":
+        x = workloads.config5_slab(0, device=dev)
+        r, c = x.shape
+        add("c5 float32 1 GiB slab block scaling 128x128 pipeline (ss 1)", x, 12, "fake_quantize_block_scaling", (r, c, 128, 128, THRESHOLD, 1))
+        add("c5 float32 1 GiB slab per-tensor pipeline (ss 4)", x, 12, "fake_quantize_block_scaling", (r, c, 128, 128, THRESHOLD, 4))
+        del x
     os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
     with open(out_path or os.path.join(ROOT, "gpurun_out", "suite.json"), "w") as f:
-        json.dump({"peak_GB/s": peak, "results": results}, f, indent=1)
+        json.dump({"peak_GB/s": peak, "impl": impl, "results": results}, f, indent=1)
     return results
 
 

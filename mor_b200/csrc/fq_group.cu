@@ -402,7 +402,7 @@ int launch_t(const void* in, void* out, float* scales, int32_t* meta, int32_t me
     }
     if (gvec <= kRowThreads * kRowMaxVec) {
         int64_t grid = (n_groups + 1) / 2;  // two groups per CTA: the second one's loads overlap the first one's arithmetic
-        if (grid > n_groups) grid = n_groups;
+        if (grid > 0x7FFFFFFF) return kErrTooLarge;
         const int nv = (gvec + kRowThreads - 1) / kRowThreads;
 #define MORB_ROW(NV) group_row_kernel<T, FMT, SF, NV><<<(unsigned)grid, kRowThreads, 0, st>>>(i4, o4, scales, gvec, n_groups, meta, meta_code)
         if (nv <= 1) MORB_ROW(1); else if (nv <= 2) MORB_ROW(2); else if (nv <= 4) MORB_ROW(4); else MORB_ROW(8);
