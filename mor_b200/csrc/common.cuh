@@ -307,6 +307,11 @@ __device__ __forceinline__ uint32_t umax16x2(uint32_t a, uint32_t b) {
     asm("max.u16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
     return r;
 }
+__device__ __forceinline__ uint32_t umin16x2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("min.u16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
 __device__ __forceinline__ uint32_t umax16x2_3(uint32_t a, uint32_t b, uint32_t c) { return __vimax3_u16x2(a, b, c); }
 __device__ __forceinline__ uint32_t smin16x2_3(uint32_t a, uint32_t b, uint32_t c) { return __vimin3_s16x2(a, b, c); }
 // packed maximum of the four magnitude words of a 16-byte vector of bf16

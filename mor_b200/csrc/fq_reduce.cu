@@ -11,6 +11,7 @@
 // reference's fmaxf ignores and never counts, show up as a packed maximum above
 // 0x7F80; a CTA that sees one redoes its part with float compares.
 #include "kernels.cuh"
+#include "tma.cuh"
 
 namespace morb {
 
@@ -134,22 +135,41 @@ __global__ void zero_scalars_kernel(ScalarsWs* ws) {
     ws->div_unsafe = 0u; ws->load_timeout = 0u;
 }
 
+// Flat tensor: every warp streams its own 4 KiB chunks through a private two-stage
+// shared-memory ring filled by bulk copies (two chunks per warp, both requested as the
+// warp starts; the grid covers the tensor once, so the hardware's CTA scheduler evens
+// out the SMs).
+constexpr int kFlatStages = 2, kFlatChunkVec = 256, kFlatWarps = kThreads / 32;
 template <typename T>
 __global__ void __launch_bounds__(kThreads) amax_nnz_flat_kernel(const typename T::vec_t* __restrict__ in,
                                                                  int64_t nvec, int64_t n_tail_elems,
                                                                  ScalarsWs* __restrict__ ws) {
-    Acc acc = acc_init();
-    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    extern __shared__ __align__(128) uint8_t s_ring[];  // [warp][stage][4 KiB]
+    __shared__ __align__(8) uint64_t s_bar[kFlatWarps][kFlatStages];
+    using V = typename T::vec_t;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int64_t n_warps = (int64_t)gridDim.x * kFlatWarps, gw = (int64_t)blockIdx.x * kFlatWarps + wid;
     const int64_t gtid = (int64_t)blockIdx.x * kThreads + threadIdx.x;
-    for (int64_t i = gtid; i < nvec; i += stride * 4) {
-        typename T::vec_t v[4];
+    const int64_t n_chunks = (nvec + kFlatChunkVec - 1) / kFlatChunkVec;
+    WarpStream<kFlatStages, kFlatChunkVec * 16> stream;
+    stream.start(s_ring + wid * (kFlatStages * kFlatChunkVec * 16), s_bar[wid], in, nvec * 16, gw, n_warps);
+    Acc acc = acc_init();
+    int st = 0;
+    for (int64_t c = gw; c < n_chunks; c += n_warps) {
+        const int64_t v0 = c * kFlatChunkVec;
+        const int nv = (int)(nvec - v0 < kFlatChunkVec ? nvec - v0 : kFlatChunkVec);
+        if (stream.acquire(st)) {
+            const V* chunk = reinterpret_cast<const V*>(stream.stage(st)) + lane;
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-            if (i + u * stride < nvec) v[u] = ld_keep(in + i + u * stride);
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-            if (i + u * stride < nvec) vec_acc_fast<T>(v[u], acc);
+            for (int r = 0; r < kFlatChunkVec / 32; ++r)
+                if (r * 32 + lane < nv) vec_acc_fast<T>(chunk[r * 32], acc);
+        } else {
+            for (int r = lane; r < nv; r += 32) vec_acc_fast<T>(ld_keep(in + v0 + r), acc);
+        }
+        stream.release(st, c + kFlatStages * n_warps);
+        st = st + 1 == kFlatStages ? 0 : st + 1;
     }
+    stream.drain();
     float amax = acc_amax<T>(acc);
     int nnz = acc_nnz<T>(acc);
     uint32_t flags = acc_flags<T>(acc, amax);
@@ -166,7 +186,11 @@ __global__ void __launch_bounds__(kThreads) amax_nnz_flat_kernel(const typename 
     cta_reduce_all(amax, nnz, flags);
     if (flags & kFlagNan) {  // a NaN somewhere in this CTA's part: float compares, as the reference does
         amax = 0.0f; nnz = 0;
-        for (int64_t i = gtid; i < nvec; i += stride) vec_acc_exact<T>(ld_keep(in + i), amax, nnz);
+        for (int64_t c = gw; c < n_chunks; c += n_warps) {
+            const int64_t v0 = c * kFlatChunkVec;
+            const int nv = (int)(nvec - v0 < kFlatChunkVec ? nvec - v0 : kFlatChunkVec);
+            for (int r = lane; r < nv; r += 32) vec_acc_exact<T>(ld_keep(in + v0 + r), amax, nnz);
+        }
         if (gtid < n_tail_elems) {
             float a;
             if constexpr (T::kBytesPerElem == 2) a = fabsf(u2f((uint32_t)reinterpret_cast<const uint16_t*>(in + nvec)[gtid] << 16));
@@ -305,12 +329,17 @@ int launch_zero_scalars(ScalarsWs* ws, cudaStream_t st) {
 int launch_amax_nnz_flat(const void* in, int is_fp32, int64_t n_elems, ScalarsWs* ws, cudaStream_t st) {
     const int epv = is_fp32 ? 4 : 8;
     const int64_t nvec = n_elems / epv, tail = n_elems % epv;
-    int64_t want = (nvec + kThreads * 4 - 1) / (kThreads * 4);
-    const int64_t cap = (int64_t)sm_count() * 8;
-    if (want > cap) want = cap;
+    constexpr int kRing = kFlatWarps * kFlatStages * kFlatChunkVec * 16;
+    constexpr int kChunksPerWarp = 2;
+    const int64_t n_chunks = (nvec + kFlatChunkVec - 1) / kFlatChunkVec;
+    int64_t want = (n_chunks + kFlatWarps * kChunksPerWarp - 1) / (kFlatWarps * kChunksPerWarp);
+    if (want > 0x7FFFFFFF) return kErrTooLarge;
     if (want < 1) want = 1;
-    if (is_fp32) amax_nnz_flat_kernel<Fp32><<<(int)want, kThreads, 0, st>>>(static_cast<const float4*>(in), nvec, tail, ws);
-    else amax_nnz_flat_kernel<Bf16><<<(int)want, kThreads, 0, st>>>(static_cast<const uint4*>(in), nvec, tail, ws);
+    static const cudaError_t a1 = cudaFuncSetAttribute(amax_nnz_flat_kernel<Fp32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing);
+    static const cudaError_t a2 = cudaFuncSetAttribute(amax_nnz_flat_kernel<Bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing);
+    if (a1 != cudaSuccess || a2 != cudaSuccess) return kErrLaunch;
+    if (is_fp32) amax_nnz_flat_kernel<Fp32><<<(int)want, kThreads, kRing, st>>>(static_cast<const float4*>(in), nvec, tail, ws);
+    else amax_nnz_flat_kernel<Bf16><<<(int)want, kThreads, kRing, st>>>(static_cast<const uint4*>(in), nvec, tail, ws);
     return check_launch();
 }
 

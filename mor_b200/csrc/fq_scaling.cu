@@ -458,87 +458,266 @@ rowgroup_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::v
 // lane, so the tensor is walked as a flat array of vectors (four in flight per lane, as
 // in the MX kernel); vector i belongs to unit i / LPU and to the group of `group_lanes`
 // lanes around it.  E8: power-of-two scale (ss_mode 2), else a binary32 scale per group.
+// One 16-byte vector of a lane in the flat layout (lane = vector index mod 32).  All 32
+// lanes of the warp call together; `valid` is false for lanes past the end of the tensor,
+// which pass a zero vector and store nothing.
+template <typename T, bool E8, bool STORE>
+__device__ __forceinline__ void rowgroup_small_vec(const typename T::vec_t& v, int64_t idx, bool valid,
+                                                   typename T::vec_t* __restrict__ out, float* __restrict__ block_err,
+                                                   int group_lanes, int ss, float gamax, bool fastdiv) {
+    constexpr int VW = T::kWordsPerVec;
+    constexpr int LPU = 64 / VW;
+    constexpr int kSlowDiv = (T::kBytesPerElem == 2) ? kDivBf16Any : kDivIeee;
+    const int p = threadIdx.x % LPU;
+    float eh[VW], el[VW];
+#pragma unroll
+    for (int k = 0; k < VW; ++k) eh[k] = el[k] = 0.0f;
+    typename T::vec_t o4;
+    bool done = false;
+    float a = -1.0f;
+    if constexpr (T::kBytesPerElem == 2) {
+        uint32_t pm = hmax_halves(umax16x2_vec(mag2(v.x), mag2(v.y), mag2(v.z), mag2(v.w)));
+        for (int o = group_lanes >> 1; o > 0; o >>= 1) pm = max(pm, __shfl_xor_sync(0xFFFFFFFFu, pm, o));
+        if constexpr (E8) {
+            // 448 / amax as a power of two straight from the amax pattern (amax >= 1e-35, normal, finite)
+            const int ea = (int)(pm >> 7);
+            const int e8 = 135 - ea - ((pm & 0x7Fu) > 0x60u ? 1 : 0);
+            const bool ok = fastdiv && (uint32_t)(ea - 12) < 243u && (uint32_t)(e8 + 119) <= 219u;
+            if (__all_sync(0xFFFFFFFFu, ok)) {
+                PathE8 pe;
+                pe.c.e8 = e8; pe.c.fast = true;
+                pe.c.up = u2f((uint32_t)(e8 + 127) << 23);
+                pe.c.down = u2f((uint32_t)(127 - e8) << 23);
+                pe.c.zero_bits = e8 < 0 ? ((uint32_t)(-e8) << 23) : 0u;
+                err_vec_split<T, PathE8, STORE, kDivBf16>(pe, v, o4, eh, el);
+                done = true;
+            }
+        }
+        // a NaN somewhere in the warp: every lane redoes its group with the NaN-ignoring float maximum
+        if (!done && !__any_sync(0xFFFFFFFFu, pm > 0x7F80u)) a = u2f(pm << 16);
+    }
+    if (!done) {
+        if (a < 0.0f) {
+            a = 0.0f;
+#pragma unroll
+            for (int k = 0; k < VW; ++k) {
+                float hi, lo;
+                T::unpack(v, k, hi, lo);
+                a = fmaxf(a, fmaxf(fabsf(hi), fabsf(lo)));
+            }
+            for (int o = group_lanes >> 1; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+        }
+        const float sf = scaling_factor(ss, gamax, a);
+        if (fastdiv) {
+            if constexpr (E8) err_vec_split<T, PathE8, STORE, kDivBf16>(PathE8{e8_consts(sf)}, v, o4, eh, el);
+            else err_vec_split<T, PathDiv, STORE, kDivBf16>(PathDiv{sf}, v, o4, eh, el);
+        } else {
+            if constexpr (E8) err_vec_split<T, PathE8, STORE, kSlowDiv>(PathE8{e8_consts(sf)}, v, o4, eh, el);
+            else err_vec_split<T, PathDiv, STORE, kSlowDiv>(PathDiv{sf}, v, o4, eh, el);
+        }
+    }
+    if constexpr (STORE) {
+        if (valid) st_stream(out + idx, o4);
+    }
+    float acc[VW];
+#pragma unroll
+    for (int k = 0; k < VW; ++k) acc[k] = __fadd_rn(eh[k], el[k]);
+    float s = logical_warp_sum<VW>(acc);                       // valid at p == 0 and p == LPU / 2
+    const float s1 = __shfl_down_sync(0xFFFFFFFFu, s, LPU / 2);
+    s = __fadd_rn(s, s1);
+    if (p == 0 && valid) block_err[idx / LPU] = s;
+}
+
 template <typename T, bool E8, bool STORE>
 __global__ void __launch_bounds__(256)
 rowgroup_small_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_t* __restrict__ out, int64_t nvec,
                       int group_lanes, int ss, float* __restrict__ block_err, const ScalarsWs* __restrict__ ws,
                       const float* __restrict__ ext_gamax, int skip_if_fallback) {
-    constexpr int VW = T::kWordsPerVec;
-    constexpr int LPU = 64 / VW;
-    constexpr int kSlowDiv = (T::kBytesPerElem == 2) ? kDivBf16Any : kDivIeee;
     if (skip_if_fallback && ws->fallback) return;
     const float gamax = read_gamax(ws, ext_gamax);
     const bool fastdiv = fast_div_ok<T>(ws);
-    const int p = threadIdx.x % LPU;
     const int64_t stride = (int64_t)gridDim.x * 256;
-    auto one = [&](const typename T::vec_t& v, int64_t idx) {
-        float eh[VW], el[VW];
-#pragma unroll
-        for (int k = 0; k < VW; ++k) eh[k] = el[k] = 0.0f;
-        typename T::vec_t o4;
-        bool done = false;
-        float a = -1.0f;
-        if constexpr (T::kBytesPerElem == 2) {
-            uint32_t pm = hmax_halves(umax16x2_vec(mag2(v.x), mag2(v.y), mag2(v.z), mag2(v.w)));
-            for (int o = group_lanes >> 1; o > 0; o >>= 1) pm = max(pm, __shfl_xor_sync(0xFFFFFFFFu, pm, o));
-            if constexpr (E8) {
-                // 448 / amax as a power of two straight from the amax pattern (amax >= 1e-35, normal, finite)
-                const int ea = (int)(pm >> 7);
-                const int e8 = 135 - ea - ((pm & 0x7Fu) > 0x60u ? 1 : 0);
-                const bool ok = fastdiv && (uint32_t)(ea - 12) < 243u && (uint32_t)(e8 + 119) <= 219u;
-                if (__all_sync(0xFFFFFFFFu, ok)) {
-                    PathE8 pe;
-                    pe.c.e8 = e8; pe.c.fast = true;
-                    pe.c.up = u2f((uint32_t)(e8 + 127) << 23);
-                    pe.c.down = u2f((uint32_t)(127 - e8) << 23);
-                    pe.c.zero_bits = e8 < 0 ? ((uint32_t)(-e8) << 23) : 0u;
-                    err_vec_split<T, PathE8, STORE, kDivBf16>(pe, v, o4, eh, el);
-                    done = true;
-                }
-            }
-            // a NaN somewhere in the warp: every lane redoes its group with the NaN-ignoring float maximum
-            if (!done && !__any_sync(0xFFFFFFFFu, pm > 0x7F80u)) a = u2f(pm << 16);
-        }
-        if (!done) {
-            if (a < 0.0f) {
-                a = 0.0f;
-#pragma unroll
-                for (int k = 0; k < VW; ++k) {
-                    float hi, lo;
-                    T::unpack(v, k, hi, lo);
-                    a = fmaxf(a, fmaxf(fabsf(hi), fabsf(lo)));
-                }
-                for (int o = group_lanes >> 1; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
-            }
-            const float sf = scaling_factor(ss, gamax, a);
-            if (fastdiv) {
-                if constexpr (E8) err_vec_split<T, PathE8, STORE, kDivBf16>(PathE8{e8_consts(sf)}, v, o4, eh, el);
-                else err_vec_split<T, PathDiv, STORE, kDivBf16>(PathDiv{sf}, v, o4, eh, el);
-            } else {
-                if constexpr (E8) err_vec_split<T, PathE8, STORE, kSlowDiv>(PathE8{e8_consts(sf)}, v, o4, eh, el);
-                else err_vec_split<T, PathDiv, STORE, kSlowDiv>(PathDiv{sf}, v, o4, eh, el);
-            }
-        }
-        if constexpr (STORE) st_stream(out + idx, o4);
-        float acc[VW];
-#pragma unroll
-        for (int k = 0; k < VW; ++k) acc[k] = __fadd_rn(eh[k], el[k]);
-        float s = logical_warp_sum<VW>(acc);                       // valid at p == 0 and p == LPU / 2
-        const float s1 = __shfl_down_sync(0xFFFFFFFFu, s, LPU / 2);
-        s = __fadd_rn(s, s1);
-        if (p == 0) block_err[idx / LPU] = s;
-    };
+    const int lane = threadIdx.x & 31;
     int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
-    // nvec is a multiple of 32 (rows of 128-column units), so whole warps enter or leave together
-    for (; i + 3 * stride < nvec; i += 4 * stride) {
+    const typename T::vec_t zero{};
+    // trip counts depend on the warp's first vector only, so all 32 lanes stay together
+    for (; i - lane + 3 * stride + 31 < nvec; i += 4 * stride) {
         typename T::vec_t v[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) v[u] = ld_stream(in + i + u * stride);
 #pragma unroll
-        for (int u = 0; u < 4; ++u) one(v[u], i + u * stride);
+        for (int u = 0; u < 4; ++u)
+            rowgroup_small_vec<T, E8, STORE>(v[u], i + u * stride, true, out, block_err, group_lanes, ss, gamax, fastdiv);
     }
-    for (; i < nvec; i += stride) one(ld_stream(in + i), i);
+    for (; i - lane < nvec; i += stride) {
+        const bool valid = i < nvec;
+        rowgroup_small_vec<T, E8, STORE>(valid ? ld_stream(in + i) : zero, i, valid, out, block_err, group_lanes, ss,
+                                         gamax, fastdiv);
+    }
 }
+
+// bf16, power-of-two scale, groups of 8..64 elements: every lane owns the 128 contiguous
+// bytes (64 elements, 32 words) that one warp of the reference's 64-thread CTA covers.
+// A warp streams 4 KiB chunks through its private shared-memory ring (bulk copies in, a
+// bulk copy out); lane l reads its eight vectors in the order k = p ^ (l & 7), which
+// makes every 16-byte shared access conflict-free, and keeps them in registers by
+// position p.  Groups are whole runs of positions, so the group maxima need no shuffle,
+// and the reference's shuffle tree over 32 words (t += t+16, +8, +4, +2, +1) pairs
+// vector k with k ^ 4, ^ 2, ^ 1 and then the words inside a vector: float addition is
+// commutative, so pairing positions p with p ^ 4, ^ 2, ^ 1 adds exactly the same pairs.
+// The second warp's sum of a unit arrives with one shuffle from the neighbouring lane.
+// Anything outside the short forms' domain (tensor not screened for the 4-instruction
+// quotient, group amax or scale exponent out of range, NaN) sends the warp's chunk
+// through rowgroup_small_vec instead.
+constexpr int kLaneStages = 2, kLaneChunkVec = 256, kLaneWarps = 8;
+
+template <bool NEG, bool HASZERO, bool STORE>
+__device__ __forceinline__ float lane_e8_word(uint32_t w, float up, float down, uint32_t zero_bits, uint32_t& ow) {
+    const float hi = bf16_hi(w), lo = bf16_lo(w);
+    float qh, ql;
+    quant_dequant_pair<kE4M3, true>(__fmul_rn(hi, up), __fmul_rn(lo, up), qh, ql);
+    float dh = __fmul_rn(qh, down), dl = __fmul_rn(ql, down);
+    if constexpr (NEG) {  // a zero code under a scale below one comes back as +-2^(-e8-127)
+        dh = qh == 0.0f ? u2f((f2u(qh) & 0x80000000u) | zero_bits) : dh;
+        dl = ql == 0.0f ? u2f((f2u(ql) & 0x80000000u) | zero_bits) : dl;
+    }
+    float eh = fabsf(div_by_bf16(__fsub_rn(dh, hi), hi, rcp_fast(hi)));
+    float el = fabsf(div_by_bf16(__fsub_rn(dl, lo), lo, rcp_fast(lo)));
+    if constexpr (HASZERO) {  // zeros are skipped by the reference: no error, written back as +0
+        const bool zh = hi == 0.0f, zl = lo == 0.0f;
+        eh = zh ? 0.0f : eh; el = zl ? 0.0f : el;
+        dh = zh ? 0.0f : dh; dl = zl ? 0.0f : dl;
+    }
+    if constexpr (STORE) ow = pack_bf16_trunc(dh, dl);
+    return __fadd_rn(eh, el);
+}
+
+template <int GVS, bool NEG, bool HASZERO, bool STORE>
+__device__ __forceinline__ float lane_e8_segment(uint4 (&v)[8], const float (&up)[8], const float (&down)[8],
+                                                 const uint32_t (&zb)[8]) {
+    float e[4][4];
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {  // vector p and its partner p + 4 of the first tree level (t += t + 16)
+        const int g = p >> GVS, h = (p + 4) >> GVS;
+        e[p][0] = __fadd_rn(lane_e8_word<NEG, HASZERO, STORE>(v[p].x, up[g], down[g], zb[g], v[p].x),
+                            lane_e8_word<NEG, HASZERO, STORE>(v[p + 4].x, up[h], down[h], zb[h], v[p + 4].x));
+        e[p][1] = __fadd_rn(lane_e8_word<NEG, HASZERO, STORE>(v[p].y, up[g], down[g], zb[g], v[p].y),
+                            lane_e8_word<NEG, HASZERO, STORE>(v[p + 4].y, up[h], down[h], zb[h], v[p + 4].y));
+        e[p][2] = __fadd_rn(lane_e8_word<NEG, HASZERO, STORE>(v[p].z, up[g], down[g], zb[g], v[p].z),
+                            lane_e8_word<NEG, HASZERO, STORE>(v[p + 4].z, up[h], down[h], zb[h], v[p + 4].z));
+        e[p][3] = __fadd_rn(lane_e8_word<NEG, HASZERO, STORE>(v[p].w, up[g], down[g], zb[g], v[p].w),
+                            lane_e8_word<NEG, HASZERO, STORE>(v[p + 4].w, up[h], down[h], zb[h], v[p + 4].w));
+    }
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        e[0][w] = __fadd_rn(e[0][w], e[2][w]);                                    // t += t + 8
+        e[1][w] = __fadd_rn(e[1][w], e[3][w]);
+        e[0][w] = __fadd_rn(e[0][w], e[1][w]);                                    // t += t + 4
+    }
+    return __fadd_rn(__fadd_rn(e[0][0], e[0][2]), __fadd_rn(e[0][1], e[0][3]));   // t += t + 2, t += t + 1
+}
+
+template <int GVS, bool STORE>
+__global__ void __launch_bounds__(32 * kLaneWarps, 3)
+rowgroup_lane_e8_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, int64_t nvec, int ss,
+                        float* __restrict__ block_err, const ScalarsWs* __restrict__ ws,
+                        const float* __restrict__ ext_gamax, int skip_if_fallback) {
+    if (skip_if_fallback && ws->fallback) return;
+    extern __shared__ __align__(128) uint8_t s_ring[];  // [warp][stage][4 KiB]
+    __shared__ __align__(8) uint64_t s_bar[kLaneWarps][kLaneStages];
+    constexpr int GV = 1 << GVS, NG = 8 >> GVS;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, sw = lane & 7;
+    const int64_t n_warps = (int64_t)gridDim.x * kLaneWarps, gw = (int64_t)blockIdx.x * kLaneWarps + wid;
+    WarpStream<kLaneStages, kLaneChunkVec * 16> stream;
+    stream.start(s_ring + wid * (kLaneStages * kLaneChunkVec * 16), s_bar[wid], in, nvec * 16, gw, n_warps);
+    const float gamax = read_gamax(ws, ext_gamax);
+    const bool fastdiv = fast_div_ok<Bf16>(ws);
+    const int64_t n_chunks = (nvec + kLaneChunkVec - 1) / kLaneChunkVec;
+    bool stored = false;
+    int st = 0;
+    for (int64_t c = gw; c < n_chunks; c += n_warps) {
+        const int64_t v0 = c * kLaneChunkVec;
+        const int nv = (int)(nvec - v0 < kLaneChunkVec ? nvec - v0 : kLaneChunkVec);  // a multiple of 16
+        const bool staged = stream.acquire(st);
+        uint4* chunk = reinterpret_cast<uint4*>(const_cast<uint8_t*>(stream.stage(st)));
+        const bool mine = lane * 8 < nv;  // this lane's 128 bytes are inside the tensor
+        bool fast = staged && fastdiv;
+        uint4 v[8];
+        float up[8], down[8];
+        uint32_t zb[8];
+        bool neg = false, has_zero = false;
+        if (fast) {
+            uint4* seg = chunk + lane * 8;
+            uint32_t pm[8], mn = 0xFFFFFFFFu;
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                v[p] = seg[p ^ sw];
+                const uint32_t m0 = mag2(v[p].x), m1 = mag2(v[p].y), m2 = mag2(v[p].z), m3 = mag2(v[p].w);
+                pm[p] = umax16x2_vec(m0, m1, m2, m3);
+                mn = umin16x2(mn, umin16x2(umin16x2(m0, m1), umin16x2(m2, m3)));
+            }
+            has_zero = (mn & 0xFFFFu) == 0u || (mn >> 16) == 0u;
+            bool ok = true;
+#pragma unroll
+            for (int g = 0; g < NG; ++g) {
+                uint32_t m = pm[g * GV];
+#pragma unroll
+                for (int q = 1; q < GV; ++q) m = umax16x2(m, pm[g * GV + q]);
+                m = hmax_halves(m);
+                // 448 / amax as a power of two straight from the amax pattern (amax >= 1e-35, normal, finite)
+                const int ea = (int)(m >> 7);
+                const int e8 = 135 - ea - ((m & 0x7Fu) > 0x60u ? 1 : 0);
+                ok = ok && (uint32_t)(ea - 12) < 243u && (uint32_t)(e8 + 119) <= 219u;
+                up[g] = u2f((uint32_t)(e8 + 127) << 23);
+                down[g] = u2f((uint32_t)(127 - e8) << 23);
+                zb[g] = e8 < 0 ? ((uint32_t)(-e8) << 23) : 0u;
+                neg = neg || e8 < 0;
+            }
+            fast = __all_sync(0xFFFFFFFFu, ok || !mine);
+        }
+        if (fast) {
+            neg = __any_sync(0xFFFFFFFFu, neg);
+            has_zero = __any_sync(0xFFFFFFFFu, has_zero);
+            float s;
+            if (neg) {
+                s = has_zero ? lane_e8_segment<GVS, true, true, STORE>(v, up, down, zb)
+                             : lane_e8_segment<GVS, true, false, STORE>(v, up, down, zb);
+            } else {
+                s = has_zero ? lane_e8_segment<GVS, false, true, STORE>(v, up, down, zb)
+                             : lane_e8_segment<GVS, false, false, STORE>(v, up, down, zb);
+            }
+            const float s1 = __shfl_down_sync(0xFFFFFFFFu, s, 1);  // the unit's second warp
+            if ((lane & 1) == 0 && mine) block_err[v0 / 16 + (lane >> 1)] = __fadd_rn(s, s1);
+            if constexpr (STORE) {
+                uint4* seg = chunk + lane * 8;
+#pragma unroll
+                for (int p = 0; p < 8; ++p) seg[p ^ sw] = v[p];
+                fence_async_shared();
+                __syncwarp();
+                if (lane == 0) {
+                    bulk_store(out + v0, chunk, (uint32_t)nv * 16u);
+                    bulk_commit();
+                    stored = true;
+                }
+            }
+        } else {
+            const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+            for (int r = 0; r * 32 < nv; ++r) {
+                const int64_t idx = v0 + r * 32 + lane;
+                const bool valid = idx < nvec;
+                const uint4 x = !valid ? zero : (staged ? chunk[r * 32 + lane] : ld_stream(in + idx));
+                rowgroup_small_vec<Bf16, true, STORE>(x, idx, valid, out, block_err, GV, ss, gamax, fastdiv);
+            }
+        }
+        // a stage is refilled only after the copy engine has read the results out of it
+        if (STORE && lane == 0 && stored && c + kLaneStages * n_warps < n_chunks) bulk_wait_reads();
+        stream.release(st, c + kLaneStages * n_warps);
+        st = st + 1 == kLaneStages ? 0 : st + 1;
+    }
+    if (STORE && lane == 0 && stored) bulk_wait_reads();
+    stream.drain();
+}
+
 
 // ---------------------------------------------------------------------------------
 // k x 1 column groups; reference CTA = 32 x 16 threads over 64 columns x k rows
@@ -682,13 +861,13 @@ finalize_kernel(const float* __restrict__ block_err, int64_t n_err, int stride, 
 
 // Long error arrays: the 1024 / stride sequential sums ("chains": what thread j * stride of
 // the reference's one CTA adds up, entries j, j + period, j + 2 * period, ... in order) do not
-// depend on one another, so they are spread over CTAs, eight chains each.  All 256 threads of
-// a CTA load (32 rows x 8 chains per step, eight steps in flight) and stage 256 rows in shared
-// memory; eight lanes then add their chain's 256 entries in order while the next 256 rows are
+// depend on one another, so they are spread over CTAs, eight chains each.  All 1024 threads of
+// a CTA load (128 rows x 8 chains per step, eight steps in flight) and stage 1024 rows in shared
+// memory; eight lanes then add their chain's 1024 entries in order while the next 1024 rows are
 // already on their way.  Rows past the end read as +0.0, which leaves a non-negative sum as it
 // is.  finalize_kernel then runs on the `period` chain sums with the same stride.
-constexpr int kChainsPerCta = 8, kChainRows = 256;
-__global__ void __launch_bounds__(256) chain_sum_kernel(const float* __restrict__ block_err, int64_t n_err, int period,
+constexpr int kChainsPerCta = 8, kChainRows = 1024, kChainThreads = 1024;
+__global__ void __launch_bounds__(kChainThreads) chain_sum_kernel(const float* __restrict__ block_err, int64_t n_err, int period,
                                                         float* __restrict__ chain_sums) {
     __shared__ float s_rows[kChainRows][kChainsPerCta];
     const int ch = threadIdx.x & 7, ry = threadIdx.x >> 3;
@@ -698,7 +877,7 @@ __global__ void __launch_bounds__(256) chain_sum_kernel(const float* __restrict_
     auto load = [&](int64_t c0) {
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-            const int64_t idx = (c0 + ry + 32 * u) * period + j;
+            const int64_t idx = (c0 + ry + (kChainThreads / 8) * u) * period + j;
             v[u] = (j < period && idx < n_err) ? __ldg(block_err + idx) : 0.0f;
         }
     };
@@ -706,7 +885,7 @@ __global__ void __launch_bounds__(256) chain_sum_kernel(const float* __restrict_
     float acc = 0.0f;
     for (int64_t c0 = 0; c0 < rows; c0 += kChainRows) {
 #pragma unroll
-        for (int u = 0; u < 8; ++u) s_rows[ry + 32 * u][ch] = v[u];
+        for (int u = 0; u < 8; ++u) s_rows[ry + (kChainThreads / 8) * u][ch] = v[u];
         __syncthreads();
         if (c0 + kChainRows < rows) load(c0 + kChainRows);
         if (threadIdx.x < kChainsPerCta) {
@@ -790,13 +969,50 @@ int launch_rowgroup_t(const ScalingArgs& a, bool store, bool skip, cudaStream_t 
         int64_t g2 = (nvec + 1023) / 1024;
         if (g2 > cap) g2 = cap;
         if (g2 < 1) g2 = 1;
+        if constexpr (T::kBytesPerElem == 2) {
+            if (mode == 2) {  // power-of-two scale: the lane-per-128-bytes kernel
+                constexpr int kRing = kLaneWarps * kLaneStages * kLaneChunkVec * 16;
+                constexpr int kChunksPerWarp = 2;
+                const int64_t n_chunks = (nvec + kLaneChunkVec - 1) / kLaneChunkVec;
+                int64_t g3 = (n_chunks + kLaneWarps * kChunksPerWarp - 1) / (kLaneWarps * kChunksPerWarp);
+                if (g3 > 0x7FFFFFFF) return kErrTooLarge;
+                if (g3 < 1) g3 = 1;
+#define MORB_LANE(G, S)                                                                                             \
+    do {                                                                                                            \
+        static const cudaError_t attr = cudaFuncSetAttribute(rowgroup_lane_e8_kernel<G, S>,                         \
+                                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kRing);  \
+        if (attr != cudaSuccess) return kErrLaunch;                                                                 \
+        rowgroup_lane_e8_kernel<G, S><<<(unsigned)g3, 32 * kLaneWarps, kRing, st>>>(                                \
+            in, out, nvec, a.ss_mode, a.block_err, a.ws, a.ext_gamax, skip ? 1 : 0);                                \
+    } while (0)
+#define MORB_LANE_G(S)                                                                                              \
+    do {                                                                                                            \
+        if (group_lanes == 1) MORB_LANE(0, S);                                                                      \
+        else if (group_lanes == 2) MORB_LANE(1, S);                                                                 \
+        else if (group_lanes == 4) MORB_LANE(2, S);                                                                 \
+        else MORB_LANE(3, S);                                                                                       \
+    } while (0)
+                if (store) MORB_LANE_G(true); else MORB_LANE_G(false);
+#undef MORB_LANE_G
+#undef MORB_LANE
+                return check_launch();
+            }
+        }
 #define MORB_SMALL(E, S) rowgroup_small_kernel<T, E, S><<<(unsigned)g2, 256, 0, st>>>(in, out, nvec, group_lanes, a.ss_mode, a.block_err, a.ws, a.ext_gamax, skip ? 1 : 0)
         if (mode == 2) { if (store) MORB_SMALL(true, true); else MORB_SMALL(true, false); }
         else { if (store) MORB_SMALL(false, true); else MORB_SMALL(false, false); }
 #undef MORB_SMALL
         return check_launch();
     }
-#define MORB_GO(M, S) rowgroup_err_cast_kernel<T, M, S><<<(unsigned)grid, 256, 0, st>>>(in, out, n_units, span / EPV, group_lanes, a.ss_mode, a.block_amax, a.block_err, a.ws, a.ext_gamax, skip ? 1 : 0)
+    // few, long-running warps (two rows each): CTAs are kept small enough that the grid is several
+    // times the number of SMs, otherwise the SMs that get one CTA more than the others set the time
+    int wpc = 8;
+    if (n_warps / wpc < (int64_t)sm_count() * 8) wpc = 4;
+    grid = (n_warps + wpc - 1) / wpc;
+    if (grid > cap * (8 / wpc)) grid = cap * (8 / wpc);
+    if (grid < 1) grid = 1;
+    const int threads = 32 * wpc;
+#define MORB_GO(M, S) rowgroup_err_cast_kernel<T, M, S><<<(unsigned)grid, threads, 0, st>>>(in, out, n_units, span / EPV, group_lanes, a.ss_mode, a.block_amax, a.block_err, a.ws, a.ext_gamax, skip ? 1 : 0)
     if (mode == 2) { if (store) MORB_GO(2, true); else MORB_GO(2, false); }
     else if (mode == 1) { if (store) MORB_GO(1, true); else MORB_GO(1, false); }
     else { if (store) MORB_GO(0, true); else MORB_GO(0, false); }
@@ -841,7 +1057,7 @@ int launch_finalize(const ScalingArgs& a, const long long* ext_nnz, int32_t* met
     if (n > 2 * kMaxChunk) {  // spread the independent sequential sums over CTAs first
         const int period = 1024 / a.err_slot_stride;
         float* chains = reinterpret_cast<float*>(reinterpret_cast<char*>(a.ws) + kChainSumsOffset);
-        chain_sum_kernel<<<period / kChainsPerCta, 256, 0, st>>>(err, n, period, chains);
+        chain_sum_kernel<<<period / kChainsPerCta, kChainThreads, 0, st>>>(err, n, period, chains);
         const int rc = check_launch();
         if (rc) return rc;
         err = chains;

@@ -41,6 +41,17 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
+// untiled bulk copy shared -> global; the issuing thread commits it to a bulk group and later
+// waits until the group's shared-memory reads are done (the buffer may then be reused or freed)
+__device__ __forceinline__ void bulk_store(void* dst, const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                 ::"l"(dst), "r"(smem_u32(src)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_reads() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// orders a thread's ordinary shared-memory writes before later reads by the copy engine
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 // A warp's private stream of fixed-size chunks of a contiguous global array through
 // shared memory: STAGES buffers, one mbarrier each, bulk copies issued by lane 0.  The
 // warp takes chunks first, first + step, ...; while it works on one, the next STAGES - 1

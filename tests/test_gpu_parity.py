@@ -249,6 +249,32 @@ def test_channel_scaling_row_groups(by, ss):
         assert_same(H.channel_scaling(x, 1, by, thr, ss), exp, f"1x{by} ss {ss} thr {thr}")
 
 
+@pytest.mark.parametrize("by", [8, 16, 32, 64])
+@pytest.mark.parametrize("kind", ["dense", "dense_large", "sparse_large", "tiny_rows"])
+@pytest.mark.parametrize("rows,cols", [(33, 384), (520, 640)])
+def test_channel_scaling_small_groups_power_of_two(by, kind, rows, cols):
+    """1 x k groups with k < 128 and a power-of-two scale (ss_mode 2): tensors without zeros, groups whose
+    amax exceeds the format maximum (scale below one), ragged ends (vector count 16 mod 32, partial chunks)."""
+    import gpu_harness as H
+    g = torch.Generator().manual_seed(by + rows)
+    t = torch.randn(rows, cols, generator=g)
+    t = torch.where(t == 0, torch.ones_like(t), t)
+    if kind in ("dense_large", "sparse_large"):
+        t = t * torch.where(torch.rand(rows, cols, generator=g) < 0.3, 3000.0, 1.0)
+    if kind == "sparse_large":
+        t = torch.where(torch.rand(rows, cols, generator=g) < 0.1, 0.0, t)
+    if kind == "tiny_rows":
+        t[::3] *= 1e-30     # group maxima below 1e-35 * 2^12 leave the short form's domain
+    x = t.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    for thr in (0.045, 3e38):
+        oracle.clear_assert_flags()
+        exp = dict(zip(("out", "meta", "gamax", "gnnz", "gerr"), oracle.channel_scaling(x, 1, by, thr, 2)))
+        if oracle.assert_flags():
+            continue
+        exp["meta"] = np.array([exp["meta"]])
+        assert_same(H.channel_scaling(x, 1, by, thr, 2), exp, f"{kind} {rows}x{cols} 1x{by} thr {thr}")
+
+
 @pytest.mark.parametrize("bx,rows", [(256, 256), (64, 256), (16, 64), (128, 384)])
 @pytest.mark.parametrize("ss", [1, 2, 3, 4])
 def test_channel_scaling_column_groups(bx, rows, ss):
