@@ -889,12 +889,21 @@ __global__ void __launch_bounds__(kChainThreads) chain_sum_kernel(const float* _
         __syncthreads();
         if (c0 + kChainRows < rows) load(c0 + kChainRows);
         if (threadIdx.x < kChainsPerCta) {
-            for (int r = 0; r < kChainRows; r += 8) {
-                float x[8];
+            // the additions form one dependent chain; the shared-memory loads of the next 16 rows
+            // are issued before the current 16 are added, so only the adds' own latency remains
+            float x[16], y[16];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) x[u] = s_rows[r + u][threadIdx.x];
+            for (int u = 0; u < 16; ++u) x[u] = s_rows[u][threadIdx.x];
+            for (int r = 0; r < kChainRows; r += 32) {
 #pragma unroll
-                for (int u = 0; u < 8; ++u) acc = __fadd_rn(acc, x[u]);
+                for (int u = 0; u < 16; ++u) y[u] = s_rows[r + 16 + u][threadIdx.x];
+#pragma unroll
+                for (int u = 0; u < 16; ++u) acc = __fadd_rn(acc, x[u]);
+                const int rn = r + 32 < kChainRows ? r + 32 : 0;   // the last reload is not used
+#pragma unroll
+                for (int u = 0; u < 16; ++u) x[u] = s_rows[rn + u][threadIdx.x];
+#pragma unroll
+                for (int u = 0; u < 16; ++u) acc = __fadd_rn(acc, y[u]);
             }
         }
         __syncthreads();

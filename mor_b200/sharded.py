@@ -129,13 +129,17 @@ class ShardedScaling:
     def __call__(self, x: torch.Tensor, out: torch.Tensor, ss_mode: int, threshold: float) -> ScalingResult:
         b = self.backend
         b.amax_nnz(x, self.amax, self.nnz)
+        nnz_done = None
         if self.world > 1:
-            dist.all_reduce(self.amax, op=dist.ReduceOp.MAX, group=self.group)
-            dist.all_reduce(self.nnz, op=dist.ReduceOp.SUM, group=self.group)
+            # the cast needs the global amax only: the non-zero count is summed while the cast runs
+            amax_done = dist.all_reduce(self.amax, op=dist.ReduceOp.MAX, group=self.group, async_op=True)
+            nnz_done = dist.all_reduce(self.nnz, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+            amax_done.wait()
             self.collectives += 2
         b.cast(x, out, ss_mode, self.amax, self.local_err)
         if self.world > 1:
             dist.all_gather_into_tensor(self.all_err, self.local_err.clone(), group=self.group)
+            nnz_done.wait()
             self.collectives += 1
         b.finalize(self.all_err, self.nnz, threshold, self.meta, self.gerr)
         b.fallback(x, out, self.meta)
