@@ -86,6 +86,7 @@ __device__ __forceinline__ void cast_pair(int fmt, float hi, float lo, float s, 
 // go from registers straight to global memory with 16-byte stores.
 
 constexpr int kTileBytes = 128 * 128 * 2;
+constexpr int kErrTableEntries = 2560;  // 20 rows of 128 magnitude patterns: 30 binades less the 11 folded ones, and slack
 template <int SF>
 struct ErrCtx {
     const float* lut4;  // SF_FP32: RN(dequant(code) / s) tables
@@ -96,7 +97,8 @@ struct ErrCtx {
 
 // |q4/x - 1| and |q5/x - 1| for one element (ref: 504-541); zero elements add nothing
 template <int SF, bool SAFE>
-__device__ __forceinline__ void word_errors_fast(const ErrCtx<SF>& e, float hi, float lo, float& e4, float& e5) {
+__device__ __forceinline__ void pair_errors(const ErrCtx<SF>& e, float hi, float lo, float& e4h, float& e4l,
+                                            float& e5h, float& e5l) {
     float q4h, q4l, q5h, q5l;
     if constexpr (SF == kSfFp32) {
         const uint32_t c4 = cvt_codes<kE4M3>(__fmul_rn(hi, e.s4), __fmul_rn(lo, e.s4));
@@ -107,7 +109,6 @@ __device__ __forceinline__ void word_errors_fast(const ErrCtx<SF>& e, float hi, 
         sqdd_e8_pair_auto<kE4M3>(hi, lo, e.c4, q4h, q4l);
         sqdd_e8_pair_auto<kE5M2>(hi, lo, e.c5, q5h, q5l);
     }
-    float e4h = 0.0f, e4l = 0.0f, e5h = 0.0f, e5l = 0.0f;
     if constexpr (SAFE) {
         // branch-free: a zero element yields NaN garbage that the selects discard
         const float rh = rcp_fast(hi), rl = rcp_fast(lo);
@@ -128,22 +129,27 @@ __device__ __forceinline__ void word_errors_fast(const ErrCtx<SF>& e, float hi, 
         e4h = zh ? 0.0f : e4h; e5h = zh ? 0.0f : e5h;
         e4l = zl ? 0.0f : e4l; e5l = zl ? 0.0f : e5l;
     }
+}
+template <int SF, bool SAFE>
+__device__ __forceinline__ void word_errors_fast(const ErrCtx<SF>& e, float hi, float lo, float& e4, float& e5) {
+    float e4h, e4l, e5h, e5l;
+    pair_errors<SF, SAFE>(e, hi, lo, e4h, e4l, e5h, e5l);
     e4 = __fadd_rn(e4h, e4l);
     e5 = __fadd_rn(e5h, e5l);
 }
 
 template <int FMT>
-__device__ __forceinline__ void fill_lut16(uint16_t* lut, float s, int tid) {
+__device__ __forceinline__ void fill_lut16(uint16_t* lut, float s, int tid, int nthreads) {
     constexpr int NCODES = (FMT == kE2M3) ? 64 : 256;
-    for (int c = tid; c < NCODES; c += 128) {
+    for (int c = tid; c < NCODES; c += nthreads) {
         float q = h_lo_to_f32(codes_to_h2<FMT>((uint32_t)c));
         if (FMT == kE2M3 && q == 0.0f) q = 0.0f;  // the custom cast returns +0
         lut[c] = (uint16_t)f32_to_bf16_bits(__fdiv_rn(q, s));
     }
 }
 template <int FMT>
-__device__ __forceinline__ void fill_lut32t(float* lut, float s, int tid) {
-    for (int c = tid; c < 256; c += 128) lut[c] = __fdiv_rn(h_lo_to_f32(codes_to_h2<FMT>((uint32_t)c)), s);
+__device__ __forceinline__ void fill_lut32t(float* lut, float s, int tid, int nthreads) {
+    for (int c = tid; c < 256; c += nthreads) lut[c] = __fdiv_rn(h_lo_to_f32(codes_to_h2<FMT>((uint32_t)c)), s);
 }
 template <int FMT>
 __device__ __forceinline__ uint32_t lut_word(const uint16_t* lut, uint32_t w, float s) {
@@ -157,19 +163,35 @@ __device__ __forceinline__ uint32_t e8_word(uint32_t w, const E8Consts& c) {
     return c.fast ? pack_bf16_trunc(rh, rl) : pack_bf16(rh, rl);
 }
 
-template <int SF>
-__global__ void __launch_bounds__(128)
-fq_tile128_kernel(const __grid_constant__ CUtensorMap tmap, uint4* __restrict__ out, int32_t* __restrict__ meta,
-                  int64_t cols_vec, int blocks_x, float clamp, int qmode, int dyn_mode) {
-    extern __shared__ __align__(128) uint8_t s_tile[];  // [4 strips][128 rows][64 B]
+// VW = words of a strip row per thread: 4 (16-byte accesses, 128 threads) or 2 (8-byte accesses,
+// 256 threads: the variant for the relative-error criterion, whose error table halves the number
+// of CTAs an SM can hold).  Either way a thread owns VW logical threads of the reference's CTA.
+template <int VW> struct TileVec;
+template <> struct TileVec<4> { using type = uint4; };
+template <> struct TileVec<2> { using type = uint2; };
+template <int VW> __device__ __forceinline__ void tile_unpack(const typename TileVec<VW>::type& v, uint32_t (&w)[VW]);
+template <> __device__ __forceinline__ void tile_unpack<4>(const uint4& v, uint32_t (&w)[4]) { w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w; }
+template <> __device__ __forceinline__ void tile_unpack<2>(const uint2& v, uint32_t (&w)[2]) { w[0] = v.x; w[1] = v.y; }
+template <int VW> __device__ __forceinline__ typename TileVec<VW>::type tile_pack(const uint32_t (&w)[VW]);
+template <> __device__ __forceinline__ uint4 tile_pack<4>(const uint32_t (&w)[4]) { return make_uint4(w[0], w[1], w[2], w[3]); }
+template <> __device__ __forceinline__ uint2 tile_pack<2>(const uint32_t (&w)[2]) { return make_uint2(w[0], w[1]); }
+
+template <int SF, int VW>
+__global__ void __launch_bounds__(512 / VW)
+fq_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename TileVec<VW>::type* __restrict__ out, int32_t* __restrict__ meta,
+                  int64_t cols_vec, int blocks_x, float clamp, int qmode, int dyn_mode, int table_entries) {
+    extern __shared__ __align__(128) uint8_t s_tile[];  // [4 strips][128 rows][64 B], then the error table
     __shared__ __align__(8) uint64_t s_bar;
-    __shared__ float s_red[2][4];
     __shared__ float s_w4[16], s_w5[16];
     __shared__ float s_tot[2];
     __shared__ __align__(16) float s_lut4[256];
     __shared__ __align__(16) float s_lut5[256];
     uint16_t* s_lut16 = reinterpret_cast<uint16_t*>(s_lut4);  // the cast table reuses the error tables' space
-    const int tid = threadIdx.x, a = tid & 3, ty = tid >> 2, lane = tid & 31, wid = tid >> 5;
+    using V = typename TileVec<VW>::type;
+    constexpr int LPR = 16 / VW;        // lanes per 64-byte strip row
+    constexpr int NT = 32 * LPR;        // threads: 32 rows x LPR lanes per step
+    constexpr int NW = NT / 32;
+    const int tid = threadIdx.x, a = tid % LPR, ty = tid / LPR, lane = tid & 31, wid = tid >> 5;
     const int64_t b = blockIdx.x;
     const int bx = (int)(b % blocks_x), by = (int)(b / blocks_x);
 
@@ -187,33 +209,73 @@ fq_tile128_kernel(const __grid_constant__ CUtensorMap tmap, uint4* __restrict__ 
         mbar_wait_bounded(&s_bar, 0);
         return;
     }
-    const uint4* tile = reinterpret_cast<const uint4*>(s_tile);
-    auto chunk = [&](int j, int i) -> uint4 { return tile[i * 512 + (ty + 32 * j) * 4 + a]; };
+    const V* tile = reinterpret_cast<const V*>(s_tile);
+    auto chunk = [&](int j, int i) -> V { return tile[i * (128 * LPR) + (ty + 32 * j) * LPR + a]; };
 
-    // amax and smallest non-zero magnitude (ref: 407-485); bf16 magnitudes order like
-    // their 15-bit patterns, and "pattern - 1" as unsigned sends zero to the top.
-    uint32_t mx = 0u, mn = 0x7F7Eu;  // 0x7F7F - 1: the reference starts amin at the bf16 maximum
-    auto scan = [&](uint32_t w) {
-        const uint32_t lo = w & 0x7FFFu, hi = (w >> 16) & 0x7FFFu;
-        // NaN patterns are ignored by the reference's fmaxf/fminf
-        const uint32_t lo_v = lo > 0x7F80u ? 0u : lo, hi_v = hi > 0x7F80u ? 0u : hi;
-        mx = max(mx, max(lo_v, hi_v));
-        mn = min(mn, min(lo_v - 1u, hi_v - 1u));
-    };
+    // amax and smallest non-zero magnitude (ref: 407-485) on packed words: one unsigned
+    // 16-bit maximum of the magnitudes, and one signed 16-bit minimum of magnitude + 0x7FFF
+    // (a zero becomes 0x7FFF, the largest; a magnitude m becomes 0x8000 + m - 1, ordered by
+    // m).  NaN patterns, which the reference's fmaxf/fminf ignore, sort above infinity: a
+    // tile that holds one is scanned again with the per-element form.
+    uint32_t pmx = 0u, pmn = 0x7FFF7FFFu;
 #pragma unroll 4
     for (int n = 0; n < 16; ++n) {
-        const uint4 v = chunk(n >> 2, n & 3);
-        scan(v.x); scan(v.y); scan(v.z); scan(v.w);
+        uint32_t w[VW];
+        tile_unpack<VW>(chunk(n >> 2, n & 3), w);
+#pragma unroll
+        for (int q = 0; q < VW; q += 2) {
+            const uint32_t m0 = mag2(w[q]), m1 = mag2(w[q + 1]);
+            pmx = umax16x2_3(pmx, m0, m1);
+            pmn = smin16x2_3(pmn, m0 + 0x7FFF7FFFu, m1 + 0x7FFF7FFFu);
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-        mx = max(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
-        mn = min(mn, __shfl_xor_sync(0xFFFFFFFFu, mn, o));
+        pmx = umax16x2(pmx, __shfl_xor_sync(0xFFFFFFFFu, pmx, o));
+        pmn = smin16x2_3(pmn, pmn, __shfl_xor_sync(0xFFFFFFFFu, pmn, o));
     }
-    if (lane == 0) { s_red[0][wid] = u2f(mx << 16); s_red[1][wid] = u2f((mn + 1u) << 16); }
+    __shared__ uint32_t s_pk[2][NW];
+    if (lane == 0) { s_pk[0][wid] = pmx; s_pk[1][wid] = pmn; }
     __syncthreads();
-    const float amax = fmaxf(fmaxf(s_red[0][0], s_red[0][1]), fmaxf(s_red[0][2], s_red[0][3]));
-    const float amin = fminf(fminf(s_red[1][0], s_red[1][1]), fminf(s_red[1][2], s_red[1][3]));
+    pmx = s_pk[0][0]; pmn = s_pk[1][0];
+#pragma unroll
+    for (int q = 1; q < NW; ++q) { pmx = umax16x2(pmx, s_pk[0][q]); pmn = smin16x2_3(pmn, pmn, s_pk[1][q]); }
+    uint32_t amax_pat = hmax_halves(pmx);
+    // halves with bit 15 set saw a non-zero magnitude: (half & 0x7FFF) + 1 is the smallest one
+    const uint32_t h0 = pmn & 0xFFFFu, h1 = pmn >> 16;
+    uint32_t amin_pat = 0x7F7Fu;  // the reference starts amin at the bf16 maximum
+    if (h0 & 0x8000u) amin_pat = min(amin_pat, (h0 & 0x7FFFu) + 1u);
+    if (h1 & 0x8000u) amin_pat = min(amin_pat, (h1 & 0x7FFFu) + 1u);
+    const bool has_nan = amax_pat > 0x7F80u;
+    if (has_nan) {
+        uint32_t mx = 0u, mn = 0x7F7Eu;
+        auto scan = [&](uint32_t w) {
+            const uint32_t lo = w & 0x7FFFu, hi = (w >> 16) & 0x7FFFu;
+            const uint32_t lo_v = lo > 0x7F80u ? 0u : lo, hi_v = hi > 0x7F80u ? 0u : hi;
+            mx = max(mx, max(lo_v, hi_v));
+            mn = min(mn, min(lo_v - 1u, hi_v - 1u));
+        };
+#pragma unroll 1
+        for (int n = 0; n < 16; ++n) {
+            uint32_t w[VW];
+            tile_unpack<VW>(chunk(n >> 2, n & 3), w);
+#pragma unroll
+            for (int q = 0; q < VW; ++q) scan(w[q]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            mx = max(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+            mn = min(mn, __shfl_xor_sync(0xFFFFFFFFu, mn, o));
+        }
+        __syncthreads();
+        if (lane == 0) { s_pk[0][wid] = mx; s_pk[1][wid] = mn; }
+        __syncthreads();
+        amax_pat = s_pk[0][0]; amin_pat = s_pk[1][0];
+#pragma unroll
+        for (int q = 1; q < NW; ++q) { amax_pat = max(amax_pat, s_pk[0][q]); amin_pat = min(amin_pat, s_pk[1][q]); }
+        amin_pat += 1u;
+    }
+    const float amax = u2f(amax_pat << 16), amin = u2f(amin_pat << 16);
 
     int repr = 0, code = 3, fmt = -1;
     if (qmode == QM_MOR) {
@@ -224,8 +286,8 @@ fq_tile128_kernel(const __grid_constant__ CUtensorMap tmap, uint4* __restrict__ 
             e.s5 = __fdiv_rn(57344.0f, amax);
             e.lut4 = s_lut4; e.lut5 = s_lut5;
             if constexpr (SF == kSfFp32) {
-                fill_lut32t<kE4M3>(s_lut4, e.s4, tid);
-                fill_lut32t<kE5M2>(s_lut5, e.s5, tid);
+                fill_lut32t<kE4M3>(s_lut4, e.s4, tid, NT);
+                fill_lut32t<kE5M2>(s_lut5, e.s5, tid, NT);
                 __syncthreads();
             } else {
                 e.c4 = e8_consts(e.s4);
@@ -233,22 +295,66 @@ fq_tile128_kernel(const __grid_constant__ CUtensorMap tmap, uint4* __restrict__ 
             }
             // every non-zero magnitude of the block lies in [amin, amax]
             const bool safe = bf16_div_safe(amin) && bf16_div_safe(amax);
-            float a4[4] = {0.f, 0.f, 0.f, 0.f}, a5[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 1
-            for (int n = 0; n < 16; ++n) {  // rows outer (j = n / 4), words inner (i = n % 4)
-                const uint4 v = chunk(n >> 2, n & 3);
-                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            float a4[VW], a5[VW];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    float e4, e5;
-                    if (safe) word_errors_fast<SF, true>(e, bf16_hi(w[k]), bf16_lo(w[k]), e4, e5);
-                    else word_errors_fast<SF, false>(e, bf16_hi(w[k]), bf16_lo(w[k]), e4, e5);
-                    a4[k] = __fadd_rn(a4[k], e4);
-                    a5[k] = __fadd_rn(a5[k], e5);
+            for (int q = 0; q < VW; ++q) a4[q] = a5[q] = 0.0f;
+            // The two errors of an element depend on its magnitude only (the casts are odd
+            // functions), and a tile that reaches this pass spans at most 30 binades: they are
+            // tabulated once per magnitude pattern in [amin, amax] (entry 0 = a zero element, no
+            // error), and the 16384 elements look them up.  Same values, same order of additions.
+            // Index i = pattern - (amin_pat - 1), so 1..n_pat are the magnitudes of the tile and 0 is
+            // a zero element.  Within 2^13 of amax both casts work on normal numbers, even with a
+            // power-of-two scale (x * scale > 224 * 2^-13 > 2^-6), and the errors repeat from one
+            // binade to the next (x and 2x give q and 2q, the same quotient): rows of 128 indices
+            // from row q_fold up share row q_fold's entries.
+            const int n_pat = (int)(amax_pat - amin_pat) + 1;
+            const int q_fold = max((n_pat >> 7) - 11, 1);
+            const int n_tab = 128 * (q_fold + 1);          // entries 0 .. n_tab - 1
+            if (!has_nan && n_tab <= table_entries) {
+                float2* tab = reinterpret_cast<float2*>(s_tile + kTileBytes);
+                if (tid == 0) tab[0] = make_float2(0.0f, 0.0f);
+                for (int i = 1 + 2 * tid; i < n_tab; i += 2 * NT) {  // two consecutive patterns per step
+                    const uint32_t pl = amin_pat - 1u + (uint32_t)i;
+                    const float lo = u2f(pl << 16), hi = u2f((pl + 1u) << 16);
+                    float e4h, e4l, e5h, e5l;
+                    if (safe) pair_errors<SF, true>(e, hi, lo, e4h, e4l, e5h, e5l);
+                    else pair_errors<SF, false>(e, hi, lo, e4h, e4l, e5h, e5l);
+                    tab[i] = make_float2(e4l, e5l);
+                    if (i + 1 < n_tab) tab[i + 1] = make_float2(e4h, e5h);
+                }
+                __syncthreads();
+                const int base = (int)amin_pat - 1, fold = q_fold << 7;
+#pragma unroll 2
+                for (int n = 0; n < 16; ++n) {  // rows outer (j = n / 4), words inner (i = n % 4)
+                    uint32_t w[VW];
+                    tile_unpack<VW>(chunk(n >> 2, n & 3), w);
+#pragma unroll
+                    for (int k = 0; k < VW; ++k) {
+                        int il = max((int)(w[k] & 0x7FFFu) - base, 0), ih = max((int)((w[k] >> 16) & 0x7FFFu) - base, 0);
+                        il = min(il, (il & 127) | fold);
+                        ih = min(ih, (ih & 127) | fold);
+                        const float2 el = tab[il], eh = tab[ih];
+                        a4[k] = __fadd_rn(a4[k], __fadd_rn(eh.x, el.x));
+                        a5[k] = __fadd_rn(a5[k], __fadd_rn(eh.y, el.y));
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int n = 0; n < 16; ++n) {  // rows outer (j = n / 4), words inner (i = n % 4)
+                    uint32_t w[VW];
+                    tile_unpack<VW>(chunk(n >> 2, n & 3), w);
+#pragma unroll
+                    for (int k = 0; k < VW; ++k) {
+                        float e4, e5;
+                        if (safe) word_errors_fast<SF, true>(e, bf16_hi(w[k]), bf16_lo(w[k]), e4, e5);
+                        else word_errors_fast<SF, false>(e, bf16_hi(w[k]), bf16_lo(w[k]), e4, e5);
+                        a4[k] = __fadd_rn(a4[k], e4);
+                        a5[k] = __fadd_rn(a5[k], e5);
+                    }
                 }
             }
-            const float w4 = logical_warp_sum<4>(a4), w5 = logical_warp_sum<4>(a5);
-            if ((tid & 7) == 0) { s_w4[tid >> 3] = w4; s_w5[tid >> 3] = w5; }
+            const float w4 = logical_warp_sum<VW>(a4), w5 = logical_warp_sum<VW>(a5);
+            if (tid % (32 / VW) == 0) { s_w4[tid / (32 / VW)] = w4; s_w5[tid / (32 / VW)] = w5; }
             __syncthreads();
             if (wid == 0) {
                 const float t4 = warp_sum_ordered(lane < 16 ? s_w4[lane] : 0.0f);
@@ -265,8 +371,8 @@ fq_tile128_kernel(const __grid_constant__ CUtensorMap tmap, uint4* __restrict__ 
     if (tid == 0) meta[b] = code;
     if (!(amax > 0.0f)) fmt = -1;  // all-zero block: copied through (ref: 759, 773, 787, 802, 814)
 
-    uint4* dst = out + ((int64_t)by * 128) * cols_vec + (int64_t)bx * 16;
-    auto store = [&](int n, const uint4& v) { st_stream(dst + (int64_t)(ty + 32 * (n >> 2)) * cols_vec + 4 * (n & 3) + a, v); };
+    V* dst = out + ((int64_t)by * 128) * cols_vec + (int64_t)bx * (4 * LPR);   // cols_vec in units of V
+    auto store = [&](int n, const V& v) { st_stream(dst + (int64_t)(ty + 32 * (n >> 2)) * cols_vec + LPR * (n & 3) + a, v); };
     if (fmt < 0) {
 #pragma unroll 4
         for (int n = 0; n < 16; ++n) store(n, chunk(n >> 2, n & 3));
@@ -274,18 +380,19 @@ fq_tile128_kernel(const __grid_constant__ CUtensorMap tmap, uint4* __restrict__ 
     }
     const float s = __fdiv_rn(fmt == kE2M3 ? 7.5f : (fmt == kE4M3 ? 448.0f : 57344.0f), amax);
     if constexpr (SF == kSfFp32) {
-        if (fmt == kE4M3) fill_lut16<kE4M3>(s_lut16, s, tid);
-        else if (fmt == kE5M2) fill_lut16<kE5M2>(s_lut16, s, tid);
-        else fill_lut16<kE2M3>(s_lut16, s, tid);
+        if (fmt == kE4M3) fill_lut16<kE4M3>(s_lut16, s, tid, NT);
+        else if (fmt == kE5M2) fill_lut16<kE5M2>(s_lut16, s, tid, NT);
+        else fill_lut16<kE2M3>(s_lut16, s, tid, NT);
         __syncthreads();
         auto cast_all = [&](auto fmt_tag) {
             constexpr int F = decltype(fmt_tag)::value;
 #pragma unroll 2
             for (int n = 0; n < 16; ++n) {
-                uint4 v = chunk(n >> 2, n & 3);
-                v.x = lut_word<F>(s_lut16, v.x, s); v.y = lut_word<F>(s_lut16, v.y, s);
-                v.z = lut_word<F>(s_lut16, v.z, s); v.w = lut_word<F>(s_lut16, v.w, s);
-                store(n, v);
+                uint32_t w[VW];
+                tile_unpack<VW>(chunk(n >> 2, n & 3), w);
+#pragma unroll
+                for (int q = 0; q < VW; ++q) w[q] = lut_word<F>(s_lut16, w[q], s);
+                store(n, tile_pack<VW>(w));
             }
         };
         if (fmt == kE4M3) cast_all(std::integral_constant<int, kE4M3>{});
@@ -297,9 +404,11 @@ fq_tile128_kernel(const __grid_constant__ CUtensorMap tmap, uint4* __restrict__ 
             constexpr int F = decltype(fmt_tag)::value;
 #pragma unroll 2
             for (int n = 0; n < 16; ++n) {
-                uint4 v = chunk(n >> 2, n & 3);
-                v.x = e8_word<F>(v.x, c); v.y = e8_word<F>(v.y, c); v.z = e8_word<F>(v.z, c); v.w = e8_word<F>(v.w, c);
-                store(n, v);
+                uint32_t w[VW];
+                tile_unpack<VW>(chunk(n >> 2, n & 3), w);
+#pragma unroll
+                for (int q = 0; q < VW; ++q) w[q] = e8_word<F>(w[q], c);
+                store(n, tile_pack<VW>(w));
             }
         };
         if (fmt == kE4M3) cast_all(std::integral_constant<int, kE4M3>{});
@@ -428,8 +537,27 @@ int launch_fq_block(const void* in, void* out, int is_fp32, int32_t* meta, int64
         CUtensorMap map;
         if (make_tile_map(&map, in, rows, cols, 2, 32, 128)) {
             auto* o4 = static_cast<uint4*>(out);
-            if (sf_type == kSfE8) fq_tile128_kernel<kSfE8><<<(unsigned)nb, 128, kTileBytes, st>>>(map, o4, meta, cols / 8, (int)bx, clamp, quant_mode, dynamic_range_mode);
-            else fq_tile128_kernel<kSfFp32><<<(unsigned)nb, 128, kTileBytes, st>>>(map, o4, meta, cols / 8, (int)bx, clamp, quant_mode, dynamic_range_mode);
+            // the relative-error criterion keeps a table of (E4M3, E5M2) errors per magnitude pattern
+            // behind the tile (at most 20 rows of 128 patterns after folding the periodic top rows) and
+            // runs as 256 threads with 8-byte accesses, so that the four CTAs an SM can hold fill it
+            const bool tabled = quant_mode == QM_MOR && !dynamic_range_mode;
+            constexpr int kTabled = kTileBytes + kErrTableEntries * (int)sizeof(float2);
+#define MORB_TILE(S)                                                                                                 \
+    do {                                                                                                             \
+        if (tabled) {                                                                                                \
+            static const cudaError_t attr = cudaFuncSetAttribute(fq_tile128_kernel<S, 2>,                            \
+                                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kTabled); \
+            if (attr != cudaSuccess) return kErrLaunch;                                                              \
+            fq_tile128_kernel<S, 2><<<(unsigned)nb, 256, kTabled, st>>>(map, static_cast<uint2*>(out), meta, cols / 4, \
+                                                                        (int)bx, clamp, quant_mode, dynamic_range_mode, \
+                                                                        kErrTableEntries);                           \
+        } else {                                                                                                     \
+            fq_tile128_kernel<S, 4><<<(unsigned)nb, 128, kTileBytes, st>>>(map, static_cast<uint4*>(out), meta, cols / 8, \
+                                                                           (int)bx, clamp, quant_mode, dynamic_range_mode, 0); \
+        }                                                                                                            \
+    } while (0)
+            if (sf_type == kSfE8) MORB_TILE(kSfE8); else MORB_TILE(kSfFp32);
+#undef MORB_TILE
             return check_launch();
         }
     }
