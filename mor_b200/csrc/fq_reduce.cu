@@ -264,7 +264,10 @@ __global__ void __launch_bounds__(kThreads) amax_nnz_blocks_kernel(const typenam
         cta_combine(amax, nnz);
     }
     if (threadIdx.x == 0) {
-        block_amax[b] = amax;
+        // the sign bit tells the cast kernel that the block holds no zero (and no NaN: those are
+        // not counted), so it may leave out the selects that keep zero elements out of the sums
+        const bool zero_free = nnz == brows * bcols_vec * (16 / T::kBytesPerElem);
+        block_amax[b] = zero_free ? -amax : amax;
         publish(ws, amax, nnz);
         if (flags) atomicOr(&ws->div_unsafe, 1u);
     }

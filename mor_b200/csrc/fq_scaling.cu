@@ -96,10 +96,23 @@ __device__ __forceinline__ void fill_lut32(float* lut, float sf, int tid, int nt
 //                of two, then the same four instructions.
 enum { kDivIeee = 0, kDivBf16 = 1, kDivBf16Any = 2 };
 
-template <int DIV, typename P>
+template <int DIV, typename P, bool NOZERO = false>
 __device__ __forceinline__ void err_pair(const P& path, float hi, float lo, float& dh, float& dl, float& eh,
                                          float& el) {
     dequant_pair(path, hi, lo, dh, dl);
+    if constexpr (NOZERO) {  // the amax pass counted as many non-zero elements as the block has
+        if constexpr (DIV == kDivBf16) {
+            eh = fabsf(div_by_bf16(__fsub_rn(dh, hi), hi, rcp_fast(hi)));
+            el = fabsf(div_by_bf16(__fsub_rn(dl, lo), lo, rcp_fast(lo)));
+        } else if constexpr (DIV == kDivBf16Any) {
+            eh = fabsf(div_by_bf16_any(__fsub_rn(dh, hi), hi));
+            el = fabsf(div_by_bf16_any(__fsub_rn(dl, lo), lo));
+        } else {
+            eh = fabsf(__fdiv_rn(__fsub_rn(dh, hi), hi));
+            el = fabsf(__fdiv_rn(__fsub_rn(dl, lo), lo));
+        }
+        return;
+    }
     const bool zh = hi == 0.0f, zl = lo == 0.0f;
     if constexpr (DIV == kDivBf16) {
         eh = fabsf(div_by_bf16(__fsub_rn(dh, hi), hi, rcp_fast(hi)));
@@ -118,14 +131,14 @@ __device__ __forceinline__ void err_pair(const P& path, float hi, float lo, floa
 }
 
 // process one 16-byte vector: VW logical threads, errors added high half first
-template <typename T, typename P, bool STORE, int DIV>
+template <typename T, typename P, bool STORE, int DIV, bool NOZERO = false>
 __device__ __forceinline__ void err_vec(const P& path, const typename T::vec_t& v, typename T::vec_t& o,
                                         float (&acc)[T::kWordsPerVec]) {
 #pragma unroll
     for (int k = 0; k < T::kWordsPerVec; ++k) {
         float hi, lo, dh, dl, eh, el;
         T::unpack(v, k, hi, lo);
-        err_pair<DIV>(path, hi, lo, dh, dl, eh, el);
+        err_pair<DIV, P, NOZERO>(path, hi, lo, dh, dl, eh, el);
         acc[k] = __fadd_rn(acc[k], eh);
         acc[k] = __fadd_rn(acc[k], el);
         if constexpr (STORE) {
@@ -141,14 +154,14 @@ __device__ __forceinline__ void err_vec(const P& path, const typename T::vec_t& 
     }
 }
 // same, separate sums for the high and the low halves (channel kernels, ref: 1694-1748)
-template <typename T, typename P, bool STORE, int DIV>
+template <typename T, typename P, bool STORE, int DIV, bool NOZERO = false>
 __device__ __forceinline__ void err_vec_split(const P& path, const typename T::vec_t& v, typename T::vec_t& o,
                                               float (&eh)[T::kWordsPerVec], float (&el)[T::kWordsPerVec]) {
 #pragma unroll
     for (int k = 0; k < T::kWordsPerVec; ++k) {
         float hi, lo, dh, dl, e_h, e_l;
         T::unpack(v, k, hi, lo);
-        err_pair<DIV>(path, hi, lo, dh, dl, e_h, e_l);
+        err_pair<DIV, P, NOZERO>(path, hi, lo, dh, dl, e_h, e_l);
         eh[k] = __fadd_rn(eh[k], e_h);
         el[k] = __fadd_rn(el[k], e_l);
         if constexpr (STORE) {
@@ -181,7 +194,7 @@ block_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_
     __shared__ float s_lut[E8 ? 1 : 256];
     const int64_t b = blockIdx.x;
     const int64_t r0 = (b / blocks_x) * brows, c0 = (b % blocks_x) * bcols_vec;
-    const float sf = scaling_factor(ss, read_gamax(ws, ext_gamax), block_amax[b]);
+    const float sf = scaling_factor(ss, read_gamax(ws, ext_gamax), fabsf(block_amax[b]));
     const int p = threadIdx.x % LPW, ty = threadIdx.x / LPW;
     float acc[VW];
 #pragma unroll
@@ -286,7 +299,9 @@ block_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename T::vec_t
                 tma_load_2d(s_tile + (j * NS + sidx) * 4096, &tmap, bx * 128 + sidx * EPS, by * 128 + j * 32, &s_bar[j]);
         }
     }
-    const float sf = scaling_factor(ss, read_gamax(ws, ext_gamax), block_amax[b]);
+    const float bamax = block_amax[b];            // sign bit set: the block holds no zero (and no NaN)
+    const bool zero_free = (f2u(bamax) >> 31) != 0u;
+    const float sf = scaling_factor(ss, read_gamax(ws, ext_gamax), fabsf(bamax));
     const int p = tid % LPW, ty = tid / LPW;
     float acc[VW];
 #pragma unroll
@@ -295,7 +310,7 @@ block_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename T::vec_t
     typename T::vec_t* dst = out + ((int64_t)by * 128 + ty) * cols_vec + (int64_t)bx * (CI * LPW) + p;
     const bool fastdiv = fast_div_ok<T>(ws);
     bool arrived = true;
-    auto run = [&](const auto& path, auto fd_tag) {
+    auto run = [&](const auto& path, auto fd_tag, auto nz_tag) {
         constexpr int FD = (T::kBytesPerElem != 2) ? kDivIeee : (decltype(fd_tag)::value ? kDivBf16 : kDivBf16Any);
         for (int j = 0; j < 4; ++j) {
             if (!mbar_wait_bounded(&s_bar[j], 0)) { arrived = false; return; }
@@ -304,19 +319,25 @@ block_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename T::vec_t
                 const int vc = p + LPW * i;
                 const typename T::vec_t v = tile[((j * NS + (vc >> 3)) * 32 + ty) * 8 + (vc & 7)];
                 typename T::vec_t o;
-                err_vec<T, std::decay_t<decltype(path)>, STORE, FD>(path, v, o, acc);
+                err_vec<T, std::decay_t<decltype(path)>, STORE, FD, decltype(nz_tag)::value>(path, v, o, acc);
                 if constexpr (STORE) st_stream(dst + (int64_t)(32 * j) * cols_vec + LPW * i, o);
             }
         }
     };
+    // the common case (short quotient allowed, or binary32 data, and no zero in the block) runs
+    // without the selects that keep zero elements out of the sums
+    auto dispatch = [&](const auto& path) {
+        const bool short_ok = fastdiv || T::kBytesPerElem != 2;
+        if (short_ok && zero_free) run(path, std::true_type{}, std::true_type{});
+        else if (short_ok) run(path, std::true_type{}, std::false_type{});
+        else run(path, std::false_type{}, std::false_type{});
+    };
     if constexpr (E8) {
-        const PathE8 path{e8_consts(sf)};
-        if (fastdiv) run(path, std::true_type{}); else run(path, std::false_type{});
+        dispatch(PathE8{e8_consts(sf)});
     } else {
         fill_lut32(s_lut, sf, tid, NT);
         __syncthreads();
-        const PathLut path{s_lut, sf};
-        if (fastdiv) run(path, std::true_type{}); else run(path, std::false_type{});
+        dispatch(PathLut{s_lut, sf});
     }
     if (__syncthreads_or(!arrived)) {
         // a load did not complete within the bounded wait: flag the call (finalize reports
@@ -368,7 +389,12 @@ rowgroup_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::v
         const typename T::vec_t* src = in + (live ? u : 0) * span_vec;
         typename T::vec_t* dst = out + (live ? u : 0) * span_vec;
         float sf = 1.0f;
-        if (group_lanes == 0 && live) sf = scaling_factor(ss, gamax, block_amax[u]);  // one block per unit
+        bool zero_free = false;
+        if (group_lanes == 0) {  // one block per unit; a negative amax marks a unit without zeros
+            const float ba = live ? block_amax[u] : -1.0f;
+            if (live) sf = scaling_factor(ss, gamax, fabsf(ba));
+            zero_free = __all_sync(0xFFFFFFFFu, (f2u(ba) >> 31) != 0u);
+        }
         float* lut = s_lut + (MODE == 1 ? unit_in_cta * 256 : 0);
         if constexpr (MODE == 1) {
             __syncwarp();
@@ -431,8 +457,10 @@ rowgroup_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::v
                 }
                 if (fastdiv) {
                     if constexpr (MODE == 2) err_vec_split<T, PathE8, STORE, kDivBf16>(PathE8{e8_consts(sf)}, v[q], o4, eh, el);
-                    else if constexpr (MODE == 1) err_vec_split<T, PathLut, STORE, kDivBf16>(PathLut{lut, sf}, v[q], o4, eh, el);
-                    else err_vec_split<T, PathDiv, STORE, kDivBf16>(PathDiv{sf}, v[q], o4, eh, el);
+                    else if constexpr (MODE == 1) {
+                        if (zero_free) err_vec_split<T, PathLut, STORE, kDivBf16, true>(PathLut{lut, sf}, v[q], o4, eh, el);
+                        else err_vec_split<T, PathLut, STORE, kDivBf16>(PathLut{lut, sf}, v[q], o4, eh, el);
+                    } else err_vec_split<T, PathDiv, STORE, kDivBf16>(PathDiv{sf}, v[q], o4, eh, el);
                 } else {
                     if constexpr (MODE == 2) err_vec_split<T, PathE8, STORE, kSlowDiv>(PathE8{e8_consts(sf)}, v[q], o4, eh, el);
                     else if constexpr (MODE == 1) err_vec_split<T, PathLut, STORE, kSlowDiv>(PathLut{lut, sf}, v[q], o4, eh, el);
