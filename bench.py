@@ -446,6 +446,7 @@ def run_suite(torch, dev, peak, only="", iters=10, out_path=None, use_graph=Fals
     r, c = x.shape
     add("c3 MX 1x32 E8M0 E4M3 single pass (fake_quantize_mx)", x, 4, "fake_quantize_mx", (r, c, 32, 0, 2))
     add("c3 MX 1x32 E8M0 E2M3 single pass (fake_quantize_mx)", x, 4, "fake_quantize_mx", (r, c, 32, 3, 2))
+    add("c3 MX 1x32 real quantization, E4M3 codes + E8M0 scales (quantize_mx)", x, 3.03125, "quantize_mx", (r, c, 32, 0))
     add("c3 MX 1x32 E4M3 pipeline (channel_scaling ss 2)", x, 6, "fake_quantize_channel_scaling", (r, c, 1, 32, 3e38, 2))
     del x
     x = workloads.config4(device=dev)

@@ -148,6 +148,19 @@ MOR_B200_API int mor_b200_e8mx(const void* input, void* output, int64_t rows, in
 MOR_B200_API int mor_b200_fake_quantize_group(const void* input, void* output, float* scales, int dtype, int64_t rows,
                                  int64_t cols, int block_cols, int format, int sf_type, void* stream);
 
+/* Extension (no counterpart in the reference, whose operators only fake-quantize; the casts
+ * it describes are fake_quantize.cu:283-305 and the wrappers :356-379): the REAL quantized form
+ * of mor_b200_fake_quantize_group with sf_type 2, i.e. what a block-scaled GEMM consumes.
+ * input: bf16 [rows, cols], 16-byte aligned.  payload: one byte per element [rows, cols], 8-byte
+ * aligned -- the fp8 code for E4M3 (format 0) / E5M2 (1), the 6-bit code in a byte for E2M3 (3).
+ * scales: one E8M0 byte per 1 x block_cols group [rows, cols / block_cols], MX convention:
+ * element = decode(code) * 2^(scale - 127); an all-zero group gets 127.  block_cols a power of
+ * two from 8 to 256, rows * cols a multiple of 256.  decode * scale equals the fake-quantized
+ * output bit for bit, except where the code is zero under a scale below one (fake quantization
+ * returns 2^(-e8-127) there, an artefact of its exponent-field arithmetic, :296-305). */
+MOR_B200_API int mor_b200_quantize_mx(const void* input, void* payload, void* scales, int64_t rows, int64_t cols,
+                         int block_cols, int format, void* stream);
+
 /* ---- row-sharded pipeline (extension): the phases of block/channel scaling as separate
  * calls, so that a caller holding one row slab per GPU can all-reduce the amax (max)
  * and the non-zero count (sum) and all-gather the block errors between them. ---- */

@@ -282,6 +282,16 @@ int mor_b200_fake_quantize_group(const void* in, void* out, float* scales, int d
                            static_cast<cudaStream_t>(stream));
 }
 
+int mor_b200_quantize_mx(const void* in, void* payload, void* scales, int64_t rows, int64_t cols, int bc, int format,
+                         void* stream) {
+    if (!in || !payload || !scales || rows <= 0 || cols <= 0 || bc <= 0) return kErrInvalidArgument;
+    if (cols % bc) return kErrInvalidArgument;
+    if (format != kE4M3 && format != kE5M2 && format != kE2M3) return kErrInvalidArgument;
+    if (!aligned16(in) || (reinterpret_cast<uintptr_t>(payload) & 7u)) return kErrUnsupportedShape;
+    return launch_quantize_mx(in, payload, static_cast<uint8_t*>(scales), rows, cols, bc, format,
+                              static_cast<cudaStream_t>(stream));
+}
+
 int mor_b200_scaling_amax(int kind, const void* in, int dtype, int64_t rows, int64_t cols, int br, int bc,
                           float* amax_out, int64_t* nnz_out, void* wsp, size_t wsb, void* stream) {
     if (!in || (dtype != MOR_B200_BF16 && dtype != MOR_B200_FP32)) return kErrInvalidArgument;

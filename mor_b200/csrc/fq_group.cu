@@ -252,6 +252,86 @@ mx_bf16_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, float* __r
     ws.drain();
 }
 
+// ---------------------------------------------------------------------------------
+// real quantized output: narrow-float codes + E8M0 scale bytes (no reference operator)
+// ---------------------------------------------------------------------------------
+// The codes are what the casts inside the power-of-two path produce before they are widened
+// again (ref: 283-305, 356-379); the scale byte follows the MX convention, element =
+// decode(code) * 2^(byte - 127).  Same stream structure and the same group amax as
+// mx_bf16_kernel; 8 payload bytes per 16-byte input vector.
+template <int FMT>
+__device__ __forceinline__ uint32_t codes_fix_zero_sign(uint32_t c) {
+    if constexpr (FMT == kE2M3 || FMT == kE3M2) {
+        // the custom cast returns +0 for a zero result: drop bit 5 of a byte whose low five bits are zero
+        const uint32_t nz = ((c & 0x1F1F1F1Fu) + 0x1F1F1F1Fu) & 0x20202020u;
+        return c & (nz | 0x1F1F1F1Fu);
+    } else {
+        return c;
+    }
+}
+template <int FMT, int GS>
+__device__ __forceinline__ uint2 mx_codes_one(const uint4& v, uint32_t& scale_byte) {
+    constexpr int K127 = ((FMT == kE4M3) ? 8 : (FMT == kE5M2 ? 15 : 2)) + 127;
+    constexpr uint32_t CMAN7 = (FMT == kE2M3) ? 0x70u : 0x60u;
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t p = vec_amax_pattern(v);
+#pragma unroll
+    for (int o = (1 << GS) >> 1; o > 0; o >>= 1) p = max(p, __shfl_xor_sync(0xFFFFFFFFu, p, o));
+    const int ea = (int)(p >> 7);
+    int e8 = K127 - ea - ((p & 0x7Fu) > CMAN7 ? 1 : 0);
+    const bool fast = (uint32_t)(ea - 1) < 254u && (uint32_t)(e8 + 119) <= 219u;
+    uint32_t c[4];
+    if (__all_sync(0xFFFFFFFFu, fast)) {
+        const float up = u2f((uint32_t)(e8 + 127) << 23);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) c[k] = cvt_codes<FMT>(__fmul_rn(bf16_hi(w[k]), up), __fmul_rn(bf16_lo(w[k]), up));
+    } else {
+        float a = u2f(p << 16);
+        if (__any_sync(0xFFFFFFFFu, p > 0x7F80u)) {  // a NaN in the warp: the reference's fmaxf skips it
+            a = vec_amax_float<Bf16>(v);
+#pragma unroll
+            for (int o = (1 << GS) >> 1; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+        }
+        e8 = 0;
+        if (a > 0.0f) e8 = e8_of_scale(__fdiv_rn(fmt_max<FMT>(), a));
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            c[k] = cvt_codes<FMT>(e8_shift_field(bf16_hi(w[k]), e8), e8_shift_field(bf16_lo(w[k]), e8));
+    }
+    scale_byte = (uint32_t)min(max(127 - e8, 0), 254);
+    return make_uint2(codes_fix_zero_sign<FMT>(c[0] | (c[1] << 16)), codes_fix_zero_sign<FMT>(c[2] | (c[3] << 16)));
+}
+
+template <int FMT, int GS>
+__global__ void __launch_bounds__(32 * kMxWarps, 5)
+mx_quantize_kernel(const uint4* __restrict__ in, uint2* __restrict__ payload, uint8_t* __restrict__ scales, int64_t nvec) {
+    extern __shared__ __align__(128) uint8_t s_ring[];  // [warp][stage][2 KiB]
+    __shared__ __align__(8) uint64_t s_bar[kMxWarps][kMxStages];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int64_t n_warps = (int64_t)gridDim.x * kMxWarps, gw = (int64_t)blockIdx.x * kMxWarps + wid;
+    WarpStream<kMxStages, kMxChunkVec * 16> ws;
+    ws.start(s_ring + wid * (kMxStages * kMxChunkVec * 16), s_bar[wid], in, nvec * 16, gw, n_warps);
+    const int64_t n_chunks = (nvec + kMxChunkVec - 1) / kMxChunkVec;
+    const bool scale_lane = (lane & ((1 << GS) - 1)) == 0;
+    int st = 0;
+    for (int64_t c = gw; c < n_chunks; c += n_warps) {
+        const int64_t v0 = c * kMxChunkVec;
+        const int nv = (int)(nvec - v0 < kMxChunkVec ? nvec - v0 : kMxChunkVec);
+        const bool staged = ws.acquire(st);
+        const uint4* chunk = reinterpret_cast<const uint4*>(ws.stage(st)) + lane;
+        for (int r = 0; r * 32 < nv; ++r) {
+            const uint4 v = staged ? chunk[r * 32] : ld_stream(in + v0 + r * 32 + lane);
+            uint32_t sb;
+            const uint2 codes = mx_codes_one<FMT, GS>(v, sb);
+            st_stream(payload + v0 + r * 32 + lane, codes);
+            if (scale_lane) scales[(v0 + r * 32 + lane) >> GS] = (uint8_t)sb;
+        }
+        ws.release(st, c + kMxStages * n_warps);
+        st = st + 1 == kMxStages ? 0 : st + 1;
+    }
+    ws.drain();
+}
+
 constexpr int kRowThreads = 256;
 constexpr int kRowMaxVec = 8;
 
@@ -425,6 +505,49 @@ int launch_fmt(const void* in, void* out, float* scales, int32_t* meta, int32_t 
 }
 
 }  // namespace
+
+int launch_quantize_mx(const void* in, void* payload, uint8_t* scales, int64_t rows, int64_t cols, int bcols, int fmt,
+                       cudaStream_t st) {
+    if (bcols % 8 || cols % bcols) return kErrUnsupportedShape;
+    const int gvec = bcols / 8;
+    const int64_t nvec = rows * cols / 8;
+    if (gvec > 32 || (gvec & (gvec - 1)) || nvec % 32) return kErrUnsupportedShape;
+    int shift = 0;
+    while ((1 << shift) < gvec) ++shift;
+    constexpr int kRing = kMxWarps * kMxStages * kMxChunkVec * 16;
+    constexpr int kChunksPerWarp = 2;
+    const int64_t n_chunks = (nvec + kMxChunkVec - 1) / kMxChunkVec;
+    int64_t grid = (n_chunks + kMxWarps * kChunksPerWarp - 1) / (kMxWarps * kChunksPerWarp);
+    if (grid > 0x7FFFFFFF) return kErrTooLarge;
+    if (grid < 1) grid = 1;
+    auto* i4 = static_cast<const uint4*>(in);
+    auto* p2 = static_cast<uint2*>(payload);
+#define MORB_Q(F, GS)                                                                                                \
+    do {                                                                                                             \
+        static const cudaError_t attr =                                                                              \
+            cudaFuncSetAttribute(mx_quantize_kernel<F, GS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing);     \
+        if (attr != cudaSuccess) return kErrLaunch;                                                                  \
+        mx_quantize_kernel<F, GS><<<(unsigned)grid, 32 * kMxWarps, kRing, st>>>(i4, p2, scales, nvec);               \
+    } while (0)
+#define MORB_QS(F)                                                                                                   \
+    do {                                                                                                             \
+        switch (shift) {                                                                                             \
+            case 0: MORB_Q(F, 0); break;                                                                             \
+            case 1: MORB_Q(F, 1); break;                                                                             \
+            case 2: MORB_Q(F, 2); break;                                                                             \
+            case 3: MORB_Q(F, 3); break;                                                                             \
+            case 4: MORB_Q(F, 4); break;                                                                             \
+            default: MORB_Q(F, 5); break;                                                                            \
+        }                                                                                                            \
+    } while (0)
+    if (fmt == kE4M3) MORB_QS(kE4M3);
+    else if (fmt == kE5M2) MORB_QS(kE5M2);
+    else if (fmt == kE2M3) MORB_QS(kE2M3);
+    else return kErrInvalidArgument;
+#undef MORB_QS
+#undef MORB_Q
+    return check_launch();
+}
 
 int launch_fq_group(const void* in, void* out, int is_fp32, float* scales, int32_t* meta, int32_t meta_code,
                     int64_t rows, int64_t cols, int bcols, int fmt, int sf_type, cudaStream_t st) {

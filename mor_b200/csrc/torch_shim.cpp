@@ -217,6 +217,23 @@ std::vector<at::Tensor> fake_quantize_mx(const at::Tensor& input, int64_t rows, 
     return {out, scales};
 }
 
+// ---- extension: real quantized output (codes + E8M0 scale bytes) -----------------------
+// returns [payload uint8 [dim_x, dim_y], scales uint8 [dim_x, dim_y / block_y]]
+std::vector<at::Tensor> quantize_mx(const at::Tensor& input, int64_t rows, int64_t cols, int64_t bc, int64_t elem_format) {
+    const c10::cuda::CUDAGuard guard(input.device());
+    at::Tensor in = checked_input(input, rows, cols, "quantize_mx");
+    TORCH_CHECK(in.scalar_type() == at::kBFloat16, "mor::quantize_mx: bfloat16 input only");
+    TORCH_CHECK(bc > 0 && cols % bc == 0, "mor::quantize_mx: block_y must divide dim_y");
+    TORCH_CHECK(elem_format == MOR_B200_E4M3 || elem_format == MOR_B200_E5M2 || elem_format == MOR_B200_E2M3,
+                "mor::quantize_mx: elem_format must be 0 (E4M3), 1 (E5M2) or 3 (E2M3)");
+    at::Tensor payload = torch::empty({rows, cols}, in.options().dtype(torch::kUInt8));
+    at::Tensor scales = torch::empty({rows, cols / bc}, in.options().dtype(torch::kUInt8));
+    check_status(mor_b200_quantize_mx(in.data_ptr(), payload.data_ptr(), scales.data_ptr(), rows, cols, (int)bc,
+                                      (int)elem_format, cur_stream()),
+                 "quantize_mx");
+    return {payload, scales};
+}
+
 }  // namespace
 
 // Registers _C as a Python extension module.
@@ -240,6 +257,7 @@ TORCH_LIBRARY(mor, m) {
   m.def("fake_quantize_channel_scaling_inplace(Tensor input, int dim_x, int dim_y, int block_x, int block_y, float e4m3_threshold, int ss_mode) -> Tensor[]");
   // addition: one scale per 1 x block_y group (MX), E4M3 / E5M2 / E2M3 elements
   m.def("fake_quantize_mx(Tensor input, int dim_x, int dim_y, int block_y, int elem_format, int sf_type) -> Tensor[]");
+  m.def("quantize_mx(Tensor input, int dim_x, int dim_y, int block_y, int elem_format) -> Tensor[]");
 }
 
 TORCH_LIBRARY_IMPL(mor, CUDA, m) {
@@ -258,6 +276,7 @@ TORCH_LIBRARY_IMPL(mor, CUDA, m) {
   m.impl("fake_quantize_channel_scaling", &fake_quantize_channel_scaling);
   m.impl("fake_quantize_channel_scaling_inplace", &fake_quantize_channel_scaling_inplace);
   m.impl("fake_quantize_mx", &fake_quantize_mx);
+  m.impl("quantize_mx", &quantize_mx);
 }
 
 }  // namespace mor

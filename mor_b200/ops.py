@@ -24,6 +24,7 @@ __all__ = [
     "quant_dequant_e4m3", "quant_dequant_e5m2", "quant_dequant_e2m3", "quant_dequant_e3m2",
     "e4m3_with_e8_scale_rne", "e4m3_with_e8_scale_rz",
     "fake_quantize_mx",
+    "quantize_mx",
 ]
 
 
@@ -129,6 +130,14 @@ def fake_quantize_mx(a: Tensor, dim_x: int, dim_y: int, block_y: int, elem_forma
     """Single-pass fake-quantize with one scale per 1 x ``block_y`` group (MX: ``block_y = 32``,
     ``sf_type = 2``).  ``elem_format``: 0 E4M3, 1 E5M2, 3 E2M3.  Returns ``[out, scales]``."""
     return _ops.fake_quantize_mx.default(a, dim_x, dim_y, block_y, elem_format, sf_type)
+
+
+def quantize_mx(a: Tensor, dim_x: int, dim_y: int, block_y: int, elem_format: int) -> List[Tensor]:
+    """The real quantized form of :func:`fake_quantize_mx` with a power-of-two scale: returns
+    ``[payload, scales]``, both ``uint8``: one narrow-float code per element (fp8 byte for E4M3 / E5M2, the
+    6-bit code in a byte for E2M3) and one E8M0 byte per 1 x ``block_y`` group;
+    ``element = decode(code) * 2 ** (scale - 127)``.  No gradient."""
+    return _ops.quantize_mx.default(a, dim_x, dim_y, block_y, elem_format)
 
 
 # --------------------------------------------------------------------------- straight-through backward

@@ -67,6 +67,8 @@ def lib() -> C.CDLL:
         L.mor_o_e4m3_with_e8_scale.argtypes = [vp, vp, i64, i32]
         L.mor_o_fake_quantize_group.argtypes = [vp, vp, i32, vp, i64, i64, i32, i32, i32, i32]
         L.mor_o_amax_nnz.argtypes = [vp, i32, i64, vp, vp]
+        L.mor_o_quantize_mx.argtypes = [vp, vp, vp, i64, i64, i32, i32]
+        L.mor_o_dequantize_mx.argtypes = [vp, vp, vp, i64, i64, i32, i32]
         L.mor_o_finalize.restype = f32
         L.mor_o_finalize.argtypes = [vp, i64, i32, i64, dbl, vp]
         L.mor_o_num_threads.restype = i32
@@ -196,6 +198,28 @@ def fake_quantize_group(x, brows, bcols, fmt, sf_type, want_scales=False):
     _rc(lib().mor_o_fake_quantize_group(_p(x), _p(out), is_f32, _p(scales), rows, cols, brows, bcols, fmt, sf_type),
         "fake_quantize_group")
     return (out, scales) if want_scales else out
+
+
+def quantize_mx(x, bcols, fmt):
+    """Real quantized form of ``fake_quantize_group`` with a power-of-two scale: (codes uint8 [rows, cols],
+    E8M0 scale bytes uint8 [rows, cols // bcols]); element = decode(code) * 2**(scale - 127)."""
+    x = np.ascontiguousarray(x)
+    if x.dtype != np.uint16:
+        raise TypeError("bf16 bit patterns (uint16) only")
+    rows, cols = x.shape
+    payload = np.zeros((rows, cols), np.uint8)
+    scales = np.zeros((rows, cols // bcols), np.uint8)
+    _rc(lib().mor_o_quantize_mx(_p(x), _p(payload), _p(scales), rows, cols, bcols, fmt), "quantize_mx")
+    return payload, scales
+
+
+def dequantize_mx(payload, scales, bcols, fmt):
+    payload = np.ascontiguousarray(payload, dtype=np.uint8)
+    scales = np.ascontiguousarray(scales, dtype=np.uint8)
+    rows, cols = payload.shape
+    out = np.zeros((rows, cols), np.uint16)
+    _rc(lib().mor_o_dequantize_mx(_p(payload), _p(scales), _p(out), rows, cols, bcols, fmt), "dequantize_mx")
+    return out
 
 
 def amax_nnz(x):

@@ -857,6 +857,80 @@ MOR_O_API int mor_o_fake_quantize_group(const void *in, void *out, int is_fp32, 
     return 0;
 }
 
+/* Extension (no reference operator): the REAL quantized form of fake_quantize_group with a
+ * power-of-two scale -- what the casts inside SQDD_e8_* (ref: 283-305, 356-379) produce before
+ * they are widened again.  payload[i] is the narrow-float code of element i (E4M3 / E5M2: the
+ * fp8 byte; E2M3: the 6-bit code in a byte), scales[g] the E8M0 byte of group g in the MX
+ * convention: element = decode(code) * 2^(scales[g] - 127).  A zero group has scale byte 127.
+ * A code of zero decodes to zero; fake quantization returns 2^(-e8-127) there when the
+ * scale is below one (an artefact of its exponent-field arithmetic, ref: 296-305), so the
+ * two agree on every element except those. */
+static uint8_t encode_narrow(float q, int fmt) {
+    const fmt_t *F = &FMTS[fmt];
+    const uint32_t b = f2u(q);
+    const uint32_t sign = (b >> 31) << (F->ebits + F->mbits);
+    const uint32_t mag = b & 0x7FFFFFFFu;
+    if (mag > 0x7F800000u) return 0x7F; /* the fp8 NaN that the saturating cast gives for a NaN input */
+    if (mag == 0) return (uint8_t)sign;
+    const int e = (int)(mag >> 23) - 127 + F->bias;
+    const int drop = 23 - F->mbits;
+    if (e > 0) return (uint8_t)(sign | ((uint32_t)e << F->mbits) | ((mag >> drop) & ((1u << F->mbits) - 1u)));
+    /* subnormal of the narrow format: value = man * 2^(1 - bias - mbits) */
+    const uint32_t sig = (mag & 0x7FFFFFu) | (1u << 23);
+    return (uint8_t)(sign | (sig >> (drop + 1 - e)));
+}
+static float decode_narrow(uint8_t code, int fmt) {
+    const fmt_t *F = &FMTS[fmt];
+    const uint32_t sign = (code >> (F->ebits + F->mbits)) & 1u;
+    const uint32_t e = (code >> F->mbits) & ((1u << F->ebits) - 1u), m = code & ((1u << F->mbits) - 1u);
+    float v;
+    if (fmt == FMT_E4M3 && e == 15 && m == 7) return u2f(0x7FFFE000u);
+    if (fmt == FMT_E5M2 && e == 31) return m ? u2f(0x7FFFE000u) : (sign ? -INFINITY : INFINITY);
+    if (e == 0) v = ldexpf((float)m, 1 - F->bias - F->mbits);
+    else v = ldexpf((float)((1u << F->mbits) | m), (int)e - F->bias - F->mbits);
+    return sign ? -v : v;
+}
+MOR_O_API int mor_o_quantize_mx(const void *in, uint8_t *payload, uint8_t *scales, int64_t rows, int64_t cols,
+                                int bcols, int fmt) {
+    if (rows <= 0 || cols <= 0 || bcols <= 0 || cols % bcols) return -1;
+    if (!(fmt == FMT_E4M3 || fmt == FMT_E5M2 || fmt == FMT_E2M3)) return -1;
+    io_t io = {in, NULL, 0};
+    const int cuda_cast = (fmt == FMT_E4M3 || fmt == FMT_E5M2);
+    const int64_t gx = cols / bcols, nb = rows * gx;
+    const float maxv = (fmt == FMT_E2M3) ? 7.5f : (fmt == FMT_E4M3 ? 448.0f : 57344.0f);
+#pragma omp parallel for schedule(static)
+    for (int64_t b = 0; b < nb; ++b) {
+        const int64_t i0 = (b / gx) * cols + (b % gx) * bcols;
+        float amax = 0.0f;
+        for (int64_t c = 0; c < bcols; ++c) amax = fmaxf(amax, fabsf(load_elem(&io, i0 + c)));
+        int e8 = 0;
+        if (amax > 0.0f) { volatile float t = maxv / amax; e8 = (int)((f2u(t) >> 23) & 0xFFu) - 127; }
+        scales[b] = (uint8_t)(127 - e8 < 0 ? 0 : (127 - e8 > 254 ? 254 : 127 - e8));
+        for (int64_t c = 0; c < bcols; ++c) {
+            const uint32_t xb = f2u(load_elem(&io, i0 + c));
+            int xexp = (int)((xb >> 23) & 0xFFu) + e8;   /* ref: 283-290: the scale is added to the exponent field */
+            if (xexp < 0) xexp = 0;
+            if (xexp > 254) { raise_flag(MOR_O_ASSERT_E8_EXPONENT); xexp = 254; }
+            const float scaled = u2f((xb & 0x80000000u) | ((uint32_t)xexp << 23) | (xb & 0x7FFFFFu));
+            payload[i0 + c] = encode_narrow(quant_dequant(scaled, fmt, cuda_cast), fmt);
+        }
+    }
+    return 0;
+}
+/* decode(code) * 2^(scale - 127) as bf16 bits (exact: at most four significant bits) */
+MOR_O_API int mor_o_dequantize_mx(const uint8_t *payload, const uint8_t *scales, uint16_t *out, int64_t rows,
+                                  int64_t cols, int bcols, int fmt) {
+    if (rows <= 0 || cols <= 0 || bcols <= 0 || cols % bcols) return -1;
+    const int64_t gx = cols / bcols, n = rows * cols;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) {
+        const int64_t g = (i / cols) * gx + (i % cols) / bcols;
+        const float v = ldexpf(decode_narrow(payload[i], fmt), (int)scales[g] - 127);
+        out[i] = (uint16_t)(f2u(v) >> 16);
+    }
+    return 0;
+}
+
 /* amax + non-zero count of a row slab (phase 1 of the row-sharded pipeline) */
 MOR_O_API int mor_o_amax_nnz(const void *in, int is_fp32, int64_t n, float *amax_out, int64_t *nnz_out) {
     io_t io = {in, NULL, is_fp32};

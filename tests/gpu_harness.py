@@ -116,6 +116,16 @@ def fake_quantize_group(x, by, fmt, sf, want_scales=True):
     return {"out": to_np(out), "scales": to_np(scales) if want_scales else None}
 
 
+def quantize_mx(x, by, fmt):
+    rows, cols = x.shape
+    d = to_dev(x)
+    payload = torch.zeros(rows, cols, dtype=torch.uint8, device="cuda")
+    scales = torch.zeros(rows, cols // by, dtype=torch.uint8, device="cuda")
+    cabi.call("mor_b200_quantize_mx", d.data_ptr(), payload.data_ptr(), scales.data_ptr(), rows, cols, by, fmt, stream())
+    torch.cuda.synchronize()
+    return {"payload": payload.cpu().numpy(), "scales": scales.cpu().numpy()}
+
+
 _FMT = {"quant_dequant_e4m3": cabi.E4M3, "quant_dequant_e5m2": cabi.E5M2, "quant_dequant_e3m2": cabi.E3M2,
         "quant_dequant_e2m3": cabi.E2M3}
 

@@ -407,6 +407,54 @@ def test_ordered_error_sum_of_long_arrays(n, stride):
     assert int(meta.item()) == int(want_meta)
 
 
+@pytest.mark.parametrize("fmt", [0, 1, 3])
+@pytest.mark.parametrize("by", [8, 16, 32, 64, 128, 256])
+def test_quantize_mx_codes_and_scales(fmt, by):
+    """codes and E8M0 scale bytes of the real quantized output against the oracle, bit for bit"""
+    import gpu_harness as H
+    g = torch.Generator().manual_seed(fmt * 100 + by)
+    rows, cols = 72, 1024
+    t = torch.randn(rows, cols, generator=g) * torch.where(torch.rand(rows, cols, generator=g) < 0.01, 3000.0, 1.0)
+    t[3] = 0.0
+    t[5, 40:50] = 0.0
+    t[7] *= 1e-20
+    t[9] *= 1e-36      # subnormal bf16 values: scale exponents outside the short form's range
+    t[11] *= 1e30
+    x = t.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    oracle.clear_assert_flags()
+    codes, scales = oracle.quantize_mx(x, by, fmt)
+    assert oracle.assert_flags() == 0
+    got = H.quantize_mx(x, by, fmt)
+    assert np.array_equal(got["scales"], scales), f"scale bytes fmt {fmt} 1x{by}"
+    bad = np.argwhere(got["payload"] != codes)
+    assert bad.size == 0, f"codes fmt {fmt} 1x{by}: first mismatch at {bad[0]}: {got['payload'][tuple(bad[0])]:#x} vs {codes[tuple(bad[0])]:#x}"
+
+
+def test_quantize_mx_round_trip_full_size():
+    """configuration 3 at full size (16384 x 8192, 1 x 32 groups): decode(code) * 2^(scale - 127) equals the
+    fake-quantized tensor wherever the code is non-zero or the scale is at least one"""
+    import mor
+    from mor_b200 import workloads
+    x = workloads.config3(device="cuda")
+    r, c = x.shape
+    for fmt, lut_bits in ((0, None), (3, None)):
+        payload, scales = mor.ops.quantize_mx(x, r, c, 32, fmt)
+        fq, _ = mor.ops.fake_quantize_mx(x, r, c, 32, fmt, 2)
+        if fmt == 0:
+            dec = payload.view(torch.float8_e4m3fn).to(torch.float32)
+        else:   # E2M3: sign, two exponent bits (bias 1), three mantissa bits
+            p = payload.to(torch.int32)
+            e, m = (p >> 3) & 3, (p & 7).to(torch.float32)
+            mag = torch.where(e == 0, m * 0.125, (1.0 + m * 0.125) * torch.exp2((e - 1).to(torch.float32)))
+            dec = torch.where((p & 32) != 0, -mag, mag)
+        deq = (dec.view(r, c // 32, 32) * torch.exp2(scales.to(torch.float32) - 127.0).unsqueeze(-1)).view(r, c)
+        same = deq.to(torch.bfloat16).view(torch.int16) == fq.view(torch.int16)
+        zero_code = (payload & (0x7F if fmt == 0 else 0x1F)) == 0
+        below_one = (scales > 127).repeat_interleave(32, dim=1)
+        assert bool((same | (zero_code & below_one)).all())
+        assert float(same.float().mean()) > 0.9
+
+
 def test_invalid_arguments_are_status_codes_not_faults():
     import gpu_harness as H
     from mor_b200 import cabi

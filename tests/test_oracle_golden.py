@@ -226,3 +226,31 @@ def test_recorded_reference_outputs():
             assert got["gnnz"] == r["gnnz"], name
         checked += 1
     assert checked >= 90
+
+
+@pytest.mark.parametrize("fmt", [0, 1, 3])
+@pytest.mark.parametrize("by", [8, 32, 128])
+def test_quantize_mx_round_trip(fmt, by):
+    """The real quantized form (codes + E8M0 scale bytes) decodes to the fake-quantized tensor bit for
+    bit, except where a code of zero meets a scale below one: fake quantization returns 2^(-e8-127)
+    there (its exponent-field arithmetic, fake_quantize.cu:296-305), the decoded payload zero."""
+    g = torch.Generator().manual_seed(fmt * 10 + by)
+    t = torch.randn(96, 512, generator=g) * torch.where(torch.rand(96, 512, generator=g) < 0.01, 3000.0, 1.0)
+    t[3] = 0.0
+    t[5, 40:50] = 0.0
+    t[7] *= 1e-20
+    x = t.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    codes, scales = oracle.quantize_mx(x, by, fmt)
+    assert oracle.assert_flags() == 0
+    deq = oracle.dequantize_mx(codes, scales, by, fmt)
+    fq = oracle.fake_quantize_group(x, 1, by, fmt, 2)
+    zero_code = (codes & (0x1F if fmt == 3 else 0x7F)) == 0
+    scale_below_one = np.repeat(scales > 127, by, axis=1)
+    diff = deq != fq
+    assert not (diff & ~(zero_code & scale_below_one)).any()
+    assert (scales[3] == 127).all() and (codes[3] == 0).all()
+    # codes are valid for the format: E2M3 uses six bits, E4M3 never the NaN code for finite input
+    if fmt == 3:
+        assert (codes < 64).all()
+    if fmt == 0:
+        assert ((codes & 0x7F) != 0x7F).all()
