@@ -144,3 +144,60 @@ class ShardedScaling:
         b.finalize(self.all_err, self.nnz, threshold, self.meta, self.gerr)
         b.fallback(x, out, self.meta)
         return ScalingResult(self.meta, self.amax, self.nnz, self.gerr)
+
+
+class HostScaling:
+    """:class:`ShardedScaling` for tensors that live in PINNED HOST memory.
+
+    A call enqueues, and returns without waiting: the host-to-device copy of the slab on a copy
+    stream, the four phases on the compute stream, the device-to-host copy of the result and of
+    the scalars on a second copy stream.  Two sets of device buffers alternate between calls, so
+    the upload of call k+1 runs while call k is being read back -- PCIe carries both directions
+    at once -- and the kernels (about 2 % of a call at PCIe speeds) disappear behind the copies.
+    ``synchronize()`` waits for everything enqueued; the host result of a call is complete after
+    it, or once a later call has reused that call's buffer set (every second call).
+    """
+
+    def __init__(self, rows_local: int, cols: int, brows: int, bcols: int, dtype: torch.dtype, device: torch.device,
+                 kind: int = KIND_BLOCK, group: Optional[dist.ProcessGroup] = None, backend_factory=None):
+        self.device = device
+        make = backend_factory or (lambda: None)
+        self.ops = [ShardedScaling(rows_local, cols, brows, bcols, dtype, device, kind, group, make()) for _ in range(2)]
+        self.x = [torch.empty(rows_local, cols, dtype=dtype, device=device) for _ in range(2)]
+        self.out = [torch.empty(rows_local, cols, dtype=dtype, device=device) for _ in range(2)]
+        self.s_in, self.s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+        self.uploaded = [torch.cuda.Event() for _ in range(2)]
+        self.computed = [torch.cuda.Event() for _ in range(2)]
+        self.read_back = [torch.cuda.Event() for _ in range(2)]
+        self.calls = 0
+
+    def __call__(self, x_host: torch.Tensor, out_host: torch.Tensor, scalars_host: torch.Tensor, ss_mode: int,
+                 threshold: float) -> ScalingResult:
+        """``x_host`` / ``out_host``: pinned tensors of the slab's shape; ``scalars_host``: pinned float32[2]
+        that receives (global_amax, global_error).  Returns the device-side scalars of this call."""
+        if not (x_host.is_pinned() and out_host.is_pinned() and scalars_host.is_pinned()):
+            raise ValueError("HostScaling needs pinned host tensors (torch.empty(..., pin_memory=True))")
+        b = self.calls & 1
+        main = torch.cuda.current_stream(self.device)
+        if self.calls >= 2:
+            self.s_in.wait_event(self.computed[b])     # the kernels that read this input buffer two calls ago
+        with torch.cuda.stream(self.s_in):
+            self.x[b].copy_(x_host, non_blocking=True)
+            self.uploaded[b].record()
+        main.wait_event(self.uploaded[b])
+        if self.calls >= 2:
+            main.wait_event(self.read_back[b])         # the read-back that still used this output buffer
+        res = self.ops[b](self.x[b], self.out[b], ss_mode, threshold)
+        self.computed[b].record(main)
+        self.s_out.wait_event(self.computed[b])
+        with torch.cuda.stream(self.s_out):
+            out_host.copy_(self.out[b], non_blocking=True)
+            scalars_host[0:1].copy_(res.global_amax, non_blocking=True)
+            scalars_host[1:2].copy_(res.global_error, non_blocking=True)
+            self.read_back[b].record()
+        self.calls += 1
+        return res
+
+    def synchronize(self):
+        self.s_out.synchronize()
+        torch.cuda.current_stream(self.device).synchronize()

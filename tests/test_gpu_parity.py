@@ -455,6 +455,31 @@ def test_quantize_mx_round_trip_full_size():
         assert float(same.float().mean()) > 0.9
 
 
+def test_host_pipeline_matches_device_call():
+    """HostScaling (pinned host in/out, double-buffered copies) gives the bits of the device-side call,
+    call after call, with a different tensor in every call"""
+    from mor_b200.sharded import HostScaling, ShardedScaling, KIND_BLOCK
+    dev = torch.device("cuda", 0)
+    rows, cols = 512, 1024
+    host = HostScaling(rows, cols, 128, 128, torch.float32, dev, KIND_BLOCK)
+    direct = ShardedScaling(rows, cols, 128, 128, torch.float32, dev, KIND_BLOCK)
+    g = torch.Generator().manual_seed(77)
+    xs = [torch.randn(rows, cols, generator=g) * (10.0 ** i) for i in range(5)]
+    outs_h = [torch.empty(rows, cols, pin_memory=True) for _ in xs]
+    scal_h = [torch.empty(2, pin_memory=True) for _ in xs]
+    pinned = [x.pin_memory() for x in xs]
+    for xp, oh, sh in zip(pinned, outs_h, scal_h):
+        host(xp, oh, sh, 1, 0.045)
+    host.synchronize()
+    for x, oh, sh in zip(xs, outs_h, scal_h):
+        xd = x.to(dev)
+        od = torch.empty_like(xd)
+        r = direct(xd, od, 1, 0.045)
+        torch.cuda.synchronize()
+        assert torch.equal(od.cpu().view(torch.int32), oh.view(torch.int32))
+        assert sh[0].item() == r.global_amax.item() and sh[1].item() == r.global_error.item()
+
+
 def test_invalid_arguments_are_status_codes_not_faults():
     import gpu_harness as H
     from mor_b200 import cabi
