@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(kThreads) amax_nnz_flat_kernel(const typename 
 // One CTA per (brows x bcols) block.  W lanes (a power of two) span a block row in
 // 16-byte vectors, 256 / W rows are in flight per step; no division in the loops.
 template <typename T>
-__global__ void __launch_bounds__(kThreads) amax_nnz_blocks_kernel(const typename T::vec_t* __restrict__ in,
+__global__ void __launch_bounds__(kThreads, 8) amax_nnz_blocks_kernel(const typename T::vec_t* __restrict__ in,
                                                                    int64_t cols_vec, int brows, int bcols_vec,
                                                                    int64_t blocks_x, int w_shift,
                                                                    float* __restrict__ block_amax,
@@ -220,16 +220,9 @@ __global__ void __launch_bounds__(kThreads) amax_nnz_blocks_kernel(const typenam
     const int tx = threadIdx.x & (W - 1), ty = threadIdx.x >> w_shift;
     const typename T::vec_t* base = in + r0 * cols_vec + c0;
     Acc acc = acc_init();
-    if (brows >= 4 * RPS) {  // tall blocks: eight, then four rows in flight per lane
+    if (brows >= 4 * RPS) {  // tall blocks: four rows in flight per lane, eight CTAs per SM
         for (int cv = tx; cv < bcols_vec; cv += W) {
             int r = ty;
-            for (; r + 7 * RPS < brows; r += 8 * RPS) {
-                typename T::vec_t v[8];
-#pragma unroll
-                for (int u = 0; u < 8; ++u) v[u] = ld_keep(base + (int64_t)(r + u * RPS) * cols_vec + cv);
-#pragma unroll
-                for (int u = 0; u < 8; ++u) vec_acc_fast<T>(v[u], acc);
-            }
             for (; r + 3 * RPS < brows; r += 4 * RPS) {
                 typename T::vec_t v[4];
 #pragma unroll
