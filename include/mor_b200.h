@@ -189,6 +189,26 @@ MOR_B200_API int mor_b200_scaling_finalize(const float* block_err, int64_t n_err
 /* Phase 4: if *meta == 3, copy the slab's input over its output. */
 MOR_B200_API int mor_b200_scaling_fallback(const void* input, void* output, int64_t n_bytes, const int32_t* meta, void* stream);
 
+/* ---- peer exchange for the row-sharded pipeline (extension; the reference is single-GPU) ----
+ * Replaces the scalar all-reduces and the all-gather of the error sums by plain NVLink stores
+ * into a buffer that every rank allocates (mor_b200_p2p_bytes, zero-filled, 256-byte aligned)
+ * and maps from all its peers; peer_bufs[r] is rank r's buffer as seen from this process
+ * (peer_bufs[rank] = the own one).  epoch counts the calls (1, 2, ...; the same on every rank).
+ * Order per call, all on one stream:  scaling_amax -> p2p_publish_scalars -> p2p_gather_scalars
+ * (writes global amax and nnz) -> scaling_cast -> p2p_push_errors -> p2p_wait_errors ->
+ * scaling_finalize on (own buffer + p2p_error_offset, world * n_err entries) -> scaling_fallback.
+ * Waits are bounded (about two seconds); a time-out sets a flag in the workspace head and
+ * scaling_finalize then reports meta = -1.  world <= 16. */
+MOR_B200_API size_t mor_b200_p2p_bytes(int world, int64_t n_err);
+MOR_B200_API size_t mor_b200_p2p_error_offset(int world, int64_t n_err, uint32_t epoch);
+MOR_B200_API int mor_b200_p2p_publish_scalars(const void* workspace, void* const* peer_bufs, int rank, int world,
+                                 uint32_t epoch, void* stream);
+MOR_B200_API int mor_b200_p2p_gather_scalars(void* my_buf, int world, uint32_t epoch, float* global_amax,
+                                int64_t* global_nnz, void* workspace, void* stream);
+MOR_B200_API int mor_b200_p2p_push_errors(const float* local_err, int64_t n_err, void* const* peer_bufs, int rank,
+                             int world, uint32_t epoch, void* stream);
+MOR_B200_API int mor_b200_p2p_wait_errors(const void* my_buf, int world, uint32_t epoch, void* workspace, void* stream);
+
 /* amax and non-zero count of a flat tensor (kernels 951-1049 without the block array). */
 MOR_B200_API int mor_b200_amax_nnz(const void* input, int dtype, int64_t n_elems, float* amax_out, int64_t* nnz_out,
                       void* workspace, size_t workspace_bytes, void* stream);

@@ -365,6 +365,30 @@ int mor_b200_scaling_fallback(const void* in, void* out, int64_t n_bytes, const 
     return check_launch();
 }
 
+size_t mor_b200_p2p_bytes(int world, int64_t n_err) { return p2p_buffer_bytes(world, n_err); }
+size_t mor_b200_p2p_error_offset(int world, int64_t n_err, uint32_t epoch) { return p2p_error_offset(world, n_err, epoch); }
+
+int mor_b200_p2p_publish_scalars(const void* wsp, void* const* peer_bufs, int rank, int world, uint32_t epoch,
+                                 void* stream) {
+    if (!wsp || !aligned16(wsp)) return kErrWorkspace;
+    return launch_p2p_publish_scalars(static_cast<const ScalarsWs*>(wsp), peer_bufs, rank, world, epoch,
+                                      static_cast<cudaStream_t>(stream));
+}
+int mor_b200_p2p_gather_scalars(void* my_buf, int world, uint32_t epoch, float* global_amax, int64_t* global_nnz,
+                                void* wsp, void* stream) {
+    if (!wsp || !aligned16(wsp)) return kErrWorkspace;
+    return launch_p2p_gather_scalars(my_buf, world, epoch, global_amax, reinterpret_cast<long long*>(global_nnz),
+                                     static_cast<ScalarsWs*>(wsp), static_cast<cudaStream_t>(stream));
+}
+int mor_b200_p2p_push_errors(const float* local_err, int64_t n_err, void* const* peer_bufs, int rank, int world,
+                             uint32_t epoch, void* stream) {
+    return launch_p2p_push_errors(local_err, n_err, peer_bufs, rank, world, epoch, static_cast<cudaStream_t>(stream));
+}
+int mor_b200_p2p_wait_errors(const void* my_buf, int world, uint32_t epoch, void* wsp, void* stream) {
+    if (!wsp || !aligned16(wsp)) return kErrWorkspace;
+    return launch_p2p_wait_errors(my_buf, world, epoch, static_cast<ScalarsWs*>(wsp), static_cast<cudaStream_t>(stream));
+}
+
 int mor_b200_amax_nnz(const void* in, int dtype, int64_t n, float* amax_out, int64_t* nnz_out, void* wsp, size_t wsb,
                       void* stream) {
     if (!in || n <= 0 || (dtype != MOR_B200_BF16 && dtype != MOR_B200_FP32)) return kErrInvalidArgument;

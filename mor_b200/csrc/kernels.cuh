@@ -81,4 +81,15 @@ int launch_quantize_mx(const void* in, void* payload, uint8_t* scales, int64_t r
 int launch_fq_group(const void* in, void* out, int is_fp32, float* scales, int32_t* meta, int32_t meta_code,
                     int64_t rows, int64_t cols, int bcols, int fmt, int sf_type, cudaStream_t st);
 
+// ---- p2p.cu: peer exchange of the row-sharded pipeline (plain NVLink stores + epoch flags)
+size_t p2p_buffer_bytes(int world, int64_t n_err);
+size_t p2p_error_offset(int world, int64_t n_err, uint32_t epoch);
+int launch_p2p_publish_scalars(const ScalarsWs* ws, void* const* peer_bufs, int rank, int world, uint32_t epoch,
+                               cudaStream_t st);
+int launch_p2p_gather_scalars(void* mine, int world, uint32_t epoch, float* gamax_out, long long* gnnz_out,
+                              ScalarsWs* ws, cudaStream_t st);
+int launch_p2p_push_errors(const float* local_err, int64_t n_err, void* const* peer_bufs, int rank, int world,
+                           uint32_t epoch, cudaStream_t st);
+int launch_p2p_wait_errors(const void* mine, int world, uint32_t epoch, ScalarsWs* ws, cudaStream_t st);
+
 }  // namespace morb

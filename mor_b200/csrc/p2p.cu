@@ -1,0 +1,169 @@
+// Peer exchange of the row-sharded pipeline over NVLink (no reference counterpart: the
+// reference is single-GPU).  Replaces the two scalar all-reduces and the all-gather of the
+// per-block error sums by plain stores into buffers that every rank maps from its peers,
+// completed by epoch flags:
+//
+//   publish  (after the slab amax kernel)   one lane per peer stores this rank's (amax, nnz)
+//                                           into the peer's slot, fences, stores the epoch;
+//   gather   (before the cast kernel)       one lane per peer waits for the epoch in its own
+//                                           buffer, then max / sum over the slots;
+//   push     (after the cast kernel)        copies the slab's error sums into every rank's
+//                                           gathered array, then a flag per peer;
+//   wait     (before the ordered sum)       waits for every rank's flag.
+//
+// Only plain peer stores and local loads are used (no multicast, no multimem); slots and
+// arrays alternate between two copies by epoch parity, which is enough because a rank can
+// be at most one call ahead of the slowest one.  Every wait is bounded: after the limit the
+// kernel records the time-out in the workspace head (the call then reports meta = -1) and
+// returns, so a lost peer cannot hang the GPU.
+#include "kernels.cuh"
+
+namespace morb {
+
+namespace {
+
+constexpr int kMaxWorld = 16;
+constexpr size_t kScalOffset = 0, kScalBytes = 2 * kMaxWorld * 32;
+constexpr size_t kFlagOffset = kScalBytes, kErrOffset = 2048;
+constexpr uint32_t kP2PSpinLimit = 1u << 23;  // x 200 ns of back-off: about two seconds
+
+struct ScalSlot {
+    uint32_t amax_bits;
+    uint32_t pad0;
+    unsigned long long nnz;
+    uint32_t flag;
+    uint32_t pad1[3];
+};
+static_assert(sizeof(ScalSlot) == 32, "slot size");
+
+struct PeerPtrs {
+    unsigned char* p[kMaxWorld];
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ bool wait_epoch(const uint32_t* flag, uint32_t epoch) {
+    for (uint32_t i = 0; i < kP2PSpinLimit; ++i) {
+        if (ld_acquire_sys(flag) == epoch) return true;
+        __nanosleep(200);
+    }
+    return false;
+}
+
+__global__ void p2p_publish_scalars_kernel(const ScalarsWs* __restrict__ ws, PeerPtrs peers, int rank, int world,
+                                           uint32_t epoch) {
+    const int p = threadIdx.x;
+    if (p >= world) return;
+    ScalSlot* slot = reinterpret_cast<ScalSlot*>(peers.p[p] + kScalOffset) + (epoch & 1u) * kMaxWorld + rank;
+    slot->amax_bits = ws->gamax_bits;
+    slot->nnz = ws->gnnz;
+    __threadfence_system();
+    st_release_sys(&slot->flag, epoch);
+}
+
+__global__ void p2p_gather_scalars_kernel(unsigned char* __restrict__ mine, int world, uint32_t epoch,
+                                          float* __restrict__ gamax_out, long long* __restrict__ gnnz_out,
+                                          ScalarsWs* __restrict__ ws) {
+    const int p = threadIdx.x;  // one warp
+    const ScalSlot* slot = reinterpret_cast<const ScalSlot*>(mine + kScalOffset) + (epoch & 1u) * kMaxWorld + p;
+    uint32_t amax_bits = 0u;
+    unsigned long long nnz = 0ull;
+    bool ok = true;
+    if (p < world) {
+        ok = wait_epoch(&slot->flag, epoch);
+        if (ok) { amax_bits = *reinterpret_cast<const volatile uint32_t*>(&slot->amax_bits); nnz = *reinterpret_cast<const volatile unsigned long long*>(&slot->nnz); }
+    }
+    if (!__all_sync(0xFFFFFFFFu, ok) && p == 0) atomicOr(&ws->load_timeout, 1u);
+    amax_bits = __reduce_max_sync(0xFFFFFFFFu, amax_bits);   // non-negative floats order like their bit patterns
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) nnz += __shfl_xor_sync(0xFFFFFFFFu, nnz, o);
+    if (p == 0) {
+        *gamax_out = u2f(amax_bits);
+        *gnnz_out = (long long)nnz;
+    }
+}
+
+__global__ void __launch_bounds__(256) p2p_push_errors_kernel(const float* __restrict__ local_err, int64_t n_err,
+                                                             PeerPtrs peers, int rank, int world, uint32_t epoch) {
+    const int64_t stride = (int64_t)gridDim.x * 256;
+    const size_t base = kErrOffset + ((size_t)(epoch & 1u) * world + rank) * (size_t)n_err * sizeof(float);
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n_err; i += stride) {
+        const float v = local_err[i];
+        for (int p = 0; p < world; ++p) reinterpret_cast<float*>(peers.p[p] + base)[i] = v;
+    }
+}
+// launched behind the copy on the same stream: the copy's stores are complete when this starts
+__global__ void p2p_flag_errors_kernel(PeerPtrs peers, int rank, int world, uint32_t epoch) {
+    const int p = threadIdx.x;
+    if (p >= world) return;
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<uint32_t*>(peers.p[p] + kFlagOffset) + (epoch & 1u) * kMaxWorld + rank, epoch);
+}
+
+__global__ void p2p_wait_errors_kernel(const unsigned char* __restrict__ mine, int world, uint32_t epoch,
+                                       ScalarsWs* __restrict__ ws) {
+    const int p = threadIdx.x;  // one warp
+    bool ok = true;
+    if (p < world) ok = wait_epoch(reinterpret_cast<const uint32_t*>(mine + kFlagOffset) + (epoch & 1u) * kMaxWorld + p, epoch);
+    if (!__all_sync(0xFFFFFFFFu, ok) && p == 0) atomicOr(&ws->load_timeout, 1u);
+}
+
+bool fill_peers(PeerPtrs& pp, void* const* peer_bufs, int world) {
+    if (!peer_bufs || world < 1 || world > kMaxWorld) return false;
+    for (int i = 0; i < kMaxWorld; ++i) pp.p[i] = nullptr;
+    for (int i = 0; i < world; ++i) {
+        if (!peer_bufs[i] || (reinterpret_cast<uintptr_t>(peer_bufs[i]) & 255u)) return false;
+        pp.p[i] = static_cast<unsigned char*>(peer_bufs[i]);
+    }
+    return true;
+}
+
+}  // namespace
+
+size_t p2p_buffer_bytes(int world, int64_t n_err) {
+    if (world < 1 || world > kMaxWorld || n_err < 1) return 0;
+    return (kErrOffset + 2 * (size_t)world * (size_t)n_err * sizeof(float) + 255) & ~size_t(255);
+}
+size_t p2p_error_offset(int world, int64_t n_err, uint32_t epoch) {
+    return kErrOffset + (size_t)(epoch & 1u) * (size_t)world * (size_t)n_err * sizeof(float);
+}
+
+int launch_p2p_publish_scalars(const ScalarsWs* ws, void* const* peer_bufs, int rank, int world, uint32_t epoch,
+                               cudaStream_t st) {
+    PeerPtrs pp;
+    if (!ws || !fill_peers(pp, peer_bufs, world) || rank < 0 || rank >= world) return kErrInvalidArgument;
+    p2p_publish_scalars_kernel<<<1, 32, 0, st>>>(ws, pp, rank, world, epoch);
+    return check_launch();
+}
+int launch_p2p_gather_scalars(void* mine, int world, uint32_t epoch, float* gamax_out, long long* gnnz_out,
+                              ScalarsWs* ws, cudaStream_t st) {
+    if (!mine || !gamax_out || !gnnz_out || !ws || world < 1 || world > kMaxWorld) return kErrInvalidArgument;
+    p2p_gather_scalars_kernel<<<1, 32, 0, st>>>(static_cast<unsigned char*>(mine), world, epoch, gamax_out, gnnz_out, ws);
+    return check_launch();
+}
+int launch_p2p_push_errors(const float* local_err, int64_t n_err, void* const* peer_bufs, int rank, int world,
+                           uint32_t epoch, cudaStream_t st) {
+    PeerPtrs pp;
+    if (!local_err || n_err < 1 || !fill_peers(pp, peer_bufs, world) || rank < 0 || rank >= world) return kErrInvalidArgument;
+    int64_t grid = (n_err + 255) / 256;
+    const int64_t cap = (int64_t)sm_count() * 4;
+    if (grid > cap) grid = cap;
+    p2p_push_errors_kernel<<<(unsigned)grid, 256, 0, st>>>(local_err, n_err, pp, rank, world, epoch);
+    int rc = check_launch();
+    if (rc) return rc;
+    p2p_flag_errors_kernel<<<1, 32, 0, st>>>(pp, rank, world, epoch);
+    return check_launch();
+}
+int launch_p2p_wait_errors(const void* mine, int world, uint32_t epoch, ScalarsWs* ws, cudaStream_t st) {
+    if (!mine || !ws || world < 1 || world > kMaxWorld) return kErrInvalidArgument;
+    p2p_wait_errors_kernel<<<1, 32, 0, st>>>(static_cast<const unsigned char*>(mine), world, epoch, ws);
+    return check_launch();
+}
+
+}  // namespace morb

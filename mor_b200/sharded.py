@@ -96,10 +96,61 @@ class CudaBackend:
                   self.ws.data_ptr(), self.ws_bytes, self._stream())
         self.launches += 2 if all_err.numel() > 65536 else 1  # long arrays: partial sums over several CTAs first
 
+    def publish_scalars(self, ex: "PeerExchange", epoch: int):
+        cabi.call("mor_b200_p2p_publish_scalars", self.ws.data_ptr(), ex.peer_array, ex.rank, ex.world, epoch, self._stream())
+        self.launches += 1
+
+    def gather_scalars(self, ex: "PeerExchange", epoch: int, amax_out, nnz_out):
+        cabi.call("mor_b200_p2p_gather_scalars", ex.mine.data_ptr(), ex.world, epoch, amax_out.data_ptr(),
+                  nnz_out.data_ptr(), self.ws.data_ptr(), self._stream())
+        self.launches += 1
+
+    def push_errors(self, ex: "PeerExchange", epoch: int, local_err):
+        cabi.call("mor_b200_p2p_push_errors", local_err.data_ptr(), local_err.numel(), ex.peer_array, ex.rank, ex.world,
+                  epoch, self._stream())
+        self.launches += 2
+
+    def wait_errors(self, ex: "PeerExchange", epoch: int):
+        cabi.call("mor_b200_p2p_wait_errors", ex.mine.data_ptr(), ex.world, epoch, self.ws.data_ptr(), self._stream())
+        self.launches += 1
+
     def fallback(self, x, out, meta):
         cabi.call("mor_b200_scaling_fallback", x.data_ptr(), out.data_ptr(), x.numel() * x.element_size(),
                   meta.data_ptr(), self._stream())
         self.launches += 1
+
+
+class PeerExchange:
+    """Buffers of all ranks mapped into every rank (CUDA IPC over NVLink), for the peer exchange of
+    include/mor_b200.h: every rank allocates one zero-filled buffer, the handles travel through the
+    process group once, and kernels store into the peers' buffers directly.  Construction is a
+    collective call; it raises if a peer's buffer cannot be opened."""
+
+    def __init__(self, n_err: int, device: torch.device, group: Optional[dist.ProcessGroup] = None):
+        import ctypes
+        from torch.multiprocessing.reductions import reduce_tensor
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.n_err = n_err
+        nbytes = int(cabi.lib().mor_b200_p2p_bytes(self.world, n_err))
+        if nbytes == 0:
+            raise ValueError(f"peer exchange supports up to 16 ranks (world = {self.world})")
+        self.mine = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        torch.cuda.synchronize(device)
+        rebuild, args = reduce_tensor(self.mine)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, (rebuild, args), group=group)
+        self.peers = [self.mine if r == self.rank else handles[r][0](*handles[r][1]) for r in range(self.world)]
+        ptrs = [t.data_ptr() for t in self.peers]
+        if any(p % 256 for p in ptrs):
+            raise RuntimeError("peer buffers are not 256-byte aligned")
+        self.peer_array = (ctypes.c_void_p * self.world)(*ptrs)
+        self.epoch = 0
+        dist.barrier(group=group)   # nobody stores into a buffer that is not mapped and zeroed yet
+
+    def error_view(self, epoch: int) -> torch.Tensor:
+        off = int(cabi.lib().mor_b200_p2p_error_offset(self.world, self.n_err, epoch))
+        return self.mine[off:off + 4 * self.world * self.n_err].view(torch.float32)
 
 
 class ShardedScaling:
@@ -111,7 +162,11 @@ class ShardedScaling:
 
     def __init__(self, rows_local: int, cols: int, brows: int, bcols: int, dtype: torch.dtype,
                  device: torch.device, kind: int = KIND_BLOCK, group: Optional[dist.ProcessGroup] = None,
-                 backend=None):
+                 backend=None, exchange: str = "auto"):
+        """``exchange``: "nccl" (two all-reduces and an all-gather), "p2p" (stores into peer-mapped
+        buffers, :class:`PeerExchange`), or "auto": p2p with the CUDA backend on more than one rank when
+        the peer buffers can be set up, NCCL otherwise.  The choice is made once, here, by all ranks
+        together; both give the same bits."""
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.device = device
@@ -125,9 +180,39 @@ class ShardedScaling:
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.local_err = self.all_err[self.rank * n_err:(self.rank + 1) * n_err]
         self.collectives = 0
+        self.peer = None
+        if exchange not in ("auto", "nccl", "p2p"):
+            raise ValueError("exchange must be 'auto', 'nccl' or 'p2p'")
+        if self.world > 1 and exchange != "nccl" and isinstance(self.backend, CudaBackend):
+            ok, err = 1, None
+            try:
+                self.peer = PeerExchange(n_err, device, group)
+            except Exception as e:  # noqa: BLE001  (no IPC between these processes, more than 16 ranks, ...)
+                ok, err = 0, e
+            flag = torch.tensor([ok], dtype=torch.int32, device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+            if int(flag.item()) == 0:   # one rank could not: every rank uses NCCL
+                self.peer = None
+                if exchange == "p2p":
+                    raise RuntimeError(f"peer exchange could not be set up on every rank: {err}")
+            else:
+                self.local_err = torch.zeros(n_err, dtype=torch.float32, device=device)
 
     def __call__(self, x: torch.Tensor, out: torch.Tensor, ss_mode: int, threshold: float) -> ScalingResult:
         b = self.backend
+        if self.peer is not None:
+            ex = self.peer
+            ex.epoch += 1
+            ep = ex.epoch
+            b.amax_nnz(x, self.amax, self.nnz)
+            b.publish_scalars(ex, ep)
+            b.gather_scalars(ex, ep, self.amax, self.nnz)
+            b.cast(x, out, ss_mode, self.amax, self.local_err)
+            b.push_errors(ex, ep, self.local_err)
+            b.wait_errors(ex, ep)
+            b.finalize(ex.error_view(ep), self.nnz, threshold, self.meta, self.gerr)
+            b.fallback(x, out, self.meta)
+            return ScalingResult(self.meta, self.amax, self.nnz, self.gerr)
         b.amax_nnz(x, self.amax, self.nnz)
         nnz_done = None
         if self.world > 1:

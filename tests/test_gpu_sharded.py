@@ -10,7 +10,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, dtype_name, ss_mode, thr, q):
+def _worker(rank, world, port, dtype_name, ss_mode, thr, q, exchange="nccl", calls=1):
     import torch.distributed as dist
     from mor_b200.sharded import KIND_BLOCK, ShardedScaling, shard_rows
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -26,8 +26,10 @@ def _worker(rank, world, port, dtype_name, ss_mode, thr, q):
         r0, r1 = shard_rows(x.shape[0], world, rank, 128)
         xs = x[r0:r1].contiguous().to(dev)
         out = torch.empty_like(xs)
-        op = ShardedScaling(r1 - r0, x.shape[1], 128, 128, dtype, dev, KIND_BLOCK)
-        res = op(xs, out, ss_mode, thr)
+        op = ShardedScaling(r1 - r0, x.shape[1], 128, 128, dtype, dev, KIND_BLOCK, exchange=exchange)
+        assert (op.peer is not None) == (exchange == "p2p")
+        for _ in range(calls):     # several calls: the epoch flags and the two buffer copies alternate
+            res = op(xs, out, ss_mode, thr)
         torch.cuda.synchronize()
         o = out.cpu()
         o = o.view(torch.int16).numpy().view(np.uint16) if dtype == torch.bfloat16 else o.numpy()
@@ -37,8 +39,10 @@ def _worker(rank, world, port, dtype_name, ss_mode, thr, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("dtype_name,ss_mode,thr", [("bfloat16", 1, 0.045), ("float32", 1, 0.045), ("float32", 4, 1e-6)])
-def test_two_gpus_equal_oracle(dtype_name, ss_mode, thr):
+@pytest.mark.parametrize("dtype_name,ss_mode,thr,exchange,calls", [
+    ("bfloat16", 1, 0.045, "nccl", 1), ("float32", 1, 0.045, "nccl", 1), ("float32", 4, 1e-6, "nccl", 1),
+    ("bfloat16", 1, 0.045, "p2p", 5), ("float32", 4, 1e-6, "p2p", 2)])
+def test_two_gpus_equal_oracle(dtype_name, ss_mode, thr, exchange, calls):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -46,7 +50,7 @@ def test_two_gpus_equal_oracle(dtype_name, ss_mode, thr):
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, dtype_name, ss_mode, thr, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, dtype_name, ss_mode, thr, q, exchange, calls)) for r in range(2)]
     for p in procs:
         p.start()
     got = sorted((q.get(timeout=180) for _ in range(2)), key=lambda t: t[0])
