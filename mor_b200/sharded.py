@@ -162,7 +162,7 @@ class ShardedScaling:
 
     def __init__(self, rows_local: int, cols: int, brows: int, bcols: int, dtype: torch.dtype,
                  device: torch.device, kind: int = KIND_BLOCK, group: Optional[dist.ProcessGroup] = None,
-                 backend=None, exchange: str = "auto"):
+                 backend=None, exchange: str = "nccl"):
         """``exchange``: "nccl" (two all-reduces and an all-gather), "p2p" (stores into peer-mapped
         buffers, :class:`PeerExchange`), or "auto": p2p with the CUDA backend on more than one rank when
         the peer buffers can be set up, NCCL otherwise.  The choice is made once, here, by all ranks
