@@ -163,6 +163,8 @@ def main():
                     help="reference: time the unmodified reference CUDA extension (oracle/_ref) on the configurations it supports")
     ap.add_argument("--suite-graph", action="store_true", help="also time the suite calls replayed as one CUDA graph")
     ap.add_argument("--suite-out", default=None, help="where --suite writes its table (default gpurun_out/suite.json)")
+    ap.add_argument("--exchange", choices=["auto", "nccl", "p2p"], default="auto",
+                    help="how ranks exchange amax / non-zero count / error sums (N > 1): NCCL collectives or peer stores")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -219,7 +221,7 @@ def main():
     for i in range(0, rows_local, chunk):
         x[i:i + chunk].normal_(generator=g)
     out = torch.empty_like(x)
-    op = ShardedScaling(rows_local, COLS, BLOCK, BLOCK, torch.float32, dev, KIND_BLOCK)
+    op = ShardedScaling(rows_local, COLS, BLOCK, BLOCK, torch.float32, dev, KIND_BLOCK, exchange=args.exchange)
 
     # events around the dominant kernel (scale + cast + error sums), on the launching stream
     cast_events = []
@@ -285,7 +287,7 @@ def main():
         out = None
         torch.cuda.empty_cache()
         from mor_b200.sharded import HostScaling
-        host_op = HostScaling(rows_local, COLS, BLOCK, BLOCK, torch.float32, dev, KIND_BLOCK)
+        host_op = HostScaling(rows_local, COLS, BLOCK, BLOCK, torch.float32, dev, KIND_BLOCK, exchange=args.exchange)
 
         def e2e_step():
             host_op(xh, oh, scal_h, SS_MODE, THRESHOLD)
@@ -330,7 +332,8 @@ def main():
             "config": {"workload": f"config5: float32 {rows}x{COLS} (8 GiB / scale {args.scale}), row-sharded over "
                                    f"{n_gpus} GPU(s), 128x128 block scaling ss_mode 1 with global amax",
                        "bytes_per_element": BYTES_PER_ELEM_TWO_PASS, "l2": "inputs larger than L2, no flush",
-                       "threshold": THRESHOLD, "meta": meta},
+                       "threshold": THRESHOLD, "meta": meta,
+                       "exchange": ("single GPU" if n_gpus == 1 else ("peer stores over NVLink" if op.peer is not None else "NCCL"))},
             "elements_per_s": total_elems / (step_ms * 1e-3),
             "per_gpu": {"GB/s": value / n_gpus, "elements_per_s": total_elems / (step_ms * 1e-3) / n_gpus,
                         "pct_of_hbm_peak": 100.0 * value / n_gpus / peak, "peak_GB/s": peak, "peak_kind": peak_kind},

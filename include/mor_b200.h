@@ -191,14 +191,23 @@ MOR_B200_API int mor_b200_scaling_fallback(const void* input, void* output, int6
 
 /* ---- peer exchange for the row-sharded pipeline (extension; the reference is single-GPU) ----
  * Replaces the scalar all-reduces and the all-gather of the error sums by plain NVLink stores
- * into a buffer that every rank allocates (mor_b200_p2p_bytes, zero-filled, 256-byte aligned)
- * and maps from all its peers; peer_bufs[r] is rank r's buffer as seen from this process
+ * into a buffer that every rank allocates (mor_b200_p2p_alloc with mor_b200_p2p_bytes) and maps
+ * from all its peers (mor_b200_p2p_open); peer_bufs[r] is rank r's buffer as seen from this process
  * (peer_bufs[rank] = the own one).  epoch counts the calls (1, 2, ...; the same on every rank).
  * Order per call, all on one stream:  scaling_amax -> p2p_publish_scalars -> p2p_gather_scalars
  * (writes global amax and nnz) -> scaling_cast -> p2p_push_errors -> p2p_wait_errors ->
  * scaling_finalize on (own buffer + p2p_error_offset, world * n_err entries) -> scaling_fallback.
  * Waits are bounded (about two seconds); a time-out sets a flag in the workspace head and
  * scaling_finalize then reports meta = -1.  world <= 16. */
+/* The exchange buffer is allocated (cudaMalloc, zero-filled), exported (64-byte CUDA IPC handle,
+ * to be sent to the other processes by any means) and opened by the library: a peer's buffer must
+ * be opened while `device`, the GPU whose kernels will store into it, is current.  close() unmaps
+ * a peer's buffer, free() releases the own one (after every peer has closed it). */
+#define MOR_B200_P2P_HANDLE_BYTES 64
+MOR_B200_API int mor_b200_p2p_alloc(int device, size_t bytes, void** ptr_out, unsigned char* handle_out);
+MOR_B200_API int mor_b200_p2p_open(int device, const unsigned char* handle, void** ptr_out);
+MOR_B200_API int mor_b200_p2p_close(int device, void* peer_ptr);
+MOR_B200_API int mor_b200_p2p_free(int device, void* own_ptr);
 MOR_B200_API size_t mor_b200_p2p_bytes(int world, int64_t n_err);
 MOR_B200_API size_t mor_b200_p2p_error_offset(int world, int64_t n_err, uint32_t epoch);
 MOR_B200_API int mor_b200_p2p_publish_scalars(const void* workspace, void* const* peer_bufs, int rank, int world,

@@ -40,6 +40,10 @@ SIGNATURES = {
     "mor_b200_scaling_finalize": (_i, [_vp, _i64, _i, _vp, _d, _vp, _vp, _vp, _sz, _vp]),
     "mor_b200_scaling_fallback": (_i, [_vp, _vp, _i64, _vp, _vp]),
     "mor_b200_amax_nnz": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _sz, _vp]),
+    "mor_b200_p2p_alloc": (_i, [_i, _sz, _vp, _vp]),
+    "mor_b200_p2p_open": (_i, [_i, _vp, _vp]),
+    "mor_b200_p2p_close": (_i, [_i, _vp]),
+    "mor_b200_p2p_free": (_i, [_i, _vp]),
     "mor_b200_p2p_bytes": (_sz, [_i, _i64]),
     "mor_b200_p2p_error_offset": (_sz, [_i, _i64, C.c_uint32]),
     "mor_b200_p2p_publish_scalars": (_i, [_vp, _vp, _i, _i, C.c_uint32, _vp]),

@@ -4,6 +4,8 @@
 
 #include <mutex>
 
+#include <cstring>
+
 #include "kernels.cuh"
 
 using namespace morb;
@@ -367,6 +369,62 @@ int mor_b200_scaling_fallback(const void* in, void* out, int64_t n_bytes, const 
 
 size_t mor_b200_p2p_bytes(int world, int64_t n_err) { return p2p_buffer_bytes(world, n_err); }
 size_t mor_b200_p2p_error_offset(int world, int64_t n_err, uint32_t epoch) { return p2p_error_offset(world, n_err, epoch); }
+
+// The buffer is allocated, exported and opened here, not through the caller's allocator: a peer's
+// buffer has to be opened while the CURRENT device is the one whose kernels will store into it
+// (cudaIpcOpenMemHandle maps it for that device and enables peer access to its owner).
+namespace {
+struct DeviceScope {
+    int prev = -1;
+    bool ok = false;
+    explicit DeviceScope(int device) { ok = cudaGetDevice(&prev) == cudaSuccess && cudaSetDevice(device) == cudaSuccess; }
+    ~DeviceScope() { if (prev >= 0) cudaSetDevice(prev); }
+};
+}  // namespace
+
+int mor_b200_p2p_alloc(int device, size_t bytes, void** ptr_out, unsigned char* handle_out) {
+    if (device < 0 || bytes == 0 || !ptr_out || !handle_out) return kErrInvalidArgument;
+    static_assert(sizeof(cudaIpcMemHandle_t) == MOR_B200_P2P_HANDLE_BYTES, "handle size");
+    DeviceScope scope(device);
+    if (!scope.ok) return kErrLaunch;
+    void* p = nullptr;
+    if (cudaMalloc(&p, bytes) != cudaSuccess) { cudaGetLastError(); return kErrWorkspace; }
+    cudaIpcMemHandle_t h;
+    if (cudaMemset(p, 0, bytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess ||
+        cudaIpcGetMemHandle(&h, p) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(p);
+        return kErrLaunch;
+    }
+    memcpy(handle_out, &h, sizeof(h));
+    *ptr_out = p;
+    return kOk;
+}
+int mor_b200_p2p_open(int device, const unsigned char* handle, void** ptr_out) {
+    if (device < 0 || !handle || !ptr_out) return kErrInvalidArgument;
+    DeviceScope scope(device);
+    if (!scope.ok) return kErrLaunch;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void* p = nullptr;
+    if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { cudaGetLastError(); return kErrLaunch; }
+    *ptr_out = p;
+    return kOk;
+}
+int mor_b200_p2p_close(int device, void* peer_ptr) {
+    if (device < 0 || !peer_ptr) return kErrInvalidArgument;
+    DeviceScope scope(device);
+    if (!scope.ok) return kErrLaunch;
+    if (cudaIpcCloseMemHandle(peer_ptr) != cudaSuccess) { cudaGetLastError(); return kErrLaunch; }
+    return kOk;
+}
+int mor_b200_p2p_free(int device, void* own_ptr) {
+    if (device < 0 || !own_ptr) return kErrInvalidArgument;
+    DeviceScope scope(device);
+    if (!scope.ok) return kErrLaunch;
+    if (cudaFree(own_ptr) != cudaSuccess) { cudaGetLastError(); return kErrLaunch; }
+    return kOk;
+}
 
 int mor_b200_p2p_publish_scalars(const void* wsp, void* const* peer_bufs, int rank, int world, uint32_t epoch,
                                  void* stream) {

@@ -924,14 +924,16 @@ __global__ void __launch_bounds__(kChainThreads) chain_sum_kernel(const float* _
             for (int u = 0; u < 16; ++u) x[u] = s_rows[u][threadIdx.x];
             for (int r = 0; r < kChainRows; r += 32) {
 #pragma unroll
-                for (int u = 0; u < 16; ++u) y[u] = s_rows[r + 16 + u][threadIdx.x];
-#pragma unroll
-                for (int u = 0; u < 16; ++u) acc = __fadd_rn(acc, x[u]);
+                for (int u = 0; u < 16; ++u) {
+                    y[u] = s_rows[r + 16 + u][threadIdx.x];
+                    acc = __fadd_rn(acc, x[u]);
+                }
                 const int rn = r + 32 < kChainRows ? r + 32 : 0;   // the last reload is not used
 #pragma unroll
-                for (int u = 0; u < 16; ++u) x[u] = s_rows[rn + u][threadIdx.x];
-#pragma unroll
-                for (int u = 0; u < 16; ++u) acc = __fadd_rn(acc, y[u]);
+                for (int u = 0; u < 16; ++u) {
+                    x[u] = s_rows[rn + u][threadIdx.x];
+                    acc = __fadd_rn(acc, y[u]);
+                }
             }
         }
         __syncthreads();

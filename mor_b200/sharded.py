@@ -101,7 +101,7 @@ class CudaBackend:
         self.launches += 1
 
     def gather_scalars(self, ex: "PeerExchange", epoch: int, amax_out, nnz_out):
-        cabi.call("mor_b200_p2p_gather_scalars", ex.mine.data_ptr(), ex.world, epoch, amax_out.data_ptr(),
+        cabi.call("mor_b200_p2p_gather_scalars", ex.mine, ex.world, epoch, amax_out.data_ptr(),
                   nnz_out.data_ptr(), self.ws.data_ptr(), self._stream())
         self.launches += 1
 
@@ -111,8 +111,13 @@ class CudaBackend:
         self.launches += 2
 
     def wait_errors(self, ex: "PeerExchange", epoch: int):
-        cabi.call("mor_b200_p2p_wait_errors", ex.mine.data_ptr(), ex.world, epoch, self.ws.data_ptr(), self._stream())
+        cabi.call("mor_b200_p2p_wait_errors", ex.mine, ex.world, epoch, self.ws.data_ptr(), self._stream())
         self.launches += 1
+
+    def finalize_ptr(self, err_ptr: int, n: int, global_nnz, threshold, meta, global_error):
+        cabi.call("mor_b200_scaling_finalize", err_ptr, n, self.stride, global_nnz.data_ptr(), float(threshold),
+                  meta.data_ptr(), global_error.data_ptr(), self.ws.data_ptr(), self.ws_bytes, self._stream())
+        self.launches += 2 if n > 65536 else 1
 
     def fallback(self, x, out, meta):
         cabi.call("mor_b200_scaling_fallback", x.data_ptr(), out.data_ptr(), x.numel() * x.element_size(),
@@ -122,35 +127,73 @@ class CudaBackend:
 
 class PeerExchange:
     """Buffers of all ranks mapped into every rank (CUDA IPC over NVLink), for the peer exchange of
-    include/mor_b200.h: every rank allocates one zero-filled buffer, the handles travel through the
-    process group once, and kernels store into the peers' buffers directly.  Construction is a
-    collective call; it raises if a peer's buffer cannot be opened."""
+    include/mor_b200.h: every rank allocates one zero-filled buffer through the library, the 64-byte
+    handles travel through the process group once, and kernels store into the peers' buffers
+    directly.  Construction is a collective call; it raises if a peer's buffer cannot be opened."""
 
     def __init__(self, n_err: int, device: torch.device, group: Optional[dist.ProcessGroup] = None):
         import ctypes
-        from torch.multiprocessing.reductions import reduce_tensor
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.n_err = n_err
-        nbytes = int(cabi.lib().mor_b200_p2p_bytes(self.world, n_err))
-        if nbytes == 0:
-            raise ValueError(f"peer exchange supports up to 16 ranks (world = {self.world})")
-        self.mine = torch.zeros(nbytes, dtype=torch.uint8, device=device)
-        torch.cuda.synchronize(device)
-        rebuild, args = reduce_tensor(self.mine)
+        self.group = group
+        self.device_index = device.index if device.index is not None else torch.cuda.current_device()
+        self.mine = 0
+        self.opened = []
+        # every rank runs the same collectives whatever happens locally: a failure is exchanged, not raised early
+        err = None
+        handle = (ctypes.c_ubyte * 64)()
+        try:
+            nbytes = int(cabi.lib().mor_b200_p2p_bytes(self.world, n_err))
+            if nbytes == 0:
+                raise ValueError(f"peer exchange supports up to 16 ranks (world = {self.world})")
+            ptr = ctypes.c_void_p()
+            cabi.call("mor_b200_p2p_alloc", self.device_index, nbytes, ctypes.byref(ptr), handle)
+            self.mine = int(ptr.value)
+        except Exception as e:  # noqa: BLE001
+            err = e
         handles = [None] * self.world
-        dist.all_gather_object(handles, (rebuild, args), group=group)
-        self.peers = [self.mine if r == self.rank else handles[r][0](*handles[r][1]) for r in range(self.world)]
-        ptrs = [t.data_ptr() for t in self.peers]
-        if any(p % 256 for p in ptrs):
-            raise RuntimeError("peer buffers are not 256-byte aligned")
+        dist.all_gather_object(handles, (err is None, bytes(handle)), group=group)
+        ptrs = []
+        if all(ok for ok, _ in handles):
+            try:
+                for r in range(self.world):
+                    if r == self.rank:
+                        ptrs.append(self.mine)
+                        continue
+                    q = ctypes.c_void_p()
+                    cabi.call("mor_b200_p2p_open", self.device_index,
+                              (ctypes.c_ubyte * 64).from_buffer_copy(handles[r][1]), ctypes.byref(q))
+                    self.opened.append(int(q.value))
+                    ptrs.append(int(q.value))
+            except Exception as e:  # noqa: BLE001
+                err = e
+        elif err is None:
+            err = RuntimeError("another rank could not allocate its exchange buffer")
+        oks = [None] * self.world
+        dist.all_gather_object(oks, err is None, group=group)   # also: nobody stores before every buffer is mapped
+        if not all(oks):
+            self.close(collective=False)
+            raise RuntimeError(f"peer exchange could not be set up on every rank ({err})")
+        self.peer_ptrs = ptrs
         self.peer_array = (ctypes.c_void_p * self.world)(*ptrs)
         self.epoch = 0
-        dist.barrier(group=group)   # nobody stores into a buffer that is not mapped and zeroed yet
 
-    def error_view(self, epoch: int) -> torch.Tensor:
-        off = int(cabi.lib().mor_b200_p2p_error_offset(self.world, self.n_err, epoch))
-        return self.mine[off:off + 4 * self.world * self.n_err].view(torch.float32)
+    def error_ptr(self, epoch: int) -> int:
+        return self.mine + int(cabi.lib().mor_b200_p2p_error_offset(self.world, self.n_err, epoch))
+
+    def close(self, collective: bool = True):
+        """Unmaps the peers' buffers, then (after a barrier, if ``collective``) frees the own one."""
+        if self.mine or self.opened:
+            torch.cuda.synchronize(self.device_index)
+        for q in self.opened:
+            cabi.lib().mor_b200_p2p_close(self.device_index, q)
+        self.opened = []
+        if collective and dist.is_initialized():
+            dist.barrier(group=self.group)
+        if self.mine:
+            cabi.lib().mor_b200_p2p_free(self.device_index, self.mine)
+        self.mine = 0
 
 
 class ShardedScaling:
@@ -162,7 +205,7 @@ class ShardedScaling:
 
     def __init__(self, rows_local: int, cols: int, brows: int, bcols: int, dtype: torch.dtype,
                  device: torch.device, kind: int = KIND_BLOCK, group: Optional[dist.ProcessGroup] = None,
-                 backend=None, exchange: str = "nccl"):
+                 backend=None, exchange: str = "auto"):
         """``exchange``: "nccl" (two all-reduces and an all-gather), "p2p" (stores into peer-mapped
         buffers, :class:`PeerExchange`), or "auto": p2p with the CUDA backend on more than one rank when
         the peer buffers can be set up, NCCL otherwise.  The choice is made once, here, by all ranks
@@ -184,17 +227,14 @@ class ShardedScaling:
         if exchange not in ("auto", "nccl", "p2p"):
             raise ValueError("exchange must be 'auto', 'nccl' or 'p2p'")
         if self.world > 1 and exchange != "nccl" and isinstance(self.backend, CudaBackend):
-            ok, err = 1, None
-            try:
+            try:   # raises on every rank or on none
                 self.peer = PeerExchange(n_err, device, group)
-            except Exception as e:  # noqa: BLE001  (no IPC between these processes, more than 16 ranks, ...)
-                ok, err = 0, e
-            flag = torch.tensor([ok], dtype=torch.int32, device=device)
-            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
-            if int(flag.item()) == 0:   # one rank could not: every rank uses NCCL
+            except RuntimeError:
                 self.peer = None
                 if exchange == "p2p":
-                    raise RuntimeError(f"peer exchange could not be set up on every rank: {err}")
+                    raise
+            if self.peer is None:
+                pass
             else:
                 self.local_err = torch.zeros(n_err, dtype=torch.float32, device=device)
 
@@ -210,7 +250,7 @@ class ShardedScaling:
             b.cast(x, out, ss_mode, self.amax, self.local_err)
             b.push_errors(ex, ep, self.local_err)
             b.wait_errors(ex, ep)
-            b.finalize(ex.error_view(ep), self.nnz, threshold, self.meta, self.gerr)
+            b.finalize_ptr(ex.error_ptr(ep), ex.world * ex.n_err, self.nnz, threshold, self.meta, self.gerr)
             b.fallback(x, out, self.meta)
             return ScalingResult(self.meta, self.amax, self.nnz, self.gerr)
         b.amax_nnz(x, self.amax, self.nnz)
@@ -244,10 +284,12 @@ class HostScaling:
     """
 
     def __init__(self, rows_local: int, cols: int, brows: int, bcols: int, dtype: torch.dtype, device: torch.device,
-                 kind: int = KIND_BLOCK, group: Optional[dist.ProcessGroup] = None, backend_factory=None):
+                 kind: int = KIND_BLOCK, group: Optional[dist.ProcessGroup] = None, backend_factory=None,
+                 exchange: str = "auto"):
         self.device = device
         make = backend_factory or (lambda: None)
-        self.ops = [ShardedScaling(rows_local, cols, brows, bcols, dtype, device, kind, group, make()) for _ in range(2)]
+        self.ops = [ShardedScaling(rows_local, cols, brows, bcols, dtype, device, kind, group, make(), exchange)
+                    for _ in range(2)]
         self.x = [torch.empty(rows_local, cols, dtype=dtype, device=device) for _ in range(2)]
         self.out = [torch.empty(rows_local, cols, dtype=dtype, device=device) for _ in range(2)]
         self.s_in, self.s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
