@@ -166,7 +166,8 @@ MOR_B200_API int mor_b200_quantize_mx(const void* input, void* payload, void* sc
  * and the non-zero count (sum) and all-gather the block errors between them. ---- */
 
 /* Phase 1 (kernels 951-1049 / 1459-1631): per-block amax into the workspace, slab amax
- * and non-zero count to amax_out / nnz_out (device). kind = MOR_B200_OP_BLOCK_SCALING or
+ * and non-zero count to amax_out / nnz_out (device; both may be NULL when the peer exchange
+ * below takes them from the workspace). kind = MOR_B200_OP_BLOCK_SCALING or
  * MOR_B200_OP_CHANNEL_SCALING. */
 MOR_B200_API int mor_b200_scaling_amax(int kind, const void* input, int dtype, int64_t rows, int64_t cols, int block_rows,
                           int block_cols, float* amax_out, int64_t* nnz_out, void* workspace, size_t workspace_bytes,
@@ -194,8 +195,8 @@ MOR_B200_API int mor_b200_scaling_fallback(const void* input, void* output, int6
  * into a buffer that every rank allocates (mor_b200_p2p_alloc with mor_b200_p2p_bytes) and maps
  * from all its peers (mor_b200_p2p_open); peer_bufs[r] is rank r's buffer as seen from this process
  * (peer_bufs[rank] = the own one).  epoch counts the calls (1, 2, ...; the same on every rank).
- * Order per call, all on one stream:  scaling_amax -> p2p_publish_scalars -> p2p_gather_scalars
- * (writes global amax and nnz) -> scaling_cast -> p2p_push_errors -> p2p_wait_errors ->
+ * Order per call, all on one stream:  scaling_amax (its two outputs may be NULL) ->
+ * p2p_exchange_scalars (writes global amax and nnz) -> scaling_cast -> p2p_exchange_errors ->
  * scaling_finalize on (own buffer + p2p_error_offset, world * n_err entries) -> scaling_fallback.
  * Waits are bounded (about two seconds); a time-out sets a flag in the workspace head and
  * scaling_finalize then reports meta = -1.  world <= 16. */
@@ -210,13 +211,11 @@ MOR_B200_API int mor_b200_p2p_close(int device, void* peer_ptr);
 MOR_B200_API int mor_b200_p2p_free(int device, void* own_ptr);
 MOR_B200_API size_t mor_b200_p2p_bytes(int world, int64_t n_err);
 MOR_B200_API size_t mor_b200_p2p_error_offset(int world, int64_t n_err, uint32_t epoch);
-MOR_B200_API int mor_b200_p2p_publish_scalars(const void* workspace, void* const* peer_bufs, int rank, int world,
-                                 uint32_t epoch, void* stream);
-MOR_B200_API int mor_b200_p2p_gather_scalars(void* my_buf, int world, uint32_t epoch, float* global_amax,
-                                int64_t* global_nnz, void* workspace, void* stream);
-MOR_B200_API int mor_b200_p2p_push_errors(const float* local_err, int64_t n_err, void* const* peer_bufs, int rank,
-                             int world, uint32_t epoch, void* stream);
-MOR_B200_API int mor_b200_p2p_wait_errors(const void* my_buf, int world, uint32_t epoch, void* workspace, void* stream);
+MOR_B200_API int mor_b200_p2p_exchange_scalars(void* workspace, void* my_buf, void* const* peer_bufs, int rank, int world,
+                                  uint32_t epoch, float* global_amax, int64_t* global_nnz, void* stream);
+MOR_B200_API int mor_b200_p2p_exchange_errors(const float* local_err, int64_t n_err, const void* my_buf,
+                                 void* const* peer_bufs, int rank, int world, uint32_t epoch, void* workspace,
+                                 void* stream);
 
 /* amax and non-zero count of a flat tensor (kernels 951-1049 without the block array). */
 MOR_B200_API int mor_b200_amax_nnz(const void* input, int dtype, int64_t n_elems, float* amax_out, int64_t* nnz_out,

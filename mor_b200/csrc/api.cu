@@ -305,6 +305,7 @@ int mor_b200_scaling_amax(int kind, const void* in, int dtype, int64_t rows, int
     auto* ws = static_cast<ScalarsWs*>(wsp);
     const int rc = phase_amax(kind, in, dtype, rows, cols, br, bc, g, ws, reinterpret_cast<float*>(static_cast<char*>(wsp) + kHead), st);
     if (rc) return rc;
+    if (!amax_out && !nnz_out) return kOk;   // the caller takes them from the workspace head (peer exchange)
     export_scalars_kernel<<<1, 1, 0, st>>>(ws, amax_out, reinterpret_cast<long long*>(nnz_out));
     return check_launch();
 }
@@ -426,25 +427,17 @@ int mor_b200_p2p_free(int device, void* own_ptr) {
     return kOk;
 }
 
-int mor_b200_p2p_publish_scalars(const void* wsp, void* const* peer_bufs, int rank, int world, uint32_t epoch,
-                                 void* stream) {
+int mor_b200_p2p_exchange_scalars(void* wsp, void* my_buf, void* const* peer_bufs, int rank, int world, uint32_t epoch,
+                                  float* global_amax, int64_t* global_nnz, void* stream) {
     if (!wsp || !aligned16(wsp)) return kErrWorkspace;
-    return launch_p2p_publish_scalars(static_cast<const ScalarsWs*>(wsp), peer_bufs, rank, world, epoch,
-                                      static_cast<cudaStream_t>(stream));
+    return launch_p2p_exchange_scalars(static_cast<ScalarsWs*>(wsp), my_buf, peer_bufs, rank, world, epoch, global_amax,
+                                       reinterpret_cast<long long*>(global_nnz), static_cast<cudaStream_t>(stream));
 }
-int mor_b200_p2p_gather_scalars(void* my_buf, int world, uint32_t epoch, float* global_amax, int64_t* global_nnz,
-                                void* wsp, void* stream) {
+int mor_b200_p2p_exchange_errors(const float* local_err, int64_t n_err, const void* my_buf, void* const* peer_bufs,
+                                 int rank, int world, uint32_t epoch, void* wsp, void* stream) {
     if (!wsp || !aligned16(wsp)) return kErrWorkspace;
-    return launch_p2p_gather_scalars(my_buf, world, epoch, global_amax, reinterpret_cast<long long*>(global_nnz),
-                                     static_cast<ScalarsWs*>(wsp), static_cast<cudaStream_t>(stream));
-}
-int mor_b200_p2p_push_errors(const float* local_err, int64_t n_err, void* const* peer_bufs, int rank, int world,
-                             uint32_t epoch, void* stream) {
-    return launch_p2p_push_errors(local_err, n_err, peer_bufs, rank, world, epoch, static_cast<cudaStream_t>(stream));
-}
-int mor_b200_p2p_wait_errors(const void* my_buf, int world, uint32_t epoch, void* wsp, void* stream) {
-    if (!wsp || !aligned16(wsp)) return kErrWorkspace;
-    return launch_p2p_wait_errors(my_buf, world, epoch, static_cast<ScalarsWs*>(wsp), static_cast<cudaStream_t>(stream));
+    return launch_p2p_exchange_errors(local_err, n_err, my_buf, peer_bufs, rank, world, epoch,
+                                      static_cast<ScalarsWs*>(wsp), static_cast<cudaStream_t>(stream));
 }
 
 int mor_b200_amax_nnz(const void* in, int dtype, int64_t n, float* amax_out, int64_t* nnz_out, void* wsp, size_t wsb,

@@ -84,12 +84,9 @@ int launch_fq_group(const void* in, void* out, int is_fp32, float* scales, int32
 // ---- p2p.cu: peer exchange of the row-sharded pipeline (plain NVLink stores + epoch flags)
 size_t p2p_buffer_bytes(int world, int64_t n_err);
 size_t p2p_error_offset(int world, int64_t n_err, uint32_t epoch);
-int launch_p2p_publish_scalars(const ScalarsWs* ws, void* const* peer_bufs, int rank, int world, uint32_t epoch,
-                               cudaStream_t st);
-int launch_p2p_gather_scalars(void* mine, int world, uint32_t epoch, float* gamax_out, long long* gnnz_out,
-                              ScalarsWs* ws, cudaStream_t st);
-int launch_p2p_push_errors(const float* local_err, int64_t n_err, void* const* peer_bufs, int rank, int world,
-                           uint32_t epoch, cudaStream_t st);
-int launch_p2p_wait_errors(const void* mine, int world, uint32_t epoch, ScalarsWs* ws, cudaStream_t st);
+int launch_p2p_exchange_scalars(ScalarsWs* ws, void* mine, void* const* peer_bufs, int rank, int world, uint32_t epoch,
+                                float* gamax_out, long long* gnnz_out, cudaStream_t st);
+int launch_p2p_exchange_errors(const float* local_err, int64_t n_err, const void* mine, void* const* peer_bufs, int rank,
+                               int world, uint32_t epoch, ScalarsWs* ws, cudaStream_t st);
 
 }  // namespace morb

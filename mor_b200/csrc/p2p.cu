@@ -3,13 +3,12 @@
 // per-block error sums by plain stores into buffers that every rank maps from its peers,
 // completed by epoch flags:
 //
-//   publish  (after the slab amax kernel)   one lane per peer stores this rank's (amax, nnz)
-//                                           into the peer's slot, fences, stores the epoch;
-//   gather   (before the cast kernel)       one lane per peer waits for the epoch in its own
-//                                           buffer, then max / sum over the slots;
-//   push     (after the cast kernel)        copies the slab's error sums into every rank's
-//                                           gathered array, then a flag per peer;
-//   wait     (before the ordered sum)       waits for every rank's flag.
+//   scalars  (between the slab amax kernel and the cast kernel)  one warp, lane p for rank p:
+//            stores this rank's (amax, nnz) into the peer's slot, fences, stores the epoch,
+//            then waits for the epoch in its own slot p; max / sum over the slots;
+//   errors   (between the cast kernel and the ordered sum)  a copy kernel stores the slab's
+//            error sums into every rank's gathered array; one warp then stores the epoch
+//            flags and waits for those of the other ranks.
 //
 // Only plain peer stores and local loads are used (no multicast, no multimem); slots and
 // arrays alternate between two copies by epoch parity, which is enough because a rank can
@@ -56,28 +55,28 @@ __device__ __forceinline__ bool wait_epoch(const uint32_t* flag, uint32_t epoch)
     return false;
 }
 
-__global__ void p2p_publish_scalars_kernel(const ScalarsWs* __restrict__ ws, PeerPtrs peers, int rank, int world,
-                                           uint32_t epoch) {
+// publish, then gather: one warp, lane p talks to rank p.  Every rank stores before it waits, so
+// the waits cannot form a cycle.
+__global__ void p2p_exchange_scalars_kernel(ScalarsWs* __restrict__ ws, unsigned char* __restrict__ mine, PeerPtrs peers,
+                                            int rank, int world, uint32_t epoch, float* __restrict__ gamax_out,
+                                            long long* __restrict__ gnnz_out) {
     const int p = threadIdx.x;
-    if (p >= world) return;
-    ScalSlot* slot = reinterpret_cast<ScalSlot*>(peers.p[p] + kScalOffset) + (epoch & 1u) * kMaxWorld + rank;
-    slot->amax_bits = ws->gamax_bits;
-    slot->nnz = ws->gnnz;
-    __threadfence_system();
-    st_release_sys(&slot->flag, epoch);
-}
-
-__global__ void p2p_gather_scalars_kernel(unsigned char* __restrict__ mine, int world, uint32_t epoch,
-                                          float* __restrict__ gamax_out, long long* __restrict__ gnnz_out,
-                                          ScalarsWs* __restrict__ ws) {
-    const int p = threadIdx.x;  // one warp
-    const ScalSlot* slot = reinterpret_cast<const ScalSlot*>(mine + kScalOffset) + (epoch & 1u) * kMaxWorld + p;
+    const uint32_t par = epoch & 1u;
     uint32_t amax_bits = 0u;
     unsigned long long nnz = 0ull;
     bool ok = true;
     if (p < world) {
-        ok = wait_epoch(&slot->flag, epoch);
-        if (ok) { amax_bits = *reinterpret_cast<const volatile uint32_t*>(&slot->amax_bits); nnz = *reinterpret_cast<const volatile unsigned long long*>(&slot->nnz); }
+        ScalSlot* out = reinterpret_cast<ScalSlot*>(peers.p[p] + kScalOffset) + par * kMaxWorld + rank;
+        out->amax_bits = ws->gamax_bits;
+        out->nnz = ws->gnnz;
+        __threadfence_system();
+        st_release_sys(&out->flag, epoch);
+        const ScalSlot* in = reinterpret_cast<const ScalSlot*>(mine + kScalOffset) + par * kMaxWorld + p;
+        ok = wait_epoch(&in->flag, epoch);
+        if (ok) {
+            amax_bits = *reinterpret_cast<const volatile uint32_t*>(&in->amax_bits);
+            nnz = *reinterpret_cast<const volatile unsigned long long*>(&in->nnz);
+        }
     }
     if (!__all_sync(0xFFFFFFFFu, ok) && p == 0) atomicOr(&ws->load_timeout, 1u);
     amax_bits = __reduce_max_sync(0xFFFFFFFFu, amax_bits);   // non-negative floats order like their bit patterns
@@ -98,19 +97,18 @@ __global__ void __launch_bounds__(256) p2p_push_errors_kernel(const float* __res
         for (int p = 0; p < world; ++p) reinterpret_cast<float*>(peers.p[p] + base)[i] = v;
     }
 }
-// launched behind the copy on the same stream: the copy's stores are complete when this starts
-__global__ void p2p_flag_errors_kernel(PeerPtrs peers, int rank, int world, uint32_t epoch) {
+// launched behind the copy on the same stream: the copy's stores are complete when this starts.
+// Tells every rank that this rank's error sums are in place, then waits for theirs.
+__global__ void p2p_flag_wait_errors_kernel(const unsigned char* __restrict__ mine, PeerPtrs peers, int rank, int world,
+                                            uint32_t epoch, ScalarsWs* __restrict__ ws) {
     const int p = threadIdx.x;
-    if (p >= world) return;
-    __threadfence_system();
-    st_release_sys(reinterpret_cast<uint32_t*>(peers.p[p] + kFlagOffset) + (epoch & 1u) * kMaxWorld + rank, epoch);
-}
-
-__global__ void p2p_wait_errors_kernel(const unsigned char* __restrict__ mine, int world, uint32_t epoch,
-                                       ScalarsWs* __restrict__ ws) {
-    const int p = threadIdx.x;  // one warp
+    const uint32_t par = epoch & 1u;
     bool ok = true;
-    if (p < world) ok = wait_epoch(reinterpret_cast<const uint32_t*>(mine + kFlagOffset) + (epoch & 1u) * kMaxWorld + p, epoch);
+    if (p < world) {
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<uint32_t*>(peers.p[p] + kFlagOffset) + par * kMaxWorld + rank, epoch);
+        ok = wait_epoch(reinterpret_cast<const uint32_t*>(mine + kFlagOffset) + par * kMaxWorld + p, epoch);
+    }
     if (!__all_sync(0xFFFFFFFFu, ok) && p == 0) atomicOr(&ws->load_timeout, 1u);
 }
 
@@ -134,35 +132,27 @@ size_t p2p_error_offset(int world, int64_t n_err, uint32_t epoch) {
     return kErrOffset + (size_t)(epoch & 1u) * (size_t)world * (size_t)n_err * sizeof(float);
 }
 
-int launch_p2p_publish_scalars(const ScalarsWs* ws, void* const* peer_bufs, int rank, int world, uint32_t epoch,
-                               cudaStream_t st) {
+int launch_p2p_exchange_scalars(ScalarsWs* ws, void* mine, void* const* peer_bufs, int rank, int world, uint32_t epoch,
+                                float* gamax_out, long long* gnnz_out, cudaStream_t st) {
     PeerPtrs pp;
-    if (!ws || !fill_peers(pp, peer_bufs, world) || rank < 0 || rank >= world) return kErrInvalidArgument;
-    p2p_publish_scalars_kernel<<<1, 32, 0, st>>>(ws, pp, rank, world, epoch);
+    if (!ws || !mine || !gamax_out || !gnnz_out || !fill_peers(pp, peer_bufs, world) || rank < 0 || rank >= world)
+        return kErrInvalidArgument;
+    p2p_exchange_scalars_kernel<<<1, 32, 0, st>>>(ws, static_cast<unsigned char*>(mine), pp, rank, world, epoch,
+                                                  gamax_out, gnnz_out);
     return check_launch();
 }
-int launch_p2p_gather_scalars(void* mine, int world, uint32_t epoch, float* gamax_out, long long* gnnz_out,
-                              ScalarsWs* ws, cudaStream_t st) {
-    if (!mine || !gamax_out || !gnnz_out || !ws || world < 1 || world > kMaxWorld) return kErrInvalidArgument;
-    p2p_gather_scalars_kernel<<<1, 32, 0, st>>>(static_cast<unsigned char*>(mine), world, epoch, gamax_out, gnnz_out, ws);
-    return check_launch();
-}
-int launch_p2p_push_errors(const float* local_err, int64_t n_err, void* const* peer_bufs, int rank, int world,
-                           uint32_t epoch, cudaStream_t st) {
+int launch_p2p_exchange_errors(const float* local_err, int64_t n_err, const void* mine, void* const* peer_bufs, int rank,
+                               int world, uint32_t epoch, ScalarsWs* ws, cudaStream_t st) {
     PeerPtrs pp;
-    if (!local_err || n_err < 1 || !fill_peers(pp, peer_bufs, world) || rank < 0 || rank >= world) return kErrInvalidArgument;
+    if (!local_err || n_err < 1 || !mine || !ws || !fill_peers(pp, peer_bufs, world) || rank < 0 || rank >= world)
+        return kErrInvalidArgument;
     int64_t grid = (n_err + 255) / 256;
     const int64_t cap = (int64_t)sm_count() * 4;
     if (grid > cap) grid = cap;
     p2p_push_errors_kernel<<<(unsigned)grid, 256, 0, st>>>(local_err, n_err, pp, rank, world, epoch);
-    int rc = check_launch();
+    const int rc = check_launch();
     if (rc) return rc;
-    p2p_flag_errors_kernel<<<1, 32, 0, st>>>(pp, rank, world, epoch);
-    return check_launch();
-}
-int launch_p2p_wait_errors(const void* mine, int world, uint32_t epoch, ScalarsWs* ws, cudaStream_t st) {
-    if (!mine || !ws || world < 1 || world > kMaxWorld) return kErrInvalidArgument;
-    p2p_wait_errors_kernel<<<1, 32, 0, st>>>(static_cast<const unsigned char*>(mine), world, epoch, ws);
+    p2p_flag_wait_errors_kernel<<<1, 32, 0, st>>>(static_cast<const unsigned char*>(mine), pp, rank, world, epoch, ws);
     return check_launch();
 }
 

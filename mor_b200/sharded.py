@@ -96,23 +96,21 @@ class CudaBackend:
                   self.ws.data_ptr(), self.ws_bytes, self._stream())
         self.launches += 2 if all_err.numel() > 65536 else 1  # long arrays: partial sums over several CTAs first
 
-    def publish_scalars(self, ex: "PeerExchange", epoch: int):
-        cabi.call("mor_b200_p2p_publish_scalars", self.ws.data_ptr(), ex.peer_array, ex.rank, ex.world, epoch, self._stream())
-        self.launches += 1
-
-    def gather_scalars(self, ex: "PeerExchange", epoch: int, amax_out, nnz_out):
-        cabi.call("mor_b200_p2p_gather_scalars", ex.mine, ex.world, epoch, amax_out.data_ptr(),
-                  nnz_out.data_ptr(), self.ws.data_ptr(), self._stream())
-        self.launches += 1
-
-    def push_errors(self, ex: "PeerExchange", epoch: int, local_err):
-        cabi.call("mor_b200_p2p_push_errors", local_err.data_ptr(), local_err.numel(), ex.peer_array, ex.rank, ex.world,
-                  epoch, self._stream())
+    def amax_nnz_local(self, x):
+        """phase 1 without the copy of the slab's own amax / count to tensors (the peer exchange reads the workspace)"""
+        cabi.call("mor_b200_scaling_amax", self.kind, x.data_ptr(), self.dt, self.rows, self.cols, self.brows,
+                  self.bcols, None, None, self.ws.data_ptr(), self.ws_bytes, self._stream())
         self.launches += 2
 
-    def wait_errors(self, ex: "PeerExchange", epoch: int):
-        cabi.call("mor_b200_p2p_wait_errors", ex.mine, ex.world, epoch, self.ws.data_ptr(), self._stream())
+    def exchange_scalars(self, ex: "PeerExchange", epoch: int, amax_out, nnz_out):
+        cabi.call("mor_b200_p2p_exchange_scalars", self.ws.data_ptr(), ex.mine, ex.peer_array, ex.rank, ex.world, epoch,
+                  amax_out.data_ptr(), nnz_out.data_ptr(), self._stream())
         self.launches += 1
+
+    def exchange_errors(self, ex: "PeerExchange", epoch: int, local_err):
+        cabi.call("mor_b200_p2p_exchange_errors", local_err.data_ptr(), local_err.numel(), ex.mine, ex.peer_array, ex.rank,
+                  ex.world, epoch, self.ws.data_ptr(), self._stream())
+        self.launches += 2
 
     def finalize_ptr(self, err_ptr: int, n: int, global_nnz, threshold, meta, global_error):
         cabi.call("mor_b200_scaling_finalize", err_ptr, n, self.stride, global_nnz.data_ptr(), float(threshold),
@@ -244,12 +242,10 @@ class ShardedScaling:
             ex = self.peer
             ex.epoch += 1
             ep = ex.epoch
-            b.amax_nnz(x, self.amax, self.nnz)
-            b.publish_scalars(ex, ep)
-            b.gather_scalars(ex, ep, self.amax, self.nnz)
+            b.amax_nnz_local(x)
+            b.exchange_scalars(ex, ep, self.amax, self.nnz)
             b.cast(x, out, ss_mode, self.amax, self.local_err)
-            b.push_errors(ex, ep, self.local_err)
-            b.wait_errors(ex, ep)
+            b.exchange_errors(ex, ep, self.local_err)
             b.finalize_ptr(ex.error_ptr(ep), ex.world * ex.n_err, self.nnz, threshold, self.meta, self.gerr)
             b.fallback(x, out, self.meta)
             return ScalingResult(self.meta, self.amax, self.nnz, self.gerr)
