@@ -226,7 +226,7 @@ def main():
     # events around the dominant kernel (scale + cast + error sums), on the launching stream
     cast_events = []
     amax_events = []
-    inner_cast, inner_amax = op.backend.cast, op.backend.amax_nnz
+    inner_cast, inner_amax, inner_amax_local = op.backend.cast, op.backend.amax_nnz, op.backend.amax_nnz_local
 
     def timed_cast(*a):
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -238,7 +238,12 @@ def main():
         s.record(); inner_amax(*a); e.record()
         amax_events.append((s, e))
 
-    op.backend.cast, op.backend.amax_nnz = timed_cast, timed_amax
+    def timed_amax_local(*a):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record(); inner_amax_local(*a); e.record()
+        amax_events.append((s, e))
+
+    op.backend.cast, op.backend.amax_nnz, op.backend.amax_nnz_local = timed_cast, timed_amax, timed_amax_local
 
     def barrier():
         if world > 1:
