@@ -266,6 +266,76 @@ __global__ void __launch_bounds__(kThreads, 8) amax_nnz_blocks_kernel(const type
     }
 }
 
+// 1 x k blocks of at least 4 KiB (a multiple of it): in a row-major tensor they are consecutive
+// runs of the flat array, so a warp streams one block through its private ring (chunks one
+// after the other) and reduces it alone: no CTA barrier until the eight warps of a CTA combine
+// their totals for the one atomic update of the tensor-wide scalars.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) amax_nnz_runs_kernel(const typename T::vec_t* __restrict__ in,
+                                                                 int chunks_per_block, int64_t n_blocks,
+                                                                 float* __restrict__ block_amax,
+                                                                 ScalarsWs* __restrict__ ws) {
+    extern __shared__ __align__(128) uint8_t s_ring[];  // [warp][stage][4 KiB]
+    __shared__ __align__(8) uint64_t s_bar[kFlatWarps][kFlatStages];
+    using V = typename T::vec_t;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int64_t b = (int64_t)blockIdx.x * kFlatWarps + wid;   // this warp's block
+    float amax = 0.0f;
+    int nnz = 0;
+    uint32_t flags = 0u;
+    if (b < n_blocks) {
+        const int64_t c0 = b * chunks_per_block;
+        const V* src = in + c0 * kFlatChunkVec;
+        WarpStream<kFlatStages, kFlatChunkVec * 16> stream;
+        stream.start(s_ring + wid * (kFlatStages * kFlatChunkVec * 16), s_bar[wid], src,
+                     (int64_t)chunks_per_block * kFlatChunkVec * 16, 0, 1);
+        Acc acc = acc_init();
+        int st = 0;
+        for (int c = 0; c < chunks_per_block; ++c) {
+            if (stream.acquire(st)) {
+                const V* chunk = reinterpret_cast<const V*>(stream.stage(st)) + lane;
+#pragma unroll
+                for (int r = 0; r < kFlatChunkVec / 32; ++r) vec_acc_fast<T>(chunk[r * 32], acc);
+            } else {
+                for (int r = lane; r < kFlatChunkVec; r += 32) vec_acc_fast<T>(ld_keep(src + (int64_t)c * kFlatChunkVec + r), acc);
+            }
+            stream.release(st, c + kFlatStages);
+            st = st + 1 == kFlatStages ? 0 : st + 1;
+        }
+        stream.drain();
+        amax = acc_amax<T>(acc);
+        nnz = acc_nnz<T>(acc);
+        flags = acc_flags<T>(acc, amax);
+        amax = u2f(__reduce_max_sync(0xFFFFFFFFu, f2u(amax)));
+        nnz = __reduce_add_sync(0xFFFFFFFFu, nnz);
+        flags = __reduce_or_sync(0xFFFFFFFFu, flags);
+        if (flags & kFlagNan) {  // a NaN in this block: float compares, as the reference does
+            amax = 0.0f; nnz = 0;
+            for (int64_t r = lane; r < (int64_t)chunks_per_block * kFlatChunkVec; r += 32) vec_acc_exact<T>(ld_keep(src + r), amax, nnz);
+            amax = warp_max(amax);
+            nnz = warp_sum_int(nnz);
+        }
+        if (lane == 0) {
+            const bool zero_free = nnz == chunks_per_block * kFlatChunkVec * (16 / T::kBytesPerElem);
+            block_amax[b] = zero_free ? -amax : amax;
+        }
+    }
+    // totals of the CTA's eight blocks (every lane of a warp holds its block's totals)
+    __shared__ uint32_t s_a[kFlatWarps], s_f[kFlatWarps];
+    __shared__ int s_n[kFlatWarps];
+    if (lane == 0) { s_a[wid] = f2u(amax); s_n[wid] = nnz; s_f[wid] = flags; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t a = 0u, f = 0u;
+        long long n = 0;
+#pragma unroll
+        for (int w = 0; w < kFlatWarps; ++w) { a = max(a, s_a[w]); n += s_n[w]; f |= s_f[w]; }
+        atomicMax(&ws->gamax_bits, a);
+        if (n) atomicAdd(&ws->gnnz, (unsigned long long)n);
+        if (f) atomicOr(&ws->div_unsafe, 1u);
+    }
+}
+
 // Column groups (k x 1): every thread owns one 16-byte column strip and walks down the
 // k rows of its block; per-column maxima go straight to block_amax.
 template <typename T>
@@ -360,6 +430,17 @@ int launch_amax_nnz_blocks(const void* in, int is_fp32, int64_t rows, int64_t co
     const int bcols_vec = bcols / epv;
     const int64_t bx = cols / bcols, nb = bx * (rows / brows);
     if (nb > 0x7FFFFFFF) return kErrTooLarge;
+    if (brows == 1 && bcols_vec % kFlatChunkVec == 0 && bcols_vec / kFlatChunkVec <= 4096) {
+        constexpr int kRing = kFlatWarps * kFlatStages * kFlatChunkVec * 16;
+        static const cudaError_t a1 = cudaFuncSetAttribute(amax_nnz_runs_kernel<Fp32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing);
+        static const cudaError_t a2 = cudaFuncSetAttribute(amax_nnz_runs_kernel<Bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing);
+        if (a1 != cudaSuccess || a2 != cudaSuccess) return kErrLaunch;
+        const unsigned grid = (unsigned)((nb + kFlatWarps - 1) / kFlatWarps);
+        const int cpb = bcols_vec / kFlatChunkVec;
+        if (is_fp32) amax_nnz_runs_kernel<Fp32><<<grid, kThreads, kRing, st>>>(static_cast<const float4*>(in), cpb, nb, block_amax, ws);
+        else amax_nnz_runs_kernel<Bf16><<<grid, kThreads, kRing, st>>>(static_cast<const uint4*>(in), cpb, nb, block_amax, ws);
+        return check_launch();
+    }
     int w_shift = 0;
     while ((2 << w_shift) <= bcols_vec && (2 << w_shift) <= kThreads) ++w_shift;  // largest power of two <= min(bcols_vec, 256)
     if (is_fp32) amax_nnz_blocks_kernel<Fp32><<<(unsigned)nb, kThreads, 0, st>>>(static_cast<const float4*>(in), cols_vec, brows, bcols_vec, bx, w_shift, block_amax, ws);

@@ -275,6 +275,30 @@ def test_channel_scaling_small_groups_power_of_two(by, kind, rows, cols):
         assert_same(H.channel_scaling(x, 1, by, thr, 2), exp, f"{kind} {rows}x{cols} 1x{by} thr {thr}")
 
 
+@pytest.mark.parametrize("by", [2048, 4096, 8192])
+@pytest.mark.parametrize("ss", [1, 2, 3, 4])
+@pytest.mark.parametrize("kind", ["normal", "wide", "nan"])
+def test_channel_scaling_long_rows(by, ss, kind):
+    """1 x k blocks of 4 KiB and more: the amax pass streams every block through one warp's ring"""
+    import gpu_harness as H
+    if kind == "nan" and ss == 2:
+        pytest.skip("non-finite inputs are outside the reference's domain for power-of-two scales")
+    x = rand_bits(by + ss, 24, 8192, "wide" if kind == "wide" else "normal")
+    x[5] = (x[5] & 0x8000) | ((x[5] & 0x7FFF) | 1)        # a row without a single zero
+    if kind == "nan":
+        x[7, 4000] = 0x7FC0
+    oracle.clear_assert_flags()
+    exp = dict(zip(("out", "meta", "gamax", "gnnz", "gerr"), oracle.channel_scaling(x, 1, by, 3e38, ss)))
+    if oracle.assert_flags():
+        pytest.skip("the reference asserts on this input")
+    exp["meta"] = np.array([exp["meta"]])
+    got = H.channel_scaling(x, 1, by, 3e38, ss)
+    if kind == "nan":
+        assert np.isnan(got["gerr"]) and np.isnan(exp["gerr"])
+        got["gerr"] = exp["gerr"] = 0.0
+    assert_same(got, exp, f"{kind} 1x{by} ss {ss}")
+
+
 @pytest.mark.parametrize("bx,rows", [(256, 256), (64, 256), (16, 64), (128, 384)])
 @pytest.mark.parametrize("ss", [1, 2, 3, 4])
 def test_channel_scaling_column_groups(bx, rows, ss):
