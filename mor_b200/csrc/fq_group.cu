@@ -318,13 +318,24 @@ mx_quantize_kernel(const uint4* __restrict__ in, uint2* __restrict__ payload, ui
         const int64_t v0 = c * kMxChunkVec;
         const int nv = (int)(nvec - v0 < kMxChunkVec ? nvec - v0 : kMxChunkVec);
         const bool staged = ws.acquire(st);
-        const uint4* chunk = reinterpret_cast<const uint4*>(ws.stage(st)) + lane;
-        for (int r = 0; r * 32 < nv; ++r) {
-            const uint4 v = staged ? chunk[r * 32] : ld_stream(in + v0 + r * 32 + lane);
-            uint32_t sb;
-            const uint2 codes = mx_codes_one<FMT, GS>(v, sb);
-            st_stream(payload + v0 + r * 32 + lane, codes);
-            if (scale_lane) scales[(v0 + r * 32 + lane) >> GS] = (uint8_t)sb;
+        uint2* o = payload + v0 + lane;
+        uint8_t* sc = scales + ((v0 + lane) >> GS);
+        if (staged && nv == kMxChunkVec) {
+            const uint4* chunk = reinterpret_cast<const uint4*>(ws.stage(st)) + lane;
+#pragma unroll
+            for (int r = 0; r < kMxChunkVec / 32; ++r) {
+                uint32_t sb;
+                const uint2 codes = mx_codes_one<FMT, GS>(chunk[r * 32], sb);
+                st_stream(o + r * 32, codes);
+                if (scale_lane) sc[r * (32 >> GS)] = (uint8_t)sb;
+            }
+        } else {  // last, partial chunk, or a copy that did not arrive: ordinary loads
+            for (int r = 0; r * 32 < nv; ++r) {
+                uint32_t sb;
+                const uint2 codes = mx_codes_one<FMT, GS>(ld_stream(in + v0 + r * 32 + lane), sb);
+                st_stream(o + r * 32, codes);
+                if (scale_lane) sc[r * (32 >> GS)] = (uint8_t)sb;
+            }
         }
         ws.release(st, c + kMxStages * n_warps);
         st = st + 1 == kMxStages ? 0 : st + 1;
