@@ -108,6 +108,12 @@ def cpu_baseline(rows_sample_hint=None, budget_s=12.0, steps=1, warmup=0):
     bounded row sample of the workload: same columns, same block scaling, all host threads."""
     import numpy as np
     import oracle
+    # all the host cores this process may use, whatever OMP_NUM_THREADS says (torchrun sets it to 1)
+    try:
+        avail = len(os.sched_getaffinity(0))
+    except AttributeError:
+        avail = os.cpu_count() or 1
+    oracle.set_num_threads(avail)
     threads = oracle.num_threads()
     rng = np.random.default_rng(4000)
     probe = rng.standard_normal((BLOCK * 2, COLS), dtype=np.float32)
