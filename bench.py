@@ -473,6 +473,10 @@ def run_suite(torch, dev, peak, only="", iters=10, out_path=None, use_graph=Fals
     del x
     x = workloads.config4(device=dev)
     r, c = x.shape
+    if impl != "reference":
+        amax_prev4 = x.float().abs().max().reshape(1)
+        add("c4 block scaling 128x128, single pass with delayed amax (ss 1)", x, 4, "fake_quantize_block_scaling_delayed",
+            (r, c, 128, 128, 3e38, 1, amax_prev4))
     add("c4 MoR 128x128 relative-error criterion (mode 1)", x, 4, "fake_quantize", (r, c, 128, 128, 1e-15, 1, 1), ref_ok=True)
     add("c4 MoR 128x128 dynamic-range criterion (mode 101)", x, 4, "fake_quantize", (r, c, 128, 128, 1e-15, 101, 1), ref_ok=True)
     add("c4 block scaling 128x128 pipeline (ss 1)", x, 6, "fake_quantize_block_scaling", (r, c, 128, 128, 3e38, 1), ref_ok=True)
@@ -481,6 +485,9 @@ def run_suite(torch, dev, peak, only="", iters=10, out_path=None, use_graph=Fals
         x = workloads.config5_slab(0, device=dev)
         r, c = x.shape
         add("c5 float32 1 GiB slab block scaling 128x128 pipeline (ss 1)", x, 12, "fake_quantize_block_scaling", (r, c, 128, 128, THRESHOLD, 1))
+        amax_prev = x.abs().max().reshape(1).float()
+        add("c5 float32 1 GiB slab block scaling, single pass with delayed amax (ss 1)", x, 8,
+            "fake_quantize_block_scaling_delayed", (r, c, 128, 128, THRESHOLD, 1, amax_prev))
         add("c5 float32 1 GiB slab per-tensor pipeline (ss 4)", x, 12, "fake_quantize_block_scaling", (r, c, 128, 128, THRESHOLD, 4))
         del x
     os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)

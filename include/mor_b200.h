@@ -148,6 +148,19 @@ MOR_B200_API int mor_b200_e8mx(const void* input, void* output, int64_t rows, in
 MOR_B200_API int mor_b200_fake_quantize_group(const void* input, void* output, float* scales, int dtype, int64_t rows,
                                  int64_t cols, int block_cols, int format, int sf_type, void* stream);
 
+/* Extension (no counterpart in the reference; arithmetic of fake_quantize_block_scaling,
+ * fake_quantize.cu:1059-1241, with the tensor amax supplied by the caller): block scaling in ONE
+ * pass over the tensor.  The scales are built from *amax_in (device), typically the amax this
+ * call reported for the previous step's tensor ("delayed scaling"); each block's own amax is
+ * taken from the tile while it is staged on chip; amax_out / nnz_out / err_out / meta describe
+ * THIS tensor.  128 x 128 blocks, input != output.  Values above the stale amax saturate in the
+ * cast, as they do in the reference's arithmetic for a scale that is too large. */
+MOR_B200_API int mor_b200_block_scaling_delayed(const void* input, void* output, int dtype, int64_t rows, int64_t cols,
+                                   int block_rows, int block_cols, double e4m3_threshold, int ss_mode,
+                                   const float* amax_in, int32_t* meta, float* amax_out, void* nnz_out,
+                                   int nnz_is_int64, float* err_out, void* workspace, size_t workspace_bytes,
+                                   void* stream);
+
 /* Extension (no counterpart in the reference, whose operators only fake-quantize; the casts
  * it describes are fake_quantize.cu:283-305 and the wrappers :356-379): the REAL quantized form
  * of mor_b200_fake_quantize_group with sf_type 2, i.e. what a block-scaled GEMM consumes.

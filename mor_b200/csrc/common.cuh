@@ -314,6 +314,12 @@ __device__ __forceinline__ uint32_t umin16x2(uint32_t a, uint32_t b) {
 }
 __device__ __forceinline__ uint32_t umax16x2_3(uint32_t a, uint32_t b, uint32_t c) { return __vimax3_u16x2(a, b, c); }
 __device__ __forceinline__ uint32_t smin16x2_3(uint32_t a, uint32_t b, uint32_t c) { return __vimin3_s16x2(a, b, c); }
+// bytes 1 and 3 of a and of b, each replaced by eight copies of its top bit
+__device__ __forceinline__ uint32_t top_bits_to_bytes(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, 0xFDB9;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
 // packed maximum of the four magnitude words of a 16-byte vector of bf16
 __device__ __forceinline__ uint32_t umax16x2_vec(uint32_t m0, uint32_t m1, uint32_t m2, uint32_t m3) {
     return umax16x2(umax16x2_3(m0, m1, m2), m3);

@@ -27,12 +27,6 @@ struct Acc {
 };
 __device__ __forceinline__ Acc acc_init() { return Acc{0u, 0.0f, 0, 0x7FFF7FFFu}; }
 
-// bytes 1 and 3 of a and of b, each replaced by eight copies of its top bit
-__device__ __forceinline__ uint32_t top_bits_to_bytes(uint32_t a, uint32_t b) {
-    uint32_t r;
-    asm("prmt.b32 %0, %1, %2, 0xFDB9;" : "=r"(r) : "r"(a), "r"(b));
-    return r;
-}
 // true when a half of the packed minimum stands for a non-zero magnitude below 2^-90
 // (bf16 pattern 0x1280): a zero leaves 0x7FFF, a magnitude m leaves 0x8000 + m - 1
 __device__ __forceinline__ bool tmin_is_tiny(uint32_t t) {

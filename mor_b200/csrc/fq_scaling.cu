@@ -269,7 +269,7 @@ template <typename T> struct Tile128 {
     static constexpr int kCtasPerSm = T::kBytesPerElem == 4 ? 3 : 6;
 };
 
-template <typename T, bool E8, bool STORE>
+template <typename T, bool E8, bool STORE, bool SCAN = false>
 __global__ void __launch_bounds__(Tile128<T>::kThreads, Tile128<T>::kCtasPerSm)
 block_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename T::vec_t* __restrict__ out, int64_t cols_vec,
                      int blocks_x, int ss, const float* __restrict__ block_amax, float* __restrict__ block_err,
@@ -299,17 +299,116 @@ block_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename T::vec_t
                 tma_load_2d(s_tile + (j * NS + sidx) * 4096, &tmap, bx * 128 + sidx * EPS, by * 128 + j * 32, &s_bar[j]);
         }
     }
-    const float bamax = block_amax[b];            // sign bit set: the block holds no zero (and no NaN)
-    const bool zero_free = (f2u(bamax) >> 31) != 0u;
-    const float sf = scaling_factor(ss, read_gamax(ws, ext_gamax), fabsf(bamax));
     const int p = tid % LPW, ty = tid / LPW;
+    const typename T::vec_t* tile = reinterpret_cast<const typename T::vec_t*>(s_tile);
+    bool arrived = true;
+    float bamax;
+    bool zero_free, fastdiv;
+    if constexpr (SCAN) {
+        // single pass: block amax, non-zero count (and, for bf16, whether the short quotient is
+        // valid for this tile) come from the staged tile; the tensor's amax and count are
+        // published for the caller's next step
+        __shared__ uint32_t s_sa[NT / 32], s_sm[NT / 32];
+        __shared__ int s_sn[NT / 32];
+        for (int j = 0; j < 4; ++j) arrived = mbar_wait_bounded(&s_bar[j], 0) && arrived;
+        uint32_t amax_bits = 0u, pmn = 0x7FFF7FFFu;
+        int nnz = 0;
+        bool nan = false;
+        if (arrived) {
+            if constexpr (T::kBytesPerElem == 2) {
+                uint32_t pmx = 0u;
+                int nnz4 = 0;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                    for (int i = 0; i < CI; ++i) {
+                        const int vc = p + LPW * i;
+                        const uint4 v = tile[((j * NS + (vc >> 3)) * 32 + ty) * 8 + (vc & 7)];
+                        const uint32_t m0 = mag2(v.x), m1 = mag2(v.y), m2 = mag2(v.z), m3 = mag2(v.w);
+                        pmx = umax16x2_3(umax16x2_3(pmx, m0, m1), m2, m3);
+                        const uint32_t s0 = m0 + 0x7FFF7FFFu, s1 = m1 + 0x7FFF7FFFu, s2 = m2 + 0x7FFF7FFFu, s3 = m3 + 0x7FFF7FFFu;
+                        pmn = smin16x2_3(smin16x2_3(pmn, s0, s1), s2, s3);
+                        nnz4 += __popc((top_bits_to_bytes(s0, s1) & 0x0F0F0F0Fu) | (top_bits_to_bytes(s2, s3) & 0xF0F0F0F0u));
+                    }
+                amax_bits = hmax_halves(pmx) << 16;
+                nnz = nnz4 >> 2;
+            } else {
+                float a = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                    for (int i = 0; i < CI; ++i) {
+                        const int vc = p + LPW * i;
+                        const float4 v = tile[((j * NS + (vc >> 3)) * 32 + ty) * 8 + (vc & 7)];
+                        const float a0 = fabsf(v.x), a1 = fabsf(v.y), a2 = fabsf(v.z), a3 = fabsf(v.w);
+                        a = fmaxf(a, fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)));
+                        nnz += (a0 > 0.0f) + (a1 > 0.0f) + (a2 > 0.0f) + (a3 > 0.0f);
+                    }
+                amax_bits = f2u(a);
+            }
+        }
+        amax_bits = __reduce_max_sync(0xFFFFFFFFu, amax_bits);
+        nnz = __reduce_add_sync(0xFFFFFFFFu, nnz);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) pmn = smin16x2_3(pmn, pmn, __shfl_xor_sync(0xFFFFFFFFu, pmn, o));
+        if ((tid & 31) == 0) { s_sa[tid >> 5] = amax_bits; s_sn[tid >> 5] = nnz; s_sm[tid >> 5] = pmn; }
+        __syncthreads();
+        amax_bits = s_sa[0]; nnz = s_sn[0]; pmn = s_sm[0];
+#pragma unroll
+        for (int w = 1; w < NT / 32; ++w) { amax_bits = max(amax_bits, s_sa[w]); nnz += s_sn[w]; pmn = smin16x2_3(pmn, pmn, s_sm[w]); }
+        if constexpr (T::kBytesPerElem == 2) nan = amax_bits > 0x7F800000u;
+        if (nan) {  // a NaN in the tile: the reference's fmaxf skips it and does not count it
+            float a = 0.0f;
+            int n = 0;
+            for (int j = 0; j < 4; ++j)
+                for (int i = 0; i < CI; ++i) {
+                    const int vc = p + LPW * i;
+                    const typename T::vec_t v = tile[((j * NS + (vc >> 3)) * 32 + ty) * 8 + (vc & 7)];
+#pragma unroll
+                    for (int k = 0; k < VW; ++k) {
+                        float hi, lo;
+                        T::unpack(v, k, hi, lo);
+                        const float ah = fabsf(hi), al = fabsf(lo);
+                        a = fmaxf(a, fmaxf(ah, al));
+                        n += (ah > 0.0f) + (al > 0.0f);
+                    }
+                }
+            a = warp_max(a);
+            n = warp_sum_int(n);
+            __syncthreads();
+            if ((tid & 31) == 0) { s_sa[tid >> 5] = f2u(a); s_sn[tid >> 5] = n; }
+            __syncthreads();
+            amax_bits = s_sa[0]; nnz = s_sn[0];
+#pragma unroll
+            for (int w = 1; w < NT / 32; ++w) { amax_bits = max(amax_bits, s_sa[w]); nnz += s_sn[w]; }
+        }
+        bamax = u2f(amax_bits);
+        zero_free = !nan && nnz == 128 * 128;
+        if constexpr (T::kBytesPerElem == 2) {
+            // smallest non-zero magnitude of the tile: halves with bit 15 set saw one
+            const uint32_t h0 = pmn & 0xFFFFu, h1 = pmn >> 16;
+            uint32_t amin_pat = 0x7F7Fu;
+            if (h0 & 0x8000u) amin_pat = min(amin_pat, (h0 & 0x7FFFu) + 1u);
+            if (h1 & 0x8000u) amin_pat = min(amin_pat, (h1 & 0x7FFFu) + 1u);
+            fastdiv = !nan && bf16_div_safe(u2f(amin_pat << 16)) && bf16_div_safe(bamax);
+        } else {
+            fastdiv = false;
+        }
+        if (tid == 0) {
+            atomicMax(&ws->gamax_bits, amax_bits);
+            if (nnz) atomicAdd(&ws->gnnz, (unsigned long long)nnz);
+        }
+    } else {
+        bamax = block_amax[b];                  // sign bit set: the block holds no zero (and no NaN)
+        zero_free = (f2u(bamax) >> 31) != 0u;
+        bamax = fabsf(bamax);
+        fastdiv = fast_div_ok<T>(ws);
+    }
+    const float sf = scaling_factor(ss, read_gamax(ws, ext_gamax), bamax);
     float acc[VW];
 #pragma unroll
     for (int k = 0; k < VW; ++k) acc[k] = 0.0f;
-    const typename T::vec_t* tile = reinterpret_cast<const typename T::vec_t*>(s_tile);
     typename T::vec_t* dst = out + ((int64_t)by * 128 + ty) * cols_vec + (int64_t)bx * (CI * LPW) + p;
-    const bool fastdiv = fast_div_ok<T>(ws);
-    bool arrived = true;
     auto run = [&](const auto& path, auto fd_tag, auto nz_tag) {
         constexpr int FD = (T::kBytesPerElem != 2) ? kDivIeee : (decltype(fd_tag)::value ? kDivBf16 : kDivBf16Any);
         for (int j = 0; j < 4; ++j) {
@@ -970,6 +1069,21 @@ int launch_block_t(const ScalingArgs& a, bool store, bool skip, cudaStream_t st)
         block_tile128_kernel<T, E, S><<<(unsigned)nb, TH, Tile128<T>::kBytes, st>>>(                                  \
             map, out, cols_vec, (int)bx, a.ss_mode, a.block_amax, a.block_err, a.ws, a.ext_gamax, skip ? 1 : 0);     \
     } while (0)
+        if (a.scan_blocks) {
+#define MORB_TILE_SCAN(E)                                                                                            \
+    do {                                                                                                             \
+        static const cudaError_t attr = cudaFuncSetAttribute(block_tile128_kernel<T, E, true, true>,                 \
+                                                             cudaFuncAttributeMaxDynamicSharedMemorySize,            \
+                                                             Tile128<T>::kBytes);                                     \
+        if (attr != cudaSuccess) return kErrLaunch;                                                                  \
+        block_tile128_kernel<T, E, true, true><<<(unsigned)nb, TH, Tile128<T>::kBytes, st>>>(                         \
+            map, out, cols_vec, (int)bx, a.ss_mode, a.block_amax, a.block_err, a.ws, a.ext_gamax, 0);                \
+    } while (0)
+            if (!store || skip) return kErrInvalidArgument;
+            if (e8) MORB_TILE_SCAN(true); else MORB_TILE_SCAN(false);
+#undef MORB_TILE_SCAN
+            return check_launch();
+        }
         if (e8 && store) MORB_TILE(true, true);
         else if (e8) MORB_TILE(true, false);
         else if (store) MORB_TILE(false, true);
@@ -977,6 +1091,7 @@ int launch_block_t(const ScalingArgs& a, bool store, bool skip, cudaStream_t st)
 #undef MORB_TILE
         return check_launch();
     }
+    if (a.scan_blocks) return kErrUnsupportedShape;   // the single-pass form exists for TMA-staged 128 x 128 tiles only
 #define MORB_GO(E, S) block_err_cast_kernel<T, E, S><<<(unsigned)nb, TH, 0, st>>>(in, out, cols_vec, a.brows, a.bcols / EPV, bx, a.ss_mode, a.block_amax, a.block_err, a.ws, a.ext_gamax, skip ? 1 : 0)
     if (e8 && store) MORB_GO(true, true);
     else if (e8) MORB_GO(true, false);

@@ -62,6 +62,9 @@ struct ScalingArgs {
     int err_slot_stride;        // the reference stores entry i at slot i * stride of its array
     ScalarsWs* ws;
     const float* ext_gamax;     // optional device pointer: amax of the whole (sharded) tensor
+    int scan_blocks;            // 1: single pass -- the cast kernel takes each block's amax from the tile it
+                                // has staged and publishes the tensor's amax / non-zero count itself
+                                // (ext_gamax then is the amax of an earlier step: delayed scaling)
 };
 int launch_block_err_cast(const ScalingArgs& a, bool store, bool only_if_not_fallback, cudaStream_t st);
 int launch_rowgroup_err_cast(const ScalingArgs& a, bool store, bool only_if_not_fallback, cudaStream_t st);

@@ -217,6 +217,38 @@ std::vector<at::Tensor> fake_quantize_mx(const at::Tensor& input, int64_t rows, 
     return {out, scales};
 }
 
+// ---- extension: single-pass block scaling with a delayed tensor amax ---------------------
+// returns [out, meta, amax of this tensor, non-zero count, error]; amax_in: float32[1] on the device
+std::vector<at::Tensor> fake_quantize_block_scaling_delayed(const at::Tensor& input, int64_t rows, int64_t cols,
+                                                            int64_t br, int64_t bc, double thr, int64_t ss,
+                                                            const at::Tensor& amax_in) {
+    const char* name = "fake_quantize_block_scaling_delayed";
+    const c10::cuda::CUDAGuard guard(input.device());
+    at::Tensor in = checked_input(input, rows, cols, name);
+    const int dt = dtype_code(in, true, name);
+    TORCH_CHECK(ss >= 1 && ss <= 4, "mor::", name, ": ss_mode must be 1..4");
+    TORCH_CHECK(br == 128 && bc == 128 && rows % 128 == 0 && cols % 128 == 0, "mor::", name,
+                ": 128 x 128 blocks that divide the tensor only");
+    TORCH_CHECK(amax_in.is_cuda() && amax_in.scalar_type() == at::kFloat && amax_in.numel() == 1, "mor::", name,
+                ": amax_in must be a float32 CUDA tensor with one element");
+    TORCH_CHECK(dt == MOR_B200_FP32 || rows * cols < (int64_t(1) << 31), "mor::", name,
+                ": bfloat16 tensors report an int32 non-zero count; use float32 for 2^31 elements and more");
+    const size_t wsb = mor_b200_workspace_bytes(MOR_B200_OP_BLOCK_SCALING, rows, cols, 128, 128);
+    at::Tensor ws = workspace(in, wsb);
+    at::Tensor out = torch::empty_like(in);
+    auto iopt = in.options().dtype(torch::kInt32);
+    auto fopt = in.options().dtype(torch::kFloat);
+    at::Tensor meta = torch::empty({1}, iopt), gamax = torch::empty({1}, fopt), gerr = torch::empty({1}, fopt);
+    const bool nnz64 = dt == MOR_B200_FP32;
+    at::Tensor gnnz = torch::empty({1}, nnz64 ? in.options().dtype(torch::kInt64) : iopt);
+    check_status(mor_b200_block_scaling_delayed(in.data_ptr(), out.data_ptr(), dt, rows, cols, 128, 128, thr, (int)ss,
+                                                amax_in.data_ptr<float>(), meta.data_ptr<int32_t>(),
+                                                gamax.data_ptr<float>(), gnnz.data_ptr(), nnz64 ? 1 : 0,
+                                                gerr.data_ptr<float>(), ws.data_ptr(), wsb, cur_stream()),
+                 name);
+    return {out, meta, gamax, gnnz, gerr};
+}
+
 // ---- extension: real quantized output (codes + E8M0 scale bytes) -----------------------
 // returns [payload uint8 [dim_x, dim_y], scales uint8 [dim_x, dim_y / block_y]]
 std::vector<at::Tensor> quantize_mx(const at::Tensor& input, int64_t rows, int64_t cols, int64_t bc, int64_t elem_format) {
@@ -258,6 +290,7 @@ TORCH_LIBRARY(mor, m) {
   // addition: one scale per 1 x block_y group (MX), E4M3 / E5M2 / E2M3 elements
   m.def("fake_quantize_mx(Tensor input, int dim_x, int dim_y, int block_y, int elem_format, int sf_type) -> Tensor[]");
   m.def("quantize_mx(Tensor input, int dim_x, int dim_y, int block_y, int elem_format) -> Tensor[]");
+  m.def("fake_quantize_block_scaling_delayed(Tensor input, int dim_x, int dim_y, int block_x, int block_y, float e4m3_threshold, int ss_mode, Tensor amax_in) -> Tensor[]");
 }
 
 TORCH_LIBRARY_IMPL(mor, CUDA, m) {
@@ -277,6 +310,7 @@ TORCH_LIBRARY_IMPL(mor, CUDA, m) {
   m.impl("fake_quantize_channel_scaling_inplace", &fake_quantize_channel_scaling_inplace);
   m.impl("fake_quantize_mx", &fake_quantize_mx);
   m.impl("quantize_mx", &quantize_mx);
+  m.impl("fake_quantize_block_scaling_delayed", &fake_quantize_block_scaling_delayed);
 }
 
 }  // namespace mor

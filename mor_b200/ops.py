@@ -25,6 +25,7 @@ __all__ = [
     "e4m3_with_e8_scale_rne", "e4m3_with_e8_scale_rz",
     "fake_quantize_mx",
     "quantize_mx",
+    "fake_quantize_block_scaling_delayed",
 ]
 
 
@@ -132,6 +133,14 @@ def fake_quantize_mx(a: Tensor, dim_x: int, dim_y: int, block_y: int, elem_forma
     return _ops.fake_quantize_mx.default(a, dim_x, dim_y, block_y, elem_format, sf_type)
 
 
+def fake_quantize_block_scaling_delayed(a: Tensor, dim_x: int, dim_y: int, block_x: int, block_y: int,
+                                        e4m3_threshold: float, ss_mode: int, amax_in: Tensor) -> List[Tensor]:
+    """Block scaling in one pass over the tensor: the scales are built from ``amax_in`` (float32[1] on the
+    device, typically the amax that this call returned for the previous step's tensor), each 128 x 128
+    block's own amax is taken on chip.  Returns ``[out, meta, amax, non_zero, error]`` of THIS tensor."""
+    return _ops.fake_quantize_block_scaling_delayed.default(a, dim_x, dim_y, block_x, block_y, e4m3_threshold, ss_mode, amax_in)
+
+
 def quantize_mx(a: Tensor, dim_x: int, dim_y: int, block_y: int, elem_format: int) -> List[Tensor]:
     """The real quantized form of :func:`fake_quantize_mx` with a power-of-two scale: returns
     ``[payload, scales]``, both ``uint8``: one narrow-float code per element (fp8 byte for E4M3 / E5M2, the
@@ -163,6 +172,7 @@ for _name, _n in {
     "quant_dequant_e4m3": 5, "quant_dequant_e5m2": 5, "quant_dequant_e2m3": 5, "quant_dequant_e3m2": 5,
     "e4m3_with_e8_scale_rne": 5, "e4m3_with_e8_scale_rz": 5,
     "fake_quantize_mx": 6,
+    "fake_quantize_block_scaling_delayed": 8,
 }.items():
     torch.library.register_autograd(f"mor::{_name}", _straight_through(_n), setup_context=_no_context)
 del _name, _n

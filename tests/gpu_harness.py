@@ -116,6 +116,26 @@ def fake_quantize_group(x, by, fmt, sf, want_scales=True):
     return {"out": to_np(out), "scales": to_np(scales) if want_scales else None}
 
 
+def block_scaling_delayed(x, thr, ss, amax_in):
+    rows, cols = x.shape
+    d = to_dev(x)
+    out = torch.empty_like(d)
+    wsb = cabi.workspace_bytes(cabi.OP_BLOCK_SCALING, rows, cols, 128, 128)
+    ws = torch.empty(wsb, dtype=torch.uint8, device="cuda")
+    f32 = x.dtype == np.float32
+    meta = torch.zeros(1, dtype=torch.int32, device="cuda")
+    gamax = torch.zeros(1, dtype=torch.float32, device="cuda")
+    gerr = torch.zeros(1, dtype=torch.float32, device="cuda")
+    gnnz = torch.zeros(1, dtype=torch.int64 if f32 else torch.int32, device="cuda")
+    ain = torch.tensor([amax_in], dtype=torch.float32, device="cuda")
+    cabi.call("mor_b200_block_scaling_delayed", d.data_ptr(), out.data_ptr(), dtype_of(x), rows, cols, 128, 128, float(thr),
+              ss, ain.data_ptr(), meta.data_ptr(), gamax.data_ptr(), gnnz.data_ptr(), 1 if f32 else 0, gerr.data_ptr(),
+              ws.data_ptr(), wsb, stream())
+    torch.cuda.synchronize()
+    return {"out": to_np(out), "meta": to_np(meta), "gamax": float(gamax.item()), "gnnz": int(gnnz.item()),
+            "gerr": float(gerr.item())}
+
+
 def quantize_mx(x, by, fmt):
     rows, cols = x.shape
     d = to_dev(x)

@@ -479,6 +479,47 @@ def test_quantize_mx_round_trip_full_size():
         assert float(same.float().mean()) > 0.9
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+@pytest.mark.parametrize("ss", [1, 2, 3, 4])
+@pytest.mark.parametrize("kind", ["same", "stale_small", "stale_large", "zeros", "nan", "tiny"])
+def test_block_scaling_delayed_amax(dtype, ss, kind):
+    """single-pass block scaling with the tensor amax of an earlier step: output, meta, count and error equal
+    the two-pass arithmetic run with that amax; the reported amax is this tensor's"""
+    import gpu_harness as H
+    g = torch.Generator().manual_seed(ss * 7 + len(kind))
+    t = torch.randn(384, 512, generator=g) * 3.0
+    if kind == "zeros":
+        t = torch.where(torch.rand(384, 512, generator=g) < 0.2, 0.0, t)
+        t[:128, :128] = 0.0
+    if kind == "tiny":
+        t[128:256, 128:256] *= 1e-30
+    if dtype == "bf16":
+        x = t.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16).copy()
+        if kind == "nan":
+            if ss == 2:
+                pytest.skip("non-finite inputs are outside the reference's domain for power-of-two scales")
+            x[200, 300] = 0x7FC0
+    else:
+        x = t.numpy().copy()
+        if kind == "nan":
+            pytest.skip("covered by the bf16 case")
+    true_amax, _ = oracle.amax_nnz(x)
+    amax_in = {"stale_small": float(true_amax) * 0.37, "stale_large": float(true_amax) * 5.0}.get(kind, float(true_amax))
+    amax_in = float(np.float32(amax_in))
+    oracle.clear_assert_flags()
+    out, meta, _, nnz, err = oracle.block_scaling(x, 128, 128, 0.045, ss, global_amax=amax_in)
+    if oracle.assert_flags():
+        pytest.skip("the reference asserts on this input")
+    got = H.block_scaling_delayed(x, 0.045, ss, amax_in)
+    assert np.array_equal(got["out"].view(np.uint8), np.ascontiguousarray(out).view(np.uint8))
+    assert int(got["meta"][0]) == meta and got["gnnz"] == nnz
+    if kind == "nan":
+        assert np.isnan(got["gerr"]) and np.isnan(err)
+    else:
+        assert np.float32(got["gerr"]).view(np.uint32) == np.float32(err).view(np.uint32)
+    assert np.float32(got["gamax"]) == np.float32(true_amax)
+
+
 def test_host_pipeline_matches_device_call():
     """HostScaling (pinned host in/out, double-buffered copies) gives the bits of the device-side call,
     call after call, with a different tensor in every call"""
