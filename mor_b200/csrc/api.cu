@@ -116,9 +116,24 @@ int scaling_op(int kind, const void* in, void* out, int dtype, int64_t rows, int
     a.block_amax = reinterpret_cast<float*>(static_cast<char*>(wsp) + kHead);
     a.block_err = reinterpret_cast<float*>(static_cast<char*>(wsp) + kHead + round256(4 * (size_t)g.n_amax));
     a.n_err = g.n_err; a.err_slot_stride = g.stride; a.ws = ws; a.ext_gamax = nullptr;
+    const bool inplace = in == out;
+    // Strategies 2 and 3 scale a block by its own amax only: on 128 x 128 blocks the tile kernel
+    // takes it from the staged tile, and the separate amax pass over the tensor is not needed.
+    if (kind == MOR_B200_OP_BLOCK_SCALING && br == 128 && bc == 128 && (ss == 2 || ss == 3) && !inplace) {
+        a.scan_blocks = 1;
+        int rc1 = launch_zero_scalars(ws, st);
+        if (rc1) return rc1;
+        rc1 = launch_block_err_cast(a, /*store=*/true, false, st);
+        if (rc1 == kOk) {
+            rc1 = launch_finalize(a, nullptr, meta, gamax, gnnz, nnz64, gerr, st);
+            if (rc1) return rc1;
+            return launch_fallback_copy(a, st);
+        }
+        if (rc1 != kErrUnsupportedShape) return rc1;
+        a.scan_blocks = 0;   // no tile path for this tensor: the two-pass form below
+    }
     int rc = phase_amax(kind, in, dtype, rows, cols, br, bc, g, ws, a.block_amax, st);
     if (rc) return rc;
-    const bool inplace = in == out;
     // In place the input must survive until the tensor-level decision is known: sum the
     // errors without storing, decide, then cast only if the tensor is kept in E4M3.
     rc = phase_cast(kind, a, /*store=*/!inplace, false, st);
