@@ -31,8 +31,9 @@ HIST_WIDTH = 0.005
 
 @dataclass
 class QuantConfig:
-    """``kind``: "block" (block scaling, global-mantissa scale by default), "row" (one scale per row),
-    "mx" (1 x 32 groups, E8M0 scale, single pass), "mor" (per-block format choice), "none"."""
+    """``kind``: "block" (block scaling, global-mantissa scale by default), "block_delayed" (the same in one
+    pass over the tensor, with the tensor amax of the previous call: delayed scaling), "row" (one scale per
+    row), "mx" (1 x 32 groups, E8M0 scale, single pass), "mor" (per-block format choice), "none"."""
     kind: str = "block"
     block_rows: int = 128
     block_cols: int = 128
@@ -51,8 +52,9 @@ class QuantStats:
     global_error: Optional[Tensor] = None
 
 
-def fake_quantize_tensor(t: Tensor, cfg: QuantConfig):
-    """Fake-quantizes a tensor of any rank >= 1 (viewed as ``[-1, last]``); returns ``(out, QuantStats)``."""
+def fake_quantize_tensor(t: Tensor, cfg: QuantConfig, state: Optional[dict] = None):
+    """Fake-quantizes a tensor of any rank >= 1 (viewed as ``[-1, last]``); returns ``(out, QuantStats)``.
+    ``state`` carries the amax from call to call for the "block_delayed" kind (first call: two passes)."""
     if cfg.kind == "none":
         return t, QuantStats()
     x = t.reshape(-1, t.shape[-1])
@@ -62,6 +64,16 @@ def fake_quantize_tensor(t: Tensor, cfg: QuantConfig):
     if cfg.kind == "block":
         out, meta, amax, nnz, err = ops.fake_quantize_block_scaling(x, r, c, cfg.block_rows, cfg.block_cols,
                                                                     cfg.threshold, cfg.ss_mode)
+        st = QuantStats(meta, amax, nnz, err)
+    elif cfg.kind == "block_delayed":
+        prev = None if state is None else state.get("amax")
+        if prev is None:   # nothing to go by yet: the two-pass form, whose amax seeds the next call
+            out, meta, amax, nnz, err = ops.fake_quantize_block_scaling(x, r, c, 128, 128, cfg.threshold, cfg.ss_mode)
+        else:
+            out, meta, amax, nnz, err = ops.fake_quantize_block_scaling_delayed(x, r, c, 128, 128, cfg.threshold,
+                                                                                cfg.ss_mode, prev)
+        if state is not None:
+            state["amax"] = amax.detach()
         st = QuantStats(meta, amax, nnz, err)
     elif cfg.kind == "row":
         out, meta, amax, nnz, err = ops.fake_quantize_channel_scaling(x, r, c, 1, c, cfg.threshold, cfg.ss_mode)
@@ -138,7 +150,7 @@ class _QuantizeGrad(torch.autograd.Function):
     def backward(ctx, grad: Tensor):
         layer = ctx.layer
         g = grad.contiguous()
-        gq, st = fake_quantize_tensor(g, layer.grad_cfg)
+        gq, st = fake_quantize_tensor(g, layer.grad_cfg, layer._state["grad"])
         if layer.logger is not None:
             layer.logger.log(f"{layer.log_name}.grad_output", g, gq, st, layer.grad_cfg)
         return gq, None
@@ -159,10 +171,11 @@ class MoRLinear(torch.nn.Linear):
         self.grad_cfg = grad_cfg or QuantConfig(kind="none")
         self.logger = logger
         self.log_name = name
+        self._state = {"input": {}, "weight": {}, "grad": {}}   # amax carried between calls (delayed scaling)
 
     def forward(self, x: Tensor) -> Tensor:
-        xq, sx = fake_quantize_tensor(x, self.input_cfg)
-        wq, sw = fake_quantize_tensor(self.weight, self.weight_cfg)
+        xq, sx = fake_quantize_tensor(x, self.input_cfg, self._state["input"])
+        wq, sw = fake_quantize_tensor(self.weight, self.weight_cfg, self._state["weight"])
         if self.logger is not None:
             self.logger.log(f"{self.log_name}.input", x, xq, sx, self.input_cfg)
             self.logger.log(f"{self.log_name}.weight", self.weight, wq, sw, self.weight_cfg)

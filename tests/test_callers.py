@@ -105,6 +105,26 @@ def test_linear_wrapper_forward_backward_and_log():
 
 
 @pytest.mark.gpu
+def test_linear_wrapper_delayed_scaling():
+    """the first call seeds the amax with the two-pass form; later calls quantize in one pass with the
+    amax of the call before"""
+    import mor
+    from mor_b200.nn import MoRLinear, QuantConfig
+    torch.manual_seed(1)
+    layer = MoRLinear(256, 128, bias=False, device="cuda", input_cfg=QuantConfig("block_delayed"),
+                      weight_cfg=QuantConfig("none"))
+    x1 = torch.randn(128, 256, device="cuda", dtype=torch.bfloat16)
+    x2 = x1 * 3.0
+    y1 = layer(x1)
+    want1 = mor.ops.fake_quantize_block_scaling(x1, 128, 256, 128, 128, 0.045, 1)
+    assert torch.equal(y1, torch.nn.functional.linear(want1[0], layer.weight))
+    y2 = layer(x2)
+    want2 = mor.ops.fake_quantize_block_scaling_delayed(x2, 128, 256, 128, 128, 0.045, 1, want1[2])
+    assert torch.equal(y2, torch.nn.functional.linear(want2[0], layer.weight))
+    assert layer._state["input"]["amax"].item() == x2.float().abs().max().item()
+
+
+@pytest.mark.gpu
 def test_bin_file_replays_through_the_operator(tmp_path):
     import mor
     from mor_b200 import binio
