@@ -4,7 +4,7 @@
     python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
     python bench.py --impl reference ...                           CPU arm (the oracle on the host cores)
     python bench.py --suite                                        also times every kernel family on
-                                                                   configurations 1-4 (gpurun_out/suite.json)
+                                                                   configurations 1-5 (table in <run-output folder>/suite.json)
 
 Workload: configuration 5 -- a float32 131072 x 16384 tensor (8 GiB, N(0,1), synthetic),
 row-sharded over the N ranks, fake-quantized to E4M3 with 128 x 128 block scaling under
@@ -168,7 +168,7 @@ def main():
     ap.add_argument("--suite-impl", choices=["ours", "reference"], default="ours",
                     help="reference: time the unmodified reference CUDA extension (oracle/_ref) on the configurations it supports")
     ap.add_argument("--suite-graph", action="store_true", help="also time the suite calls replayed as one CUDA graph")
-    ap.add_argument("--suite-out", default=None, help="where --suite writes its table (default gpurun_out/suite.json)")
+    ap.add_argument("--suite-out", default=None, help="where --suite writes its table (default: suite.json in the run-output folder)")
     ap.add_argument("--exchange", choices=["auto", "nccl", "p2p"], default="auto",
                     help="how ranks exchange amax / non-zero count / error sums (N > 1): NCCL collectives or peer stores")
     ap.add_argument("--no-e2e", action="store_true")

@@ -6,7 +6,7 @@
 # only tests/golden/make_gpu_golden.py loads it, in a process of its own, to record
 # the reference's outputs on a GPU.  Nothing in the product imports it.
 #
-# usage: oracle/build_ref.sh [reference_root]     (default /root/reference)
+# usage: oracle/build_ref.sh [reference_root]     (default: the reference checkout beside this repository's parent)
 set -euo pipefail
 REF="${1:-/root/reference}"
 HERE="$(cd "$(dirname "$0")" && pwd)"

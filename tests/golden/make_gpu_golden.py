@@ -10,7 +10,7 @@ repository's own extension must not be imported here), runs every case of
 
     tests/golden/reference_b200.json   per case: sha256 of the output bits, the meta
                                        matrix and the scalar outputs (as bit patterns)
-    gpurun_out/golden_report.txt       case-by-case comparison with the CPU oracle
+    <run-output folder>/golden_report.txt   case-by-case comparison with the CPU oracle
 
 Before a case runs on the GPU the CPU oracle evaluates it: a case on which a
 device-side assert() of the reference would fire (the reference is built with asserts
