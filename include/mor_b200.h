@@ -211,7 +211,7 @@ MOR_B200_API int mor_b200_scaling_fallback(const void* input, void* output, int6
  * Order per call, all on one stream:  scaling_amax (its two outputs may be NULL) ->
  * p2p_exchange_scalars (writes global amax and nnz) -> scaling_cast -> p2p_exchange_errors ->
  * scaling_finalize on (own buffer + p2p_error_offset, world * n_err entries) -> scaling_fallback.
- * Waits are bounded (about two seconds); a time-out sets a flag in the workspace head and
+ * Waits are bounded (several seconds); a time-out sets a flag in the workspace head and
  * scaling_finalize then reports meta = -1.  world <= 16. */
 /* The exchange buffer is allocated (cudaMalloc, zero-filled), exported (64-byte CUDA IPC handle,
  * to be sent to the other processes by any means) and opened by the library: a peer's buffer must

@@ -24,7 +24,7 @@ namespace {
 constexpr int kMaxWorld = 16;
 constexpr size_t kScalOffset = 0, kScalBytes = 2 * kMaxWorld * 32;
 constexpr size_t kFlagOffset = kScalBytes, kErrOffset = 2048;
-constexpr uint32_t kP2PSpinLimit = 1u << 23;  // x 200 ns of back-off: about two seconds
+constexpr uint32_t kP2PSpinLimit = 1u << 25;  // x 200 ns of back-off: several seconds (ranks start a first call unevenly)
 
 struct ScalSlot {
     uint32_t amax_bits;
