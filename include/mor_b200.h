@@ -223,6 +223,8 @@ MOR_B200_API int mor_b200_p2p_open(int device, const unsigned char* handle, void
 MOR_B200_API int mor_b200_p2p_close(int device, void* peer_ptr);
 MOR_B200_API int mor_b200_p2p_free(int device, void* own_ptr);
 MOR_B200_API size_t mor_b200_p2p_bytes(int world, int64_t n_err);
+/* polls (about 0.3 us each) after which a wait of the exchange kernels gives up; default 2^25 */
+MOR_B200_API void mor_b200_p2p_set_wait_limit(uint32_t polls);
 MOR_B200_API size_t mor_b200_p2p_error_offset(int world, int64_t n_err, uint32_t epoch);
 MOR_B200_API int mor_b200_p2p_exchange_scalars(void* workspace, void* my_buf, void* const* peer_bufs, int rank, int world,
                                   uint32_t epoch, float* global_amax, int64_t* global_nnz, void* stream);

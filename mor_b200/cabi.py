@@ -46,6 +46,7 @@ SIGNATURES = {
     "mor_b200_p2p_close": (_i, [_i, _vp]),
     "mor_b200_p2p_free": (_i, [_i, _vp]),
     "mor_b200_p2p_bytes": (_sz, [_i, _i64]),
+    "mor_b200_p2p_set_wait_limit": (None, [C.c_uint32]),
     "mor_b200_p2p_error_offset": (_sz, [_i, _i64, C.c_uint32]),
     "mor_b200_p2p_exchange_scalars": (_i, [_vp, _vp, _vp, _i, _i, C.c_uint32, _vp, _vp, _vp]),
     "mor_b200_p2p_exchange_errors": (_i, [_vp, _i64, _vp, _vp, _i, _i, C.c_uint32, _vp, _vp]),

@@ -416,6 +416,7 @@ int mor_b200_scaling_fallback(const void* in, void* out, int64_t n_bytes, const 
 }
 
 size_t mor_b200_p2p_bytes(int world, int64_t n_err) { return p2p_buffer_bytes(world, n_err); }
+void mor_b200_p2p_set_wait_limit(uint32_t polls) { p2p_set_wait_limit(polls); }
 size_t mor_b200_p2p_error_offset(int world, int64_t n_err, uint32_t epoch) { return p2p_error_offset(world, n_err, epoch); }
 
 // The buffer is allocated, exported and opened here, not through the caller's allocator: a peer's

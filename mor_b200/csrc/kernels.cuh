@@ -86,6 +86,7 @@ int launch_fq_group(const void* in, void* out, int is_fp32, float* scales, int32
 
 // ---- p2p.cu: peer exchange of the row-sharded pipeline (plain NVLink stores + epoch flags)
 size_t p2p_buffer_bytes(int world, int64_t n_err);
+void p2p_set_wait_limit(uint32_t polls);
 size_t p2p_error_offset(int world, int64_t n_err, uint32_t epoch);
 int launch_p2p_exchange_scalars(ScalarsWs* ws, void* mine, void* const* peer_bufs, int rank, int world, uint32_t epoch,
                                 float* gamax_out, long long* gnnz_out, cudaStream_t st);

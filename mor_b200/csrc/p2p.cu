@@ -24,7 +24,8 @@ namespace {
 constexpr int kMaxWorld = 16;
 constexpr size_t kScalOffset = 0, kScalBytes = 2 * kMaxWorld * 32;
 constexpr size_t kFlagOffset = kScalBytes, kErrOffset = 2048;
-constexpr uint32_t kP2PSpinLimit = 1u << 25;  // x 200 ns of back-off: several seconds (ranks start a first call unevenly)
+// polls of a wait, x 200 ns of back-off: several seconds by default (ranks start a first call unevenly)
+uint32_t g_spin_limit = 1u << 25;
 
 struct ScalSlot {
     uint32_t amax_bits;
@@ -47,8 +48,8 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ bool wait_epoch(const uint32_t* flag, uint32_t epoch) {
-    for (uint32_t i = 0; i < kP2PSpinLimit; ++i) {
+__device__ __forceinline__ bool wait_epoch(const uint32_t* flag, uint32_t epoch, uint32_t limit) {
+    for (uint32_t i = 0; i < limit; ++i) {
         if (ld_acquire_sys(flag) == epoch) return true;
         __nanosleep(200);
     }
@@ -59,7 +60,7 @@ __device__ __forceinline__ bool wait_epoch(const uint32_t* flag, uint32_t epoch)
 // the waits cannot form a cycle.
 __global__ void p2p_exchange_scalars_kernel(ScalarsWs* __restrict__ ws, unsigned char* __restrict__ mine, PeerPtrs peers,
                                             int rank, int world, uint32_t epoch, float* __restrict__ gamax_out,
-                                            long long* __restrict__ gnnz_out) {
+                                            long long* __restrict__ gnnz_out, uint32_t limit) {
     const int p = threadIdx.x;
     const uint32_t par = epoch & 1u;
     uint32_t amax_bits = 0u;
@@ -72,7 +73,7 @@ __global__ void p2p_exchange_scalars_kernel(ScalarsWs* __restrict__ ws, unsigned
         __threadfence_system();
         st_release_sys(&out->flag, epoch);
         const ScalSlot* in = reinterpret_cast<const ScalSlot*>(mine + kScalOffset) + par * kMaxWorld + p;
-        ok = wait_epoch(&in->flag, epoch);
+        ok = wait_epoch(&in->flag, epoch, limit);
         if (ok) {
             amax_bits = *reinterpret_cast<const volatile uint32_t*>(&in->amax_bits);
             nnz = *reinterpret_cast<const volatile unsigned long long*>(&in->nnz);
@@ -100,14 +101,14 @@ __global__ void __launch_bounds__(256) p2p_push_errors_kernel(const float* __res
 // launched behind the copy on the same stream: the copy's stores are complete when this starts.
 // Tells every rank that this rank's error sums are in place, then waits for theirs.
 __global__ void p2p_flag_wait_errors_kernel(const unsigned char* __restrict__ mine, PeerPtrs peers, int rank, int world,
-                                            uint32_t epoch, ScalarsWs* __restrict__ ws) {
+                                            uint32_t epoch, ScalarsWs* __restrict__ ws, uint32_t limit) {
     const int p = threadIdx.x;
     const uint32_t par = epoch & 1u;
     bool ok = true;
     if (p < world) {
         __threadfence_system();
         st_release_sys(reinterpret_cast<uint32_t*>(peers.p[p] + kFlagOffset) + par * kMaxWorld + rank, epoch);
-        ok = wait_epoch(reinterpret_cast<const uint32_t*>(mine + kFlagOffset) + par * kMaxWorld + p, epoch);
+        ok = wait_epoch(reinterpret_cast<const uint32_t*>(mine + kFlagOffset) + par * kMaxWorld + p, epoch, limit);
     }
     if (!__all_sync(0xFFFFFFFFu, ok) && p == 0) atomicOr(&ws->load_timeout, 1u);
 }
@@ -124,6 +125,8 @@ bool fill_peers(PeerPtrs& pp, void* const* peer_bufs, int world) {
 
 }  // namespace
 
+void p2p_set_wait_limit(uint32_t polls) { g_spin_limit = polls ? polls : 1u; }
+
 size_t p2p_buffer_bytes(int world, int64_t n_err) {
     if (world < 1 || world > kMaxWorld || n_err < 1) return 0;
     return (kErrOffset + 2 * (size_t)world * (size_t)n_err * sizeof(float) + 255) & ~size_t(255);
@@ -138,7 +141,7 @@ int launch_p2p_exchange_scalars(ScalarsWs* ws, void* mine, void* const* peer_buf
     if (!ws || !mine || !gamax_out || !gnnz_out || !fill_peers(pp, peer_bufs, world) || rank < 0 || rank >= world)
         return kErrInvalidArgument;
     p2p_exchange_scalars_kernel<<<1, 32, 0, st>>>(ws, static_cast<unsigned char*>(mine), pp, rank, world, epoch,
-                                                  gamax_out, gnnz_out);
+                                                  gamax_out, gnnz_out, g_spin_limit);
     return check_launch();
 }
 int launch_p2p_exchange_errors(const float* local_err, int64_t n_err, const void* mine, void* const* peer_bufs, int rank,
@@ -152,7 +155,7 @@ int launch_p2p_exchange_errors(const float* local_err, int64_t n_err, const void
     p2p_push_errors_kernel<<<(unsigned)grid, 256, 0, st>>>(local_err, n_err, pp, rank, world, epoch);
     const int rc = check_launch();
     if (rc) return rc;
-    p2p_flag_wait_errors_kernel<<<1, 32, 0, st>>>(static_cast<const unsigned char*>(mine), pp, rank, world, epoch, ws);
+    p2p_flag_wait_errors_kernel<<<1, 32, 0, st>>>(static_cast<const unsigned char*>(mine), pp, rank, world, epoch, ws, g_spin_limit);
     return check_launch();
 }
 

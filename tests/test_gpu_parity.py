@@ -520,6 +520,50 @@ def test_block_scaling_delayed_amax(dtype, ss, kind):
     assert np.float32(got["gamax"]) == np.float32(true_amax)
 
 
+def test_peer_exchange_wait_runs_out():
+    """A rank whose peer never shows up: the exchange kernels give up after their bounded wait, flag the
+    workspace, and the ordered sum then reports meta = -1.  The absent peer is a second local buffer that
+    nothing writes flags into; the limit is lowered so that the wait lasts milliseconds."""
+    import ctypes
+    from mor_b200 import cabi
+    L = cabi.lib()
+    n_err = 64
+    nbytes = int(L.mor_b200_p2p_bytes(2, n_err))
+    bufs, handle = [], (ctypes.c_ubyte * 64)()
+    for _ in range(2):
+        p = ctypes.c_void_p()
+        cabi.call("mor_b200_p2p_alloc", 0, nbytes, ctypes.byref(p), handle)
+        bufs.append(int(p.value))
+    peers = (ctypes.c_void_p * 2)(*bufs)
+    wsb = cabi.workspace_bytes(cabi.OP_AMAX_NNZ, 1, 1, 1, 1)
+    ws = torch.zeros(wsb, dtype=torch.uint8, device="cuda")
+    amax = torch.zeros(1, dtype=torch.float32, device="cuda")
+    nnz = torch.ones(1, dtype=torch.int64, device="cuda")
+    err = torch.rand(n_err, device="cuda")
+    meta = torch.zeros(1, dtype=torch.int32, device="cuda")
+    total = torch.zeros(1, dtype=torch.float32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    L.mor_b200_p2p_set_wait_limit(1 << 12)
+    try:
+        cabi.call("mor_b200_p2p_exchange_scalars", ws.data_ptr(), bufs[0], peers, 0, 2, 1, amax.data_ptr(), nnz.data_ptr(), st)
+        torch.cuda.synchronize()
+        assert ws[28:32].view(torch.int32).item() == 1          # the time-out flag of the workspace head
+        ws.zero_()
+        cabi.call("mor_b200_p2p_exchange_errors", err.data_ptr(), n_err, bufs[0], peers, 0, 2, 1, ws.data_ptr(), st)
+        torch.cuda.synchronize()
+        assert ws[28:32].view(torch.int32).item() == 1
+        nnz.fill_(1000)
+        cabi.call("mor_b200_scaling_finalize", err.data_ptr(), n_err, 1, nnz.data_ptr(), 0.045, meta.data_ptr(),
+                  total.data_ptr(), ws.data_ptr(), wsb, st)
+        torch.cuda.synchronize()
+        assert meta.item() == -1
+    finally:
+        L.mor_b200_p2p_set_wait_limit(1 << 25)
+        torch.cuda.synchronize()
+        for b in bufs:
+            L.mor_b200_p2p_free(0, b)
+
+
 def test_host_pipeline_matches_device_call():
     """HostScaling (pinned host in/out, double-buffered copies) gives the bits of the device-side call,
     call after call, with a different tensor in every call"""
