@@ -174,6 +174,12 @@ MOR_B200_API int mor_b200_block_scaling_delayed(const void* input, void* output,
 MOR_B200_API int mor_b200_quantize_mx(const void* input, void* payload, void* scales, int64_t rows, int64_t cols,
                          int block_cols, int format, void* stream);
 
+/* The same with E2M3 elements packed six bits each: payload is [rows, cols * 3 / 4] bytes (2-byte
+ * aligned), every run of eight elements a little-endian 48-bit group with code i in bits
+ * [6 i, 6 i + 6).  No counterpart in the reference. */
+MOR_B200_API int mor_b200_quantize_mx_fp6(const void* input, void* payload, void* scales, int64_t rows, int64_t cols,
+                             int block_cols, void* stream);
+
 /* ---- row-sharded pipeline (extension): the phases of block/channel scaling as separate
  * calls, so that a caller holding one row slab per GPU can all-reduce the amax (max)
  * and the non-zero count (sum) and all-gather the block errors between them. ---- */

@@ -337,7 +337,15 @@ int mor_b200_quantize_mx(const void* in, void* payload, void* scales, int64_t ro
     if (cols % bc) return kErrInvalidArgument;
     if (format != kE4M3 && format != kE5M2 && format != kE2M3) return kErrInvalidArgument;
     if (!aligned16(in) || (reinterpret_cast<uintptr_t>(payload) & 7u)) return kErrUnsupportedShape;
-    return launch_quantize_mx(in, payload, static_cast<uint8_t*>(scales), rows, cols, bc, format,
+    return launch_quantize_mx(in, payload, static_cast<uint8_t*>(scales), rows, cols, bc, format, 0,
+                              static_cast<cudaStream_t>(stream));
+}
+int mor_b200_quantize_mx_fp6(const void* in, void* payload, void* scales, int64_t rows, int64_t cols, int bc,
+                             void* stream) {
+    if (!in || !payload || !scales || rows <= 0 || cols <= 0 || bc <= 0) return kErrInvalidArgument;
+    if (cols % bc) return kErrInvalidArgument;
+    if (!aligned16(in) || (reinterpret_cast<uintptr_t>(payload) & 1u)) return kErrUnsupportedShape;
+    return launch_quantize_mx(in, payload, static_cast<uint8_t*>(scales), rows, cols, bc, kE2M3, 1,
                               static_cast<cudaStream_t>(stream));
 }
 

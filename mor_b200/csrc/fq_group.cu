@@ -302,7 +302,23 @@ __device__ __forceinline__ uint2 mx_codes_one(const uint4& v, uint32_t& scale_by
     return make_uint2(codes_fix_zero_sign<FMT>(c[0] | (c[1] << 16)), codes_fix_zero_sign<FMT>(c[2] | (c[3] << 16)));
 }
 
-template <int FMT, int GS>
+// eight codes of a vector: one byte each, or (PACK6) six bits each in 6 bytes, code i in bits
+// [6 i, 6 i + 6) of the little-endian 48-bit group
+template <bool PACK6>
+__device__ __forceinline__ void store_codes(uint2* __restrict__ payload, int64_t idx, const uint2& c) {
+    if constexpr (PACK6) {
+        const uint32_t a = c.x, b = c.y;   // bytes c0..c3, c4..c7, each below 64
+        const uint32_t lo = (a & 0x3Fu) | ((a >> 2) & 0xFC0u) | ((a >> 4) & 0x3F000u) | ((a >> 6) & 0xFC0000u) |
+                            ((b & 0x3Fu) << 24) | ((b & 0x300u) << 22);
+        const uint32_t hi = ((b >> 10) & 0xFu) | ((b >> 12) & 0x3F0u) | ((b >> 14) & 0xFC00u);
+        uint16_t* p = reinterpret_cast<uint16_t*>(payload) + 3 * idx;
+        p[0] = (uint16_t)lo; p[1] = (uint16_t)(lo >> 16); p[2] = (uint16_t)hi;
+    } else {
+        st_stream(payload + idx, c);
+    }
+}
+
+template <int FMT, int GS, bool PACK6 = false>
 __global__ void __launch_bounds__(32 * kMxWarps, 5)
 mx_quantize_kernel(const uint4* __restrict__ in, uint2* __restrict__ payload, uint8_t* __restrict__ scales, int64_t nvec) {
     extern __shared__ __align__(128) uint8_t s_ring[];  // [warp][stage][2 KiB]
@@ -318,7 +334,7 @@ mx_quantize_kernel(const uint4* __restrict__ in, uint2* __restrict__ payload, ui
         const int64_t v0 = c * kMxChunkVec;
         const int nv = (int)(nvec - v0 < kMxChunkVec ? nvec - v0 : kMxChunkVec);
         const bool staged = ws.acquire(st);
-        uint2* o = payload + v0 + lane;
+        const int64_t o = v0 + lane;
         uint8_t* sc = scales + ((v0 + lane) >> GS);
         if (staged && nv == kMxChunkVec) {
             const uint4* chunk = reinterpret_cast<const uint4*>(ws.stage(st)) + lane;
@@ -326,14 +342,14 @@ mx_quantize_kernel(const uint4* __restrict__ in, uint2* __restrict__ payload, ui
             for (int r = 0; r < kMxChunkVec / 32; ++r) {
                 uint32_t sb;
                 const uint2 codes = mx_codes_one<FMT, GS>(chunk[r * 32], sb);
-                st_stream(o + r * 32, codes);
+                store_codes<PACK6>(payload, o + r * 32, codes);
                 if (scale_lane) sc[r * (32 >> GS)] = (uint8_t)sb;
             }
         } else {  // last, partial chunk, or a copy that did not arrive: ordinary loads
             for (int r = 0; r * 32 < nv; ++r) {
                 uint32_t sb;
                 const uint2 codes = mx_codes_one<FMT, GS>(ld_stream(in + v0 + r * 32 + lane), sb);
-                st_stream(o + r * 32, codes);
+                store_codes<PACK6>(payload, o + r * 32, codes);
                 if (scale_lane) sc[r * (32 >> GS)] = (uint8_t)sb;
             }
         }
@@ -518,7 +534,8 @@ int launch_fmt(const void* in, void* out, float* scales, int32_t* meta, int32_t 
 }  // namespace
 
 int launch_quantize_mx(const void* in, void* payload, uint8_t* scales, int64_t rows, int64_t cols, int bcols, int fmt,
-                       cudaStream_t st) {
+                       int pack6, cudaStream_t st) {
+    if (pack6 && fmt != kE2M3) return kErrInvalidArgument;
     if (bcols % 8 || cols % bcols) return kErrUnsupportedShape;
     const int gvec = bcols / 8;
     const int64_t nvec = rows * cols / 8;
@@ -551,10 +568,27 @@ int launch_quantize_mx(const void* in, void* payload, uint8_t* scales, int64_t r
             default: MORB_Q(F, 5); break;                                                                            \
         }                                                                                                            \
     } while (0)
-    if (fmt == kE4M3) MORB_QS(kE4M3);
+#define MORB_Q6(GS)                                                                                                  \
+    do {                                                                                                             \
+        static const cudaError_t attr =                                                                              \
+            cudaFuncSetAttribute(mx_quantize_kernel<kE2M3, GS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing); \
+        if (attr != cudaSuccess) return kErrLaunch;                                                                  \
+        mx_quantize_kernel<kE2M3, GS, true><<<(unsigned)grid, 32 * kMxWarps, kRing, st>>>(i4, p2, scales, nvec);     \
+    } while (0)
+    if (pack6) {
+        switch (shift) {
+            case 0: MORB_Q6(0); break;
+            case 1: MORB_Q6(1); break;
+            case 2: MORB_Q6(2); break;
+            case 3: MORB_Q6(3); break;
+            case 4: MORB_Q6(4); break;
+            default: MORB_Q6(5); break;
+        }
+    } else if (fmt == kE4M3) MORB_QS(kE4M3);
     else if (fmt == kE5M2) MORB_QS(kE5M2);
     else if (fmt == kE2M3) MORB_QS(kE2M3);
     else return kErrInvalidArgument;
+#undef MORB_Q6
 #undef MORB_QS
 #undef MORB_Q
     return check_launch();

@@ -80,7 +80,7 @@ int launch_fq_block(const void* in, void* out, int is_fp32, int32_t* meta, int64
 // ---- fq_group.cu: single-pass per-group scaling (1 x k groups, MX style) ----------
 // narrow-float codes + E8M0 scale bytes of 1 x bcols groups (bf16 input, power-of-two scale)
 int launch_quantize_mx(const void* in, void* payload, uint8_t* scales, int64_t rows, int64_t cols, int bcols, int fmt,
-                       cudaStream_t st);
+                       int pack6, cudaStream_t st);
 int launch_fq_group(const void* in, void* out, int is_fp32, float* scales, int32_t* meta, int32_t meta_code,
                     int64_t rows, int64_t cols, int bcols, int fmt, int sf_type, cudaStream_t st);
 

@@ -266,6 +266,20 @@ std::vector<at::Tensor> quantize_mx(const at::Tensor& input, int64_t rows, int64
     return {payload, scales};
 }
 
+// returns [payload uint8 [dim_x, dim_y * 3 / 4] (E2M3, six bits per element), scales uint8 [dim_x, dim_y / block_y]]
+std::vector<at::Tensor> quantize_mx_fp6(const at::Tensor& input, int64_t rows, int64_t cols, int64_t bc) {
+    const c10::cuda::CUDAGuard guard(input.device());
+    at::Tensor in = checked_input(input, rows, cols, "quantize_mx_fp6");
+    TORCH_CHECK(in.scalar_type() == at::kBFloat16, "mor::quantize_mx_fp6: bfloat16 input only");
+    TORCH_CHECK(bc > 0 && cols % bc == 0 && cols % 8 == 0, "mor::quantize_mx_fp6: block_y must divide dim_y, dim_y a multiple of 8");
+    at::Tensor payload = torch::empty({rows, cols * 3 / 4}, in.options().dtype(torch::kUInt8));
+    at::Tensor scales = torch::empty({rows, cols / bc}, in.options().dtype(torch::kUInt8));
+    check_status(mor_b200_quantize_mx_fp6(in.data_ptr(), payload.data_ptr(), scales.data_ptr(), rows, cols, (int)bc,
+                                          cur_stream()),
+                 "quantize_mx_fp6");
+    return {payload, scales};
+}
+
 }  // namespace
 
 // Registers _C as a Python extension module.
@@ -290,6 +304,7 @@ TORCH_LIBRARY(mor, m) {
   // addition: one scale per 1 x block_y group (MX), E4M3 / E5M2 / E2M3 elements
   m.def("fake_quantize_mx(Tensor input, int dim_x, int dim_y, int block_y, int elem_format, int sf_type) -> Tensor[]");
   m.def("quantize_mx(Tensor input, int dim_x, int dim_y, int block_y, int elem_format) -> Tensor[]");
+  m.def("quantize_mx_fp6(Tensor input, int dim_x, int dim_y, int block_y) -> Tensor[]");
   m.def("fake_quantize_block_scaling_delayed(Tensor input, int dim_x, int dim_y, int block_x, int block_y, float e4m3_threshold, int ss_mode, Tensor amax_in) -> Tensor[]");
 }
 
@@ -310,6 +325,7 @@ TORCH_LIBRARY_IMPL(mor, CUDA, m) {
   m.impl("fake_quantize_channel_scaling_inplace", &fake_quantize_channel_scaling_inplace);
   m.impl("fake_quantize_mx", &fake_quantize_mx);
   m.impl("quantize_mx", &quantize_mx);
+  m.impl("quantize_mx_fp6", &quantize_mx_fp6);
   m.impl("fake_quantize_block_scaling_delayed", &fake_quantize_block_scaling_delayed);
 }
 

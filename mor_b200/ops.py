@@ -25,6 +25,7 @@ __all__ = [
     "e4m3_with_e8_scale_rne", "e4m3_with_e8_scale_rz",
     "fake_quantize_mx",
     "quantize_mx",
+    "quantize_mx_fp6",
     "fake_quantize_block_scaling_delayed",
 ]
 
@@ -147,6 +148,12 @@ def quantize_mx(a: Tensor, dim_x: int, dim_y: int, block_y: int, elem_format: in
     6-bit code in a byte for E2M3) and one E8M0 byte per 1 x ``block_y`` group;
     ``element = decode(code) * 2 ** (scale - 127)``.  No gradient."""
     return _ops.quantize_mx.default(a, dim_x, dim_y, block_y, elem_format)
+
+
+def quantize_mx_fp6(a: Tensor, dim_x: int, dim_y: int, block_y: int) -> List[Tensor]:
+    """:func:`quantize_mx` for E2M3 with the codes packed six bits each: ``payload`` is ``uint8 [dim_x, dim_y * 3 / 4]``,
+    every run of eight elements a little-endian 48-bit group with code i in bits [6 i, 6 i + 6)."""
+    return _ops.quantize_mx_fp6.default(a, dim_x, dim_y, block_y)
 
 
 # --------------------------------------------------------------------------- straight-through backward

@@ -213,6 +213,21 @@ def quantize_mx(x, bcols, fmt):
     return payload, scales
 
 
+def pack_fp6(codes):
+    """Six-bit codes (one per byte, [rows, cols], cols a multiple of 8) -> [rows, cols * 3 / 4] bytes: every run of
+    eight codes is a little-endian 48-bit group with code i in bits [6 i, 6 i + 6)."""
+    c = np.ascontiguousarray(codes, dtype=np.uint8)
+    rows, cols = c.shape
+    g = c.reshape(rows, cols // 8, 8).astype(np.uint64)
+    word = np.zeros((rows, cols // 8), np.uint64)
+    for i in range(8):
+        word |= (g[:, :, i] & np.uint64(63)) << np.uint64(6 * i)
+    out = np.zeros((rows, cols // 8, 6), np.uint8)
+    for k in range(6):
+        out[:, :, k] = ((word >> np.uint64(8 * k)) & np.uint64(255)).astype(np.uint8)
+    return out.reshape(rows, cols * 3 // 4)
+
+
 def dequantize_mx(payload, scales, bcols, fmt):
     payload = np.ascontiguousarray(payload, dtype=np.uint8)
     scales = np.ascontiguousarray(scales, dtype=np.uint8)

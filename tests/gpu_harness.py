@@ -146,6 +146,16 @@ def quantize_mx(x, by, fmt):
     return {"payload": payload.cpu().numpy(), "scales": scales.cpu().numpy()}
 
 
+def quantize_mx_fp6(x, by):
+    rows, cols = x.shape
+    d = to_dev(x)
+    payload = torch.zeros(rows, cols * 3 // 4, dtype=torch.uint8, device="cuda")
+    scales = torch.zeros(rows, cols // by, dtype=torch.uint8, device="cuda")
+    cabi.call("mor_b200_quantize_mx_fp6", d.data_ptr(), payload.data_ptr(), scales.data_ptr(), rows, cols, by, stream())
+    torch.cuda.synchronize()
+    return {"payload": payload.cpu().numpy(), "scales": scales.cpu().numpy()}
+
+
 _FMT = {"quant_dequant_e4m3": cabi.E4M3, "quant_dequant_e5m2": cabi.E5M2, "quant_dequant_e3m2": cabi.E3M2,
         "quant_dequant_e2m3": cabi.E2M3}
 

@@ -454,6 +454,22 @@ def test_quantize_mx_codes_and_scales(fmt, by):
     assert bad.size == 0, f"codes fmt {fmt} 1x{by}: first mismatch at {bad[0]}: {got['payload'][tuple(bad[0])]:#x} vs {codes[tuple(bad[0])]:#x}"
 
 
+@pytest.mark.parametrize("by", [8, 32, 128])
+def test_quantize_mx_fp6_packed(by):
+    """E2M3 codes packed six bits each equal the oracle's codes packed on the CPU"""
+    import gpu_harness as H
+    g = torch.Generator().manual_seed(by)
+    t = torch.randn(40, 1024, generator=g) * torch.where(torch.rand(40, 1024, generator=g) < 0.01, 300.0, 1.0)
+    t[3] = 0.0
+    x = t.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    oracle.clear_assert_flags()
+    codes, scales = oracle.quantize_mx(x, by, 3)
+    assert oracle.assert_flags() == 0
+    got = H.quantize_mx_fp6(x, by)
+    assert np.array_equal(got["scales"], scales)
+    assert np.array_equal(got["payload"], oracle.pack_fp6(codes))
+
+
 def test_quantize_mx_round_trip_full_size():
     """configuration 3 at full size (16384 x 8192, 1 x 32 groups): decode(code) * 2^(scale - 127) equals the
     fake-quantized tensor wherever the code is non-zero or the scale is at least one"""

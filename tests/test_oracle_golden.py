@@ -254,3 +254,17 @@ def test_quantize_mx_round_trip(fmt, by):
         assert (codes < 64).all()
     if fmt == 0:
         assert ((codes & 0x7F) != 0x7F).all()
+
+
+def test_pack_fp6_layout():
+    codes = np.arange(64, dtype=np.uint8).reshape(2, 32)
+    p = oracle.pack_fp6(codes)
+    assert p.shape == (2, 24)
+    # first group 0..7: 0 | 1<<6 | 2<<12 | 3<<18 | 4<<24 | 5<<30 | 6<<36 | 7<<42
+    word = sum(i << (6 * i) for i in range(8))
+    assert bytes(p[0, :6]) == word.to_bytes(6, "little")
+    back = np.zeros_like(codes)
+    for gi in range(8):
+        w = int.from_bytes(bytes(p.reshape(-1)[6 * gi:6 * gi + 6]), "little")
+        back.reshape(-1)[8 * gi:8 * gi + 8] = [(w >> (6 * i)) & 63 for i in range(8)]
+    assert np.array_equal(back, codes)
