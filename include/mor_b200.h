@@ -59,6 +59,15 @@ extern "C" {
 MOR_B200_API int mor_b200_version(void);
 MOR_B200_API const char* mor_b200_status_string(int status);
 
+/* Test switch, no counterpart in the reference.  Several kernels can serve the same operator and all
+ * give the same bits; the parity tests use this mask to run each of them on the same input.
+ * bit 0: operators that would take a TMA-staged 128 x 128 tile kernel or a single-pass group kernel
+ *        take the generic kernel for any block shape instead;
+ * bit 1: block scaling does not take the single-launch kernel that keeps a small tensor in shared
+ *        memory between its two passes (it then runs as the sequence of launches used for large tensors).
+ * Process-wide, 0 by default, not meant for production callers. */
+MOR_B200_API void mor_b200_debug_kernel_selection(int mask);
+
 /* Bytes of device workspace for one call of `op` on a [rows, cols] tensor with the
  * given block shape (0 for operators that need none).  Replaces the torch::empty
  * temporaries of the reference launchers (fake_quantize.cu:2070-2078, 2272-2277,

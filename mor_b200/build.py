@@ -20,7 +20,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 BUILD = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libmor_b200.so")
-CU_SOURCES = ["fq_elementwise.cu", "fq_reduce.cu", "fq_scaling.cu", "fq_block.cu", "fq_group.cu", "p2p.cu", "api.cu"]
+CU_SOURCES = ["fq_elementwise.cu", "fq_reduce.cu", "fq_scaling.cu", "fq_block.cu", "fq_group.cu", "fq_resident.cu", "p2p.cu", "api.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 

@@ -23,6 +23,7 @@ _vp, _i, _i64, _d, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_double, C.c_size_t
 SIGNATURES = {
     "mor_b200_version": (_i, []),
     "mor_b200_status_string": (C.c_char_p, [_i]),
+    "mor_b200_debug_kernel_selection": (None, [_i]),
     "mor_b200_workspace_bytes": (_sz, [_i, _i64, _i64, _i, _i]),
     "mor_b200_fake_quantize": (_i, [_vp, _vp, _vp, _i, _i64, _i64, _i, _i, _d, _i, _i, _vp]),
     "mor_b200_quant_dequant": (_i, [_vp, _vp, _i64, _i64, _i, _vp]),

@@ -117,6 +117,12 @@ int scaling_op(int kind, const void* in, void* out, int dtype, int64_t rows, int
     a.block_err = reinterpret_cast<float*>(static_cast<char*>(wsp) + kHead + round256(4 * (size_t)g.n_amax));
     a.n_err = g.n_err; a.err_slot_stride = g.stride; a.ws = ws; a.ext_gamax = nullptr;
     const bool inplace = in == out;
+    // Small tensors (all tiles fit in the shared memories of the device): one cooperative launch that
+    // reads the tensor once, whatever the strategy; in place too.
+    if (kind == MOR_B200_OP_BLOCK_SCALING && br == 128 && bc == 128) {
+        const int rcr = launch_block_resident(a, meta, gamax, gnnz, nnz64, gerr, st);
+        if (rcr != kErrUnsupportedShape) return rcr;
+    }
     // Strategies 2 and 3 scale a block by its own amax only: on 128 x 128 blocks the tile kernel
     // takes it from the staged tile, and the separate amax pass over the tensor is not needed.
     if (kind == MOR_B200_OP_BLOCK_SCALING && br == 128 && bc == 128 && (ss == 2 || ss == 3) && !inplace) {
@@ -177,7 +183,9 @@ void* static_scratch_ptr(int* status) {
 
 extern "C" {
 
-int mor_b200_version(void) { return 100; }
+int mor_b200_version(void) { return 110; }
+
+void mor_b200_debug_kernel_selection(int mask) { set_kernel_selection(mask); }
 
 const char* mor_b200_status_string(int status) {
     switch (status) {
@@ -225,8 +233,7 @@ int mor_b200_fake_quantize(const void* in, void* out, int32_t* meta, int dtype, 
     }
     if (qm == 1 && (int64_t)br * bc > 1024 && (br < 32 || bc < 32)) return kErrUnsupportedShape;  // ref: 1781-1784
     // per-row groups in the fixed-format modes take the single-pass group kernels
-    static const bool force_generic = getenv("MOR_B200_FORCE_GENERIC") != nullptr;
-    if (qm != 1 && br == 1 && cols % bc == 0 && aligned16(in) && aligned16(out) && !force_generic) {
+    if (qm != 1 && br == 1 && cols % bc == 0 && aligned16(in) && aligned16(out) && !force_generic()) {
         const int rc = launch_fq_group(in, out, dtype == MOR_B200_FP32, nullptr, meta, qm == 2 ? 1 : 2, rows, cols, bc,
                                        qm == 2 ? kE4M3 : kE5M2, sf_type, st);
         if (rc != kErrUnsupportedShape) return rc;

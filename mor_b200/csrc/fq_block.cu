@@ -531,8 +531,7 @@ int launch_fq_block(const void* in, void* out, int is_fp32, int32_t* meta, int64
     const int64_t bx = (colsw - 1) / bcolsw + 1, by = (rows - 1) / brows + 1, nb = bx * by;
     if (nb > 0x7FFFFFFF) return kErrTooLarge;
     const bool aligned = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
-    static const bool force_generic = getenv("MOR_B200_FORCE_GENERIC") != nullptr;
-    if (!is_fp32 && brows == 128 && bcols == 128 && rows % 128 == 0 && cols % 128 == 0 && aligned && !force_generic &&
+    if (!is_fp32 && brows == 128 && bcols == 128 && rows % 128 == 0 && cols % 128 == 0 && aligned && !force_generic() &&
         rows < (int64_t(1) << 31) && cols < (int64_t(1) << 31)) {
         CUtensorMap map;
         if (make_tile_map(&map, in, rows, cols, 2, 32, 128)) {
@@ -545,9 +544,8 @@ int launch_fq_block(const void* in, void* out, int is_fp32, int32_t* meta, int64
 #define MORB_TILE(S)                                                                                                 \
     do {                                                                                                             \
         if (tabled) {                                                                                                \
-            static const cudaError_t attr = cudaFuncSetAttribute(fq_tile128_kernel<S, 2>,                            \
-                                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kTabled); \
-            if (attr != cudaSuccess) return kErrLaunch;                                                              \
+            static SmemOptIn opt;                                                                                    \
+            if (!opt(fq_tile128_kernel<S, 2>, kTabled)) return kErrLaunch;                                           \
             fq_tile128_kernel<S, 2><<<(unsigned)nb, 256, kTabled, st>>>(map, static_cast<uint2*>(out), meta, cols / 4, \
                                                                         (int)bx, clamp, quant_mode, dynamic_range_mode, \
                                                                         kErrTableEntries);                           \

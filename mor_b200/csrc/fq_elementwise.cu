@@ -227,6 +227,11 @@ int sm_count() {
 
 int check_launch() { return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch; }
 
+namespace { int g_kernel_selection = 0; }
+bool force_generic() { return (g_kernel_selection & 1) != 0; }
+bool resident_disabled() { return (g_kernel_selection & 2) != 0; }
+void set_kernel_selection(int mask) { g_kernel_selection = mask; }
+
 int launch_cast_uniform(const void* in, void* out, int64_t n_elems, int fmt, int sf_type, float scale,
                         int32_t* meta, int64_t n_meta, int32_t meta_code, cudaStream_t st) {
     const int64_t nvec = n_elems / 8;

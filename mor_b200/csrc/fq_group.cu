@@ -487,9 +487,8 @@ int launch_t(const void* in, void* out, float* scales, int32_t* meta, int32_t me
             if (g2 < 1) g2 = 1;
 #define MORB_MX(GS)                                                                                                    \
     do {                                                                                                               \
-        static const cudaError_t attr =                                                                                \
-            cudaFuncSetAttribute(mx_bf16_kernel<FMT, GS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing);         \
-        if (attr != cudaSuccess) return kErrLaunch;                                                                    \
+        static SmemOptIn opt;                                                                                          \
+        if (!opt(mx_bf16_kernel<FMT, GS>, kRing)) return kErrLaunch;                                                   \
         mx_bf16_kernel<FMT, GS><<<(unsigned)g2, 32 * kMxWarps, kRing, st>>>(i4, o4, scales, nvec, meta,               \
                                                                             meta ? n_groups : 0, meta_code);           \
     } while (0)
@@ -552,9 +551,8 @@ int launch_quantize_mx(const void* in, void* payload, uint8_t* scales, int64_t r
     auto* p2 = static_cast<uint2*>(payload);
 #define MORB_Q(F, GS)                                                                                                \
     do {                                                                                                             \
-        static const cudaError_t attr =                                                                              \
-            cudaFuncSetAttribute(mx_quantize_kernel<F, GS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing);     \
-        if (attr != cudaSuccess) return kErrLaunch;                                                                  \
+        static SmemOptIn opt;                                                                                        \
+        if (!opt(mx_quantize_kernel<F, GS>, kRing)) return kErrLaunch;                                               \
         mx_quantize_kernel<F, GS><<<(unsigned)grid, 32 * kMxWarps, kRing, st>>>(i4, p2, scales, nvec);               \
     } while (0)
 #define MORB_QS(F)                                                                                                   \
@@ -570,9 +568,8 @@ int launch_quantize_mx(const void* in, void* payload, uint8_t* scales, int64_t r
     } while (0)
 #define MORB_Q6(GS)                                                                                                  \
     do {                                                                                                             \
-        static const cudaError_t attr =                                                                              \
-            cudaFuncSetAttribute(mx_quantize_kernel<kE2M3, GS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing); \
-        if (attr != cudaSuccess) return kErrLaunch;                                                                  \
+        static SmemOptIn opt;                                                                                        \
+        if (!opt(mx_quantize_kernel<kE2M3, GS, true>, kRing)) return kErrLaunch;                                     \
         mx_quantize_kernel<kE2M3, GS, true><<<(unsigned)grid, 32 * kMxWarps, kRing, st>>>(i4, p2, scales, nvec);     \
     } while (0)
     if (pack6) {

@@ -126,7 +126,7 @@ __device__ __forceinline__ void publish(ScalarsWs* ws, float amax, int nnz) {
 }
 __global__ void zero_scalars_kernel(ScalarsWs* ws) {
     ws->gamax_bits = 0u; ws->fallback = 0; ws->gnnz = 0ull; ws->gerr = 0.0f; ws->meta = 0;
-    ws->div_unsafe = 0u; ws->load_timeout = 0u;
+    ws->div_unsafe = 0u; ws->load_timeout = 0u; ws->bar[0] = 0u; ws->bar[1] = 0u;
 }
 
 // Flat tensor: every warp streams its own 4 KiB chunks through a private two-stage
@@ -395,9 +395,8 @@ int launch_amax_nnz_flat(const void* in, int is_fp32, int64_t n_elems, ScalarsWs
     int64_t want = (n_chunks + kFlatWarps * kChunksPerWarp - 1) / (kFlatWarps * kChunksPerWarp);
     if (want > 0x7FFFFFFF) return kErrTooLarge;
     if (want < 1) want = 1;
-    static const cudaError_t a1 = cudaFuncSetAttribute(amax_nnz_flat_kernel<Fp32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing);
-    static const cudaError_t a2 = cudaFuncSetAttribute(amax_nnz_flat_kernel<Bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing);
-    if (a1 != cudaSuccess || a2 != cudaSuccess) return kErrLaunch;
+    static SmemOptIn opt32, opt16;
+    if (!(is_fp32 ? opt32(amax_nnz_flat_kernel<Fp32>, kRing) : opt16(amax_nnz_flat_kernel<Bf16>, kRing))) return kErrLaunch;
     if (is_fp32) amax_nnz_flat_kernel<Fp32><<<(int)want, kThreads, kRing, st>>>(static_cast<const float4*>(in), nvec, tail, ws);
     else amax_nnz_flat_kernel<Bf16><<<(int)want, kThreads, kRing, st>>>(static_cast<const uint4*>(in), nvec, tail, ws);
     return check_launch();
@@ -426,9 +425,8 @@ int launch_amax_nnz_blocks(const void* in, int is_fp32, int64_t rows, int64_t co
     if (nb > 0x7FFFFFFF) return kErrTooLarge;
     if (brows == 1 && bcols_vec % kFlatChunkVec == 0 && bcols_vec / kFlatChunkVec <= 4096) {
         constexpr int kRing = kFlatWarps * kFlatStages * kFlatChunkVec * 16;
-        static const cudaError_t a1 = cudaFuncSetAttribute(amax_nnz_runs_kernel<Fp32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing);
-        static const cudaError_t a2 = cudaFuncSetAttribute(amax_nnz_runs_kernel<Bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing);
-        if (a1 != cudaSuccess || a2 != cudaSuccess) return kErrLaunch;
+        static SmemOptIn opt32, opt16;
+        if (!(is_fp32 ? opt32(amax_nnz_runs_kernel<Fp32>, kRing) : opt16(amax_nnz_runs_kernel<Bf16>, kRing))) return kErrLaunch;
         const unsigned grid = (unsigned)((nb + kFlatWarps - 1) / kFlatWarps);
         const int cpb = bcols_vec / kFlatChunkVec;
         if (is_fp32) amax_nnz_runs_kernel<Fp32><<<grid, kThreads, kRing, st>>>(static_cast<const float4*>(in), cpb, nb, block_amax, ws);

@@ -12,6 +12,26 @@ namespace morb {
 
 int sm_count();                 // SMs of the current device (cached per device)
 int check_launch();             // cudaGetLastError() -> status code
+// test switches (mor_b200_debug_kernel_selection)
+bool force_generic();           // skip the TMA-staged tile kernels and the single-pass group kernels
+bool resident_disabled();       // skip the single-launch kernel for tensors that fit in shared memory
+void set_kernel_selection(int mask);
+
+// Opt-in to more than 48 KiB of dynamic shared memory.  The attribute belongs to a (kernel,
+// device) pair, so each launch site keeps one of these and asks it before every launch: the
+// runtime call is made once per device, with that device current.
+struct SmemOptIn {
+    unsigned char done[64] = {};
+    template <typename K>
+    bool operator()(K kernel, int bytes) {
+        int dev = -1;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+        if (done[dev]) return true;
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+        done[dev] = 1;
+        return true;
+    }
+};
 
 // ---- fq_elementwise.cu: one scale for the whole tensor, or none ------------------
 // fake_quantize CURRENT_SCALING modes and the BF16 pass-through (ref: 825-844).
@@ -31,14 +51,15 @@ int launch_e8mx_cast(const void* in, void* out, int64_t n_elems, int qtype, int 
 // bytes, then room for the 1024 partial sums of a long error array (launch_finalize).
 constexpr size_t kChainSumsOffset = 256;
 constexpr size_t kWsHeadBytes = kChainSumsOffset + 1024 * sizeof(float);
-struct ScalarsWs {              // 32 bytes, zeroed by launch_zero_scalars
+struct ScalarsWs {              // 40 bytes, zeroed by launch_zero_scalars
     uint32_t gamax_bits;        // max |x| as the bit pattern of a non-negative float
     int32_t fallback;           // 1 when the tensor-level BF16 fallback fired
     unsigned long long gnnz;    // count of non-zero elements
     float gerr;                 // ordered sum of the block errors
     int32_t meta;
     uint32_t div_unsafe;        // a non-zero bf16 magnitude below 2^-90 was seen: take the IEEE division
-    uint32_t load_timeout;      // a TMA tile load did not complete within its bounded wait
+    uint32_t load_timeout;      // a bounded wait (TMA tile load, grid barrier, peer flag) ran out
+    uint32_t bar[2];            // arrival counters of the single-launch kernel's two grid barriers
 };
 int launch_zero_scalars(ScalarsWs* ws, cudaStream_t st);
 // amax and nnz of a flat tensor (phase 1 of e8mx and of the row-sharded pipeline)
@@ -72,6 +93,11 @@ int launch_colgroup_err_cast(const ScalingArgs& a, bool store, bool only_if_not_
 int launch_finalize(const ScalingArgs& a, const long long* ext_nnz, int32_t* meta, float* gamax, void* gnnz,
                     int nnz_is_i64, float* gerr, cudaStream_t st);
 int launch_fallback_copy(const ScalingArgs& a, cudaStream_t st);
+
+// ---- fq_resident.cu: block scaling on 128 x 128 blocks as one cooperative kernel, for tensors
+// that fit in the shared memories of the device (kErrUnsupportedShape otherwise: use the phases above)
+int launch_block_resident(const ScalingArgs& a, int32_t* meta, float* gamax, void* gnnz, int nnz_is_i64, float* gerr,
+                          cudaStream_t st);
 
 // ---- fq_block.cu: fake_quantize per-block modes (MoR, block E4M3 / E5M2) ----------
 int launch_fq_block(const void* in, void* out, int is_fp32, int32_t* meta, int64_t rows, int64_t cols, int brows,

@@ -51,8 +51,20 @@ def assert_same(got: dict, exp: dict, what: str):
 ALL_CASES = cases()
 
 
+@pytest.fixture(params=[0, 2], ids=["single-launch", "launch-sequence"])
+def selection(request):
+    """Small block-scaled tensors take the single-launch kernel by default; mask 2 sends them through the
+    sequence of launches that large tensors use, so that both are compared with the oracle on the same input."""
+    from mor_b200 import cabi
+    cabi.lib().mor_b200_debug_kernel_selection(request.param)
+    yield request.param
+    cabi.lib().mor_b200_debug_kernel_selection(0)
+
+
 @pytest.mark.parametrize("case", ALL_CASES, ids=[c[0] for c in ALL_CASES])
-def test_golden_case_matches_oracle(case):
+def test_golden_case_matches_oracle(case, selection):
+    if selection and case[1] != "fake_quantize_block_scaling":
+        pytest.skip("one kernel only")
     import gpu_harness as H
     name, op, fn, kw = case
     x = fn()
@@ -315,9 +327,11 @@ def test_channel_scaling_column_groups(bx, rows, ss):
 
 @pytest.mark.parametrize("kind", ["block", "row", "col"])
 @pytest.mark.parametrize("thr", [0.045, 1e-6])
-def test_scaling_in_place(kind, thr):
+def test_scaling_in_place(kind, thr, selection):
     """in place: the input must survive until the tensor-level BF16 decision (thr=1e-6 forces it)"""
     import gpu_harness as H
+    if selection and kind != "block":
+        pytest.skip("one kernel only")
     x = rand_bits(91, 256, 256, "normal")
     if kind == "block":
         exp = oracle.block_scaling(x, 128, 128, thr, 1)
@@ -336,7 +350,7 @@ def test_scaling_in_place(kind, thr):
 
 @pytest.mark.parametrize("kind", ["tiny", "huge", "nan"])
 @pytest.mark.parametrize("ss", [1, 2, 3, 4])
-def test_scaling_with_extreme_magnitudes(kind, ss):
+def test_scaling_with_extreme_magnitudes(kind, ss, selection):
     """values outside [2^-90, 2^90) (or a NaN) switch the error quotient to the IEEE division: same bits"""
     import gpu_harness as H
     x = rand_bits(300 + ss, 256, 256, "normal")
@@ -364,7 +378,7 @@ def test_scaling_with_extreme_magnitudes(kind, ss):
 
 
 @pytest.mark.parametrize("ss", [1, 2, 3, 4])
-def test_block_scaling_float32(ss):
+def test_block_scaling_float32(ss, selection):
     import gpu_harness as H
     g = torch.Generator().manual_seed(50 + ss)
     x = torch.randn(256, 512, generator=g).numpy()
@@ -392,20 +406,24 @@ def test_group_and_generic_float32():
 
 
 def test_generic_block_kernel_matches_tile_kernel():
-    """MOR_B200_FORCE_GENERIC routes 128x128 blocks through the generic kernel; same bits expected."""
-    code = (
-        "import sys; sys.path[:0]=[%r, %r, %r]\n"
-        "import numpy as np, oracle, gpu_harness as H\n"
-        "from cases import mixed_blocks_bf16\n"
-        "x = mixed_blocks_bf16(7)\n"
-        "for mode, sf in ((1,1),(101,1),(1,2),(2,1),(3,2)):\n"
-        "    out, meta = oracle.fake_quantize(x,128,128,1e-15,mode,sf)\n"
-        "    g = H.fake_quantize(x,128,128,1e-15,mode,sf)\n"
-        "    assert np.array_equal(g['out'], out) and np.array_equal(g['meta'], meta), (mode, sf)\n"
-        "print('generic ok')\n" % (ROOT, os.path.join(ROOT, "tests"), os.path.join(ROOT, "tests", "golden")))
-    env = dict(os.environ, MOR_B200_FORCE_GENERIC="1")
-    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
-    assert r.returncode == 0 and "generic ok" in r.stdout, r.stdout + r.stderr
+    """mor_b200_debug_kernel_selection(1) routes 128x128 blocks (and the block pipeline) through the generic kernels;
+    same bits expected."""
+    import gpu_harness as H
+    from cases import mixed_blocks_bf16
+    from mor_b200 import cabi
+    x = mixed_blocks_bf16(7)
+    cabi.lib().mor_b200_debug_kernel_selection(1)
+    try:
+        for mode, sf in ((1, 1), (101, 1), (1, 2), (2, 1), (3, 2)):
+            out, meta = oracle.fake_quantize(x, 128, 128, 1e-15, mode, sf)
+            g = H.fake_quantize(x, 128, 128, 1e-15, mode, sf)
+            assert np.array_equal(g["out"], out) and np.array_equal(g["meta"], meta), (mode, sf)
+        for ss in (1, 2, 3, 4):
+            exp = dict(zip(("out", "meta", "gamax", "gnnz", "gerr"), oracle.block_scaling(x, 128, 128, 0.045, ss)))
+            exp["meta"] = np.array([exp["meta"]])
+            assert_same(H.block_scaling(x, 128, 128, 0.045, ss), exp, f"generic block pipeline ss {ss}")
+    finally:
+        cabi.lib().mor_b200_debug_kernel_selection(0)
 
 
 @pytest.mark.parametrize("stride", [1, 4, 64])
