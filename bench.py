@@ -3,20 +3,26 @@
     python bench.py [--gpus N] [--steps K] [--warmup W]            one JSON line on stdout
     python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
     python bench.py --impl reference ...                           CPU arm (the oracle on the host cores)
-    python bench.py --suite                                        also times every kernel family on
-                                                                   configurations 1-5 (table in <run-output folder>/suite.json)
+    python bench.py --suite                                        every kernel family on configurations 1-5,
+                                                                   full table in <out-dir>/suite.json
 
 Workload: configuration 5 -- a float32 131072 x 16384 tensor (8 GiB, N(0,1), synthetic),
 row-sharded over the N ranks, fake-quantized to E4M3 with 128 x 128 block scaling under
-the global-mantissa rule (ss_mode 1): slab amax kernel, amax/nnz all-reduce, scale +
-cast + error kernel, error all-gather, ordered error sum and BF16-fallback decision.
+the global-mantissa rule (ss_mode 1): slab amax kernel, amax/nnz exchange, scale +
+cast + error kernel, error gather, ordered error sum and BF16-fallback decision.
 Total work is fixed as N grows ("strong" scaling).  A step is one pass over the tensor.
+The tensor is drawn per 16384-row slab (seed 4000 + slab index), so it holds the same bits
+whatever N is, and the line carries checksums of the output and the bit patterns of the
+scalar results: equal across N means equal output.
 
 Metric: algorithmic GB/s, whole job = 12 bytes per element (two reads and one write of
 float32, the accounting of the reference authors' own harness) / step time; inputs are
 resident in HBM when the timed region starts and are far larger than L2, so no flush
 is needed.  `e2e` is the same metric from pinned HOST buffers through the same call
-with both copies inside the timed region.
+with both copies inside the timed region, next to a copy-only loop over the same buffers.
+
+At N = 1 the line also carries `configs`: the other benchmark configurations (and the E8Mx and
+column-group operators) timed eagerly and as a CUDA graph, each checked against the CPU oracle.
 """
 from __future__ import annotations
 
@@ -34,6 +40,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 ROWS, COLS, BLOCK = 131072, 16384, 128
+SLAB_ROWS = 16384              # rows drawn from one seed (1 GiB of float32)
 BYTES_PER_ELEM_TWO_PASS = 12   # 2 x 4-byte reads + 1 x 4-byte write
 THRESHOLD = 0.045              # the reference tests' e4m3_threshold
 SS_MODE = 1
@@ -52,6 +59,25 @@ def measured_peak():
         except Exception:
             pass
     return FALLBACK_HBM_GBS, "fallback"
+
+
+def host_threads():
+    """all the host cores this process may use, whatever OMP_NUM_THREADS says (torchrun sets it to 1)"""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def gpu_numa_node(index: int):
+    """NUMA node of the GPU's PCIe slot as the kernel reports it (None where that is not exposed)"""
+    try:
+        bus = subprocess.run(["nvidia-smi", "--query-gpu=pci.bus_id", "--format=csv,noheader", "-i", str(index)],
+                             capture_output=True, text=True, timeout=20).stdout.strip().lower()
+        dom, rest = bus.split(":", 1)
+        return int(open(f"/sys/bus/pci/devices/{dom[-4:]}:{rest}/numa_node").read().strip())
+    except Exception:
+        return None
 
 
 class ClockSampler:
@@ -103,44 +129,83 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_baseline(rows_sample_hint=None, budget_s=12.0, steps=1, warmup=0):
-    """Times the CPU oracle (a port of the reference arithmetic, OpenMP over blocks) on a
-    bounded row sample of the workload: same columns, same block scaling, all host threads."""
+# --------------------------------------------------------------------------------------
+# CPU legs: the only places where the oracle (a CPU port of the reference arithmetic) is used
+# --------------------------------------------------------------------------------------
+def cpu_baseline(sample=None, budget_s=12.0, passes=3, gpu_result=None):
+    """Times the CPU oracle (OpenMP over blocks, all host threads) on a bounded row sample of the workload:
+    one untimed pass, then the median of `passes` timed ones.  `sample` is a float32 [rows, COLS] array (the
+    benchmark passes the first slab of the tensor it timed); without one a sample is drawn here.  With
+    `gpu_result` = (global_amax, output rows, block errors) of the GPU run on that sample, the oracle's output
+    for the same global amax is compared with it bit for bit."""
     import numpy as np
     import oracle
-    # all the host cores this process may use, whatever OMP_NUM_THREADS says (torchrun sets it to 1)
-    try:
-        avail = len(os.sched_getaffinity(0))
-    except AttributeError:
-        avail = os.cpu_count() or 1
-    oracle.set_num_threads(avail)
+    oracle.set_num_threads(host_threads())
     threads = oracle.num_threads()
-    rng = np.random.default_rng(4000)
-    probe = rng.standard_normal((BLOCK * 2, COLS), dtype=np.float32)
-    t0 = time.perf_counter()
-    oracle.block_scaling(probe, BLOCK, BLOCK, THRESHOLD, SS_MODE)
-    dt = max(time.perf_counter() - t0, 1e-4)
-    rate = probe.size / dt
-    rows = rows_sample_hint or int(min(16384, max(256, (rate * budget_s / max(steps + warmup, 1)) // COLS // BLOCK * BLOCK)))
-    x = rng.standard_normal((rows, COLS), dtype=np.float32)
-    for _ in range(warmup):
-        oracle.block_scaling(x, BLOCK, BLOCK, THRESHOLD, SS_MODE)
-    t0 = time.perf_counter()
-    for _ in range(max(steps, 1)):
-        oracle.block_scaling(x, BLOCK, BLOCK, THRESHOLD, SS_MODE)
-    dt = (time.perf_counter() - t0) / max(steps, 1)
-    gbs = x.size * BYTES_PER_ELEM_TWO_PASS / dt / 1e9
-    return {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
-            "sample": f"{rows} of {ROWS} rows x {COLS} float32, block scaling ss_mode 1, {threads} OpenMP threads, "
-                      f"{dt * 1e3:.0f} ms per pass",
-            "elements_per_s": x.size / dt, "ms_per_step": dt * 1e3}
+    origin = "the first rows of the timed tensor"
+    if sample is None:
+        origin = "N(0,1) drawn on the host"
+        rng = np.random.default_rng(4000)
+        probe = rng.standard_normal((BLOCK * 2, COLS), dtype=np.float32)
+        t0 = time.perf_counter()
+        oracle.block_scaling(probe, BLOCK, BLOCK, THRESHOLD, SS_MODE)
+        rate = probe.size / max(time.perf_counter() - t0, 1e-4)
+        rows = int(min(SLAB_ROWS, max(256, (rate * budget_s / (passes + 1)) // COLS // BLOCK * BLOCK)))
+        sample = rng.standard_normal((rows, COLS), dtype=np.float32)
+    rows = sample.shape[0]
+    oracle.block_scaling(sample, BLOCK, BLOCK, THRESHOLD, SS_MODE)   # warm-up: page faults, thread pool
+    times = []
+    for _ in range(max(passes, 1)):
+        t0 = time.perf_counter()
+        oracle.block_scaling(sample, BLOCK, BLOCK, THRESHOLD, SS_MODE)
+        times.append(time.perf_counter() - t0)
+    dt = statistics.median(times)
+    gbs = sample.size * BYTES_PER_ELEM_TWO_PASS / dt / 1e9
+    res = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+           "sample": f"{rows} of {ROWS} rows x {COLS} float32 ({origin}), block scaling ss_mode 1, "
+                     f"{threads} OpenMP threads, median of {len(times)} warmed passes, {dt * 1e3:.0f} ms per pass",
+           "elements_per_s": sample.size / dt, "ms_per_step": dt * 1e3}
+    if gpu_result is not None:
+        gamax, gpu_out, gpu_err = gpu_result
+        # threshold out of reach: the tensor-level BF16 decision belongs to the whole tensor, not to the sample
+        out, _, _, _, _, _, berr = oracle.block_scaling(sample, BLOCK, BLOCK, 3e38, SS_MODE, global_amax=gamax,
+                                                        want_blocks=True)
+        same_out = bool(np.array_equal(out.view(np.uint32), gpu_out.view(np.uint32)))
+        same_err = bool(np.array_equal(berr.view(np.uint32), gpu_err.view(np.uint32)))
+        res["parity"] = {"slab0_bit_exact": same_out, "slab0_block_errors_bit_exact": same_err, "rows_checked": rows}
+    return res
+
+
+def cpu_baseline_torch():
+    """The reference's PyTorch CPU path (the computation its tests compare the kernels with,
+    test/test_fake_quantize.py:96-104: scale = 448 / amax, cast to float8_e4m3fn and back, divide) on
+    configuration 1 (bf16 4096 x 4096), at 4 bytes per element."""
+    import torch
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(4096, 4096, generator=g).to(torch.bfloat16)
+
+    def once():
+        xf = x.float()
+        scale = torch.tensor(448.0) / xf.abs().max()
+        return ((xf * scale).to(torch.float8_e4m3fn).float() / scale).to(torch.bfloat16)
+
+    once()
+    times = []
+    for _ in range(5):
+        t0 = time.perf_counter()
+        once()
+        times.append(time.perf_counter() - t0)
+    dt = statistics.median(times)
+    return {"value": x.numel() * 4 / dt / 1e9, "unit": "GB/s", "threads": torch.get_num_threads(),
+            "host_cores": os.cpu_count(), "kind": "reference tests' torch CPU path",
+            "sample": f"configuration 1 (bf16 4096 x 4096, per-tensor E4M3), median of 5 passes, {dt * 1e3:.1f} ms per pass"}
 
 
 def reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    b = cpu_baseline(budget_s=20.0, steps=args.steps, warmup=args.warmup)
+    b = cpu_baseline(budget_s=20.0, passes=max(args.steps, 1))
     line = {
         "impl": "reference", "metric": "fake_quantize_throughput", "value": b["value"], "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": b["ms_per_step"],
@@ -150,8 +215,41 @@ def reference_arm(args):
         "e2e": {"value": b["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "elements_per_s": b["elements_per_s"], "gpu_launches": 0,
     }
+    try:
+        line["cpu_baseline_torch"] = cpu_baseline_torch()
+    except Exception as e:  # a torch build without float8 on the CPU: the oracle number stands alone
+        line["cpu_baseline_torch"] = {"unavailable": str(e)[:200]}
     print(json.dumps(line))
     return 0
+
+
+# --------------------------------------------------------------------------------------
+def draw_rows(torch, dev, r0, r1):
+    """rows [r0, r1) of the benchmark tensor: slab s (SLAB_ROWS rows) is N(0,1) from seed 4000 + s"""
+    x = torch.empty(r1 - r0, COLS, dtype=torch.float32, device=dev)
+    s = r0 // SLAB_ROWS
+    while s * SLAB_ROWS < r1:
+        g = torch.Generator(device=dev).manual_seed(4000 + s)
+        slab = torch.empty(SLAB_ROWS, COLS, dtype=torch.float32, device=dev)
+        for i in range(0, SLAB_ROWS, 4096):
+            slab[i:i + 4096].normal_(generator=g)
+        a, b = max(r0, s * SLAB_ROWS), min(r1, (s + 1) * SLAB_ROWS)
+        x[a - r0:b - r0] = slab[a - s * SLAB_ROWS:b - s * SLAB_ROWS]
+        del slab
+        s += 1
+    return x
+
+
+def checksums(torch, out, first_row):
+    """two 64-bit sums of the output's 32-bit words (the second weighted by the global row number), additive over
+    ranks, so that equal values across N mean equal output bits"""
+    total = torch.zeros(2, dtype=torch.int64, device=out.device)
+    for a in range(0, out.shape[0], 8192):      # in row chunks: the widened copy of 8 GiB would not be small
+        w = out[a:a + 8192].view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+        rowsum = w.sum(dim=1)
+        weights = torch.arange(first_row + a + 1, first_row + a + 1 + rowsum.numel(), device=out.device, dtype=torch.int64)
+        total += torch.stack([rowsum.sum(), (rowsum * weights).sum()])
+    return total
 
 
 def main():
@@ -160,7 +258,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--suite", action="store_true", help="also time configurations 1-4 (single GPU)")
+    ap.add_argument("--suite", action="store_true", help="time every suite entry (the default line carries a compact set)")
     ap.add_argument("--scale", type=int, default=1, help="divide the row count (development only; reported)")
     ap.add_argument("--no-main", action="store_true", help="skip the configuration-5 workload (profiling the suite)")
     ap.add_argument("--suite-only", default="", help="substring filter on suite entry names")
@@ -168,16 +266,19 @@ def main():
     ap.add_argument("--suite-impl", choices=["ours", "reference"], default="ours",
                     help="reference: time the unmodified reference CUDA extension (oracle/_ref) on the configurations it supports")
     ap.add_argument("--suite-graph", action="store_true", help="also time the suite calls replayed as one CUDA graph")
-    ap.add_argument("--suite-out", default=None, help="where --suite writes its table (default: suite.json in the run-output folder)")
+    ap.add_argument("--out-dir", default=None, help="folder for suite.json (default: suite_out under the current directory)")
+    ap.add_argument("--suite-out", default=None, help="file for the suite table (overrides --out-dir)")
     ap.add_argument("--exchange", choices=["auto", "nccl", "p2p"], default="auto",
                     help="how ranks exchange amax / non-zero count / error sums (N > 1): NCCL collectives or peer stores")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-configs", action="store_true", help="leave the other configurations out of the line")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
         return reference_arm(args)
+    suite_path = args.suite_out or os.path.join(args.out_dir or os.path.join(os.getcwd(), "suite_out"), "suite.json")
 
     import torch
     import torch.distributed as dist
@@ -193,12 +294,11 @@ def main():
         if not torch.cuda.is_available():
             raise SystemExit("the reference extension needs a CUDA device")
         peak, _ = measured_peak()
-        run_suite(torch, torch.device("cuda", 0), peak, args.suite_only, args.suite_iters, args.suite_out, False,
+        run_suite(torch, torch.device("cuda", 0), peak, args.suite_only, args.suite_iters, suite_path, False,
                   "reference", wl)
         return 0
 
     import mor_b200  # noqa: F401  fails loudly if the CUDA library or the shim is missing
-    from mor_b200 import workloads
     from mor_b200.sharded import KIND_BLOCK, ShardedScaling, shard_rows
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -214,42 +314,17 @@ def main():
 
     if args.no_main:
         peak, _ = measured_peak()
-        run_suite(torch, dev, peak, args.suite_only, args.suite_iters, args.suite_out, args.suite_graph, args.suite_impl)
+        run_suite(torch, dev, peak, args.suite_only, args.suite_iters, suite_path, args.suite_graph, args.suite_impl)
         return 0
 
     rows = ROWS // args.scale
+    if (rows // BLOCK) % world:
+        raise SystemExit(f"{rows // BLOCK} block rows do not divide over {world} ranks: every rank must hold a slab of the same height")
     r0, r1 = shard_rows(rows, world, rank, BLOCK)
     rows_local = r1 - r0
-    # synthetic N(0,1) float32 slab, drawn on the device (seed 4000 + rank)
-    g = torch.Generator(device=dev).manual_seed(4000 + rank)
-    x = torch.empty(rows_local, COLS, dtype=torch.float32, device=dev)
-    chunk = 4096
-    for i in range(0, rows_local, chunk):
-        x[i:i + chunk].normal_(generator=g)
+    x = draw_rows(torch, dev, r0, r1)
     out = torch.empty_like(x)
     op = ShardedScaling(rows_local, COLS, BLOCK, BLOCK, torch.float32, dev, KIND_BLOCK, exchange=args.exchange)
-
-    # events around the dominant kernel (scale + cast + error sums), on the launching stream
-    cast_events = []
-    amax_events = []
-    inner_cast, inner_amax, inner_amax_local = op.backend.cast, op.backend.amax_nnz, op.backend.amax_nnz_local
-
-    def timed_cast(*a):
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record(); inner_cast(*a); e.record()
-        cast_events.append((s, e))
-
-    def timed_amax(*a):
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record(); inner_amax(*a); e.record()
-        amax_events.append((s, e))
-
-    def timed_amax_local(*a):
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record(); inner_amax_local(*a); e.record()
-        amax_events.append((s, e))
-
-    op.backend.cast, op.backend.amax_nnz, op.backend.amax_nnz_local = timed_cast, timed_amax, timed_amax_local
 
     def barrier():
         if world > 1:
@@ -259,7 +334,6 @@ def main():
     for _ in range(args.warmup):
         res = op(x, out, SS_MODE, THRESHOLD)
     barrier()
-    cast_events.clear(); amax_events.clear()
     launches0 = op.backend.launches
     with ClockSampler(local_rank) as clocks:
         barrier()
@@ -271,20 +345,80 @@ def main():
         barrier()
     step_ms = ev0.elapsed_time(ev1) / args.steps
     launches = op.backend.launches - launches0
-    cast_ms = statistics.mean(s.elapsed_time(e) for s, e in cast_events)
-    amax_ms = statistics.mean(s.elapsed_time(e) for s, e in amax_events)
-    meta = int(res.meta.item())
 
-    t = torch.tensor([step_ms, cast_ms, amax_ms], dtype=torch.float64, device=dev)
+    # ---- where a step's time goes: CUDA events around every phase, in a loop of its own (outside the timed region)
+    phase_events = {}
+    names = {"amax_nnz": "amax", "amax_nnz_local": "amax", "exchange_scalars": "exchange1", "cast": "cast",
+             "exchange_errors": "exchange2", "finalize": "sum", "finalize_ptr": "sum", "fallback": "fallback"}
+    originals = {}
+    for meth, label in names.items():
+        inner = getattr(op.backend, meth)
+        originals[meth] = inner
+
+        def timed(*a, _inner=inner, _label=label):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record(); _inner(*a); e.record()
+            phase_events.setdefault(_label, []).append((s, e))
+        setattr(op.backend, meth, timed)
+    barrier()
+    for _ in range(5):
+        res = op(x, out, SS_MODE, THRESHOLD)
+    barrier()
+    for meth, inner in originals.items():
+        setattr(op.backend, meth, inner)
+    phases_ms = {k: statistics.mean(s.elapsed_time(e) for s, e in v) for k, v in phase_events.items()}
+    order = ["amax", "exchange1", "cast", "exchange2", "sum", "fallback"]
+    t = torch.tensor([step_ms] + [phases_ms.get(k, 0.0) for k in order], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    step_ms, cast_ms, amax_ms = t.tolist()
+    vals = t.tolist()
+    step_ms = vals[0]
+    phases_ms = dict(zip(order, vals[1:]))
+    cast_ms, amax_ms = phases_ms["cast"], phases_ms["amax"]
+
+    # ---- what was computed: bit patterns of the scalars, checksums of the output, cross-checks ----
+    meta = int(res.meta.item())
+    amax_bits = int(res.global_amax.view(torch.int32).item()) & 0xFFFFFFFF
+    err_bits = int(res.global_error.view(torch.int32).item()) & 0xFFFFFFFF
+    nnz = int(res.global_nnz.item())
+    cs = checksums(torch, out, r0)
+    # amax and count recomputed by torch, reduced over the ranks by NCCL: independent of the kernels and of the exchange
+    chk = torch.zeros(2, dtype=torch.float64, device=dev)
+    for a in range(0, rows_local, 8192):
+        xc = x[a:a + 8192]
+        chk[0] = torch.maximum(chk[0], xc.abs().max().to(torch.float64))
+        chk[1] += (xc != 0).sum().to(torch.float64)
+    if world > 1:
+        dist.all_reduce(cs, op=dist.ReduceOp.SUM)
+        mx = chk[0:1].clone(); sm = chk[1:2].clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        chk = torch.cat([mx, sm])
+        same = torch.tensor([meta, amax_bits, err_bits, nnz], dtype=torch.int64, device=dev)
+        lo, hi = same.clone(), same.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        ranks_agree = bool((lo == hi).all().item())
+    else:
+        ranks_agree = True
+    verified = {"amax_equals_torch_max": float(res.global_amax.item()) == chk[0].item(),
+                "nnz_equals_torch_count": nnz == int(chk[1].item()),
+                "scalars_identical_on_every_rank": ranks_agree}
+    result = {"meta": meta, "global_amax_bits": f"0x{amax_bits:08x}", "global_error_bits": f"0x{err_bits:08x}", "global_nnz": nnz,
+              "output_checksum": [f"0x{int(v) & 0xFFFFFFFFFFFFFFFF:016x}" for v in cs.tolist()]}
 
     total_elems = rows * COLS
     value = total_elems * BYTES_PER_ELEM_TWO_PASS / (step_ms * 1e-3) / 1e9
     peak, peak_kind = measured_peak()
     cast_bytes = rows_local * COLS * 8          # algorithmic bytes of one launch: float32 read + write
     achieved = cast_bytes / (cast_ms * 1e-3) / 1e9
+
+    # the first rows of the timed tensor and what the GPU made of them, for the CPU leg's comparison
+    cpu_sample = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        n_chk = min(SLAB_ROWS, rows_local)
+        cpu_sample = (x[:n_chk].cpu().numpy(), (float(res.global_amax.item()), out[:n_chk].cpu().numpy(),
+                                                op.local_err[:(n_chk // BLOCK) * (COLS // BLOCK)].cpu().numpy()))
 
     # ---- end to end from pinned host buffers ---------------------------------------
     e2e = None
@@ -317,23 +451,47 @@ def main():
         host_op.synchronize()
         barrier()
         e2e_ms = e0.elapsed_time(e1) / e2e_steps
-        tt = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
+        # the same buffers, the same two copy streams, no kernels: what the host links give on their own
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        cur = torch.cuda.current_stream()
+        host_op.s_in.wait_stream(cur); host_op.s_out.wait_stream(cur)
+        c0.record()
+        host_op.s_in.wait_event(c0); host_op.s_out.wait_event(c0)
+        for i in range(e2e_steps):
+            with torch.cuda.stream(host_op.s_in):
+                host_op.x[i & 1].copy_(xh, non_blocking=True)
+            with torch.cuda.stream(host_op.s_out):
+                oh.copy_(host_op.out[i & 1], non_blocking=True)
+        cur.wait_stream(host_op.s_in); cur.wait_stream(host_op.s_out)
+        c1.record()
+        barrier()
+        copy_ms = c0.elapsed_time(c1) / e2e_steps
+        tt = torch.tensor([e2e_ms, copy_ms], dtype=torch.float64, device=dev)
         if world > 1:
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        e2e_ms = tt.item()
-        e2e = {"value": total_elems * BYTES_PER_ELEM_TWO_PASS / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+        e2e_ms, copy_ms = tt.tolist()
+        job_bytes = total_elems * BYTES_PER_ELEM_TWO_PASS
+        numa = gpu_numa_node(local_rank)
+        e2e = {"value": job_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
                "h2d_bytes_per_step": nbytes * world, "d2h_bytes_per_step": (nbytes + 8) * world,
                "ms_per_step": e2e_ms, "steps": e2e_steps,
+               "copy_only_GBs": job_bytes / (copy_ms * 1e-3) / 1e9, "copy_only_ms_per_step": copy_ms,
+               "frac_of_copy": copy_ms / e2e_ms,
+               "host_link_GBs_per_direction_per_gpu": nbytes / (copy_ms * 1e-3) / 1e9,
+               "host": {"cpu_affinity_cores": host_threads(), "gpu_numa_node": numa},
                "note": "mor_b200.sharded.HostScaling: pinned host float32 in and out, every step uploads its input and "
                        "reads its output back; two device buffer sets, so one step's upload overlaps the previous "
-                       "step's read-back"}
+                       "step's read-back.  copy_only: the same uploads and read-backs with no kernels between them, "
+                       "in the same units (12 B per element / time)"}
         del xh, oh, host_op
 
-    suite = None
-    if args.suite and rank == 0 and world == 1:
+    configs = None
+    if rank == 0 and world == 1 and (args.suite or not args.no_configs):
         out = None
+        x = None
         torch.cuda.empty_cache()
-        suite = run_suite(torch, dev, peak, args.suite_only, args.suite_iters, args.suite_out, args.suite_graph, args.suite_impl)
+        configs = run_suite(torch, dev, peak, args.suite_only, args.suite_iters, suite_path, True, args.suite_impl,
+                            compact=not args.suite, check=not args.no_cpu)
 
     if rank == 0:
         line = {
@@ -343,7 +501,7 @@ def main():
             "config": {"workload": f"config5: float32 {rows}x{COLS} (8 GiB / scale {args.scale}), row-sharded over "
                                    f"{n_gpus} GPU(s), 128x128 block scaling ss_mode 1 with global amax",
                        "bytes_per_element": BYTES_PER_ELEM_TWO_PASS, "l2": "inputs larger than L2, no flush",
-                       "threshold": THRESHOLD, "meta": meta,
+                       "threshold": THRESHOLD, "meta": meta, "seed": "4000 + index of the 16384-row slab",
                        "exchange": ("single GPU" if n_gpus == 1 else ("peer stores over NVLink" if op.peer is not None else "NCCL"))},
             "elements_per_s": total_elems / (step_ms * 1e-3),
             "per_gpu": {"GB/s": value / n_gpus, "elements_per_s": total_elems / (step_ms * 1e-3) / n_gpus,
@@ -355,29 +513,93 @@ def main():
                          "traffic_source": "ncu dram__bytes_read+write on a 1 GiB slab, scaled by elements",
                          "amax_kernel": {"ms_per_launch": amax_ms,
                                          "achieved": rows_local * COLS * 4 / (amax_ms * 1e-3) / 1e9}},
+            "phases_us": {k: round(v * 1e3, 2) for k, v in phases_ms.items()},
+            "result": result, "verified": verified,
             "clocks": clocks.summary(),
             "gpu_launches": launches * n_gpus,
         }
         if e2e:
             line["e2e"] = e2e
-        if not args.no_cpu and world == 1:
-            b = cpu_baseline()
+        if cpu_sample is not None:
+            b = cpu_baseline(sample=cpu_sample[0], gpu_result=cpu_sample[1])
             line["cpu_baseline"] = {k: b[k] for k in ("value", "unit", "cores", "kind", "sample")}
-        if suite:
-            line["suite_file"] = "gpurun_out/suite.json"
+            line["parity"] = b["parity"]
+            try:
+                line["cpu_baseline_torch"] = cpu_baseline_torch()
+            except Exception as e:
+                line["cpu_baseline_torch"] = {"unavailable": str(e)[:200]}
+        if configs is not None:
+            line["configs"] = [{k: (round(v, 5) if isinstance(v, float) else v) for k, v in c.items()
+                                if k in ("name", "ms", "GB/s", "frac_of_peak", "graph_ms", "graph_frac_of_peak", "parity", "launches")}
+                               for c in configs]
         print(json.dumps(line))
     if world > 1:
+        op.close()
         dist.destroy_process_group()
     return 0
 
 
-def run_suite(torch, dev, peak, only="", iters=10, out_path=None, use_graph=False, impl="ours", workloads=None):
+# --------------------------------------------------------------------------------------
+def oracle_check(op, x, args, outs):
+    """Compares one suite call with the CPU oracle, bit for bit (bench.py's CPU leg: a checker, never timed)."""
+    import numpy as np
+    import torch
+    import oracle
+
+    def bits(t):
+        t = t.detach().cpu().contiguous()
+        if t.dtype == torch.bfloat16:
+            return t.view(torch.int16).numpy().view(np.uint16)
+        return t.numpy()
+
+    def same(a, b):
+        a, b = np.ascontiguousarray(a), np.ascontiguousarray(b)
+        return a.shape == b.shape and bool(np.array_equal(a.view(np.uint8), b.view(np.uint8)))
+
+    def f32(v):
+        return int(np.array([v], np.float32).view(np.uint32)[0])
+
+    xb = bits(x)
+    outs = outs if isinstance(outs, (list, tuple)) else [outs]
+    if op == "fake_quantize":
+        _, _, bx, by, clamp, mode, sf = args
+        eo, em = oracle.fake_quantize(xb, bx, by, clamp, mode, sf)
+        return same(bits(outs[0]), eo) and same(outs[1].cpu().numpy(), em)
+    if op in ("fake_quantize_block_scaling", "fake_quantize_channel_scaling"):
+        _, _, bx, by, thr, ss = args
+        fn = oracle.block_scaling if op == "fake_quantize_block_scaling" else oracle.channel_scaling
+        e = fn(xb, bx, by, thr, ss)
+        return (same(bits(outs[0]), e[0]) and int(outs[1].item()) == e[1] and f32(outs[2].item()) == f32(e[2]) and
+                int(outs[3].item()) == e[3] and f32(outs[4].item()) == f32(e[4]))
+    if op == "fake_quantize_block_scaling_delayed":
+        _, _, bx, by, thr, ss, amax_in = args
+        e = oracle.block_scaling(xb, bx, by, thr, ss, global_amax=float(amax_in.item()))
+        return same(bits(outs[0]), e[0]) and int(outs[1].item()) == e[1] and int(outs[3].item()) == e[3] and f32(outs[4].item()) == f32(e[4])
+    if op == "fake_quantize_mx":
+        _, _, by, fmt, sf = args
+        eo, es = oracle.fake_quantize_group(xb, 1, by, fmt, sf, want_scales=True)
+        return same(bits(outs[0]), eo) and same(outs[1].cpu().numpy().reshape(-1), es)
+    if op == "quantize_mx":
+        _, _, by, fmt = args
+        ep, es = oracle.quantize_mx(xb, by, fmt)
+        return same(outs[0].cpu().numpy(), ep) and same(outs[1].cpu().numpy(), es)
+    if op == "fake_quantize_e8mx":
+        _, _, _, _, qt, strat = args
+        eo, _ = oracle.e8mx(xb, qt, strat)
+        return same(bits(outs[0]), eo)
+    return None
+
+
+def run_suite(torch, dev, peak, only="", iters=10, out_path=None, use_graph=False, impl="ours", workloads=None,
+              compact=False, check=False):
     """Times every kernel family on configurations 1-5 (one GPU).  Every operator runs
     `iters` times back to back between one pair of CUDA events on the launching stream;
     successive calls take their input from, and leave their outputs in, a ring of distinct
     buffers whose total size is at least four times the L2, so that no call finds its
     input or the lines of its output in cache.  The time per call is the total divided
-    by `iters`: launch gaps between the kernels of a pipeline are part of it."""
+    by `iters`: launch gaps between the kernels of a pipeline are part of it.
+    `compact` keeps one or two entries per configuration (what the default benchmark line carries);
+    `check` compares each entry's output with the CPU oracle (outside every timed region)."""
     if workloads is None:
         from mor_b200 import workloads
     if impl == "reference":
@@ -430,8 +652,10 @@ def run_suite(torch, dev, peak, only="", iters=10, out_path=None, use_graph=Fals
                 print(f"[suite] graph capture failed: {ex}", file=sys.stderr)
         return eager_ms, graph_ms, k
 
-    def add(name, x, bytes_per_elem, op, args, ref_ok=False):
+    def add(name, x, bytes_per_elem, op, args, ref_ok=False, headline=True):
         if only and only not in name:
+            return
+        if compact and not headline:
             return
         if impl == "reference" and not ref_ok:   # shapes or operators the reference does not have, or asserts on
             return
@@ -447,6 +671,12 @@ def run_suite(torch, dev, peak, only="", iters=10, out_path=None, use_graph=Fals
             ggbs = n * bytes_per_elem / (graph_ms * 1e-3) / 1e9
             rec.update({"graph_ms": graph_ms, "graph_GB/s": ggbs, "graph_frac_of_peak": ggbs / peak})
             line += f"   | as a CUDA graph: {graph_ms:.4f} ms  {ggbs:.0f} GB/s  {100 * ggbs / peak:.1f}%"
+        if check and impl != "reference":
+            try:
+                rec["parity"] = oracle_check(op, x, args, fn(x))
+            except Exception as ex:
+                rec["parity"] = f"check failed: {str(ex)[:120]}"
+            line += f"   | oracle: {rec['parity']}"
         results.append(rec)
         print(line, file=sys.stderr)
 
@@ -455,20 +685,23 @@ def run_suite(torch, dev, peak, only="", iters=10, out_path=None, use_graph=Fals
     scale = (torch.tensor(448.0) / x.float().abs().max().cpu()).item()   # binary32 division, as the cast kernels do
     add("c1 per-tensor E4M3, scale given (fake_quantize mode 4)", x, 4, "fake_quantize", (r, c, 128, 128, scale, 4, 1), ref_ok=True)
     add("c1 per-tensor E4M3, self-contained (block_scaling ss 4)", x, 6, "fake_quantize_block_scaling", (r, c, 128, 128, 3e38, 4), ref_ok=True)
+    add("c1 block scaling 128x128 (ss 1)", x, 6, "fake_quantize_block_scaling", (r, c, 128, 128, 3e38, 1), ref_ok=True, headline=False)
+    add("c1 E8M3 with tensor scale (fake_quantize_e8mx)", x, 6, "fake_quantize_e8mx", (r, c, 128, 128, 3, 1), ref_ok=True)
     del x
     x = workloads.config2(device=dev)
     r, c = x.shape
     add("c2 per-row E4M3 single pass (fake_quantize mode 2, 1x8192)", x, 4, "fake_quantize", (r, c, 1, c, 0.0, 2, 1))
-    add("c2 per-row E5M2 single pass (fake_quantize mode 3, 1x8192)", x, 4, "fake_quantize", (r, c, 1, c, 0.0, 3, 1))
+    add("c2 per-row E5M2 single pass (fake_quantize mode 3, 1x8192)", x, 4, "fake_quantize", (r, c, 1, c, 0.0, 3, 1), headline=False)
     # not for the reference arm: its channel path launches the 1024-thread reductions with the 64-thread
     # kernels' shared-memory size (fake_quantize.cu:2515-2522) and raised an illegal memory access at this size
     add("c2 per-row E4M3 pipeline (channel_scaling ss 3)", x, 6, "fake_quantize_channel_scaling", (r, c, 1, c, 3e38, 3))
+    add("c2 per-column E4M3 pipeline (channel_scaling 8192x1, ss 1)", x, 6, "fake_quantize_channel_scaling", (r, c, r, 1, 3e38, 1))
     del x
     x = workloads.config3(device=dev)
     r, c = x.shape
     add("c3 MX 1x32 E8M0 E4M3 single pass (fake_quantize_mx)", x, 4, "fake_quantize_mx", (r, c, 32, 0, 2))
-    add("c3 MX 1x32 E8M0 E2M3 single pass (fake_quantize_mx)", x, 4, "fake_quantize_mx", (r, c, 32, 3, 2))
-    add("c3 MX 1x32 real quantization, E4M3 codes + E8M0 scales (quantize_mx)", x, 3.03125, "quantize_mx", (r, c, 32, 0))
+    add("c3 MX 1x32 E8M0 E2M3 single pass (fake_quantize_mx)", x, 4, "fake_quantize_mx", (r, c, 32, 3, 2), headline=False)
+    add("c3 MX 1x32 real quantization, E4M3 codes + E8M0 scales (quantize_mx)", x, 3.03125, "quantize_mx", (r, c, 32, 0), headline=False)
     add("c3 MX 1x32 E4M3 pipeline (channel_scaling ss 2)", x, 6, "fake_quantize_channel_scaling", (r, c, 1, 32, 3e38, 2))
     del x
     x = workloads.config4(device=dev)
@@ -476,12 +709,12 @@ def run_suite(torch, dev, peak, only="", iters=10, out_path=None, use_graph=Fals
     if impl != "reference":
         amax_prev4 = x.float().abs().max().reshape(1)
         add("c4 block scaling 128x128, single pass with delayed amax (ss 1)", x, 4, "fake_quantize_block_scaling_delayed",
-            (r, c, 128, 128, 3e38, 1, amax_prev4))
+            (r, c, 128, 128, 3e38, 1, amax_prev4), headline=False)
     add("c4 MoR 128x128 relative-error criterion (mode 1)", x, 4, "fake_quantize", (r, c, 128, 128, 1e-15, 1, 1), ref_ok=True)
-    add("c4 MoR 128x128 dynamic-range criterion (mode 101)", x, 4, "fake_quantize", (r, c, 128, 128, 1e-15, 101, 1), ref_ok=True)
+    add("c4 MoR 128x128 dynamic-range criterion (mode 101)", x, 4, "fake_quantize", (r, c, 128, 128, 1e-15, 101, 1), ref_ok=True, headline=False)
     add("c4 block scaling 128x128 pipeline (ss 1)", x, 6, "fake_quantize_block_scaling", (r, c, 128, 128, 3e38, 1), ref_ok=True)
     del x
-    if impl != "reference":
+    if impl != "reference" and not compact:
         x = workloads.config5_slab(0, device=dev)
         r, c = x.shape
         add("c5 float32 1 GiB slab block scaling 128x128 pipeline (ss 1)", x, 12, "fake_quantize_block_scaling", (r, c, 128, 128, THRESHOLD, 1))
@@ -490,9 +723,10 @@ def run_suite(torch, dev, peak, only="", iters=10, out_path=None, use_graph=Fals
             "fake_quantize_block_scaling_delayed", (r, c, 128, 128, THRESHOLD, 1, amax_prev))
         add("c5 float32 1 GiB slab per-tensor pipeline (ss 4)", x, 12, "fake_quantize_block_scaling", (r, c, 128, 128, THRESHOLD, 4))
         del x
-    os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
-    with open(out_path or os.path.join(ROOT, "gpurun_out", "suite.json"), "w") as f:
-        json.dump({"peak_GB/s": peak, "impl": impl, "results": results}, f, indent=1)
+    if out_path:
+        os.makedirs(os.path.dirname(os.path.abspath(out_path)), exist_ok=True)
+        with open(out_path, "w") as f:
+            json.dump({"peak_GB/s": peak, "impl": impl, "results": results}, f, indent=1)
     return results
 
 

@@ -54,6 +54,8 @@ Geometry channel_geometry(int64_t rows, int64_t cols, int br, int bc, int dtype)
         }
     } else {
         if (cols % 64 || br % 16) { g.status = kErrUnsupportedShape; return g; }
+        // the column kernels index row blocks with grid.y and slices of a block's rows with grid.z
+        if (rows / br > 65535 || (br + 255) / 256 > 65535) { g.status = kErrTooLarge; return g; }
         g.stride = 64;
         g.n_amax = (rows / br) * cols;
         g.n_err = (rows / br) * (cols / 64);

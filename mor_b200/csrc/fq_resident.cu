@@ -3,21 +3,31 @@
 // fake_quantize.cu:2093-2099; the reference authors' cooperative prototype is
 // jatin/fake_quantize_num_blocks.cu:973-1233).
 //
-// One CTA of 1024 threads per SM, launched cooperatively so that every CTA is resident.  A CTA
-// owns up to kSlots tiles (7 of bf16, 3 of binary32) and requests all of them by TMA as it
-// starts: the tensor is read from HBM exactly once.
+// One CTA per SM, launched cooperatively so that every CTA is resident.  A CTA owns up to
+// kSlots tiles (7 of bf16, 3 of binary32), each handled from start to end by its own group of
+// threads (128 for bf16, 256 for binary32), and requests all of them by TMA as it starts: the
+// tensor is read from HBM exactly once.
 //
 //   pass 1   per tile, as it arrives: amax, non-zero count and the screening flags of the short
 //            quotient, from shared memory; one atomicMax / atomicAdd per CTA for the tensor.
 //   barrier  every CTA now knows the tensor's amax.
-//   pass 2   per tile: scale (ref: 1059-1093), table of quotients, E4M3 cast, store, error sum
-//            in the reference's order (ref: 1117-1156): thread (tx, ty) of the 32 x 32 CTA is a
-//            real thread here, rows ty + 32 j outer, words tx + 32 i inner, high half first.
+//   pass 2   per tile: scale (ref: 1059-1093), E4M3 cast through a table of quotients, store,
+//            error sum in the reference's order (ref: 1117-1156).  A thread stands for the
+//            logical threads (tx .. tx + VW - 1, ty) and (same, ty + 16) of the reference's
+//            32 x 32 CTA: rows ty + 32 j outer, words tx + 32 i inner, high half first, then
+//            the reference's two shuffle trees (logical_warp_sum, warp_sum_ordered).
 //   barrier  every CTA now sees every block's error sum.
 //   decide   every CTA repeats the reference's ordered sum (thread t adds entries t, t + 1024;
 //            ref: 1183-1196) -- same additions, same bits -- and, if the tensor stays BF16
 //            (ref: 1203-1241), writes its tiles back from shared memory.  The input is never
 //            read again, so output == input needs no special order.
+//
+// Tables.  Under the tensor-wide scale (ss_mode 4) all tiles share one table of RN(q / scale).
+// Under the global-mantissa rule (ss_mode 1) every block's scale is the significand of
+// 448 / global_amax times a power of two, so all tiles share one table for that significand and
+// multiply by their own power of two (PathLutExp); a tile whose exponent would take a quotient
+// out of the normal range divides per element instead.  ss_mode 2 (power-of-two scales) needs no
+// table.  ss_mode 3 (a different significand per block) is not taken by this kernel.
 //
 // The two grid barriers are counters in the workspace head (zeroed by the launch before this
 // one); every wait -- barrier or TMA -- is bounded, and a wait that runs out is reported as
@@ -32,20 +42,28 @@ namespace morb {
 
 namespace {
 
-constexpr int kResThreads = 1024;
+// development hook: a probe that includes this file may define it to record where the time goes
+#ifndef MORB_TRACE_POINT
+#define MORB_TRACE_POINT(i)
+#endif
 
 template <typename T> struct Res {
     static constexpr int kTileBytes = 128 * 128 * T::kBytesPerElem;
-    static constexpr int kSlots = T::kBytesPerElem == 2 ? 7 : 3;
-    // behind the tiles: mbarriers, per-tile statistics, warp sums, two quotient tables
+    static constexpr int kSlots = T::kBytesPerElem == 2 ? 7 : 3;         // tiles (= thread groups) per CTA
+    static constexpr int kGroupThreads = T::kBytesPerElem == 2 ? 128 : 256;
+    static constexpr int kThreads = kSlots * kGroupThreads;               // 896 / 768
+    static constexpr int kVecPerRow = 128 * T::kBytesPerElem / 16;        // 16 / 32
+    static constexpr int kLanesPerRow = kVecPerRow / 2;                   // a lane takes vectors p and p + kLanesPerRow
+    // behind the tiles: mbarriers, per-tile statistics and scales, warp sums, one quotient table
     static constexpr int kBarOff = kSlots * kTileBytes;   // 8 x uint64
     static constexpr int kAmaxOff = kBarOff + 64;          // 8 x uint32  tile amax bits
     static constexpr int kNnzOff = kAmaxOff + 32;          // 8 x int32   tile non-zero count
     static constexpr int kFlagOff = kNnzOff + 32;          // 8 x uint32  bit 0: short quotient not allowed, bit 1: NaN seen
-    static constexpr int kWsumOff = kFlagOff + 32;         // 32 x float
-    static constexpr int kMiscOff = kWsumOff + 128;        // 8 x uint32
-    static constexpr int kLutOff = kMiscOff + 32;          // 2 x 256 x float
-    static constexpr int kSmem = kLutOff + 2 * 1024;
+    static constexpr int kSfOff = kFlagOff + 32;           // 8 x float   tile scale
+    static constexpr int kMiscOff = kSfOff + 32;           // 8 x uint32
+    static constexpr int kWsumOff = kMiscOff + 32;         // kSlots x 32 x float (also the 32 partial sums of the decision)
+    static constexpr int kLutOff = kWsumOff + kSlots * 128;
+    static constexpr int kSmem = kLutOff + 1024;
     static_assert(kLutOff % 16 == 0, "table alignment");
     static_assert(kSmem <= 227 * 1024, "shared memory of one SM");
 };
@@ -55,6 +73,10 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+// barrier among the `count` threads (a multiple of 32) that name the same id (1 .. 15)
+__device__ __forceinline__ void group_sync(int id, int count) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
 
 // All CTAs of the (cooperative) grid meet here.  False for every thread of the CTA if the
 // others did not show up within the limit.
@@ -62,156 +84,153 @@ __device__ __forceinline__ bool grid_barrier(uint32_t* counter, uint32_t expecte
     __syncthreads();
     bool ok = true;
     if (threadIdx.x == 0) {
-        __threadfence();
-        atomicAdd(counter, 1u);
+        uint32_t seen;
+        // release: what this CTA wrote before is visible to whoever sees the count; acquire: and the reverse
+        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(seen) : "l"(counter) : "memory");
         uint32_t polls = 0;
-        while (ld_acquire_gpu(counter) < expected) {
-            if (++polls > limit) { ok = false; break; }
+        if (seen + 1u < expected) {   // the last one to arrive does not have to look again
+            while (ld_acquire_gpu(counter) < expected) {
+                if (++polls > limit) { ok = false; break; }
+            }
         }
-        __threadfence();
     }
     return __syncthreads_and(ok) != 0;
 }
 
-// word = the pair of elements (2w, 2w + 1): 4 bytes of bf16, 8 bytes of binary32
-template <typename T> struct Word;
-template <> struct Word<Bf16> {
-    using type = uint32_t;
-    __device__ static __forceinline__ void unpack(uint32_t w, float& hi, float& lo) { hi = bf16_hi(w); lo = bf16_lo(w); }
-};
-template <> struct Word<Fp32> {
-    using type = float2;
-    __device__ static __forceinline__ void unpack(float2 w, float& hi, float& lo) { hi = w.y; lo = w.x; }
-};
-
-// pass 2 of one tile: thread (tx, ty) walks its eight words in the reference's order
+// pass 2 of one tile by its thread group; returns the error sums of the two logical warps (rows ty
+// and ty + 16) this lane belongs to, valid in the lanes with p == 0
 template <typename T, int DIV, bool NOZERO, typename P>
-__device__ __forceinline__ float cast_tile(const P& path, const uint8_t* tile, typename Word<T>::type* dst, int64_t cols_w,
-                                           int tx, int ty) {
-    using W = typename Word<T>::type;
-    const W* t = reinterpret_cast<const W*>(tile);
-    float acc = 0.0f;
+__device__ __forceinline__ void cast_tile(const P& path, const typename T::vec_t* tile, typename T::vec_t* dst,
+                                          int64_t cols_vec, int p, int tyh, float& sum0, float& sum1) {
+    using R = Res<T>;
+    constexpr int VW = T::kWordsPerVec, VPR = R::kVecPerRow, LPR = R::kLanesPerRow;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int half = 0; half < 2; ++half) {
+        const int ty = tyh + 16 * half;
+        const typename T::vec_t* src = tile + ty * VPR + p;
+        typename T::vec_t* o = dst + (int64_t)ty * cols_vec + p;
+        float acc[VW];
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int r = ty + 32 * j, c = tx + 32 * i;
-            float hi, lo, dh, dl, eh, el;
-            Word<T>::unpack(t[r * 64 + c], hi, lo);
-            err_pair<DIV, P, NOZERO>(path, hi, lo, dh, dl, eh, el);
-            acc = __fadd_rn(acc, eh);
-            acc = __fadd_rn(acc, el);
-            if constexpr (T::kBytesPerElem == 2) {
-                uint32_t w;
-                if constexpr (PathTraits<P>::kExactBf16) w = path.c.fast ? pack_bf16_trunc(dh, dl) : pack_bf16(dh, dl);
-                else w = pack_bf16_round(dh, dl);
-                __stcs(dst + (int64_t)r * cols_w + c, w);
-            } else {
-                __stcs(dst + (int64_t)r * cols_w + c, make_float2(dl, dh));
+        for (int k = 0; k < VW; ++k) acc[k] = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                typename T::vec_t out;
+                err_vec<T, P, true, DIV, NOZERO>(path, src[j * 32 * VPR + i * LPR], out, acc);
+                st_stream(o + i * LPR, out);
             }
+            o += 32 * cols_vec;
         }
+        const float s = logical_warp_sum<VW>(acc);
+        if (half == 0) sum0 = s; else sum1 = s;
     }
-    return acc;
 }
 
 template <typename T, bool E8>
-__global__ void __launch_bounds__(kResThreads, 1)
+__global__ void __launch_bounds__(Res<T>::kThreads, 1)
 block_resident_kernel(const __grid_constant__ CUtensorMap tmap, void* __restrict__ out_raw, int64_t cols, int blocks_x,
                       int n_tiles, int ss, float threshold, float* __restrict__ block_err, ScalarsWs* __restrict__ ws,
                       int32_t* __restrict__ meta_out, float* __restrict__ gamax_out, void* __restrict__ gnnz_out,
                       int nnz_is_i64, float* __restrict__ gerr_out, uint32_t spin_limit) {
     using R = Res<T>;
-    using W = typename Word<T>::type;
+    using V = typename T::vec_t;
+    constexpr int GT = R::kGroupThreads, NT = R::kThreads;
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + R::kBarOff);
     uint32_t* s_amax = reinterpret_cast<uint32_t*>(smem + R::kAmaxOff);
     int* s_nnz = reinterpret_cast<int*>(smem + R::kNnzOff);
     uint32_t* s_flag = reinterpret_cast<uint32_t*>(smem + R::kFlagOff);
-    float* s_wsum = reinterpret_cast<float*>(smem + R::kWsumOff);
+    float* s_sf = reinterpret_cast<float*>(smem + R::kSfOff);
     uint32_t* s_misc = reinterpret_cast<uint32_t*>(smem + R::kMiscOff);
+    float* s_wsum = reinterpret_cast<float*>(smem + R::kWsumOff);
     float* s_lut = reinterpret_cast<float*>(smem + R::kLutOff);
 
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int g = tid / GT, gt = tid % GT;            // thread group = tile slot, thread within the group
     const int G = gridDim.x;
     // this CTA's tiles: blockIdx.x, blockIdx.x + G, ...
     const int n_mine = (n_tiles - (int)blockIdx.x + G - 1) / G;   // 1 .. kSlots (the launcher guarantees it)
+    const bool have = g < n_mine;
+    const int t = (int)blockIdx.x + g * G;             // this group's tile
+    const int bx = have ? t % blocks_x : 0, by = have ? t / blocks_x : 0;
+    const V* tile = reinterpret_cast<const V*>(smem + g * R::kTileBytes);
 
+    if (tid == 0) MORB_TRACE_POINT(0);
     if (tid == 0) {
         for (int k = 0; k < R::kSlots; ++k) mbar_init(&s_bar[k], 1);
     }
     if (tid < 8) { s_amax[tid] = 0u; s_nnz[tid] = 0; s_flag[tid] = 0u; }
     __syncthreads();
-    if (lane == 0 && wid < n_mine) {
-        const int t = (int)blockIdx.x + wid * G;
-        mbar_expect_tx(&s_bar[wid], R::kTileBytes);
-        tma_load_2d(smem + wid * R::kTileBytes, &tmap, (t % blocks_x) * 128, (t / blocks_x) * 128, &s_bar[wid]);
+    if (gt == 0 && have) {
+        mbar_expect_tx(&s_bar[g], R::kTileBytes);
+        tma_load_2d(smem + g * R::kTileBytes, &tmap, bx * 128, by * 128, &s_bar[g]);
     }
 
-    // ---- pass 1: statistics of every tile, as it arrives --------------------------------
+    // ---- pass 1: statistics of the group's tile, as soon as it has arrived ---------------
     bool arrived = true;
-    for (int k = 0; k < n_mine; ++k) {
-        if (!__all_sync(0xFFFFFFFFu, mbar_wait_bounded(&s_bar[k], 0))) { arrived = false; break; }   // warp-uniform
-        const uint8_t* tile = smem + k * R::kTileBytes;
-        uint32_t amax_bits, flags = 0u;
-        int nnz = 0;
-        if constexpr (T::kBytesPerElem == 2) {
-            const uint4* tv = reinterpret_cast<const uint4*>(tile);
-            uint32_t pmx = 0u, pmn = 0x7FFF7FFFu;
-            int nnz4 = 0;
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const uint4 v = tv[tid + u * kResThreads];
-                const uint32_t m0 = mag2(v.x), m1 = mag2(v.y), m2 = mag2(v.z), m3 = mag2(v.w);
-                pmx = umax16x2_3(umax16x2_3(pmx, m0, m1), m2, m3);
-                const uint32_t s0 = m0 + 0x7FFF7FFFu, s1 = m1 + 0x7FFF7FFFu, s2 = m2 + 0x7FFF7FFFu, s3 = m3 + 0x7FFF7FFFu;
-                pmn = smin16x2_3(smin16x2_3(pmn, s0, s1), s2, s3);
-                nnz4 += __popc((top_bits_to_bytes(s0, s1) & 0x0F0F0F0Fu) | (top_bits_to_bytes(s2, s3) & 0xF0F0F0F0u));
+    if (have) {
+        arrived = __all_sync(0xFFFFFFFFu, mbar_wait_bounded(&s_bar[g], 0));   // warp-uniform
+        if (gt == 0) MORB_TRACE_POINT(8 + g);
+        if (arrived) {
+            constexpr int kVecPerThread = R::kTileBytes / 16 / GT;   // 16
+            uint32_t amax_bits, flags = 0u;
+            int nnz = 0;
+            if constexpr (T::kBytesPerElem == 2) {
+                uint32_t pmx = 0u, pmn = 0x7FFF7FFFu;
+                int nnz4 = 0;
+#pragma unroll 4
+                for (int u = 0; u < kVecPerThread; ++u) {
+                    const uint4 v = tile[gt + u * GT];
+                    const uint32_t m0 = mag2(v.x), m1 = mag2(v.y), m2 = mag2(v.z), m3 = mag2(v.w);
+                    pmx = umax16x2_3(umax16x2_3(pmx, m0, m1), m2, m3);
+                    const uint32_t s0 = m0 + 0x7FFF7FFFu, s1 = m1 + 0x7FFF7FFFu, s2 = m2 + 0x7FFF7FFFu, s3 = m3 + 0x7FFF7FFFu;
+                    pmn = smin16x2_3(smin16x2_3(pmn, s0, s1), s2, s3);
+                    nnz4 += __popc((top_bits_to_bytes(s0, s1) & 0x0F0F0F0Fu) | (top_bits_to_bytes(s2, s3) & 0xF0F0F0F0u));
+                }
+                nnz = nnz4 >> 2;
+                const uint32_t top = hmax_halves(pmx);
+                amax_bits = top << 16;
+                // smallest non-zero magnitude this thread saw (a half with bit 15 set saw one)
+                const uint32_t h0 = pmn & 0xFFFFu, h1 = pmn >> 16;
+                uint32_t amin_pat = 0x3F80u;
+                if (h0 & 0x8000u) amin_pat = min(amin_pat, (h0 & 0x7FFFu) + 1u);
+                if (h1 & 0x8000u) amin_pat = min(amin_pat, (h1 & 0x7FFFu) + 1u);
+                if (top > 0x7F80u) flags |= 3u;                                            // NaN: exact rescan below
+                if (!bf16_div_safe(u2f(amin_pat << 16)) || (top != 0u && !bf16_div_safe(u2f(top << 16)))) flags |= 1u;
+            } else {
+                float a = 0.0f;
+#pragma unroll 4
+                for (int u = 0; u < kVecPerThread; ++u) {
+                    const float4 v = tile[gt + u * GT];
+                    const float a0 = fabsf(v.x), a1 = fabsf(v.y), a2 = fabsf(v.z), a3 = fabsf(v.w);
+                    a = fmaxf(a, fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)));   // fmaxf skips NaNs, as the reference's does
+                    nnz += (a0 > 0.0f) + (a1 > 0.0f) + (a2 > 0.0f) + (a3 > 0.0f);
+                }
+                amax_bits = f2u(a);
             }
-            nnz = nnz4 >> 2;
-            const uint32_t top = hmax_halves(pmx);
-            amax_bits = top << 16;
-            // smallest non-zero magnitude this thread saw (a half with bit 15 set saw one)
-            const uint32_t h0 = pmn & 0xFFFFu, h1 = pmn >> 16;
-            uint32_t amin_pat = 0x3F80u;
-            if (h0 & 0x8000u) amin_pat = min(amin_pat, (h0 & 0x7FFFu) + 1u);
-            if (h1 & 0x8000u) amin_pat = min(amin_pat, (h1 & 0x7FFFu) + 1u);
-            if (top > 0x7F80u) flags |= 3u;                                            // NaN: exact rescan below
-            if (!bf16_div_safe(u2f(amin_pat << 16)) || (top != 0u && !bf16_div_safe(u2f(top << 16)))) flags |= 1u;
-        } else {
-            const float4* tv = reinterpret_cast<const float4*>(tile);
-            float a = 0.0f;
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const float4 v = tv[tid + u * kResThreads];
-                const float a0 = fabsf(v.x), a1 = fabsf(v.y), a2 = fabsf(v.z), a3 = fabsf(v.w);
-                a = fmaxf(a, fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)));   // fmaxf skips NaNs, as the reference's does
-                nnz += (a0 > 0.0f) + (a1 > 0.0f) + (a2 > 0.0f) + (a3 > 0.0f);
+            amax_bits = __reduce_max_sync(0xFFFFFFFFu, amax_bits);
+            nnz = __reduce_add_sync(0xFFFFFFFFu, nnz);
+            flags = __reduce_or_sync(0xFFFFFFFFu, flags);
+            if (lane == 0) {
+                atomicMax(&s_amax[g], amax_bits);
+                if (nnz) atomicAdd(&s_nnz[g], nnz);
+                if (flags) atomicOr(&s_flag[g], flags);
             }
-            amax_bits = f2u(a);
-        }
-        amax_bits = __reduce_max_sync(0xFFFFFFFFu, amax_bits);
-        nnz = __reduce_add_sync(0xFFFFFFFFu, nnz);
-        flags = __reduce_or_sync(0xFFFFFFFFu, flags);
-        if (lane == 0) {
-            atomicMax(&s_amax[k], amax_bits);
-            if (nnz) atomicAdd(&s_nnz[k], nnz);
-            if (flags) atomicOr(&s_flag[k], flags);
         }
     }
     arrived = __syncthreads_and(arrived) != 0;
     if constexpr (T::kBytesPerElem == 2) {
-        // a NaN in a tile: the packed maximum is not the reference's (fmaxf ignores NaNs and they are
-        // not counted); redo that tile with float compares
-        for (int k = 0; k < n_mine && arrived; ++k) {
-            if (!(s_flag[k] & 2u)) continue;      // CTA-uniform
-            __syncthreads();
-            if (tid == 0) { s_amax[k] = 0u; s_nnz[k] = 0; }
-            __syncthreads();
-            const uint4* tv = reinterpret_cast<const uint4*>(smem + k * R::kTileBytes);
+        // a NaN in the tile: the packed maximum is not the reference's (fmaxf ignores NaNs and they are
+        // not counted); redo the tile with float compares
+        if (have && arrived && (s_flag[g] & 2u)) {   // uniform within the group
+            group_sync(1 + g, GT);
+            if (gt == 0) { s_amax[g] = 0u; s_nnz[g] = 0; }
+            group_sync(1 + g, GT);
             float a = 0.0f;
             int n = 0;
-            for (int u = 0; u < 2; ++u) {
-                const uint4 v = tv[tid + u * kResThreads];
+            for (int u = 0; u < R::kTileBytes / 16 / GT; ++u) {
+                const uint4 v = tile[gt + u * GT];
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     float hi, lo;
@@ -223,9 +242,9 @@ block_resident_kernel(const __grid_constant__ CUtensorMap tmap, void* __restrict
             }
             a = warp_max(a);
             n = warp_sum_int(n);
-            if (lane == 0) { atomicMax(&s_amax[k], f2u(a)); if (n) atomicAdd(&s_nnz[k], n); }
-            __syncthreads();
+            if (lane == 0) { atomicMax(&s_amax[g], f2u(a)); if (n) atomicAdd(&s_nnz[g], n); }
         }
+        __syncthreads();
     }
     if (tid == 0) {
         uint32_t a = 0u;
@@ -238,7 +257,9 @@ block_resident_kernel(const __grid_constant__ CUtensorMap tmap, void* __restrict
             atomicOr(&ws->load_timeout, 1u);
         }
     }
+    if (tid == 0) MORB_TRACE_POINT(1);
     bool alive = grid_barrier(&ws->bar[0], (uint32_t)G, spin_limit);
+    if (tid == 0) MORB_TRACE_POINT(2);
     // a CTA whose tile did not arrive told the others before the barrier: everybody stops here
     alive = alive && *reinterpret_cast<volatile uint32_t*>(&ws->load_timeout) == 0u;
     if (!alive) {
@@ -246,57 +267,60 @@ block_resident_kernel(const __grid_constant__ CUtensorMap tmap, void* __restrict
             atomicOr(&ws->load_timeout, 1u);
             if (blockIdx.x == 0 && meta_out) *meta_out = -1;
         }
-        // give copies that may still be in flight a last bounded chance before the shared memory is released
-        for (int k = 0; k < n_mine; ++k) mbar_wait_bounded(&s_bar[k], 0);
+        // give a copy that may still be in flight a last bounded chance before the shared memory is released
+        if (have) mbar_wait_bounded(&s_bar[g], 0);
         return;
     }
 
     // ---- pass 2: scale, cast, store, error sums ---------------------------------------
     const float gamax = u2f(*reinterpret_cast<volatile uint32_t*>(&ws->gamax_bits));
-    W* out = static_cast<W*>(out_raw);
-    const int64_t cols_w = cols / 2;
-    const int tx = lane, ty = wid;
-    for (int k = 0; k < n_mine; ++k) {
-        const int t = (int)blockIdx.x + k * G;
-        const int bx = t % blocks_x, by = t / blocks_x;
-        const uint8_t* tile = smem + k * R::kTileBytes;
-        const float bamax = u2f(s_amax[k]);
-        const bool zero_free = s_nnz[k] == 128 * 128 && !(s_flag[k] & 2u);
-        const bool short_ok = T::kBytesPerElem != 2 || !(s_flag[k] & 1u);
-        const float sf = scaling_factor(ss, gamax, bamax);
-        W* dst = out + (int64_t)by * 128 * cols_w + (int64_t)bx * 64;
-        float acc;
+    if (tid < n_mine) s_sf[tid] = scaling_factor(ss, gamax, u2f(s_amax[tid]));
+    if constexpr (!E8) {
+        // one table for the whole CTA: the tensor-wide scale (ss_mode 4), or the significand that all
+        // block scales share under the global-mantissa rule (ss_mode 1)
+        if (tid >= NT - 256) {
+            float base = scaling_factor(ss, gamax, gamax);
+            if (ss == 1) base = u2f(0x3F800000u | (f2u(base) & 0x007FFFFFu));
+            fill_lut32(s_lut, base, tid - (NT - 256), 256);
+        }
+    }
+    __syncthreads();
+    if (have) {
+        const int p = gt % R::kLanesPerRow, tyh = gt / R::kLanesPerRow;   // tyh: 0 .. 15
+        const int64_t cols_vec = cols * T::kBytesPerElem / 16;
+        V* dst = static_cast<V*>(out_raw) + (int64_t)by * 128 * cols_vec + (int64_t)bx * R::kVecPerRow;
+        const bool zero_free = s_nnz[g] == 128 * 128 && !(s_flag[g] & 2u);
+        const bool short_ok = T::kBytesPerElem != 2 || !(s_flag[g] & 1u);
+        const float sf = s_sf[g];
+        float sum0 = 0.0f, sum1 = 0.0f;
         auto dispatch = [&](const auto& path) {
             using P = std::decay_t<decltype(path)>;
             constexpr int kShort = T::kBytesPerElem == 2 ? kDivBf16 : kDivIeee;
             constexpr int kLong = T::kBytesPerElem == 2 ? kDivBf16Any : kDivIeee;
-            if (short_ok && zero_free) acc = cast_tile<T, kShort, true, P>(path, tile, dst, cols_w, tx, ty);
-            else if (short_ok) acc = cast_tile<T, kShort, false, P>(path, tile, dst, cols_w, tx, ty);
-            else acc = cast_tile<T, kLong, false, P>(path, tile, dst, cols_w, tx, ty);
+            if (short_ok && zero_free) cast_tile<T, kShort, true, P>(path, tile, dst, cols_vec, p, tyh, sum0, sum1);
+            else if (short_ok) cast_tile<T, kShort, false, P>(path, tile, dst, cols_vec, p, tyh, sum0, sum1);
+            else cast_tile<T, kLong, false, P>(path, tile, dst, cols_vec, p, tyh, sum0, sum1);
         };
         if constexpr (E8) {
             dispatch(PathE8{e8_consts(sf)});
         } else {
-            float* lut = s_lut + (k & 1) * 256;
-            // the table depends on the scale only: under the tensor-wide scale (ss_mode 4) it is filled once
-            if (k == 0 || ss != 4) {
-                fill_lut32(lut, sf, tid, kResThreads);
-                __syncthreads();
-            } else {
-                lut = s_lut;
-            }
-            dispatch(PathLut{lut, sf});
+            const uint32_t field = (f2u(sf) >> 23) & 0xFFu;
+            if (ss != 1) dispatch(PathLut{s_lut, sf});
+            else if (field >= 12u && field <= 240u) dispatch(PathLutExp{s_lut, sf, u2f((254u - field) << 23)});
+            else dispatch(PathDiv{sf});
         }
-        const float s = warp_sum_ordered(acc);
-        if (lane == 0) s_wsum[wid] = s;
-        __syncthreads();
-        if (wid == 0) {
-            const float tot = warp_sum_ordered(s_wsum[lane]);
-            if (lane == 0) block_err[t] = tot;
+        float* wsum = s_wsum + g * 32;
+        if (p == 0) { wsum[tyh] = sum0; wsum[tyh + 16] = sum1; }
+        group_sync(1 + g, GT);
+        if (gt < 32) {
+            const float tot = warp_sum_ordered(wsum[gt]);
+            if (gt == 0) block_err[t] = tot;
         }
-        if (E8 || ss == 4) __syncthreads();   // no table barrier in the next round: keep s_wsum until warp 0 has read it
     }
-    if (!grid_barrier(&ws->bar[1], (uint32_t)G, spin_limit)) {
+    if (tid == 0) MORB_TRACE_POINT(3);
+    const bool met = grid_barrier(&ws->bar[1], (uint32_t)G, spin_limit);
+    if (tid == 0) MORB_TRACE_POINT(4);
+    if (!met) {
         if (tid == 0) {
             atomicOr(&ws->load_timeout, 1u);
             if (blockIdx.x == 0 && meta_out) *meta_out = -1;
@@ -305,11 +329,13 @@ block_resident_kernel(const __grid_constant__ CUtensorMap tmap, void* __restrict
     }
 
     // ---- decision: every CTA repeats the ordered sum of all blocks' errors -------------
-    float acc = 0.0f;
-    for (int e = tid; e < n_tiles; e += kResThreads) acc = __fadd_rn(acc, __ldcg(block_err + e));
-    acc = warp_sum_ordered(acc);
-    __syncthreads();
-    if (lane == 0) s_wsum[wid] = acc;
+    // logical thread l of 1024 adds entries l, l + 1024, ...; logical warp w = threads 32 w .. 32 w + 31
+    for (int w = wid; w < 32; w += NT / 32) {
+        float acc = 0.0f;
+        for (int e = w * 32 + lane; e < n_tiles; e += 1024) acc = __fadd_rn(acc, __ldcg(block_err + e));
+        acc = warp_sum_ordered(acc);
+        if (lane == 0) s_wsum[w] = acc;
+    }
     __syncthreads();
     if (wid == 0) {
         const float total = warp_sum_ordered(s_wsum[lane]);
@@ -333,26 +359,14 @@ block_resident_kernel(const __grid_constant__ CUtensorMap tmap, void* __restrict
         }
     }
     __syncthreads();
-    if (s_misc[0]) {
-        // the tensor stays as it was: the tiles are still in shared memory
-        constexpr int kVecPerRow = 128 * T::kBytesPerElem / 16;
-        const int64_t cols_v = cols * T::kBytesPerElem / 16;
-        uint4* out_v = static_cast<uint4*>(out_raw);
-        for (int k = 0; k < n_mine; ++k) {
-            const int t = (int)blockIdx.x + k * G;
-            const int bx = t % blocks_x, by = t / blocks_x;
-            const uint4* tv = reinterpret_cast<const uint4*>(smem + k * R::kTileBytes);
-            for (int v = tid; v < 128 * kVecPerRow; v += kResThreads) {
-                const int r = v / kVecPerRow, c = v % kVecPerRow;
-                __stcs(out_v + ((int64_t)by * 128 + r) * cols_v + (int64_t)bx * kVecPerRow + c, tv[v]);
-            }
-        }
+    if (tid == 0) MORB_TRACE_POINT(5);
+    if (s_misc[0] && have) {
+        // the tensor stays as it was: the tile is still in shared memory
+        constexpr int VPR = R::kVecPerRow;
+        const int64_t cols_vec = cols * T::kBytesPerElem / 16;
+        V* out_v = static_cast<V*>(out_raw) + (int64_t)by * 128 * cols_vec + (int64_t)bx * VPR;
+        for (int v = gt; v < 128 * VPR; v += GT) st_stream(out_v + (int64_t)(v / VPR) * cols_vec + (v % VPR), tile[v]);
     }
-}
-
-// box of one whole 128 x 128 tile (row-major in shared memory)
-bool make_whole_tile_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int elem_bytes) {
-    return make_tile_map(map, base, rows, cols, elem_bytes, 128, 128);
 }
 
 struct DeviceCaps {
@@ -374,7 +388,7 @@ int launch_resident_t(const ScalingArgs& a, int32_t* meta, float* gamax, void* g
         int coop = 0, per_sm = 0;
         static SmemOptIn opt;
         if (cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev) == cudaSuccess && coop && opt(kernel, R::kSmem) &&
-            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kResThreads, R::kSmem) == cudaSuccess && per_sm >= 1) {
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, R::kThreads, R::kSmem) == cudaSuccess && per_sm >= 1) {
             c.ctas = sm_count();   // one CTA per SM: it uses all of the SM's shared memory
             c.checked = 1;
         } else {
@@ -384,7 +398,8 @@ int launch_resident_t(const ScalingArgs& a, int32_t* meta, float* gamax, void* g
     }
     if (c.checked < 0 || nt64 > (int64_t)c.ctas * R::kSlots) return kErrUnsupportedShape;
     CUtensorMap map;
-    if (!make_whole_tile_map(&map, a.in, a.rows, a.cols, T::kBytesPerElem)) return kErrUnsupportedShape;
+    // one box = one whole 128 x 128 tile, row-major in shared memory
+    if (!make_tile_map(&map, a.in, a.rows, a.cols, T::kBytesPerElem, 128, 128)) return kErrUnsupportedShape;
     int rc = launch_zero_scalars(a.ws, st);
     if (rc) return rc;
     int n_tiles = (int)nt64, blocks_x = (int)bx, ss = a.ss_mode, nnz_is_i64 = nnz64;
@@ -397,7 +412,7 @@ int launch_resident_t(const ScalingArgs& a, int32_t* meta, float* gamax, void* g
     uint32_t limit = kSpinLimit;
     void* args[] = {&map, &out, &cols, &blocks_x, &n_tiles, &ss, &thr, &block_err, &ws, &meta, &gamax, &gnnz,
                     &nnz_is_i64, &gerr, &limit};
-    if (cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), dim3((unsigned)grid), dim3(kResThreads), args,
+    if (cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), dim3((unsigned)grid), dim3(R::kThreads), args,
                                     (size_t)R::kSmem, st) != cudaSuccess) {
         cudaGetLastError();
         return kErrLaunch;
@@ -407,11 +422,11 @@ int launch_resident_t(const ScalingArgs& a, int32_t* meta, float* gamax, void* g
 
 }  // namespace
 
-// kErrUnsupportedShape: the tensor is not one this kernel takes (too large, other blocks, a device
-// without cooperative launch) and the caller runs the sequence of launches instead.
+// kErrUnsupportedShape: the tensor is not one this kernel takes (too large, other blocks, ss_mode 3, a
+// device without cooperative launch) and the caller runs the sequence of launches instead.
 int launch_block_resident(const ScalingArgs& a, int32_t* meta, float* gamax, void* gnnz, int nnz_is_i64, float* gerr,
                           cudaStream_t st) {
-    if (a.brows != 128 || a.bcols != 128 || resident_disabled() || force_generic()) return kErrUnsupportedShape;
+    if (a.brows != 128 || a.bcols != 128 || a.ss_mode == 3 || resident_disabled() || force_generic()) return kErrUnsupportedShape;
     if (a.rows % 128 || a.cols % 128 || a.rows >= (int64_t(1) << 31) || a.cols >= (int64_t(1) << 31)) return kErrUnsupportedShape;
     const bool e8 = a.ss_mode == 2;
     if (a.is_fp32) return e8 ? launch_resident_t<Fp32, true>(a, meta, gamax, gnnz, nnz_is_i64, gerr, st)

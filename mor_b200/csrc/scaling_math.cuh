@@ -45,6 +45,11 @@ __device__ __forceinline__ bool fast_div_ok(const ScalarsWs* ws) {
 //   E8    power-of-two scale: two multiplies (or the literal exponent-field form
 //         outside the range where they are provably identical).
 struct PathLut { const float* lut; float sf; };
+// Scales that share their significand and differ by a power of two (the global-mantissa rule,
+// ref: 1067-1076, gives every block the significand of 448 / global_amax): one table for the
+// significand alone, `descale` = 2^-(exponent of sf).  RN(q / (m 2^e)) = RN(q / m) 2^-e as long as
+// nothing leaves the normal range, which the caller checks from the exponent of sf.
+struct PathLutExp { const float* lut; float sf; float descale; };
 struct PathDiv { float sf; };
 struct PathE8 { E8Consts c; };
 
@@ -52,6 +57,11 @@ __device__ __forceinline__ void dequant_pair(const PathLut& p, float hi, float l
     const uint32_t c = cvt_codes<kE4M3>(__fmul_rn(hi, p.sf), __fmul_rn(lo, p.sf));
     dh = p.lut[c >> 8];
     dl = p.lut[c & 0xFFu];
+}
+__device__ __forceinline__ void dequant_pair(const PathLutExp& p, float hi, float lo, float& dh, float& dl) {
+    const uint32_t c = cvt_codes<kE4M3>(__fmul_rn(hi, p.sf), __fmul_rn(lo, p.sf));
+    dh = __fmul_rn(p.lut[c >> 8], p.descale);
+    dl = __fmul_rn(p.lut[c & 0xFFu], p.descale);
 }
 __device__ __forceinline__ void dequant_pair(const PathDiv& p, float hi, float lo, float& dh, float& dl) {
     sqdd_fp32_pair<kE4M3>(hi, lo, p.sf, dh, dl);

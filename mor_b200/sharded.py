@@ -123,6 +123,21 @@ class CudaBackend:
         self.launches += 1
 
 
+def check_same_on_every_rank(values, what: str, group: Optional[dist.ProcessGroup] = None) -> None:
+    """Collective: raises ``ValueError`` on EVERY rank if the ranks do not all hold the same ``values``.
+
+    The row-sharded pipeline gathers fixed-size arrays (every rank computes its offsets into the peers'
+    buffers from its OWN slab height), so slabs of different heights would write outside a peer's
+    buffer; :func:`shard_rows` gives uneven slabs when the block rows do not divide by the world size."""
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return
+    world = dist.get_world_size(group)
+    seen = [None] * world
+    dist.all_gather_object(seen, tuple(values), group=group)
+    if any(v != seen[0] for v in seen):
+        raise ValueError(f"every rank must hold the same {what}; ranks report {seen}")
+
+
 class PeerExchange:
     """Buffers of all ranks mapped into every rank (CUDA IPC over NVLink), for the peer exchange of
     include/mor_b200.h: every rank allocates one zero-filled buffer through the library, the 64-byte
@@ -197,8 +212,13 @@ class PeerExchange:
 class ShardedScaling:
     """Row-sharded ``fake_quantize_block_scaling`` / ``fake_quantize_channel_scaling``.
 
-    All ranks must call with slabs of the SAME height (the all-gather is fixed-size);
-    :func:`shard_rows` gives such a partition when the row count divides evenly.
+    All ranks must call with slabs of the SAME height (the gathered arrays are fixed-size);
+    :func:`shard_rows` gives such a partition when the row count divides evenly.  The constructor is a
+    collective call and raises ``ValueError`` on every rank when the slabs differ.
+
+    A call whose peer wait ran out reports ``meta == -1`` (its output is not valid): see :meth:`timed_out`.
+    After that the ranks are no longer in step -- drop the object (``close()``) and build a new one on
+    every rank before the next call.
     """
 
     def __init__(self, rows_local: int, cols: int, brows: int, bcols: int, dtype: torch.dtype,
@@ -213,6 +233,8 @@ class ShardedScaling:
         self.device = device
         self.backend = backend if backend is not None else CudaBackend(kind, rows_local, cols, brows, bcols, dtype, device)
         n_err = self.backend.n_err
+        # both exchanges move fixed-size arrays: refuse slabs of different shapes before anything is stored
+        check_same_on_every_rank((rows_local, cols, brows, bcols, n_err), "slab shape (rows, cols, block, error entries)", group)
         self.amax = torch.zeros(1, dtype=torch.float32, device=device)
         self.nnz = torch.zeros(1, dtype=torch.int64, device=device)
         self.meta = torch.zeros(1, dtype=torch.int32, device=device)
@@ -235,6 +257,16 @@ class ShardedScaling:
                 pass
             else:
                 self.local_err = torch.zeros(n_err, dtype=torch.float32, device=device)
+
+    def timed_out(self, result: ScalingResult) -> bool:
+        """True if a bounded wait of the call that produced ``result`` ran out (synchronises on one int)."""
+        return int(result.meta.item()) == -1
+
+    def close(self) -> None:
+        """Collective: releases the peer-exchange buffers (a no-op for the NCCL exchange)."""
+        if self.peer is not None:
+            self.peer.close()
+            self.peer = None
 
     def __call__(self, x: torch.Tensor, out: torch.Tensor, ss_mode: int, threshold: float) -> ScalingResult:
         b = self.backend

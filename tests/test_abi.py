@@ -133,13 +133,30 @@ def test_ops_surface_matches_reference_signatures():
         assert list(inspect.signature(getattr(mor.ops, name)).parameters) == params, name
 
 
+# the operator schemas of the reference extension (mor/csrc/fake_quantize.cpp:12-25), which a drop-in must register unchanged
+REFERENCE_SCHEMAS = [
+    "fake_quantize(Tensor input, int dim_x, int dim_y, int block_x, int block_y, float clamp_threshold, int mode, int sf_type) -> Tensor[]",
+    "fake_quantize_no_alloc(Tensor input, int dim_x, int dim_y, int block_x, int block_y, float clamp_threshold, int mode, int sf_type, Tensor result) -> Tensor",
+    "quant_dequant_e4m3(Tensor input, int dim_x, int dim_y, int block_x, int block_y) -> Tensor",
+    "quant_dequant_e5m2(Tensor input, int dim_x, int dim_y, int block_x, int block_y) -> Tensor",
+    "quant_dequant_e3m2(Tensor input, int dim_x, int dim_y, int block_x, int block_y) -> Tensor",
+    "quant_dequant_e2m3(Tensor input, int dim_x, int dim_y, int block_x, int block_y) -> Tensor",
+    "e4m3_with_e8_scale_rne(Tensor input, int dim_x, int dim_y, int block_x, int block_y) -> Tensor",
+    "e4m3_with_e8_scale_rz(Tensor input, int dim_x, int dim_y, int block_x, int block_y) -> Tensor",
+    "fake_quantize_block_scaling(Tensor input, int dim_x, int dim_y, int block_x, int block_y, float e4m3_threshold, int ss_mode) -> Tensor[]",
+    "fake_quantize_block_scaling_inplace(Tensor input, int dim_x, int dim_y, int block_x, int block_y, float e4m3_threshold, int ss_mode) -> Tensor[]",
+    "fake_quantize_e8mx(Tensor input, int dim_x, int dim_y, int block_x, int block_y, int quantize_type, int scaling_strategy) -> Tensor",
+    "fake_quantize_e8mx_inplace(Tensor input, int dim_x, int dim_y, int block_x, int block_y, int quantize_type, int scaling_strategy, Tensor result) -> ()",
+    "fake_quantize_channel_scaling(Tensor input, int dim_x, int dim_y, int block_x, int block_y, float e4m3_threshold, int ss_mode) -> Tensor[]",
+    "fake_quantize_channel_scaling_inplace(Tensor input, int dim_x, int dim_y, int block_x, int block_y, float e4m3_threshold, int ss_mode) -> Tensor[]",
+]
+
+
 def test_registered_schemas_are_the_reference_ones():
     import torch
     import mor  # noqa: F401
-    s = str(torch.ops.mor.fake_quantize.default._schema)
-    assert s == ("mor::fake_quantize(Tensor input, int dim_x, int dim_y, int block_x, int block_y, "
-                 "float clamp_threshold, int mode, int sf_type) -> Tensor[]")
-    s = str(torch.ops.mor.fake_quantize_e8mx_inplace.default._schema)
-    assert s.endswith("int quantize_type, int scaling_strategy, Tensor result) -> ()")
+    for schema in REFERENCE_SCHEMAS:
+        name = schema.split("(", 1)[0]
+        assert str(getattr(torch.ops.mor, name).default._schema) == "mor::" + schema, name
     with pytest.raises(NotImplementedError):   # CUDA only: no CPU kernel, no fallback
         torch.ops.mor.fake_quantize.default(torch.zeros(4, 4, dtype=torch.bfloat16), 4, 4, 2, 2, 1.0, 1, 1)

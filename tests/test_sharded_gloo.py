@@ -111,6 +111,38 @@ def test_two_ranks_equal_one_process(dtype_name, ss_mode, thr, wide):
     assert (full[1] == 3) == wide or thr > 1.0
 
 
+def uneven_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        r0, r1 = shard_rows(384, world, rank, 128)            # three block rows on two ranks: 256 and 128 rows
+        try:
+            ShardedScaling(r1 - r0, 256, 128, 128, torch.float32, torch.device("cpu"), KIND_BLOCK,
+                           backend=OracleBackend(r1 - r0, 256, 128, 128))
+            q.put((rank, "accepted"))
+        except ValueError as e:
+            q.put((rank, "refused: " + str(e)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_uneven_slabs_are_refused_on_every_rank():
+    """The gathered error arrays are fixed-size and every rank computes its offsets from its own slab: slabs of
+    different heights must be refused before anything is exchanged, and by all ranks alike."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    procs = [ctx.Process(target=uneven_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = sorted(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(g[1].startswith("refused") and "slab shape" in g[1] for g in got), got
+
+
 def test_shard_rows_partition():
     for rows, world, mult in ((131072, 8, 128), (1024, 3, 128), (256, 4, 128), (4096, 5, 32)):
         spans = [shard_rows(rows, world, r, mult) for r in range(world)]
