@@ -270,6 +270,7 @@ def main():
     ap.add_argument("--suite-out", default=None, help="file for the suite table (overrides --out-dir)")
     ap.add_argument("--exchange", choices=["auto", "nccl", "p2p"], default="auto",
                     help="how ranks exchange amax / non-zero count / error sums (N > 1): NCCL collectives or peer stores")
+    ap.add_argument("--no-overlap", action="store_true", help="do not pipeline consecutive steps (every step's kernels in one stream)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="leave the other configurations out of the line")
@@ -324,7 +325,10 @@ def main():
     rows_local = r1 - r0
     x = draw_rows(torch, dev, r0, r1)
     out = torch.empty_like(x)
-    op = ShardedScaling(rows_local, COLS, BLOCK, BLOCK, torch.float32, dev, KIND_BLOCK, exchange=args.exchange)
+    # consecutive steps are pipelined: the chain of small kernels after the cast (error exchange, ordered sum,
+    # decision, conditional copy) runs on a second stream under the amax pass of the next step
+    op = ShardedScaling(rows_local, COLS, BLOCK, BLOCK, torch.float32, dev, KIND_BLOCK, exchange=args.exchange,
+                        overlap=not args.no_overlap)
 
     def barrier():
         if world > 1:
@@ -334,7 +338,7 @@ def main():
     for _ in range(args.warmup):
         res = op(x, out, SS_MODE, THRESHOLD)
     barrier()
-    launches0 = op.backend.launches
+    launches0 = sum(b.launches for b in op.backends)
     with ClockSampler(local_rank) as clocks:
         barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -344,28 +348,29 @@ def main():
         ev1.record()
         barrier()
     step_ms = ev0.elapsed_time(ev1) / args.steps
-    launches = op.backend.launches - launches0
+    launches = sum(b.launches for b in op.backends) - launches0
 
     # ---- where a step's time goes: CUDA events around every phase, in a loop of its own (outside the timed region)
     phase_events = {}
     names = {"amax_nnz": "amax", "amax_nnz_local": "amax", "exchange_scalars": "exchange1", "cast": "cast",
              "exchange_errors": "exchange2", "finalize": "sum", "finalize_ptr": "sum", "fallback": "fallback"}
-    originals = {}
-    for meth, label in names.items():
-        inner = getattr(op.backend, meth)
-        originals[meth] = inner
+    originals = []
+    for bk in op.backends:
+        for meth, label in names.items():
+            inner = getattr(bk, meth)
+            originals.append((bk, meth, inner))
 
-        def timed(*a, _inner=inner, _label=label):
-            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s.record(); _inner(*a); e.record()
-            phase_events.setdefault(_label, []).append((s, e))
-        setattr(op.backend, meth, timed)
+            def timed(*a, _inner=inner, _label=label):
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record(); _inner(*a); e.record()   # on the stream the phase is enqueued on
+                phase_events.setdefault(_label, []).append((s, e))
+            setattr(bk, meth, timed)
     barrier()
-    for _ in range(5):
+    for _ in range(6):
         res = op(x, out, SS_MODE, THRESHOLD)
-    barrier()
-    for meth, inner in originals.items():
-        setattr(op.backend, meth, inner)
+        barrier()                                    # one step at a time here: each phase's own duration
+    for bk, meth, inner in originals:
+        setattr(bk, meth, inner)
     phases_ms = {k: statistics.mean(s.elapsed_time(e) for s, e in v) for k, v in phase_events.items()}
     order = ["amax", "exchange1", "cast", "exchange2", "sum", "fallback"]
     t = torch.tensor([step_ms] + [phases_ms.get(k, 0.0) for k in order], dtype=torch.float64, device=dev)
@@ -502,6 +507,7 @@ def main():
                                    f"{n_gpus} GPU(s), 128x128 block scaling ss_mode 1 with global amax",
                        "bytes_per_element": BYTES_PER_ELEM_TWO_PASS, "l2": "inputs larger than L2, no flush",
                        "threshold": THRESHOLD, "meta": meta, "seed": "4000 + index of the 16384-row slab",
+                       "steps_pipelined": op.overlap,
                        "exchange": ("single GPU" if n_gpus == 1 else ("peer stores over NVLink" if op.peer is not None else "NCCL"))},
             "elements_per_s": total_elems / (step_ms * 1e-3),
             "per_gpu": {"GB/s": value / n_gpus, "elements_per_s": total_elems / (step_ms * 1e-3) / n_gpus,
@@ -534,6 +540,7 @@ def main():
                                for c in configs]
         print(json.dumps(line))
     if world > 1:
+        torch.cuda.synchronize()
         op.close()
         dist.destroy_process_group()
     return 0
@@ -694,7 +701,8 @@ def run_suite(torch, dev, peak, only="", iters=10, out_path=None, use_graph=Fals
     add("c2 per-row E5M2 single pass (fake_quantize mode 3, 1x8192)", x, 4, "fake_quantize", (r, c, 1, c, 0.0, 3, 1), headline=False)
     # not for the reference arm: its channel path launches the 1024-thread reductions with the 64-thread
     # kernels' shared-memory size (fake_quantize.cu:2515-2522) and raised an illegal memory access at this size
-    add("c2 per-row E4M3 pipeline (channel_scaling ss 3)", x, 6, "fake_quantize_channel_scaling", (r, c, 1, c, 3e38, 3))
+    # strategies 2 and 3 scale a group by its own amax: one pass over the tensor (read + write)
+    add("c2 per-row E4M3 pipeline (channel_scaling ss 3)", x, 4, "fake_quantize_channel_scaling", (r, c, 1, c, 3e38, 3))
     add("c2 per-column E4M3 pipeline (channel_scaling 8192x1, ss 1)", x, 6, "fake_quantize_channel_scaling", (r, c, r, 1, 3e38, 1))
     del x
     x = workloads.config3(device=dev)
@@ -702,7 +710,7 @@ def run_suite(torch, dev, peak, only="", iters=10, out_path=None, use_graph=Fals
     add("c3 MX 1x32 E8M0 E4M3 single pass (fake_quantize_mx)", x, 4, "fake_quantize_mx", (r, c, 32, 0, 2))
     add("c3 MX 1x32 E8M0 E2M3 single pass (fake_quantize_mx)", x, 4, "fake_quantize_mx", (r, c, 32, 3, 2), headline=False)
     add("c3 MX 1x32 real quantization, E4M3 codes + E8M0 scales (quantize_mx)", x, 3.03125, "quantize_mx", (r, c, 32, 0), headline=False)
-    add("c3 MX 1x32 E4M3 pipeline (channel_scaling ss 2)", x, 6, "fake_quantize_channel_scaling", (r, c, 1, 32, 3e38, 2))
+    add("c3 MX 1x32 E4M3 pipeline (channel_scaling ss 2)", x, 4, "fake_quantize_channel_scaling", (r, c, 1, 32, 3e38, 2))
     del x
     x = workloads.config4(device=dev)
     r, c = x.shape

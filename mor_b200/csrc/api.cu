@@ -140,6 +140,21 @@ int scaling_op(int kind, const void* in, void* out, int dtype, int64_t rows, int
         if (rc1 != kErrUnsupportedShape) return rc1;
         a.scan_blocks = 0;   // no tile path for this tensor: the two-pass form below
     }
+    // The same for 1 x k row groups (strategies 2 and 3 again): the cast kernels that recompute a group's amax
+    // themselves also publish the tensor's amax and count, and the amax pass is left out.
+    if (kind == MOR_B200_OP_CHANNEL_SCALING && br == 1 && (ss == 2 || ss == 3) && !inplace && !force_generic()) {
+        a.scan_blocks = 1;
+        int rc1 = launch_zero_scalars(ws, st);
+        if (rc1) return rc1;
+        rc1 = launch_rowgroup_err_cast(a, /*store=*/true, false, st);
+        if (rc1 == kOk) {
+            rc1 = launch_finalize(a, nullptr, meta, gamax, gnnz, nnz64, gerr, st);
+            if (rc1) return rc1;
+            return launch_fallback_copy(a, st);
+        }
+        if (rc1 != kErrUnsupportedShape) return rc1;
+        a.scan_blocks = 0;   // no single-pass kernel for this shape: the two-pass form below
+    }
     int rc = phase_amax(kind, in, dtype, rows, cols, br, bc, g, ws, a.block_amax, st);
     if (rc) return rc;
     // In place the input must survive until the tensor-level decision is known: sum the

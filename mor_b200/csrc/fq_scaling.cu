@@ -426,6 +426,176 @@ rowgroup_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::v
 }
 
 // ---------------------------------------------------------------------------------
+// 1 x k blocks of 128 columns and more in ONE pass (strategies 2 and 3: a block's scale needs its own amax only)
+// ---------------------------------------------------------------------------------
+// A CTA takes `units` consecutive blocks -- consecutive in memory, so one bulk copy stages them in shared
+// memory -- and gives each to 64 threads, the threads of the reference's CTA for such a block (ref:
+// 1633-1752): amax, non-zero count and the screening of the short quotient from shared memory, then the
+// scale (and its table of quotients), then thread t walks words t, t + 64, ... with separate error sums for
+// the high and the low halves, as the reference does, and stores the results straight to the output.
+// The tensor is read from HBM once; no amax kernel runs before this one, and the CTA publishes its share
+// of the tensor's amax and count with one atomicMax / atomicAdd.
+constexpr int kRowsUnitThreads = 64, kRowsMaxUnits = 8;
+
+template <typename T, bool E8>
+__global__ void __launch_bounds__(kRowsUnitThreads * kRowsMaxUnits)
+rows_single_pass_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int64_t n_units, int span_bytes,
+                        int units, int ss, float* __restrict__ block_err, ScalarsWs* __restrict__ ws) {
+    using W = typename PairWord<T>::type;
+    using V = typename T::vec_t;
+    extern __shared__ __align__(128) uint8_t s_rows[];   // [units][span_bytes], then [units][256] floats of tables
+    __shared__ __align__(8) uint64_t s_bar;
+    __shared__ uint32_t s_pa[kRowsMaxUnits][2], s_pf[kRowsMaxUnits][2];
+    __shared__ int s_pn[kRowsMaxUnits][2];
+    __shared__ float s_ps[kRowsMaxUnits][2];
+    const int tid = threadIdx.x, lane = tid & 31, u = tid / kRowsUnitThreads, t = tid % kRowsUnitThreads, wu = (tid >> 5) & 1;
+    const int64_t unit0 = (int64_t)blockIdx.x * units;
+    const int n_here = (int)(n_units - unit0 < units ? n_units - unit0 : units);
+    const bool have = u < n_here;
+    if (tid == 0) mbar_init(&s_bar, 1);
+    __syncthreads();
+    if (tid == 0) {
+        const uint32_t bytes = (uint32_t)n_here * (uint32_t)span_bytes;
+        mbar_expect_tx(&s_bar, bytes);
+        bulk_load(s_rows, in + unit0 * span_bytes, bytes, &s_bar);
+    }
+    const bool arrived = mbar_wait_bounded(&s_bar, 0);
+    if (__syncthreads_or(!arrived)) {
+        // the copy did not complete within the bounded wait: flag the call (the decision kernel reports meta = -1)
+        // and give it one more bounded chance to land before the shared memory is handed on
+        if (tid == 0) atomicOr(&ws->load_timeout, 1u);
+        mbar_wait_bounded(&s_bar, 0);
+        return;
+    }
+    const uint8_t* row = s_rows + (size_t)u * span_bytes;
+    float amax = 0.0f;
+    int nnz = 0;
+    bool nan = false, tiny = false;
+    if (have) {
+        const V* rv = reinterpret_cast<const V*>(row);
+        const int nvec = span_bytes / 16;
+        uint32_t flags = 0u;
+        if constexpr (T::kBytesPerElem == 2) {
+            uint32_t pmx = 0u, tmn = 0x7FFF7FFFu;
+            int nnz4 = 0;
+            for (int v = t; v < nvec; v += kRowsUnitThreads) {
+                const uint4 x = rv[v];
+                const uint32_t m0 = mag2(x.x), m1 = mag2(x.y), m2 = mag2(x.z), m3 = mag2(x.w);
+                pmx = umax16x2_3(umax16x2_3(pmx, m0, m1), m2, m3);
+                const uint32_t s0 = m0 + 0x7FFF7FFFu, s1 = m1 + 0x7FFF7FFFu, s2 = m2 + 0x7FFF7FFFu, s3 = m3 + 0x7FFF7FFFu;
+                tmn = smin16x2_3(smin16x2_3(tmn, s0, s1), s2, s3);
+                nnz4 += __popc((top_bits_to_bytes(s0, s1) & 0x0F0F0F0Fu) | (top_bits_to_bytes(s2, s3) & 0xF0F0F0F0u));
+            }
+            const uint32_t top = hmax_halves(pmx);
+            const uint32_t h0 = tmn & 0xFFFFu, h1 = tmn >> 16;   // a half with bit 15 set saw a non-zero magnitude
+            if (((h0 & 0x8000u) && (h0 & 0x7FFFu) < 0x127Fu) || ((h1 & 0x8000u) && (h1 & 0x7FFFu) < 0x127Fu)) flags |= 1u;
+            if (top > 0x7F80u) flags |= 2u;
+            amax = u2f(top << 16);
+            nnz = nnz4 >> 2;
+        } else {
+            for (int v = t; v < nvec; v += kRowsUnitThreads) {
+                const float4 x = rv[v];
+                const float a0 = fabsf(x.x), a1 = fabsf(x.y), a2 = fabsf(x.z), a3 = fabsf(x.w);
+                amax = fmaxf(amax, fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)));   // fmaxf skips NaNs, as the reference's does
+                nnz += (a0 > 0.0f) + (a1 > 0.0f) + (a2 > 0.0f) + (a3 > 0.0f);
+            }
+        }
+        const uint32_t wa = __reduce_max_sync(0xFFFFFFFFu, f2u(amax));
+        const int wn = __reduce_add_sync(0xFFFFFFFFu, nnz);
+        const uint32_t wf = __reduce_or_sync(0xFFFFFFFFu, flags);
+        if (lane == 0) { s_pa[u][wu] = wa; s_pn[u][wu] = wn; s_pf[u][wu] = wf; }
+    }
+    __syncthreads();
+    if (have) {
+        amax = u2f(max(s_pa[u][0], s_pa[u][1]));
+        nnz = s_pn[u][0] + s_pn[u][1];
+        const uint32_t f = s_pf[u][0] | s_pf[u][1];
+        tiny = (f & 1u) != 0u;
+        nan = (f & 2u) != 0u;
+    }
+    if constexpr (T::kBytesPerElem == 2) {
+        if (__syncthreads_or(nan)) {
+            // a NaN in one of the CTA's blocks: that block redoes its statistics with float compares, which skip NaNs
+            // and do not count them, as the reference's do
+            float a = 0.0f;
+            int n = 0;
+            if (have && nan) {
+                const uint4* rv = reinterpret_cast<const uint4*>(row);
+                for (int v = t; v < span_bytes / 16; v += kRowsUnitThreads) {
+                    const uint4 x = rv[v];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        float hi, lo;
+                        Bf16::unpack(x, k, hi, lo);
+                        const float ah = fabsf(hi), al = fabsf(lo);
+                        a = fmaxf(a, fmaxf(ah, al));
+                        n += (ah > 0.0f) + (al > 0.0f);
+                    }
+                }
+                a = warp_max(a);
+                n = warp_sum_int(n);
+                if (lane == 0) { s_pa[u][wu] = f2u(a); s_pn[u][wu] = n; }
+            }
+            __syncthreads();
+            if (have && nan) {
+                amax = u2f(max(s_pa[u][0], s_pa[u][1]));
+                nnz = s_pn[u][0] + s_pn[u][1];
+            }
+        }
+    }
+    const int elems = span_bytes / T::kBytesPerElem;
+    const float sf = scaling_factor(ss, 0.0f, amax);   // strategies 2 and 3 do not look at the tensor's amax
+    float* lut = reinterpret_cast<float*>(s_rows + (size_t)units * span_bytes) + u * 256;
+    if constexpr (!E8) {
+        if (have) fill_lut32(lut, sf, t, kRowsUnitThreads);
+        __syncthreads();
+    }
+    float total = 0.0f;
+    if (have) {
+        const bool zero_free = !nan && nnz == elems;
+        const bool short_ok = T::kBytesPerElem == 2 && !nan && !tiny && f2u(amax) < 0x6C800000u;   // all in [2^-90, 2^90)
+        const W* rw = reinterpret_cast<const W*>(row);
+        W* ow = reinterpret_cast<W*>(out + (unit0 + u) * span_bytes);
+        const int n_words = span_bytes / (int)sizeof(W);
+        auto run = [&](const auto& path, auto div_tag, auto nz_tag) {
+            constexpr int DIV = decltype(div_tag)::value;
+            constexpr bool NZ = decltype(nz_tag)::value;
+            float eh = 0.0f, el = 0.0f;
+#pragma unroll 4
+            for (int i = t; i < n_words; i += kRowsUnitThreads) {
+                float hi, lo, dh, dl, e_h, e_l;
+                PairWord<T>::unpack(rw[i], hi, lo);
+                err_pair<DIV, std::decay_t<decltype(path)>, NZ>(path, hi, lo, dh, dl, e_h, e_l);
+                eh = __fadd_rn(eh, e_h);
+                el = __fadd_rn(el, e_l);
+                __stcs(ow + i, PairWord<T>::pack(path, dh, dl));
+            }
+            total = warp_sum_ordered(__fadd_rn(eh, el));
+        };
+        auto dispatch = [&](const auto& path) {
+            constexpr int kShort = T::kBytesPerElem == 2 ? kDivBf16 : kDivIeee;
+            constexpr int kLong = T::kBytesPerElem == 2 ? kDivBf16Any : kDivIeee;
+            const bool s_ok = short_ok || T::kBytesPerElem != 2;
+            if (s_ok && zero_free) run(path, std::integral_constant<int, kShort>{}, std::true_type{});
+            else if (s_ok) run(path, std::integral_constant<int, kShort>{}, std::false_type{});
+            else run(path, std::integral_constant<int, kLong>{}, std::false_type{});
+        };
+        if constexpr (E8) dispatch(PathE8{e8_consts(sf)});
+        else dispatch(PathLut{lut, sf});
+        if (lane == 0) s_ps[u][wu] = total;
+    }
+    __syncthreads();
+    if (have && t == 0) block_err[unit0 + u] = __fadd_rn(s_ps[u][0], s_ps[u][1]);   // the reference's second tree: s0 + s1
+    if (tid == 0) {
+        uint32_t ca = 0u;
+        long long cn = 0;
+        for (int k = 0; k < n_here; ++k) { ca = max(ca, max(s_pa[k][0], s_pa[k][1])); cn += s_pn[k][0] + s_pn[k][1]; }
+        atomicMax(&ws->gamax_bits, ca);
+        if (cn) atomicAdd(&ws->gnnz, (unsigned long long)cn);
+    }
+}
+
+// ---------------------------------------------------------------------------------
 // 1 x k row groups with k < 128: flat traversal
 // ---------------------------------------------------------------------------------
 // A reference CTA covers 128 columns here, i.e. exactly one 16-byte vector per physical
@@ -591,10 +761,14 @@ __device__ __forceinline__ float lane_e8_segment(uint4 (&v)[8], const float (&up
     return __fadd_rn(__fadd_rn(e[0][0], e[0][2]), __fadd_rn(e[0][1], e[0][3]));   // t += t + 2, t += t + 1
 }
 
-template <int GVS, bool STORE>
+// SCAN: single pass (the scale of a group depends on the group's own amax only: ss_mode 2).  There is no
+// amax pass before this kernel, so it screens its own data for the short quotient chunk by chunk (every
+// non-zero magnitude inside [2^-90, 2^90), no NaN), and counts non-zero elements and tracks the largest
+// magnitude on the way: one atomicMax / atomicAdd per CTA publishes the tensor's amax and count.
+template <int GVS, bool STORE, bool SCAN = false>
 __global__ void __launch_bounds__(32 * kLaneWarps, 3)
 rowgroup_lane_e8_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, int64_t nvec, int ss,
-                        float* __restrict__ block_err, const ScalarsWs* __restrict__ ws,
+                        float* __restrict__ block_err, ScalarsWs* __restrict__ ws,
                         const float* __restrict__ ext_gamax, int skip_if_fallback) {
     if (skip_if_fallback && ws->fallback) return;
     extern __shared__ __align__(128) uint8_t s_ring[];  // [warp][stage][4 KiB]
@@ -604,34 +778,60 @@ rowgroup_lane_e8_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, i
     const int64_t n_warps = (int64_t)gridDim.x * kLaneWarps, gw = (int64_t)blockIdx.x * kLaneWarps + wid;
     WarpStream<kLaneStages, kLaneChunkVec * 16> stream;
     stream.start(s_ring + wid * (kLaneStages * kLaneChunkVec * 16), s_bar[wid], in, nvec * 16, gw, n_warps);
-    const float gamax = read_gamax(ws, ext_gamax);
-    const bool fastdiv = fast_div_ok<Bf16>(ws);
+    const float gamax = SCAN ? 0.0f : read_gamax(ws, ext_gamax);   // ss_mode 2 does not look at it
+    const bool fastdiv = SCAN ? false : fast_div_ok<Bf16>(ws);
     const int64_t n_chunks = (nvec + kLaneChunkVec - 1) / kLaneChunkVec;
     bool stored = false;
     int st = 0;
+    uint32_t seen_pat = 0u;   // SCAN: largest magnitude pattern of the chunks that took the short form
+    float seen_max = 0.0f;    //       and of the others (float compares, which skip NaNs as the reference does)
+    int seen_nnz = 0;
     for (int64_t c = gw; c < n_chunks; c += n_warps) {
         const int64_t v0 = c * kLaneChunkVec;
         const int nv = (int)(nvec - v0 < kLaneChunkVec ? nvec - v0 : kLaneChunkVec);  // a multiple of 16
         const bool staged = stream.acquire(st);
         uint4* chunk = reinterpret_cast<uint4*>(const_cast<uint8_t*>(stream.stage(st)));
         const bool mine = lane * 8 < nv;  // this lane's 128 bytes are inside the tensor
-        bool fast = staged && fastdiv;
+        bool fast = staged && (SCAN || fastdiv);
         uint4 v[8];
         float up[8], down[8];
         uint32_t zb[8];
         bool neg = false, has_zero = false;
+        uint32_t lane_pat = 0u;
+        int lane_nnz = 0;
         if (fast) {
             uint4* seg = chunk + lane * 8;
-            uint32_t pm[8], mn = 0xFFFFFFFFu;
+            uint32_t pm[8], mn = SCAN ? 0x7FFF7FFFu : 0xFFFFFFFFu;
+            int nnz4 = 0;
 #pragma unroll
             for (int p = 0; p < 8; ++p) {
                 v[p] = seg[p ^ sw];
                 const uint32_t m0 = mag2(v[p].x), m1 = mag2(v[p].y), m2 = mag2(v[p].z), m3 = mag2(v[p].w);
                 pm[p] = umax16x2_vec(m0, m1, m2, m3);
-                mn = umin16x2(mn, umin16x2(umin16x2(m0, m1), umin16x2(m2, m3)));
+                if constexpr (SCAN) {
+                    // m + 0x7FFF per half: bit 15 says "non-zero", and as a signed number it orders the non-zero
+                    // magnitudes below every zero: one packed minimum tracks the smallest non-zero magnitude
+                    const uint32_t s0 = m0 + 0x7FFF7FFFu, s1 = m1 + 0x7FFF7FFFu, s2 = m2 + 0x7FFF7FFFu, s3 = m3 + 0x7FFF7FFFu;
+                    mn = smin16x2_3(smin16x2_3(mn, s0, s1), s2, s3);
+                    nnz4 += __popc((top_bits_to_bytes(s0, s1) & 0x0F0F0F0Fu) | (top_bits_to_bytes(s2, s3) & 0xF0F0F0F0u));
+                } else {
+                    mn = umin16x2(mn, umin16x2(umin16x2(m0, m1), umin16x2(m2, m3)));
+                }
             }
-            has_zero = (mn & 0xFFFFu) == 0u || (mn >> 16) == 0u;
             bool ok = true;
+            if constexpr (SCAN) {
+                lane_nnz = nnz4 >> 2;
+                has_zero = lane_nnz < 64;
+                uint32_t all = pm[0];
+#pragma unroll
+                for (int p = 1; p < 8; ++p) all = umax16x2(all, pm[p]);
+                lane_pat = hmax_halves(all);
+                const uint32_t h0 = mn & 0xFFFFu, h1 = mn >> 16;   // a half with bit 15 set saw a non-zero magnitude
+                const bool tiny = ((h0 & 0x8000u) && (h0 & 0x7FFFu) < 0x127Fu) || ((h1 & 0x8000u) && (h1 & 0x7FFFu) < 0x127Fu);
+                ok = !tiny && lane_pat < 0x6C80u;                  // every non-zero magnitude in [2^-90, 2^90), no NaN
+            } else {
+                has_zero = (mn & 0xFFFFu) == 0u || (mn >> 16) == 0u;
+            }
 #pragma unroll
             for (int g = 0; g < NG; ++g) {
                 uint32_t m = pm[g * GV];
@@ -650,6 +850,9 @@ rowgroup_lane_e8_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, i
             fast = __all_sync(0xFFFFFFFFu, ok || !mine);
         }
         if (fast) {
+            if constexpr (SCAN) {
+                if (mine) { seen_pat = max(seen_pat, lane_pat); seen_nnz += lane_nnz; }
+            }
             neg = __any_sync(0xFFFFFFFFu, neg);
             has_zero = __any_sync(0xFFFFFFFFu, has_zero);
             float s;
@@ -680,6 +883,16 @@ rowgroup_lane_e8_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, i
                 const int64_t idx = v0 + r * 32 + lane;
                 const bool valid = idx < nvec;
                 const uint4 x = !valid ? zero : (staged ? chunk[r * 32 + lane] : ld_stream(in + idx));
+                if constexpr (SCAN) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        float hi, lo;
+                        Bf16::unpack(x, k, hi, lo);
+                        const float ah = fabsf(hi), al = fabsf(lo);
+                        seen_max = fmaxf(seen_max, fmaxf(ah, al));
+                        seen_nnz += (ah > 0.0f) + (al > 0.0f);
+                    }
+                }
                 rowgroup_small_vec<Bf16, true, STORE>(x, idx, valid, out, block_err, GV, ss, gamax, fastdiv);
             }
         }
@@ -690,6 +903,22 @@ rowgroup_lane_e8_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, i
     }
     if (STORE && lane == 0 && stored) bulk_wait_reads();
     stream.drain();
+    if constexpr (SCAN) {
+        __shared__ uint32_t s_a[kLaneWarps];
+        __shared__ int s_n[kLaneWarps];
+        const uint32_t a = __reduce_max_sync(0xFFFFFFFFu, max(seen_pat << 16, f2u(seen_max)));   // non-negative floats order like their bits
+        const int n = __reduce_add_sync(0xFFFFFFFFu, seen_nnz);
+        if (lane == 0) { s_a[wid] = a; s_n[wid] = n; }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            uint32_t ca = 0u;
+            long long cn = 0;
+#pragma unroll
+            for (int w = 0; w < kLaneWarps; ++w) { ca = max(ca, s_a[w]); cn += s_n[w]; }
+            atomicMax(&ws->gamax_bits, ca);
+            if (cn) atomicAdd(&ws->gnnz, (unsigned long long)cn);
+        }
+    }
 }
 
 
@@ -944,6 +1173,31 @@ int launch_block_t(const ScalingArgs& a, bool store, bool skip, cudaStream_t st)
 }
 
 template <typename T>
+int launch_rows_single_pass(const ScalingArgs& a, cudaStream_t st) {
+    if (a.brows != 1 || a.bcols < 128 || (a.ss_mode != 2 && a.ss_mode != 3)) return kErrUnsupportedShape;
+    const int64_t span = (int64_t)a.bcols * T::kBytesPerElem;       // a multiple of 256 bytes
+    if (span > 96 * 1024) return kErrUnsupportedShape;
+    const int64_t n_units = a.rows * (a.cols / a.bcols);
+    int units = (int)(32768 / span);
+    units = units < 1 ? 1 : (units > kRowsMaxUnits ? kRowsMaxUnits : units);
+    const int64_t grid = (n_units + units - 1) / units;
+    if (grid > 0x7FFFFFFF) return kErrTooLarge;
+    const int smem = (int)(units * span) + units * 1024;
+    auto* in = static_cast<const uint8_t*>(a.in);
+    auto* out = static_cast<uint8_t*>(a.out);
+#define MORB_ROWS(E)                                                                                                \
+    do {                                                                                                            \
+        static SmemOptIn opt;                                                                                       \
+        if (smem > 48 * 1024 && !opt(rows_single_pass_kernel<T, E>, 97 * 1024 + kRowsMaxUnits * 1024)) return kErrLaunch; \
+        rows_single_pass_kernel<T, E><<<(unsigned)grid, kRowsUnitThreads * units, smem, st>>>(                      \
+            in, out, n_units, (int)span, units, a.ss_mode, a.block_err, a.ws);                                      \
+    } while (0)
+    if (a.ss_mode == 2) MORB_ROWS(true); else MORB_ROWS(false);
+#undef MORB_ROWS
+    return check_launch();
+}
+
+template <typename T>
 int launch_rowgroup_t(const ScalingArgs& a, bool store, bool skip, cudaStream_t st) {
     constexpr int EPV = 16 / T::kBytesPerElem;
     const int span = a.bcols < 128 ? 128 : a.bcols;
@@ -973,26 +1227,31 @@ int launch_rowgroup_t(const ScalingArgs& a, bool store, bool skip, cudaStream_t 
                 int64_t g3 = (n_chunks + kLaneWarps * kChunksPerWarp - 1) / (kLaneWarps * kChunksPerWarp);
                 if (g3 > 0x7FFFFFFF) return kErrTooLarge;
                 if (g3 < 1) g3 = 1;
-#define MORB_LANE(G, S)                                                                                             \
+#define MORB_LANE(G, S, SC)                                                                                         \
     do {                                                                                                            \
         static SmemOptIn opt;                                                                                       \
-        if (!opt(rowgroup_lane_e8_kernel<G, S>, kRing)) return kErrLaunch;                                          \
-        rowgroup_lane_e8_kernel<G, S><<<(unsigned)g3, 32 * kLaneWarps, kRing, st>>>(                                \
+        if (!opt(rowgroup_lane_e8_kernel<G, S, SC>, kRing)) return kErrLaunch;                                      \
+        rowgroup_lane_e8_kernel<G, S, SC><<<(unsigned)g3, 32 * kLaneWarps, kRing, st>>>(                            \
             in, out, nvec, a.ss_mode, a.block_err, a.ws, a.ext_gamax, skip ? 1 : 0);                                \
     } while (0)
-#define MORB_LANE_G(S)                                                                                              \
+#define MORB_LANE_G(S, SC)                                                                                          \
     do {                                                                                                            \
-        if (group_lanes == 1) MORB_LANE(0, S);                                                                      \
-        else if (group_lanes == 2) MORB_LANE(1, S);                                                                 \
-        else if (group_lanes == 4) MORB_LANE(2, S);                                                                 \
-        else MORB_LANE(3, S);                                                                                       \
+        if (group_lanes == 1) MORB_LANE(0, S, SC);                                                                  \
+        else if (group_lanes == 2) MORB_LANE(1, S, SC);                                                             \
+        else if (group_lanes == 4) MORB_LANE(2, S, SC);                                                             \
+        else MORB_LANE(3, S, SC);                                                                                   \
     } while (0)
-                if (store) MORB_LANE_G(true); else MORB_LANE_G(false);
+                if (a.scan_blocks) {
+                    if (!store || skip) return kErrInvalidArgument;
+                    MORB_LANE_G(true, true);
+                }
+                else if (store) MORB_LANE_G(true, false); else MORB_LANE_G(false, false);
 #undef MORB_LANE_G
 #undef MORB_LANE
                 return check_launch();
             }
         }
+        if (a.scan_blocks) return kErrUnsupportedShape;   // single pass: the power-of-two lane kernel (above) and blocks of 128 columns and more
 #define MORB_SMALL(E, S) rowgroup_small_kernel<T, E, S><<<(unsigned)g2, 256, 0, st>>>(in, out, nvec, group_lanes, a.ss_mode, a.block_err, a.ws, a.ext_gamax, skip ? 1 : 0)
         if (mode == 2) { if (store) MORB_SMALL(true, true); else MORB_SMALL(true, false); }
         else { if (store) MORB_SMALL(false, true); else MORB_SMALL(false, false); }
@@ -1007,6 +1266,10 @@ int launch_rowgroup_t(const ScalingArgs& a, bool store, bool skip, cudaStream_t 
     if (grid > cap * (8 / wpc)) grid = cap * (8 / wpc);
     if (grid < 1) grid = 1;
     const int threads = 32 * wpc;
+    if (a.scan_blocks) {   // blocks of 128 columns and more: staged whole in shared memory
+        if (!store || skip) return kErrInvalidArgument;
+        return launch_rows_single_pass<T>(a, st);
+    }
 #define MORB_GO(M, S) rowgroup_err_cast_kernel<T, M, S><<<(unsigned)grid, threads, 0, st>>>(in, out, n_units, span / EPV, group_lanes, a.ss_mode, a.block_amax, a.block_err, a.ws, a.ext_gamax, skip ? 1 : 0)
     if (mode == 2) { if (store) MORB_GO(2, true); else MORB_GO(2, false); }
     else if (mode == 1) { if (store) MORB_GO(1, true); else MORB_GO(1, false); }

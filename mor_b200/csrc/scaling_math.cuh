@@ -172,5 +172,23 @@ __device__ __forceinline__ void err_vec_split(const P& path, const typename T::v
     }
 }
 
+// the pair of elements (2w, 2w + 1) as one word: 4 bytes of bf16, 8 bytes of binary32
+template <typename T> struct PairWord;
+template <> struct PairWord<Bf16> {
+    using type = uint32_t;
+    __device__ static __forceinline__ void unpack(uint32_t w, float& hi, float& lo) { hi = bf16_hi(w); lo = bf16_lo(w); }
+    template <typename P>
+    __device__ static __forceinline__ uint32_t pack(const P& path, float dh, float dl) {
+        if constexpr (PathTraits<P>::kExactBf16) return path.c.fast ? pack_bf16_trunc(dh, dl) : pack_bf16(dh, dl);
+        else return pack_bf16_round(dh, dl);
+    }
+};
+template <> struct PairWord<Fp32> {
+    using type = float2;
+    __device__ static __forceinline__ void unpack(float2 w, float& hi, float& lo) { hi = w.y; lo = w.x; }
+    template <typename P>
+    __device__ static __forceinline__ float2 pack(const P&, float dh, float dl) { return make_float2(dl, dh); }
+};
+
 }  // namespace
 }  // namespace morb

@@ -51,10 +51,18 @@ def shard_rows(rows: int, world_size: int, rank: int, multiple: int):
 
 @dataclass
 class ScalingResult:
-    meta: torch.Tensor          # int32[1]: 1 = E4M3 kept, 3 = tensor left as it was
+    meta: torch.Tensor          # int32[1]: 1 = E4M3 kept, 3 = tensor left as it was, -1 = a bounded wait ran out
     global_amax: torch.Tensor   # float32[1]
     global_nnz: torch.Tensor    # int64[1]
     global_error: torch.Tensor  # float32[1]
+    ready: Optional[torch.cuda.Event] = None   # set by a pipelined operator: see ShardedScaling(overlap=True)
+
+    def wait(self) -> "ScalingResult":
+        """Makes the current stream wait until the output tensor and these scalars are final (a no-op unless the
+        operator was built with ``overlap=True``)."""
+        if self.ready is not None:
+            torch.cuda.current_stream().wait_event(self.ready)
+        return self
 
 
 class CudaBackend:
@@ -216,6 +224,13 @@ class ShardedScaling:
     :func:`shard_rows` gives such a partition when the row count divides evenly.  The constructor is a
     collective call and raises ``ValueError`` on every rank when the slabs differ.
 
+    ``overlap=True`` pipelines consecutive calls: everything after the cast kernel (error exchange, ordered
+    sum, decision, conditional copy -- a chain of small latency-bound kernels) is enqueued on a second
+    stream, so that it runs under the amax pass of the NEXT call; two sets of scratch and scalar tensors
+    alternate between calls.  The output and the scalars of a call are then final once ``result.wait()``
+    (or a device synchronisation) has been passed, and the next call's cast waits for them by itself
+    before it writes ``out`` again.
+
     A call whose peer wait ran out reports ``meta == -1`` (its output is not valid): see :meth:`timed_out`.
     After that the ranks are no longer in step -- drop the object (``close()``) and build a new one on
     every rank before the next call.
@@ -223,7 +238,7 @@ class ShardedScaling:
 
     def __init__(self, rows_local: int, cols: int, brows: int, bcols: int, dtype: torch.dtype,
                  device: torch.device, kind: int = KIND_BLOCK, group: Optional[dist.ProcessGroup] = None,
-                 backend=None, exchange: str = "auto"):
+                 backend=None, exchange: str = "auto", overlap: bool = False):
         """``exchange``: "nccl" (two all-reduces and an all-gather), "p2p" (stores into peer-mapped
         buffers, :class:`PeerExchange`), or "auto": p2p with the CUDA backend on more than one rank when
         the peer buffers can be set up, NCCL otherwise.  The choice is made once, here, by all ranks
@@ -231,18 +246,18 @@ class ShardedScaling:
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.device = device
-        self.backend = backend if backend is not None else CudaBackend(kind, rows_local, cols, brows, bcols, dtype, device)
+        if overlap and backend is not None:
+            raise ValueError("overlap=True builds its own two CUDA backends")
+        n_sets = 2 if overlap else 1
+        self.backends = [backend if backend is not None else CudaBackend(kind, rows_local, cols, brows, bcols, dtype, device)
+                         for _ in range(n_sets)]
+        self.backend = self.backends[0]
         n_err = self.backend.n_err
         # both exchanges move fixed-size arrays: refuse slabs of different shapes before anything is stored
         check_same_on_every_rank((rows_local, cols, brows, bcols, n_err), "slab shape (rows, cols, block, error entries)", group)
-        self.amax = torch.zeros(1, dtype=torch.float32, device=device)
-        self.nnz = torch.zeros(1, dtype=torch.int64, device=device)
-        self.meta = torch.zeros(1, dtype=torch.int32, device=device)
-        self.gerr = torch.zeros(1, dtype=torch.float32, device=device)
-        self.all_err = torch.zeros(n_err * self.world, dtype=torch.float32, device=device)
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
-        self.local_err = self.all_err[self.rank * n_err:(self.rank + 1) * n_err]
         self.collectives = 0
+        self.calls = 0
         self.peer = None
         if exchange not in ("auto", "nccl", "p2p"):
             raise ValueError("exchange must be 'auto', 'nccl' or 'p2p'")
@@ -253,13 +268,30 @@ class ShardedScaling:
                 self.peer = None
                 if exchange == "p2p":
                     raise
-            if self.peer is None:
-                pass
-            else:
-                self.local_err = torch.zeros(n_err, dtype=torch.float32, device=device)
+        self.sets = []
+        for _ in range(n_sets):
+            all_err = torch.zeros(n_err * self.world, dtype=torch.float32, device=device)
+            local = (torch.zeros(n_err, dtype=torch.float32, device=device) if self.peer is not None
+                     else all_err[self.rank * n_err:(self.rank + 1) * n_err])
+            self.sets.append({"amax": torch.zeros(1, dtype=torch.float32, device=device),
+                              "nnz": torch.zeros(1, dtype=torch.int64, device=device),
+                              "meta": torch.zeros(1, dtype=torch.int32, device=device),
+                              "gerr": torch.zeros(1, dtype=torch.float32, device=device),
+                              "all_err": all_err, "local_err": local})
+        self.overlap = overlap
+        if overlap:
+            self.side = torch.cuda.Stream(device)
+            self.cast_done = [torch.cuda.Event() for _ in range(2)]
+            self.finished = [torch.cuda.Event() for _ in range(2)]
+
+    # the scalars and error sums of the most recent call
+    @property
+    def local_err(self):
+        return self.sets[(self.calls - 1) & (len(self.sets) - 1)]["local_err"] if self.calls else self.sets[0]["local_err"]
 
     def timed_out(self, result: ScalingResult) -> bool:
         """True if a bounded wait of the call that produced ``result`` ran out (synchronises on one int)."""
+        result.wait()
         return int(result.meta.item()) == -1
 
     def close(self) -> None:
@@ -268,35 +300,53 @@ class ShardedScaling:
             self.peer.close()
             self.peer = None
 
+    def _finish(self, b, s, x, out, threshold, ep):
+        """everything after the cast: error exchange, ordered sum and decision, conditional copy"""
+        if self.peer is not None:
+            ex = self.peer
+            b.exchange_errors(ex, ep, s["local_err"])
+            b.finalize_ptr(ex.error_ptr(ep), ex.world * ex.n_err, s["nnz"], threshold, s["meta"], s["gerr"])
+        else:
+            if self.world > 1:
+                dist.all_gather_into_tensor(s["all_err"], s["local_err"].clone(), group=self.group)
+                self._nnz_done.wait()
+                self.collectives += 1
+            b.finalize(s["all_err"], s["nnz"], threshold, s["meta"], s["gerr"])
+        b.fallback(x, out, s["meta"])
+
     def __call__(self, x: torch.Tensor, out: torch.Tensor, ss_mode: int, threshold: float) -> ScalingResult:
-        b = self.backend
+        i = self.calls & (len(self.sets) - 1)
+        b, s = self.backends[i], self.sets[i]
+        self.calls += 1
+        ep = 0
         if self.peer is not None:
             ex = self.peer
             ex.epoch += 1
             ep = ex.epoch
             b.amax_nnz_local(x)
-            b.exchange_scalars(ex, ep, self.amax, self.nnz)
-            b.cast(x, out, ss_mode, self.amax, self.local_err)
-            b.exchange_errors(ex, ep, self.local_err)
-            b.finalize_ptr(ex.error_ptr(ep), ex.world * ex.n_err, self.nnz, threshold, self.meta, self.gerr)
-            b.fallback(x, out, self.meta)
-            return ScalingResult(self.meta, self.amax, self.nnz, self.gerr)
-        b.amax_nnz(x, self.amax, self.nnz)
-        nnz_done = None
-        if self.world > 1:
-            # the cast needs the global amax only: the non-zero count is summed while the cast runs
-            amax_done = dist.all_reduce(self.amax, op=dist.ReduceOp.MAX, group=self.group, async_op=True)
-            nnz_done = dist.all_reduce(self.nnz, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
-            amax_done.wait()
-            self.collectives += 2
-        b.cast(x, out, ss_mode, self.amax, self.local_err)
-        if self.world > 1:
-            dist.all_gather_into_tensor(self.all_err, self.local_err.clone(), group=self.group)
-            nnz_done.wait()
-            self.collectives += 1
-        b.finalize(self.all_err, self.nnz, threshold, self.meta, self.gerr)
-        b.fallback(x, out, self.meta)
-        return ScalingResult(self.meta, self.amax, self.nnz, self.gerr)
+            b.exchange_scalars(ex, ep, s["amax"], s["nnz"])
+        else:
+            b.amax_nnz(x, s["amax"], s["nnz"])
+            if self.world > 1:
+                # the cast needs the global amax only: the non-zero count is summed while the cast runs
+                amax_done = dist.all_reduce(s["amax"], op=dist.ReduceOp.MAX, group=self.group, async_op=True)
+                self._nnz_done = dist.all_reduce(s["nnz"], op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+                amax_done.wait()
+                self.collectives += 2
+        if not self.overlap:
+            b.cast(x, out, ss_mode, s["amax"], s["local_err"])
+            self._finish(b, s, x, out, threshold, ep)
+            return ScalingResult(s["meta"], s["amax"], s["nnz"], s["gerr"])
+        main = torch.cuda.current_stream(self.device)
+        if self.calls >= 2:
+            main.wait_event(self.finished[1 - i])    # the previous call's decision and conditional copy, before `out` is written again
+        b.cast(x, out, ss_mode, s["amax"], s["local_err"])
+        self.cast_done[i].record(main)
+        self.side.wait_event(self.cast_done[i])
+        with torch.cuda.stream(self.side):
+            self._finish(b, s, x, out, threshold, ep)
+            self.finished[i].record(self.side)
+        return ScalingResult(s["meta"], s["amax"], s["nnz"], s["gerr"], ready=self.finished[i])
 
 
 class HostScaling:

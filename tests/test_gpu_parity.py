@@ -247,10 +247,22 @@ def test_fake_quantize_in_place(mode, sf):
     assert_same(H.fake_quantize(x, 128, 128, clamp, mode, sf, inplace=True), exp, f"in place mode {mode}")
 
 
+@pytest.fixture(params=[0, 1], ids=["single-pass", "two-pass"])
+def channel_passes(request):
+    """1 x k groups under strategies 2 and 3 run in one pass by default; mask 1 sends them through the amax
+    pass and the generic kernels, so that both are compared with the oracle on the same input."""
+    from mor_b200 import cabi
+    cabi.lib().mor_b200_debug_kernel_selection(request.param)
+    yield request.param
+    cabi.lib().mor_b200_debug_kernel_selection(0)
+
+
 @pytest.mark.parametrize("by", [8, 16, 32, 64, 128, 256, 512])
 @pytest.mark.parametrize("ss", [1, 2, 3, 4])
-def test_channel_scaling_row_groups(by, ss):
+def test_channel_scaling_row_groups(by, ss, channel_passes):
     import gpu_harness as H
+    if channel_passes and ss not in (2, 3):
+        pytest.skip("strategies 1 and 4 always run two passes")
     x = rand_bits(by * 10 + ss, 96, 512, "wide" if ss != 2 else "normal")
     for thr in (0.045, 3e38):
         oracle.clear_assert_flags()
@@ -264,7 +276,7 @@ def test_channel_scaling_row_groups(by, ss):
 @pytest.mark.parametrize("by", [8, 16, 32, 64])
 @pytest.mark.parametrize("kind", ["dense", "dense_large", "sparse_large", "tiny_rows"])
 @pytest.mark.parametrize("rows,cols", [(33, 384), (520, 640)])
-def test_channel_scaling_small_groups_power_of_two(by, kind, rows, cols):
+def test_channel_scaling_small_groups_power_of_two(by, kind, rows, cols, channel_passes):
     """1 x k groups with k < 128 and a power-of-two scale (ss_mode 2): tensors without zeros, groups whose
     amax exceeds the format maximum (scale below one), ragged ends (vector count 16 mod 32, partial chunks)."""
     import gpu_harness as H
@@ -290,7 +302,7 @@ def test_channel_scaling_small_groups_power_of_two(by, kind, rows, cols):
 @pytest.mark.parametrize("by", [2048, 4096, 8192])
 @pytest.mark.parametrize("ss", [1, 2, 3, 4])
 @pytest.mark.parametrize("kind", ["normal", "wide", "nan"])
-def test_channel_scaling_long_rows(by, ss, kind):
+def test_channel_scaling_long_rows(by, ss, kind, channel_passes):
     """1 x k blocks of 4 KiB and more: the amax pass streams every block through one warp's ring"""
     import gpu_harness as H
     if kind == "nan" and ss == 2:
@@ -621,6 +633,37 @@ def test_host_pipeline_matches_device_call():
         torch.cuda.synchronize()
         assert torch.equal(od.cpu().view(torch.int32), oh.view(torch.int32))
         assert sh[0].item() == r.global_amax.item() and sh[1].item() == r.global_error.item()
+
+
+def test_pipelined_calls_match_plain_calls():
+    """ShardedScaling(overlap=True): the post-cast chain of a call runs on a second stream under the next call's amax
+    pass, with two alternating sets of scratch; a different tensor in every call (one of them falls back to BF16),
+    one output buffer reused by every call"""
+    from mor_b200.sharded import ShardedScaling, KIND_BLOCK
+    dev = torch.device("cuda", 0)
+    rows, cols = 1024, 1024
+    piped = ShardedScaling(rows, cols, 128, 128, torch.float32, dev, KIND_BLOCK, overlap=True)
+    plain = ShardedScaling(rows, cols, 128, 128, torch.float32, dev, KIND_BLOCK)
+    g = torch.Generator().manual_seed(78)
+    xs = [torch.randn(rows, cols, generator=g) * (10.0 ** i) for i in range(6)]
+    xs[2] = xs[2] * 10.0 ** (torch.rand(rows, cols, generator=g) * 8 - 4)
+    xd = [x.to(dev) for x in xs]
+    out = torch.empty(rows, cols, device=dev)
+    kept, metas = [], []
+    for x in xd:
+        r = piped(x, out, 1, 0.045)
+        r.wait()                                           # the current stream waits; the host does not
+        kept.append((out.clone(), r.meta.clone(), r.global_amax.clone(), r.global_nnz.clone(), r.global_error.clone()))
+    torch.cuda.synchronize()
+    for x, k in zip(xd, kept):
+        o = torch.empty_like(x)
+        r = plain(x, o, 1, 0.045)
+        torch.cuda.synchronize()
+        assert torch.equal(o.view(torch.int32), k[0].view(torch.int32))
+        assert r.meta.item() == k[1].item() and r.global_nnz.item() == k[3].item()
+        assert r.global_amax.item() == k[2].item() and r.global_error.item() == k[4].item()
+        metas.append(r.meta.item())
+    assert set(metas) == {1, 3}
 
 
 def test_invalid_arguments_are_status_codes_not_faults():
