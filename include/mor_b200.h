@@ -189,6 +189,20 @@ MOR_B200_API int mor_b200_quantize_mx(const void* input, void* payload, void* sc
 MOR_B200_API int mor_b200_quantize_mx_fp6(const void* input, void* payload, void* scales, int64_t rows, int64_t cols,
                              int block_cols, void* stream);
 
+/* Extension (no counterpart in the reference, whose operators only fake-quantize; the scale is
+ * get_scaling_factor, fake_quantize.cu:1059-1093, the cast the one inside SQDD_fp32_scale, :310-316): the
+ * REAL quantized form of mor_b200_block_scaling / mor_b200_channel_scaling under a binary32 scale
+ * (ss_mode 1, 3 or 4).  payload: one E4M3 byte per element [rows, cols], 8-byte aligned, cols % 8 == 0;
+ * scales: one float per block [rows / block_rows, cols / block_cols] (k x 1 blocks: one per column of
+ * every row block).  element = decode(code) / scale -- the reference's division -- equals the
+ * fake-quantized value bit for bit; a zero element gets code 0.  amax_in (device, optional): amax of the
+ * whole tensor when `input` is a slab of it (row sharding), NULL to use this tensor's; amax_out
+ * (device, optional) receives the amax used.  Block shapes as for the two operators, except 1 x k groups
+ * of fewer than 128 columns.  Workspace: mor_b200_workspace_bytes of the matching operator. */
+MOR_B200_API int mor_b200_quantize_scaled(const void* input, void* payload, float* scales, int dtype, int64_t rows,
+                             int64_t cols, int block_rows, int block_cols, int ss_mode, const float* amax_in,
+                             float* amax_out, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- row-sharded pipeline (extension): the phases of block/channel scaling as separate
  * calls, so that a caller holding one row slab per GPU can all-reduce the amax (max)
  * and the non-zero count (sum) and all-gather the block errors between them. ---- */

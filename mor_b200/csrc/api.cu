@@ -373,6 +373,25 @@ int mor_b200_quantize_mx_fp6(const void* in, void* payload, void* scales, int64_
                               static_cast<cudaStream_t>(stream));
 }
 
+int mor_b200_quantize_scaled(const void* in, void* payload, float* scales, int dtype, int64_t rows, int64_t cols, int br,
+                             int bc, int ss, const float* amax_in, float* amax_out, void* wsp, size_t wsb, void* stream) {
+    if (!in || !payload || !scales || (dtype != MOR_B200_BF16 && dtype != MOR_B200_FP32)) return kErrInvalidArgument;
+    if (ss != 1 && ss != 3 && ss != 4) return kErrInvalidArgument;   // strategy 2 is a power of two: mor_b200_quantize_mx
+    const int kind = (br == 1 || bc == 1) ? MOR_B200_OP_CHANNEL_SCALING : MOR_B200_OP_BLOCK_SCALING;
+    const Geometry g = geometry(kind, rows, cols, br, bc, dtype);
+    if (g.status) return g.status;
+    if (g.n_amax == 0) return kErrUnsupportedShape;   // 1 x k groups below 128 columns keep no amax array
+    if (!aligned16(in) || (reinterpret_cast<uintptr_t>(payload) & 7u) || cols % 8) return kErrUnsupportedShape;
+    if (!wsp || wsb < ws_bytes_for(g) || !aligned16(wsp)) return kErrWorkspace;
+    auto st = static_cast<cudaStream_t>(stream);
+    auto* ws = static_cast<ScalarsWs*>(wsp);
+    float* block_amax = reinterpret_cast<float*>(static_cast<char*>(wsp) + kHead);
+    const int rc = phase_amax(kind, in, dtype, rows, cols, br, bc, g, ws, block_amax, st);
+    if (rc) return rc;
+    return launch_quantize_scaled(in, dtype == MOR_B200_FP32, static_cast<uint8_t*>(payload), scales, amax_out, rows, cols,
+                                  br, bc, ss, block_amax, g.n_amax, &ws->gamax_bits, amax_in, st);
+}
+
 int mor_b200_scaling_amax(int kind, const void* in, int dtype, int64_t rows, int64_t cols, int br, int bc,
                           float* amax_out, int64_t* nnz_out, void* wsp, size_t wsb, void* stream) {
     if (!in || (dtype != MOR_B200_BF16 && dtype != MOR_B200_FP32)) return kErrInvalidArgument;

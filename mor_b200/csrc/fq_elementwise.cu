@@ -180,7 +180,27 @@ __global__ void __launch_bounds__(kThreads) e8mx_cast_kernel(const uint4* __rest
         if (v != 0.0f) d = e8m_round<M>(v);
         return __fdiv_rn(d, s);
     };
-    auto word = [&](uint32_t w) -> uint32_t { return pack_bf16(one(bf16_hi(w)), one(bf16_lo(w))); };
+    auto slow_word = [&](uint32_t w) -> uint32_t { return pack_bf16(one(bf16_hi(w)), one(bf16_lo(w))); };
+    // Every step of `one` commutes with a power of two as long as nothing leaves the normal range (the product
+    // and the quotient are correctly rounded, the mantissa rounding keeps the exponent or raises it by one), and
+    // the result has the sign of the input: for an exponent field in [2, 251] the output pattern is the input
+    // pattern plus a small offset that depends on the seven mantissa bits only.  The 128 offsets are tabulated
+    // per CTA with the literal arithmetic; zeros give +0 as in the reference; anything else (subnormals, the top
+    // binades, Inf, NaN) takes the literal path.
+    __shared__ uint32_t s_off[128];   // offset + 256, so that the packed sum below never borrows
+    if (threadIdx.x < 128) {
+        const uint32_t pat = (127u << 7) | threadIdx.x;
+        s_off[threadIdx.x] = f32_to_bf16_bits(one(u2f(pat << 16))) + 256u - pat;
+    }
+    __syncthreads();
+    auto word = [&](uint32_t w) -> uint32_t {
+        const uint32_t m = mag2(w);
+        const uint32_t nz = (((m + 0x7FFF7FFFu) & 0x80008000u) >> 15) * 0xFFFFu;   // 0xFFFF in every non-zero half
+        const uint32_t mp = m | (~nz & 0x3F803F80u);                               // a zero half stands in as 1.0
+        if (umax16x2(mp, 0x01000100u) != mp || umin16x2(mp, 0x7DFF7DFFu) != mp) return slow_word(w);
+        const uint32_t off = s_off[mp & 0x7Fu] + (s_off[(mp >> 16) & 0x7Fu] << 16);
+        return ((mp + off - 0x01000100u) | (w & 0x80008000u)) & nz;
+    };
     for (int64_t i = gtid; i < nvec; i += stride * kUnroll) {
         uint4 v[kUnroll];
 #pragma unroll
@@ -198,6 +218,67 @@ __global__ void __launch_bounds__(kThreads) e8mx_cast_kernel(const uint4* __rest
         const uint32_t* tin = reinterpret_cast<const uint32_t*>(in + nvec);
         uint32_t* tout = reinterpret_cast<uint32_t*>(out + nvec);
         tout[gtid] = word(tin[gtid]);
+    }
+}
+
+// ---- real quantized output under binary32 scales (no reference operator; get_scaling_factor ref: 1059-1093,
+// the cast of SQDD_fp32_scale ref: 310-316) ----------------------------------------------------------
+// ref: 1059-1093 for strategies 1, 3 and 4; the block amax is floored at 1e-35
+__device__ __forceinline__ float payload_scale(int ss, float gamax, float bamax) {
+    if (bamax < 1e-35f) bamax = 1e-35f;
+    if (ss == 1) {
+        const uint32_t gman = f2u(__fdiv_rn(448.0f, gamax)) & 0x007FFFFFu;
+        const uint32_t bb = f2u(__fdiv_rn(448.0f, bamax));
+        const float adj = u2f((bb & 0xFF800000u) | gman);
+        return (gman <= (bb & 0x007FFFFFu)) ? adj : __fdiv_rn(adj, 2.0f);
+    }
+    if (ss == 3) return __fdiv_rn(448.0f, bamax);
+    return gamax > 0.0f ? __fdiv_rn(448.0f, gamax) : 1.0f;
+}
+__global__ void __launch_bounds__(kThreads) block_scales_kernel(const float* __restrict__ block_amax, int64_t n_blocks, int ss,
+                                                                const uint32_t* __restrict__ gamax_bits,
+                                                                const float* __restrict__ ext_gamax,
+                                                                float* __restrict__ scales, float* __restrict__ gamax_out) {
+    const float gamax = ext_gamax ? *ext_gamax : u2f(*gamax_bits);
+    const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (i < n_blocks) scales[i] = payload_scale(ss, gamax, fabsf(block_amax[i]));   // the sign bit of a stored amax is a flag
+    if (i == 0 && gamax_out) *gamax_out = gamax;
+}
+// One 16-byte vector of input per thread and step: E4M3 bytes of RN(x * scale), a zero element -> code 0.
+// The scale of an element is scales[(row / brows) * blocks_x + col / bcols]; a vector never straddles two
+// blocks unless bcols == 1 (one scale per column), where every element looks its own scale up.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) quantize_scaled_kernel(const typename T::vec_t* __restrict__ in,
+                                                                   uint8_t* __restrict__ payload,
+                                                                   const float* __restrict__ scales, int64_t nvec,
+                                                                   int64_t cols_vec, int brows, int bcols, int64_t blocks_x) {
+    constexpr int EPV = 16 / T::kBytesPerElem;
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < nvec; i += stride) {
+        const typename T::vec_t v = ld_stream(in + i);
+        const int64_t r = i / cols_vec, c0 = (i - r * cols_vec) * EPV;
+        const int64_t brow = (r / brows) * blocks_x;
+        uint32_t codes[EPV / 2];
+        const float s_all = bcols == 1 ? 0.0f : __ldg(scales + brow + c0 / bcols);
+#pragma unroll
+        for (int k = 0; k < T::kWordsPerVec; ++k) {
+            float hi, lo;
+            T::unpack(v, k, hi, lo);
+            const float sl = bcols == 1 ? __ldg(scales + brow + c0 + 2 * k) : s_all;
+            const float sh = bcols == 1 ? __ldg(scales + brow + c0 + 2 * k + 1) : s_all;
+            uint32_t c = cvt_codes<kE4M3>(__fmul_rn(hi, sh), __fmul_rn(lo, sl));
+            if (hi == 0.0f) c &= 0x00FFu;     // zeros (of either sign) are stored as +0
+            if (lo == 0.0f) c &= 0xFF00u;
+            codes[k] = c;                     // low byte: element 2k, high byte: element 2k + 1
+        }
+        if constexpr (EPV == 8) {
+            uint2 o;
+            o.x = codes[0] | (codes[1] << 16);
+            o.y = codes[2] | (codes[3] << 16);
+            *reinterpret_cast<uint2*>(payload + i * 8) = o;
+        } else {
+            *reinterpret_cast<uint32_t*>(payload + i * 4) = codes[0] | (codes[1] << 16);
+        }
     }
 }
 
@@ -255,6 +336,21 @@ int launch_copy(const void* in, void* out, int64_t n_bytes, int32_t* meta, int64
     const int g = grid_for(nvec > n_meta ? nvec : n_meta);
     copy_kernel<<<g, kThreads, 0, st>>>(static_cast<const uint4*>(in), static_cast<uint4*>(out), nvec, n_bytes % 16,
                                         meta, n_meta, meta_code);
+    return check_launch();
+}
+
+int launch_quantize_scaled(const void* in, int is_fp32, uint8_t* payload, float* scales, float* gamax_out, int64_t rows,
+                           int64_t cols, int brows, int bcols, int ss, const float* block_amax, int64_t n_blocks,
+                           const uint32_t* gamax_bits, const float* ext_gamax, cudaStream_t st) {
+    block_scales_kernel<<<(unsigned)((n_blocks + kThreads - 1) / kThreads), kThreads, 0, st>>>(block_amax, n_blocks, ss, gamax_bits,
+                                                                                                ext_gamax, scales, gamax_out);
+    int rc = check_launch();
+    if (rc) return rc;
+    const int epv = is_fp32 ? 4 : 8;
+    const int64_t nvec = rows * cols / epv, cols_vec = cols / epv, blocks_x = cols / bcols;
+    const int g = grid_for(nvec);
+    if (is_fp32) quantize_scaled_kernel<Fp32><<<g, kThreads, 0, st>>>(static_cast<const float4*>(in), payload, scales, nvec, cols_vec, brows, bcols, blocks_x);
+    else quantize_scaled_kernel<Bf16><<<g, kThreads, 0, st>>>(static_cast<const uint4*>(in), payload, scales, nvec, cols_vec, brows, bcols, blocks_x);
     return check_launch();
 }
 

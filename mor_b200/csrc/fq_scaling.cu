@@ -985,6 +985,135 @@ colgroup_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::v
     }
 }
 
+// The same CTA as real threads, fed by TMA: thread (tx, ty) of 32 x 16 owns word tx (columns 2 tx and 2 tx + 1,
+// each with its own scale) of rows ty, ty + 16, ... of a strip of 64 columns.  Boxes of 64 columns x 64 (or 16)
+// rows travel through a ring of four shared-memory stages: one mbarrier per stage says "full" (the copy has
+// landed), one says "empty" (all sixteen warps are done with it) and lets thread 0 request the box four ahead.
+// Binary32 scales use one table of quotients per column (64 x 256 entries, filled once per CTA).
+constexpr int kColStages = 4, kColThreads = 512;
+template <typename T> struct ColStrip {
+    static constexpr int kRowBytes = 64 * T::kBytesPerElem;           // 128 / 256
+    static constexpr int kMaxBoxRows = 64;
+    static constexpr int kRingBytes = kColStages * kMaxBoxRows * kRowBytes;
+    static constexpr int kLutBytes = 64 * 256 * 4;
+};
+
+template <typename T, bool E8, bool STORE>
+__global__ void __launch_bounds__(kColThreads)
+colstrip_tma_kernel(const __grid_constant__ CUtensorMap tmap, void* __restrict__ out_raw, int64_t cols, int brows,
+                    int box_rows, int ss, const float* __restrict__ block_amax, float* __restrict__ block_err,
+                    ScalarsWs* __restrict__ ws, const float* __restrict__ ext_gamax, int skip_if_fallback) {
+    using W = typename PairWord<T>::type;
+    using CS = ColStrip<T>;
+    constexpr int kDiv = (T::kBytesPerElem == 2) ? kDivBf16Any : kDivIeee;   // the column amax pass does not screen magnitudes
+    if (skip_if_fallback && ws->fallback) return;
+    extern __shared__ __align__(128) uint8_t s_col[];   // ring of stages, then the tables
+    __shared__ __align__(8) uint64_t s_full[kColStages], s_empty[kColStages];
+    __shared__ float s_sf[64];
+    __shared__ float s_wsum[32];
+    float* s_lut = reinterpret_cast<float*>(s_col + CS::kRingBytes);
+    const int tid = threadIdx.x, tx = tid & 31, ty = tid >> 5;
+    const int64_t ctas_x = cols / 64;
+    const int64_t rb = blockIdx.x / ctas_x, cx = blockIdx.x % ctas_x;
+    const int n_boxes = brows / box_rows, rounds = box_rows / 16;
+    const uint32_t box_bytes = (uint32_t)box_rows * CS::kRowBytes;
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < kColStages; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], kColThreads / 32); }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        for (int b = 0; b < kColStages && b < n_boxes; ++b) {
+            mbar_expect_tx(&s_full[b], box_bytes);
+            tma_load_2d(s_col + b * (CS::kMaxBoxRows * CS::kRowBytes), &tmap, (int)(cx * 64), (int)(rb * brows + (int64_t)b * box_rows), &s_full[b]);
+        }
+    }
+    // the scales of the strip's 64 columns (and their tables), while the first boxes travel
+    const float gamax = read_gamax(ws, ext_gamax);
+    if (tid < 64) s_sf[tid] = scaling_factor(ss, gamax, block_amax[rb * cols + cx * 64 + tid]);
+    if (tid < 32) s_wsum[tid] = 0.0f;
+    __syncthreads();
+    if constexpr (!E8) {
+        for (int i = tid; i < 64 * 256; i += kColThreads)
+            s_lut[i] = canon_nan(__fdiv_rn(h_lo_to_f32(codes_to_h2<kE4M3>((uint32_t)(i & 255))), s_sf[i >> 8]));
+        __syncthreads();
+    }
+    const float sfl = s_sf[2 * tx], sfh = s_sf[2 * tx + 1];
+    const E8Consts cl = e8_consts(sfl), ch = e8_consts(sfh);
+    const float* lut_l = s_lut + (2 * tx) * 256;
+    const float* lut_h = lut_l + 256;
+    W* out = static_cast<W*>(out_raw) + (rb * brows + ty) * (cols / 2) + cx * 32 + tx;
+    const int64_t out_step = 16 * (cols / 2);
+    float eh = 0.0f, el = 0.0f;
+    bool ok = true;
+    for (int b = 0; b < n_boxes; ++b) {
+        const int s = b % kColStages;
+        const uint32_t parity = (uint32_t)(b / kColStages) & 1u;
+        if (!__all_sync(0xFFFFFFFFu, mbar_wait_bounded(&s_full[s], parity))) { ok = false; break; }
+        const W* stage = reinterpret_cast<const W*>(s_col + s * (CS::kMaxBoxRows * CS::kRowBytes));
+        for (int r = 0; r < rounds; ++r) {
+            float hi, lo, dh, dl;
+            PairWord<T>::unpack(stage[(ty + 16 * r) * 32 + tx], hi, lo);
+            if constexpr (E8) {
+                // the two halves of a word belong to different columns, hence different scales
+                float th, tl, uh, ul;
+                sqdd_e8_pair_auto<kE4M3>(hi, hi, ch, dh, th);
+                sqdd_e8_pair_auto<kE4M3>(lo, lo, cl, ul, dl);
+                (void)th; (void)tl; (void)uh; (void)ul;
+            } else {
+                const uint32_t c = cvt_codes<kE4M3>(__fmul_rn(hi, sfh), __fmul_rn(lo, sfl));
+                dh = lut_h[c >> 8];
+                dl = lut_l[c & 0xFFu];
+            }
+            const bool zh = hi == 0.0f, zl = lo == 0.0f;
+            float e_h, e_l;
+            if constexpr (kDiv == kDivBf16Any) {
+                e_h = fabsf(div_by_bf16_any(__fsub_rn(dh, hi), hi));
+                e_l = fabsf(div_by_bf16_any(__fsub_rn(dl, lo), lo));
+            } else {
+                e_h = fabsf(__fdiv_rn(__fsub_rn(dh, hi), zh ? 1.0f : hi));
+                e_l = fabsf(__fdiv_rn(__fsub_rn(dl, lo), zl ? 1.0f : lo));
+            }
+            eh = __fadd_rn(eh, zh ? 0.0f : e_h);
+            el = __fadd_rn(el, zl ? 0.0f : e_l);
+            if constexpr (STORE) {
+                dh = zh ? 0.0f : dh;
+                dl = zl ? 0.0f : dl;
+                W w;
+                if constexpr (T::kBytesPerElem == 2) w = pack_bf16(dh, dl);
+                else w = make_float2(dl, dh);
+                __stcs(out, w);
+            }
+            out += out_step;
+        }
+        __syncwarp();
+        if (tx == 0) mbar_arrive(&s_empty[s]);
+        if (tid == 0 && b + kColStages < n_boxes) {
+            if (!mbar_wait_bounded(&s_empty[s], parity)) { ok = false; }
+            else {
+                mbar_expect_tx(&s_full[s], box_bytes);
+                tma_load_2d(s_col + s * (CS::kMaxBoxRows * CS::kRowBytes), &tmap, (int)(cx * 64),
+                            (int)(rb * brows + (int64_t)(b + kColStages) * box_rows), &s_full[s]);
+            }
+        }
+        ok = __shfl_sync(0xFFFFFFFFu, (int)ok, 0) != 0 || ty != 0 ? ok : false;
+    }
+    if (__syncthreads_or(!ok)) {
+        // a copy (or the other warps) did not show up within the bounded wait: flag the call -- the decision kernel
+        // reports meta = -1 -- and give copies still in flight a last bounded chance before the shared memory goes
+        if (tid == 0) atomicOr(&ws->load_timeout, 1u);
+        for (int s = 0; s < kColStages; ++s) { mbar_wait_bounded(&s_full[s], 0); mbar_wait_bounded(&s_full[s], 1); }
+        return;
+    }
+    const float sum = warp_sum_ordered(__fadd_rn(eh, el));
+    if (tx == 0) s_wsum[ty] = sum;
+    __syncthreads();
+    if (tid < 32) {
+        const float t = warp_sum_ordered(s_wsum[tid]);
+        if (tid == 0) block_err[blockIdx.x] = t;
+    }
+}
+
 // ---------------------------------------------------------------------------------
 // ordered tensor-level error sum + decision (ref: 1178-1241)
 // ---------------------------------------------------------------------------------
@@ -1283,6 +1412,26 @@ int launch_colgroup_t(const ScalingArgs& a, bool store, bool skip, cudaStream_t 
     const int64_t n_cta = (a.rows / a.brows) * (a.cols / 64);
     if (n_cta > 0x7FFFFFFF) return kErrTooLarge;
     const bool e8 = a.ss_mode == 2;
+    CUtensorMap map;
+    const int box_rows = a.brows % 64 == 0 ? 64 : 16;
+    if (!force_generic() && a.rows < (int64_t(1) << 31) && a.cols < (int64_t(1) << 31) &&
+        make_tile_map(&map, a.in, a.rows, a.cols, T::kBytesPerElem, 64, box_rows)) {
+        using CS = ColStrip<T>;
+        const int smem = CS::kRingBytes + (e8 ? 0 : CS::kLutBytes);
+#define MORB_COL(E, S)                                                                                              \
+    do {                                                                                                            \
+        static SmemOptIn opt;                                                                                       \
+        if (!opt(colstrip_tma_kernel<T, E, S>, CS::kRingBytes + CS::kLutBytes)) return kErrLaunch;                   \
+        colstrip_tma_kernel<T, E, S><<<(unsigned)n_cta, kColThreads, smem, st>>>(                                   \
+            map, a.out, a.cols, a.brows, box_rows, a.ss_mode, a.block_amax, a.block_err, a.ws, a.ext_gamax, skip ? 1 : 0); \
+    } while (0)
+        if (e8 && store) MORB_COL(true, true);
+        else if (e8) MORB_COL(true, false);
+        else if (store) MORB_COL(false, true);
+        else MORB_COL(false, false);
+#undef MORB_COL
+        return check_launch();
+    }
     auto* in = static_cast<const typename T::vec_t*>(a.in);
     auto* out = static_cast<typename T::vec_t*>(a.out);
     constexpr int TH = 512 / T::kWordsPerVec;

@@ -39,6 +39,10 @@ int launch_cast_uniform(const void* in, void* out, int64_t n_elems, int fmt, int
                         int32_t* meta, int64_t n_meta, int32_t meta_code, cudaStream_t st);
 int launch_copy(const void* in, void* out, int64_t n_bytes, int32_t* meta, int64_t n_meta, int32_t meta_code,
                 cudaStream_t st);
+// E4M3 bytes + one binary32 scale per block (strategies 1, 3, 4), from the block amax left by launch_amax_nnz_blocks
+int launch_quantize_scaled(const void* in, int is_fp32, uint8_t* payload, float* scales, float* gamax_out, int64_t rows,
+                           int64_t cols, int brows, int bcols, int ss, const float* block_amax, int64_t n_blocks,
+                           const uint32_t* gamax_bits, const float* ext_gamax, cudaStream_t st);
 // test operators (ref: 854-875), binary32 in/out
 int launch_quant_dequant(const float* in, float* out, int64_t n, int fmt, cudaStream_t st);
 int launch_e4m3_e8_scale(const float* in, float* out, int64_t n, int rne, cudaStream_t st);

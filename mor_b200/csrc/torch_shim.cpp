@@ -280,6 +280,27 @@ std::vector<at::Tensor> quantize_mx_fp6(const at::Tensor& input, int64_t rows, i
     return {payload, scales};
 }
 
+// returns [payload uint8 [dim_x, dim_y] (E4M3 bytes), scales float32 [dim_x / block_x, dim_y / block_y], global_amax float32[1]]
+std::vector<at::Tensor> quantize_scaled(const at::Tensor& input, int64_t rows, int64_t cols, int64_t br, int64_t bc,
+                                        int64_t ss) {
+    const c10::cuda::CUDAGuard guard(input.device());
+    at::Tensor in = checked_input(input, rows, cols, "quantize_scaled");
+    const int dt = dtype_code(in, true, "quantize_scaled");
+    TORCH_CHECK(ss == 1 || ss == 3 || ss == 4, "mor::quantize_scaled: ss_mode must be 1, 3 or 4 (binary32 scales)");
+    TORCH_CHECK(br > 0 && bc > 0 && rows % br == 0 && cols % bc == 0, "mor::quantize_scaled: block shape must divide the tensor");
+    const int op = (br == 1 || bc == 1) ? MOR_B200_OP_CHANNEL_SCALING : MOR_B200_OP_BLOCK_SCALING;
+    const size_t wsb = mor_b200_workspace_bytes(op, rows, cols, (int)br, (int)bc);
+    TORCH_CHECK(wsb > 0, "mor::quantize_scaled: unsupported block shape ", br, " x ", bc);
+    at::Tensor ws = workspace(in, wsb);
+    at::Tensor payload = torch::empty({rows, cols}, in.options().dtype(torch::kUInt8));
+    at::Tensor scales = torch::empty({rows / br, cols / bc}, in.options().dtype(torch::kFloat));
+    at::Tensor gamax = torch::empty({1}, in.options().dtype(torch::kFloat));
+    check_status(mor_b200_quantize_scaled(in.data_ptr(), payload.data_ptr(), scales.data_ptr<float>(), dt, rows, cols, (int)br,
+                                          (int)bc, (int)ss, nullptr, gamax.data_ptr<float>(), ws.data_ptr(), wsb, cur_stream()),
+                 "quantize_scaled");
+    return {payload, scales, gamax};
+}
+
 }  // namespace
 
 // Registers _C as a Python extension module.
@@ -305,6 +326,7 @@ TORCH_LIBRARY(mor, m) {
   m.def("fake_quantize_mx(Tensor input, int dim_x, int dim_y, int block_y, int elem_format, int sf_type) -> Tensor[]");
   m.def("quantize_mx(Tensor input, int dim_x, int dim_y, int block_y, int elem_format) -> Tensor[]");
   m.def("quantize_mx_fp6(Tensor input, int dim_x, int dim_y, int block_y) -> Tensor[]");
+  m.def("quantize_scaled(Tensor input, int dim_x, int dim_y, int block_x, int block_y, int ss_mode) -> Tensor[]");
   m.def("fake_quantize_block_scaling_delayed(Tensor input, int dim_x, int dim_y, int block_x, int block_y, float e4m3_threshold, int ss_mode, Tensor amax_in) -> Tensor[]");
 }
 
@@ -326,6 +348,7 @@ TORCH_LIBRARY_IMPL(mor, CUDA, m) {
   m.impl("fake_quantize_mx", &fake_quantize_mx);
   m.impl("quantize_mx", &quantize_mx);
   m.impl("quantize_mx_fp6", &quantize_mx_fp6);
+  m.impl("quantize_scaled", &quantize_scaled);
   m.impl("fake_quantize_block_scaling_delayed", &fake_quantize_block_scaling_delayed);
 }
 

@@ -26,6 +26,7 @@ __all__ = [
     "fake_quantize_mx",
     "quantize_mx",
     "quantize_mx_fp6",
+    "quantize_scaled",
     "fake_quantize_block_scaling_delayed",
 ]
 
@@ -154,6 +155,14 @@ def quantize_mx_fp6(a: Tensor, dim_x: int, dim_y: int, block_y: int) -> List[Ten
     """:func:`quantize_mx` for E2M3 with the codes packed six bits each: ``payload`` is ``uint8 [dim_x, dim_y * 3 / 4]``,
     every run of eight elements a little-endian 48-bit group with code i in bits [6 i, 6 i + 6)."""
     return _ops.quantize_mx_fp6.default(a, dim_x, dim_y, block_y)
+
+
+def quantize_scaled(a: Tensor, dim_x: int, dim_y: int, block_x: int, block_y: int, ss_mode: int) -> List[Tensor]:
+    """The real quantized form of :func:`fake_quantize_block_scaling` / :func:`fake_quantize_channel_scaling` under a
+    float scale (``ss_mode`` 1, 3 or 4): returns ``[payload, scales, global_amax]`` -- one E4M3 byte per element
+    (``uint8 [dim_x, dim_y]``, viewable as ``torch.float8_e4m3fn``), one ``float32`` scale per block
+    (``[dim_x // block_x, dim_y // block_y]``) and the tensor's amax; ``element = decode(code) / scale``.  No gradient."""
+    return _ops.quantize_scaled.default(a, dim_x, dim_y, block_x, block_y, ss_mode)
 
 
 # --------------------------------------------------------------------------- straight-through backward

@@ -69,6 +69,8 @@ def lib() -> C.CDLL:
         L.mor_o_amax_nnz.argtypes = [vp, i32, i64, vp, vp]
         L.mor_o_quantize_mx.argtypes = [vp, vp, vp, i64, i64, i32, i32]
         L.mor_o_dequantize_mx.argtypes = [vp, vp, vp, i64, i64, i32, i32]
+        L.mor_o_quantize_scaled.argtypes = [vp, i32, vp, vp, i64, i64, i32, i32, i32, vp, vp]
+        L.mor_o_dequantize_scaled.argtypes = [vp, vp, vp, i32, i64, i64, i32, i32]
         L.mor_o_finalize.restype = f32
         L.mor_o_finalize.argtypes = [vp, i64, i32, i64, dbl, vp]
         L.mor_o_num_threads.restype = i32
@@ -234,6 +236,33 @@ def dequantize_mx(payload, scales, bcols, fmt):
     rows, cols = payload.shape
     out = np.zeros((rows, cols), np.uint16)
     _rc(lib().mor_o_dequantize_mx(_p(payload), _p(scales), _p(out), rows, cols, bcols, fmt), "dequantize_mx")
+    return out
+
+
+def quantize_scaled(x, brows, bcols, ss, global_amax=None):
+    """Real quantized form of block / channel scaling under a binary32 scale (ss_mode 1, 3 or 4): (E4M3 bytes
+    uint8 [rows, cols], scales float32 [rows // brows, cols // bcols], global_amax);
+    element = decode(code) / scale."""
+    x = np.ascontiguousarray(x)
+    is_f32 = _check_in(x)
+    rows, cols = x.shape
+    payload = np.zeros((rows, cols), np.uint8)
+    scales = np.zeros((rows // brows, cols // bcols), np.float32)
+    ext = None if global_amax is None else np.array([global_amax], np.float32)
+    gamax = np.zeros(1, np.float32)
+    _rc(lib().mor_o_quantize_scaled(_p(x), is_f32, _p(payload), _p(scales), rows, cols, brows, bcols, ss, _p(ext),
+                                    _p(gamax)), "quantize_scaled")
+    return payload, scales, gamax[0]
+
+
+def dequantize_scaled(payload, scales, brows, bcols, float32=False):
+    """decode(code) / scale as bf16 bits (uint16) or float32, rounded as the fake-quantize operators round"""
+    payload = np.ascontiguousarray(payload, dtype=np.uint8)
+    scales = np.ascontiguousarray(scales, dtype=np.float32)
+    rows, cols = payload.shape
+    out = np.zeros((rows, cols), np.float32 if float32 else np.uint16)
+    _rc(lib().mor_o_dequantize_scaled(_p(payload), _p(scales), _p(out), int(float32), rows, cols, brows, bcols),
+        "dequantize_scaled")
     return out
 
 

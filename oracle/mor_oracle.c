@@ -931,6 +931,63 @@ MOR_O_API int mor_o_dequantize_mx(const uint8_t *payload, const uint8_t *scales,
     return 0;
 }
 
+/* Extension (no reference operator): the REAL quantized form of fake_quantize_block_scaling /
+ * _channel_scaling under a binary32 scale (strategies 1, 3 and 4; ref: get_scaling_factor 1059-1093, the
+ * cast inside SQDD_fp32_scale 310-316): payload[i] is the E4M3 byte of RN_e4m3(x * scale), scales[b] the
+ * binary32 scale of block b (blocks of brows x bcols in row-major block order; brows x 1 blocks give one
+ * scale per column of every row block), and element = decode(code) / scale -- the division the reference
+ * applies -- is the fake-quantized value.  A zero element gets code 0 (the reference writes zeros back as
+ * +0).  ext_global_amax: amax of the whole tensor when `in` is a slab of it, else NULL. */
+MOR_O_API int mor_o_quantize_scaled(const void *in, int is_fp32, uint8_t *payload, float *scales, int64_t rows,
+                                    int64_t cols, int brows, int bcols, int ss, const float *ext_global_amax,
+                                    float *global_amax_out) {
+    if (rows <= 0 || cols <= 0 || brows <= 0 || bcols <= 0 || rows % brows || cols % bcols) return -1;
+    if (!(ss == 1 || ss == 3 || ss == 4)) return -1;
+    io_t io = {in, NULL, is_fp32};
+    const int64_t gx = cols / bcols, gy = rows / brows, nb = gx * gy;
+    float *bamax = (float *)malloc(sizeof(float) * (size_t)nb);
+    float gamax = -FLT_MAX;
+#pragma omp parallel for reduction(max : gamax)
+    for (int64_t b = 0; b < nb; ++b) {
+        const int64_t r0 = (b / gx) * brows, c0 = (b % gx) * bcols;
+        float a = -INFINITY;
+        for (int64_t r = r0; r < r0 + brows; ++r)
+            for (int64_t c = c0; c < c0 + bcols; ++c) a = fmaxf(a, fabsf(load_elem(&io, r * cols + c)));
+        bamax[b] = a;
+        gamax = fmaxf(gamax, a);
+    }
+    if (ext_global_amax) gamax = *ext_global_amax;
+    if (global_amax_out) *global_amax_out = gamax;
+#pragma omp parallel for schedule(static)
+    for (int64_t b = 0; b < nb; ++b) {
+        const int64_t r0 = (b / gx) * brows, c0 = (b % gx) * bcols;
+        const float sf = mor_o_scaling_factor(ss, gamax, bamax[b]);
+        scales[b] = sf;
+        for (int64_t r = r0; r < r0 + brows; ++r)
+            for (int64_t c = c0; c < c0 + bcols; ++c) {
+                const float x = load_elem(&io, r * cols + c);
+                volatile float xs = x * sf;
+                payload[r * cols + c] = (x == 0.0f) ? 0 : encode_narrow(quant_dequant(xs, FMT_E4M3, 1), FMT_E4M3);
+            }
+    }
+    free(bamax);
+    return 0;
+}
+/* decode(code) / scale, rounded to the output type as the fake-quantize operators round it */
+MOR_O_API int mor_o_dequantize_scaled(const uint8_t *payload, const float *scales, void *out, int out_is_fp32,
+                                      int64_t rows, int64_t cols, int brows, int bcols) {
+    if (rows <= 0 || cols <= 0 || brows <= 0 || bcols <= 0 || rows % brows || cols % bcols) return -1;
+    io_t io = {NULL, out, out_is_fp32};
+    const int64_t gx = cols / bcols, n = rows * cols;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) {
+        const int64_t b = ((i / cols) / brows) * gx + (i % cols) / bcols;
+        volatile float v = decode_narrow(payload[i], FMT_E4M3) / scales[b];
+        store_elem(&io, i, v);
+    }
+    return 0;
+}
+
 /* amax + non-zero count of a row slab (phase 1 of the row-sharded pipeline) */
 MOR_O_API int mor_o_amax_nnz(const void *in, int is_fp32, int64_t n, float *amax_out, int64_t *nnz_out) {
     io_t io = {in, NULL, is_fp32};

@@ -156,6 +156,23 @@ def quantize_mx_fp6(x, by):
     return {"payload": payload.cpu().numpy(), "scales": scales.cpu().numpy()}
 
 
+def quantize_scaled(x, bx, by, ss, amax_in=None):
+    rows, cols = x.shape
+    d = to_dev(x)
+    op = cabi.OP_CHANNEL_SCALING if (bx == 1 or by == 1) else cabi.OP_BLOCK_SCALING
+    wsb = cabi.workspace_bytes(op, rows, cols, bx, by)
+    assert wsb > 0, "unsupported shape"
+    ws = torch.empty(wsb, dtype=torch.uint8, device="cuda")
+    payload = torch.zeros(rows, cols, dtype=torch.uint8, device="cuda")
+    scales = torch.zeros(rows // bx, cols // by, dtype=torch.float32, device="cuda")
+    gamax = torch.zeros(1, dtype=torch.float32, device="cuda")
+    ain = None if amax_in is None else torch.tensor([amax_in], dtype=torch.float32, device="cuda")
+    cabi.call("mor_b200_quantize_scaled", d.data_ptr(), payload.data_ptr(), scales.data_ptr(), dtype_of(x), rows, cols, bx, by,
+              ss, None if ain is None else ain.data_ptr(), gamax.data_ptr(), ws.data_ptr(), wsb, stream())
+    torch.cuda.synchronize()
+    return {"payload": payload.cpu().numpy(), "scales": scales.cpu().numpy(), "gamax": float(gamax.item())}
+
+
 _FMT = {"quant_dequant_e4m3": cabi.E4M3, "quant_dequant_e5m2": cabi.E5M2, "quant_dequant_e3m2": cabi.E3M2,
         "quant_dequant_e2m3": cabi.E2M3}
 

@@ -191,6 +191,26 @@ def test_config4_block_scaling_delayed(c4):
     assert f32_bits(got["gamax"]) == f32_bits(amax)
 
 
+def test_config4_quantize_scaled_round_trip(c4):
+    """real quantized form at full size: decode(code) / scale equals the fake-quantized tensor"""
+    import gpu_harness as H
+    got = H.quantize_scaled(c4, 128, 128, 1)
+    payload, scales, gamax = oracle.quantize_scaled(c4, 128, 128, 1)
+    same_bytes(got["payload"], payload, "config 4, quantize_scaled codes")
+    same_bytes(got["scales"], scales, "config 4, quantize_scaled scales")
+    fq = H.block_scaling(c4, 128, 128, BIG, 1)
+    same_bytes(oracle.dequantize_scaled(got["payload"], got["scales"], 128, 128), fq["out"], "config 4, decode / scale")
+
+
+def test_config2_quantize_scaled_per_row(c2):
+    import gpu_harness as H
+    rows, cols = c2.shape
+    got = H.quantize_scaled(c2, 1, cols, 3)
+    payload, scales, _ = oracle.quantize_scaled(c2, 1, cols, 3)
+    same_bytes(got["payload"], payload, "config 2, per-row codes")
+    same_bytes(got["scales"], scales, "config 2, per-row scales")
+
+
 # ------------------------------------------------------------------ configuration 5
 @pytest.mark.parametrize("ss", [1, 4])
 def test_config5_first_slab(ss):

@@ -143,6 +143,26 @@ def test_group_scaled_with_nan_and_inf_elements(by):
     assert torch.zeros(1, device="cuda").item() == 0.0
 
 
+@pytest.mark.parametrize("qtype", [1, 2, 3])
+@pytest.mark.parametrize("strategy", [0, 1])
+@pytest.mark.parametrize("top", [0x7F7F, 0x4680, 0x3F80, 0x0200])
+def test_e8mx_every_bf16_pattern(qtype, strategy, top):
+    """E8Mx on every finite bf16 pattern up to a largest magnitude `top` (which sets the tensor scale under strategy 1):
+    the tabulated offsets of the fast path, the literal path at both ends of the exponent range, zeros of both signs"""
+    import gpu_harness as H
+    mags = np.arange(0, top + 1, dtype=np.uint32)
+    pats = np.concatenate([mags, mags | 0x8000]).astype(np.uint16)
+    pad = (-pats.size) % 512
+    x = np.concatenate([pats, np.zeros(pad, np.uint16)]).reshape(-1, 512)
+    oracle.clear_assert_flags()
+    exp, _ = oracle.e8mx(x, qtype, strategy)
+    if oracle.assert_flags():
+        pytest.skip("the reference asserts on this input")
+    got = H.e8mx(x, qtype, strategy)["out"]
+    bad = np.nonzero(got.reshape(-1) != exp.reshape(-1))[0]
+    assert bad.size == 0, f"e8m{qtype} strategy {strategy}: {bad.size} differ, e.g. in {x.reshape(-1)[bad[:5]]} got {got.reshape(-1)[bad[:5]]} want {exp.reshape(-1)[bad[:5]]}"
+
+
 def test_unscaled_casts_every_bf16_pattern_and_neighbours():
     """quant_dequant_*: all bf16 patterns widened to float32, plus values just off the rounding ties."""
     import gpu_harness as H
@@ -498,6 +518,28 @@ def test_quantize_mx_fp6_packed(by):
     got = H.quantize_mx_fp6(x, by)
     assert np.array_equal(got["scales"], scales)
     assert np.array_equal(got["payload"], oracle.pack_fp6(codes))
+
+
+@pytest.mark.parametrize("bx,by", [(128, 128), (32, 64), (1, 256), (1, 2048), (64, 1), (256, 1)])
+@pytest.mark.parametrize("ss", [1, 3, 4])
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+def test_quantize_scaled_codes_and_scales(bx, by, ss, dtype):
+    """E4M3 bytes and binary32 scales of the block / channel pipelines: equal to the oracle's, with this tensor's amax
+    and with a larger one handed in (row sharding)"""
+    import gpu_harness as H
+    g = torch.Generator().manual_seed(bx + by + ss)
+    t = torch.randn(256, 2048, generator=g) * 10.0 ** (torch.rand(256, 2048, generator=g) * 4 - 2)
+    t[5, 7] = 0.0
+    t[9, 11] = -0.0
+    t[128:, :512] = 0.0
+    x = t.numpy().copy() if dtype == "f32" else oracle.bf16_bits(t.to(torch.bfloat16))
+    for amax_in in (None, 3.0e4):
+        payload, scales, gamax = oracle.quantize_scaled(x, bx, by, ss, global_amax=amax_in)
+        got = H.quantize_scaled(x, bx, by, ss, amax_in)
+        assert np.array_equal(got["scales"].view(np.uint32), scales.view(np.uint32)), f"scales, amax_in {amax_in}"
+        bad = np.nonzero(got["payload"] != payload)
+        assert bad[0].size == 0, f"{bad[0].size} codes differ, first at {bad[0][:4]}, {bad[1][:4]}"
+        assert np.float32(got["gamax"]) == np.float32(gamax)
 
 
 def test_quantize_mx_round_trip_full_size():

@@ -166,6 +166,15 @@ def test_additional_operators():
     ep, eb = oracle.quantize_mx(xb, 32, 0)
     same(payload, ep, "quantize_mx codes")
     same(sb, eb, "quantize_mx scale bytes")
+    pq, sq, aq = mor.ops.quantize_scaled(xd, R, C, 128, 128, 1)
+    ep, es, ea = oracle.quantize_scaled(xb, 128, 128, 1)
+    same(pq, ep, "quantize_scaled codes")
+    same(sq, es, "quantize_scaled scales")
+    assert aq.item() == float(ea) and pq.dtype == torch.uint8 and sq.shape == (R // 128, C // 128)
+    # the bytes are torch's float8_e4m3fn: dividing by the scale gives the fake-quantized tensor
+    fq = mor.ops.fake_quantize_block_scaling(xd, R, C, 128, 128, 3e38, 1)[0]
+    deq = pq.view(torch.float8_e4m3fn).float() / sq.repeat_interleave(128, 0).repeat_interleave(128, 1)
+    assert torch.equal(deq.to(torch.bfloat16).view(torch.int16)[xd != 0], fq.view(torch.int16)[xd != 0])
     p6, sb6 = mor.ops.quantize_mx_fp6(xd, R, C, 32)
     c6, e6 = oracle.quantize_mx(xb, 32, 3)
     same(p6, oracle.pack_fp6(c6), "quantize_mx_fp6 payload")

@@ -268,3 +268,28 @@ def test_pack_fp6_layout():
         w = int.from_bytes(bytes(p.reshape(-1)[6 * gi:6 * gi + 6]), "little")
         back.reshape(-1)[8 * gi:8 * gi + 8] = [(w >> (6 * i)) & 63 for i in range(8)]
     assert np.array_equal(back, codes)
+
+
+@pytest.mark.parametrize("brows,bcols", [(128, 128), (32, 64), (1, 256), (64, 1)])
+@pytest.mark.parametrize("ss", [1, 3, 4])
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+def test_quantize_scaled_round_trip(brows, bcols, ss, dtype):
+    """E4M3 bytes + binary32 scales: decode(code) / scale is the fake-quantized tensor, bit for bit"""
+    g = torch.Generator().manual_seed(brows + bcols + ss)
+    t = torch.randn(256, 512, generator=g) * 10.0 ** (torch.rand(256, 512, generator=g) * 4 - 2)
+    t[5, 7] = 0.0
+    t[9, 11] = -0.0
+    x = t.numpy().copy() if dtype == "f32" else oracle.bf16_bits(t.to(torch.bfloat16))
+    payload, scales, gamax = oracle.quantize_scaled(x, brows, bcols, ss)
+    fn = oracle.channel_scaling if (brows == 1 or bcols == 1) else oracle.block_scaling
+    fq = fn(x, brows, bcols, 3e38, ss)
+    assert np.float32(gamax) == np.float32(fq[2])
+    deq = oracle.dequantize_scaled(payload, scales, brows, bcols, float32=(dtype == "f32"))
+    assert np.array_equal(deq.view(np.uint8), np.ascontiguousarray(fq[0]).view(np.uint8))
+    assert payload[5, 7] == 0 and payload[9, 11] == 0
+    # the bytes are what torch's own E4M3 type holds for the scaled values
+    xf = t.numpy() if dtype == "f32" else t.to(torch.bfloat16).float().numpy()
+    s_full = np.repeat(np.repeat(scales, brows, axis=0), bcols, axis=1)
+    ref = (torch.from_numpy(xf * s_full).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8).numpy())
+    nz = xf != 0
+    assert np.array_equal(payload[nz], ref[nz])
