@@ -330,48 +330,74 @@ __global__ void __launch_bounds__(kThreads) amax_nnz_runs_kernel(const typename 
     }
 }
 
-// Column groups (k x 1): every thread owns one 16-byte column strip and walks down the
-// k rows of its block; per-column maxima go straight to block_amax.
+// Column groups (k x 1): a CTA covers 32 consecutive 16-byte column strips (one warp spans them: 512
+// contiguous bytes of a row) and a slice of `rows_per_cta` rows of one row block; its eight warps take
+// every eighth row, four loads in flight per lane.  The warps' per-column maxima meet in shared memory
+// and one atomicMax per column and CTA goes to block_amax.  bf16 data is screened for the short
+// quotient of the cast kernels on the way (every non-zero magnitude in [2^-90, 2^90), no NaN).
 template <typename T>
 __global__ void __launch_bounds__(kThreads) amax_nnz_colgroups_kernel(const typename T::vec_t* __restrict__ in,
                                                                       int64_t cols_vec, int brows, int rows_per_cta,
                                                                       float* __restrict__ block_amax,
                                                                       ScalarsWs* __restrict__ ws) {
     constexpr int EPV = 16 / T::kBytesPerElem;
-    const int64_t cv = (int64_t)blockIdx.x * kThreads + threadIdx.x;     // vector column
+    __shared__ float s_cmax[8][32][EPV + 1];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int64_t cv = (int64_t)blockIdx.x * 32 + lane;                  // vector column
     const int64_t rb = blockIdx.y;                                       // row block
     const int seg = blockIdx.z;                                          // slice of the k rows
     float cmax[EPV];
 #pragma unroll
     for (int e = 0; e < EPV; ++e) cmax[e] = 0.0f;
-    float amax = 0.0f;
     int nnz = 0;
+    bool unsafe = false;
     if (cv < cols_vec) {
         const int64_t r_begin = rb * brows + (int64_t)seg * rows_per_cta;
         int64_t r_end = r_begin + rows_per_cta;
         if (r_end > (rb + 1) * (int64_t)brows) r_end = (rb + 1) * (int64_t)brows;
-        for (int64_t r = r_begin; r < r_end; ++r) {
-            const typename T::vec_t v = ld_keep(in + r * cols_vec + cv);
+        auto take = [&](const typename T::vec_t& v) {
 #pragma unroll
             for (int k = 0; k < T::kWordsPerVec; ++k) {
                 float hi, lo;
                 T::unpack(v, k, hi, lo);
                 const float ah = fabsf(hi), al = fabsf(lo);
-                cmax[2 * k] = fmaxf(cmax[2 * k], al);
+                cmax[2 * k] = fmaxf(cmax[2 * k], al);          // fmaxf skips NaNs, as the reference's does
                 cmax[2 * k + 1] = fmaxf(cmax[2 * k + 1], ah);
                 nnz += (ah > 0.0f) + (al > 0.0f);
+                // outside the short quotient's range: NaN, or a non-zero magnitude below 2^-90 or at least 2^90
+                unsafe = unsafe || !(ah == 0.0f || (ah >= 8.0779357e-28f && ah < 1.2379400e27f)) ||
+                         !(al == 0.0f || (al >= 8.0779357e-28f && al < 1.2379400e27f));
             }
-        }
+        };
+        int64_t r = r_begin + wid;
+        for (; r + 24 < r_end; r += 32) {
+            typename T::vec_t v[4];
 #pragma unroll
-        for (int e = 0; e < EPV; ++e) {
-            amax = fmaxf(amax, cmax[e]);
-            atomicMax(reinterpret_cast<uint32_t*>(block_amax) + rb * cols_vec * EPV + cv * EPV + e, f2u(cmax[e]));
+            for (int u = 0; u < 4; ++u) v[u] = ld_keep(in + (r + 8 * u) * cols_vec + cv);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) take(v[u]);
         }
+        for (; r < r_end; r += 8) take(ld_keep(in + r * cols_vec + cv));
     }
+#pragma unroll
+    for (int e = 0; e < EPV; ++e) s_cmax[wid][lane][e] = cmax[e];
+    float amax = 0.0f;
+#pragma unroll
+    for (int e = 0; e < EPV; ++e) amax = fmaxf(amax, cmax[e]);
+    __syncthreads();
+    for (int t = threadIdx.x; t < 32 * EPV; t += kThreads) {
+        const int l = t / EPV, e = t % EPV;
+        float m = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) m = fmaxf(m, s_cmax[w][l][e]);
+        const int64_t col_vec = (int64_t)blockIdx.x * 32 + l;
+        if (col_vec < cols_vec) atomicMax(reinterpret_cast<uint32_t*>(block_amax) + rb * cols_vec * EPV + col_vec * EPV + e, f2u(m));
+    }
+    const bool any_unsafe = __syncthreads_or(unsafe) != 0;
     cta_combine(amax, nnz);
     if (threadIdx.x == 0) {
         publish(ws, amax, nnz);
-        atomicOr(&ws->div_unsafe, 1u);  // this traversal does not screen magnitudes: keep the IEEE division
+        if (any_unsafe || T::kBytesPerElem != 2) atomicOr(&ws->div_unsafe, 1u);
     }
 }
 
@@ -413,7 +439,7 @@ int launch_amax_nnz_blocks(const void* in, int is_fp32, int64_t rows, int64_t co
         zero_floats_kernel<<<(int)((n_amax + 255) / 256 < 1024 ? (n_amax + 255) / 256 : 1024), 256, 0, st>>>(block_amax, n_amax);
         int rows_per_cta = 256;
         if (rows_per_cta > brows) rows_per_cta = brows;
-        dim3 grid((unsigned)((cols_vec + kThreads - 1) / kThreads), (unsigned)(rows / brows),
+        dim3 grid((unsigned)((cols_vec + 31) / 32), (unsigned)(rows / brows),
                   (unsigned)((brows + rows_per_cta - 1) / rows_per_cta));
         if (is_fp32) amax_nnz_colgroups_kernel<Fp32><<<grid, kThreads, 0, st>>>(static_cast<const float4*>(in), cols_vec, brows, rows_per_cta, block_amax, ws);
         else amax_nnz_colgroups_kernel<Bf16><<<grid, kThreads, 0, st>>>(static_cast<const uint4*>(in), cols_vec, brows, rows_per_cta, block_amax, ws);

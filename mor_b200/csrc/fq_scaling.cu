@@ -1005,8 +1005,8 @@ colstrip_tma_kernel(const __grid_constant__ CUtensorMap tmap, void* __restrict__
                     ScalarsWs* __restrict__ ws, const float* __restrict__ ext_gamax, int skip_if_fallback) {
     using W = typename PairWord<T>::type;
     using CS = ColStrip<T>;
-    constexpr int kDiv = (T::kBytesPerElem == 2) ? kDivBf16Any : kDivIeee;   // the column amax pass does not screen magnitudes
     if (skip_if_fallback && ws->fallback) return;
+    const bool fastdiv = fast_div_ok<T>(ws);   // bf16, every non-zero magnitude in [2^-90, 2^90), no NaN: the short quotient
     extern __shared__ __align__(128) uint8_t s_col[];   // ring of stages, then the tables
     __shared__ __align__(8) uint64_t s_full[kColStages], s_empty[kColStages];
     __shared__ float s_sf[64];
@@ -1067,9 +1067,14 @@ colstrip_tma_kernel(const __grid_constant__ CUtensorMap tmap, void* __restrict__
             }
             const bool zh = hi == 0.0f, zl = lo == 0.0f;
             float e_h, e_l;
-            if constexpr (kDiv == kDivBf16Any) {
-                e_h = fabsf(div_by_bf16_any(__fsub_rn(dh, hi), hi));
-                e_l = fabsf(div_by_bf16_any(__fsub_rn(dl, lo), lo));
+            if constexpr (T::kBytesPerElem == 2) {
+                if (fastdiv) {   // warp-uniform
+                    e_h = fabsf(div_by_bf16(__fsub_rn(dh, hi), hi, rcp_fast(hi)));
+                    e_l = fabsf(div_by_bf16(__fsub_rn(dl, lo), lo, rcp_fast(lo)));
+                } else {
+                    e_h = fabsf(div_by_bf16_any(__fsub_rn(dh, hi), hi));
+                    e_l = fabsf(div_by_bf16_any(__fsub_rn(dl, lo), lo));
+                }
             } else {
                 e_h = fabsf(__fdiv_rn(__fsub_rn(dh, hi), zh ? 1.0f : hi));
                 e_l = fabsf(__fdiv_rn(__fsub_rn(dl, lo), zl ? 1.0f : lo));
@@ -1080,7 +1085,7 @@ colstrip_tma_kernel(const __grid_constant__ CUtensorMap tmap, void* __restrict__
                 dh = zh ? 0.0f : dh;
                 dl = zl ? 0.0f : dl;
                 W w;
-                if constexpr (T::kBytesPerElem == 2) w = pack_bf16(dh, dl);
+                if constexpr (T::kBytesPerElem == 2) w = (E8 || !fastdiv) ? pack_bf16(dh, dl) : pack_bf16_round(dh, dl);
                 else w = make_float2(dl, dh);
                 __stcs(out, w);
             }
