@@ -582,6 +582,14 @@ def oracle_check(op, x, args, outs):
         _, _, bx, by, thr, ss, amax_in = args
         e = oracle.block_scaling(xb, bx, by, thr, ss, global_amax=float(amax_in.item()))
         return same(bits(outs[0]), e[0]) and int(outs[1].item()) == e[1] and int(outs[3].item()) == e[3] and f32(outs[4].item()) == f32(e[4])
+    if op == "fake_quantize_block_scaling_delayed_t":
+        _, _, bx, by, thr, ss, amax_in = args
+        e = oracle.block_scaling(xb, bx, by, thr, ss, global_amax=float(amax_in.item()))
+        return same(bits(outs[0]), e[0]) and same(bits(outs[1]), np.ascontiguousarray(e[0].T)) and int(outs[2].item()) == e[1]
+    if op == "quantize_scaled":
+        _, _, bx, by, ss = args
+        ep, es, _ = oracle.quantize_scaled(xb, bx, by, ss)
+        return same(outs[0].cpu().numpy(), ep) and same(outs[1].cpu().numpy(), es)
     if op == "fake_quantize_mx":
         _, _, by, fmt, sf = args
         eo, es = oracle.fake_quantize_group(xb, 1, by, fmt, sf, want_scales=True)
@@ -718,6 +726,10 @@ def run_suite(torch, dev, peak, only="", iters=10, out_path=None, use_graph=Fals
         amax_prev4 = x.float().abs().max().reshape(1)
         add("c4 block scaling 128x128, single pass with delayed amax (ss 1)", x, 4, "fake_quantize_block_scaling_delayed",
             (r, c, 128, 128, 3e38, 1, amax_prev4), headline=False)
+        add("c4 block scaling 128x128, single pass, result also transposed (ss 1)", x, 6, "fake_quantize_block_scaling_delayed_t",
+            (r, c, 128, 128, 3e38, 1, amax_prev4), headline=False)
+        add("c4 real quantization, E4M3 bytes + float32 block scales (quantize_scaled ss 1)", x, 5, "quantize_scaled",
+            (r, c, 128, 128, 1), headline=False)
     add("c4 MoR 128x128 relative-error criterion (mode 1)", x, 4, "fake_quantize", (r, c, 128, 128, 1e-15, 1, 1), ref_ok=True)
     add("c4 MoR 128x128 dynamic-range criterion (mode 101)", x, 4, "fake_quantize", (r, c, 128, 128, 1e-15, 101, 1), ref_ok=True, headline=False)
     add("c4 block scaling 128x128 pipeline (ss 1)", x, 6, "fake_quantize_block_scaling", (r, c, 128, 128, 3e38, 1), ref_ok=True)

@@ -170,6 +170,16 @@ MOR_B200_API int mor_b200_block_scaling_delayed(const void* input, void* output,
                                    int nnz_is_int64, float* err_out, void* workspace, size_t workspace_bytes,
                                    void* stream);
 
+/* mor_b200_block_scaling_delayed that also writes the result transposed: output_t is [cols, rows], the
+ * layout a weight-gradient GEMM reads, produced from the tile while it is still on chip instead of by a
+ * second pass over the tensor.  output may be NULL (transposed result only).  If the tensor stays BF16
+ * (meta 3) output_t receives the transposed input.  No counterpart in the reference. */
+MOR_B200_API int mor_b200_block_scaling_delayed_t(const void* input, void* output, void* output_t, int dtype, int64_t rows,
+                                     int64_t cols, int block_rows, int block_cols, double e4m3_threshold, int ss_mode,
+                                     const float* amax_in, int32_t* meta, float* amax_out, void* nnz_out,
+                                     int nnz_is_int64, float* err_out, void* workspace, size_t workspace_bytes,
+                                     void* stream);
+
 /* Extension (no counterpart in the reference, whose operators only fake-quantize; the casts
  * it describes are fake_quantize.cu:283-305 and the wrappers :356-379): the REAL quantized form
  * of mor_b200_fake_quantize_group with sf_type 2, i.e. what a block-scaled GEMM consumes.

@@ -37,6 +37,7 @@ SIGNATURES = {
     "mor_b200_quantize_mx_fp6": (_i, [_vp, _vp, _vp, _i64, _i64, _i, _vp]),
     "mor_b200_quantize_scaled": (_i, [_vp, _vp, _vp, _i, _i64, _i64, _i, _i, _i, _vp, _vp, _vp, _sz, _vp]),
     "mor_b200_block_scaling_delayed": (_i, [_vp, _vp, _i, _i64, _i64, _i, _i, _d, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _sz, _vp]),
+    "mor_b200_block_scaling_delayed_t": (_i, [_vp, _vp, _vp, _i, _i64, _i64, _i, _i, _d, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _sz, _vp]),
     "mor_b200_scaling_amax": (_i, [_i, _vp, _i, _i64, _i64, _i, _i, _vp, _vp, _vp, _sz, _vp]),
     "mor_b200_scaling_cast": (_i, [_i, _vp, _vp, _i, _i64, _i64, _i, _i, _i, _vp, _vp, _vp, _sz, _vp]),
     "mor_b200_scaling_num_errors": (_i64, [_i, _i64, _i64, _i, _i]),

@@ -326,15 +326,38 @@ int mor_b200_fake_quantize_group(const void* in, void* out, float* scales, int d
 // Single pass with a delayed tensor amax: the scales use `amax_in` (device, e.g. the amax this call
 // reported for the previous step's tensor), every block's own amax comes from the staged tile, and
 // the tensor's amax / non-zero count / error of THIS call are reported for the next one.
+namespace {
+int delayed_op(const void* in, void* out, void* out_t, int dtype, int64_t rows, int64_t cols, int br, int bc, double thr, int ss,
+               const float* amax_in, int32_t* meta, float* amax_out, void* nnz_out, int nnz64, float* err_out, void* wsp,
+               size_t wsb, void* stream);
+}  // namespace
+
 int mor_b200_block_scaling_delayed(const void* in, void* out, int dtype, int64_t rows, int64_t cols, int br, int bc,
                                    double thr, int ss, const float* amax_in, int32_t* meta, float* amax_out,
                                    void* nnz_out, int nnz64, float* err_out, void* wsp, size_t wsb, void* stream) {
-    if (!in || !out || !amax_in || (dtype != MOR_B200_BF16 && dtype != MOR_B200_FP32)) return kErrInvalidArgument;
+    if (!out) return kErrInvalidArgument;
+    return delayed_op(in, out, nullptr, dtype, rows, cols, br, bc, thr, ss, amax_in, meta, amax_out, nnz_out, nnz64, err_out,
+                      wsp, wsb, stream);
+}
+
+int mor_b200_block_scaling_delayed_t(const void* in, void* out, void* out_t, int dtype, int64_t rows, int64_t cols, int br,
+                                     int bc, double thr, int ss, const float* amax_in, int32_t* meta, float* amax_out,
+                                     void* nnz_out, int nnz64, float* err_out, void* wsp, size_t wsb, void* stream) {
+    if (!out_t || out_t == in || out_t == out || !aligned16(out_t)) return kErrInvalidArgument;
+    return delayed_op(in, out, out_t, dtype, rows, cols, br, bc, thr, ss, amax_in, meta, amax_out, nnz_out, nnz64, err_out,
+                      wsp, wsb, stream);
+}
+
+namespace {
+int delayed_op(const void* in, void* out, void* out_t, int dtype, int64_t rows, int64_t cols, int br, int bc, double thr, int ss,
+               const float* amax_in, int32_t* meta, float* amax_out, void* nnz_out, int nnz64, float* err_out, void* wsp,
+               size_t wsb, void* stream) {
+    if (!in || (!out && !out_t) || !amax_in || (dtype != MOR_B200_BF16 && dtype != MOR_B200_FP32)) return kErrInvalidArgument;
     if (ss < 1 || ss > 4) return kErrInvalidArgument;
     if (br != 128 || bc != 128 || in == out) return kErrUnsupportedShape;   // TMA-staged tiles; the fallback needs the input
     const Geometry g = block_geometry(rows, cols, br, bc);
     if (g.status) return g.status;
-    if (!aligned16(in) || !aligned16(out)) return kErrUnsupportedShape;
+    if (!aligned16(in) || (out && !aligned16(out))) return kErrUnsupportedShape;
     if (!wsp || wsb < ws_bytes_for(g) || !aligned16(wsp)) return kErrWorkspace;
     auto st = static_cast<cudaStream_t>(stream);
     auto* ws = static_cast<ScalarsWs*>(wsp);
@@ -343,7 +366,7 @@ int mor_b200_block_scaling_delayed(const void* in, void* out, int dtype, int64_t
     a.brows = br; a.bcols = bc; a.threshold = (float)thr; a.ss_mode = ss;
     a.block_amax = reinterpret_cast<float*>(static_cast<char*>(wsp) + kHead);
     a.block_err = reinterpret_cast<float*>(static_cast<char*>(wsp) + kHead + round256(4 * (size_t)g.n_amax));
-    a.n_err = g.n_err; a.err_slot_stride = g.stride; a.ws = ws; a.ext_gamax = amax_in; a.scan_blocks = 1;
+    a.n_err = g.n_err; a.err_slot_stride = g.stride; a.ws = ws; a.ext_gamax = amax_in; a.scan_blocks = 1; a.out_t = out_t;
     int rc = launch_zero_scalars(ws, st);
     if (rc) return rc;
     rc = launch_block_err_cast(a, /*store=*/true, false, st);
@@ -352,8 +375,11 @@ int mor_b200_block_scaling_delayed(const void* in, void* out, int dtype, int64_t
     f.ext_gamax = nullptr;   // report the amax found in this tensor, not the one the scales were built from
     rc = launch_finalize(f, nullptr, meta, amax_out, nnz_out, nnz64, err_out, st);
     if (rc) return rc;
-    return launch_fallback_copy(a, st);
+    rc = launch_fallback_copy(a, st);
+    if (rc) return rc;
+    return launch_fallback_transpose(a, st);
 }
+}  // namespace
 
 int mor_b200_quantize_mx(const void* in, void* payload, void* scales, int64_t rows, int64_t cols, int bc, int format,
                          void* stream) {

@@ -116,11 +116,17 @@ template <typename T> struct Tile128 {
     static constexpr int kCtasPerSm = T::kBytesPerElem == 4 ? 3 : 6;
 };
 
-template <typename T, bool E8, bool STORE, bool SCAN = false>
+// TRANS (single pass only): the results also go out transposed (out_t is [cols, rows], the layout a
+// weight-gradient GEMM reads), from the tile itself: every thread puts its result vectors back where it
+// read the inputs, and after a barrier each warp walks 32 consecutive columns -- one lane per column, 2- or
+// 4-byte shared loads down the rows, conflict-free -- and stores 16 or 32 bytes of a transposed row per lane.
+// `out` may then be NULL (transposed output only).
+template <typename T, bool E8, bool STORE, bool SCAN = false, bool TRANS = false>
 __global__ void __launch_bounds__(Tile128<T>::kThreads, Tile128<T>::kCtasPerSm)
 block_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename T::vec_t* __restrict__ out, int64_t cols_vec,
                      int blocks_x, int ss, const float* __restrict__ block_amax, float* __restrict__ block_err,
-                     ScalarsWs* __restrict__ ws, const float* __restrict__ ext_gamax, int skip_if_fallback) {
+                     ScalarsWs* __restrict__ ws, const float* __restrict__ ext_gamax, int skip_if_fallback,
+                     typename T::vec_t* __restrict__ out_t = nullptr, int64_t rows_vec = 0) {
     constexpr int VW = T::kWordsPerVec, LPW = 32 / VW, NT = Tile128<T>::kThreads, NS = Tile128<T>::kStrips;
     constexpr int EPS = 128 / T::kBytesPerElem;  // elements per strip
     constexpr int CI = 2;                        // vectors per lane and row: 128 columns / (LPW lanes x 16 bytes)
@@ -266,7 +272,12 @@ block_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename T::vec_t
                 const typename T::vec_t v = tile[((j * NS + (vc >> 3)) * 32 + ty) * 8 + (vc & 7)];
                 typename T::vec_t o;
                 err_vec<T, std::decay_t<decltype(path)>, STORE, FD, decltype(nz_tag)::value>(path, v, o, acc);
-                if constexpr (STORE) st_stream(dst + (int64_t)(32 * j) * cols_vec + LPW * i, o);
+                if constexpr (TRANS) {
+                    const_cast<typename T::vec_t*>(tile)[((j * NS + (vc >> 3)) * 32 + ty) * 8 + (vc & 7)] = o;
+                    if (out) st_stream(dst + (int64_t)(32 * j) * cols_vec + LPW * i, o);
+                } else if constexpr (STORE) {
+                    st_stream(dst + (int64_t)(32 * j) * cols_vec + LPW * i, o);
+                }
             }
         }
     };
@@ -295,10 +306,59 @@ block_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename T::vec_t
     }
     const float s = logical_warp_sum<VW>(acc);
     if (p == 0) wsum[ty] = s;
-    __syncthreads();
+    __syncthreads();   // also: every result vector is back in the tile (TRANS)
     if (tid < 32) {
         const float t = warp_sum_ordered(wsum[tid]);
         if (tid == 0) block_err[b] = t;
+    }
+    if constexpr (TRANS) {
+        // element (r, c) of the tile sits at [r / 32][strip of c][r % 32][byte of c in the strip]
+        using E = std::conditional_t<T::kBytesPerElem == 2, uint16_t, uint32_t>;
+        constexpr int EPV = 16 / T::kBytesPerElem;          // elements of a 16-byte store: 8 / 4 rows of one column
+        constexpr int NW = NT / 32;                          // 8 / 16 warps: four column groups x 2 / 4 row ranges
+        constexpr int ROWS_PER_WARP = 128 / (NW / 4);        // 64 / 32
+        const int lane = tid & 31, w = tid >> 5;
+        const int c = (w & 3) * 32 + lane;                   // this lane's column of the tile
+        const int r_begin = (w >> 2) * ROWS_PER_WARP;
+        const uint8_t* col = s_tile + ((c * T::kBytesPerElem) >> 7) * 4096 + ((c * T::kBytesPerElem) & 127);
+        typename T::vec_t* trow = out_t + ((int64_t)bx * 128 + c) * rows_vec + (int64_t)by * (128 / EPV);
+#pragma unroll 2
+        for (int r0 = r_begin; r0 < r_begin + ROWS_PER_WARP; r0 += EPV) {
+            E e[EPV];
+#pragma unroll
+            for (int k = 0; k < EPV; ++k) {
+                const int r = r0 + k;
+                e[k] = *reinterpret_cast<const E*>(col + (r >> 5) * (NS * 4096) + (r & 31) * 128);
+            }
+            typename T::vec_t o;
+            if constexpr (T::kBytesPerElem == 2) {
+                o.x = (uint32_t)e[0] | ((uint32_t)e[1] << 16); o.y = (uint32_t)e[2] | ((uint32_t)e[3] << 16);
+                o.z = (uint32_t)e[4] | ((uint32_t)e[5] << 16); o.w = (uint32_t)e[6] | ((uint32_t)e[7] << 16);
+            } else {
+                o.x = __uint_as_float(e[0]); o.y = __uint_as_float(e[1]); o.z = __uint_as_float(e[2]); o.w = __uint_as_float(e[3]);
+            }
+            st_stream(trow + r0 / EPV, o);
+        }
+    }
+}
+
+// Only when the tensor stays BF16: the transposed output is then the transposed input (32 x 32 tiles through
+// shared memory, 2- or 4-byte elements).
+template <typename E>
+__global__ void __launch_bounds__(256) fallback_transpose_kernel(const E* __restrict__ in, E* __restrict__ out_t, int64_t rows,
+                                                                 int64_t cols, const ScalarsWs* __restrict__ ws) {
+    if (!ws->fallback) return;
+    __shared__ E s[32][33];
+    const int64_t tiles_x = cols / 32, n_tiles = tiles_x * (rows / 32);
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+        const int64_t r0 = (t / tiles_x) * 32, c0 = (t % tiles_x) * 32;
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 4; ++k) s[ty + 8 * k][tx] = in[(r0 + ty + 8 * k) * cols + c0 + tx];
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 4; ++k) out_t[(c0 + ty + 8 * k) * rows + r0 + tx] = s[tx][ty + 8 * k];
     }
 }
 
@@ -1285,6 +1345,21 @@ int launch_block_t(const ScalingArgs& a, bool store, bool skip, cudaStream_t st)
             map, out, cols_vec, (int)bx, a.ss_mode, a.block_amax, a.block_err, a.ws, a.ext_gamax, 0);                \
     } while (0)
             if (!store || skip) return kErrInvalidArgument;
+            if (a.out_t) {
+                constexpr int EPVT = 16 / T::kBytesPerElem;
+                auto* out_t = static_cast<typename T::vec_t*>(a.out_t);
+#define MORB_TILE_T(E)                                                                                               \
+    do {                                                                                                             \
+        static SmemOptIn opt;                                                                                        \
+        if (!opt(block_tile128_kernel<T, E, true, true, true>, Tile128<T>::kBytes)) return kErrLaunch;               \
+        block_tile128_kernel<T, E, true, true, true><<<(unsigned)nb, TH, Tile128<T>::kBytes, st>>>(                   \
+            map, out, cols_vec, (int)bx, a.ss_mode, a.block_amax, a.block_err, a.ws, a.ext_gamax, 0, out_t,           \
+            a.rows / EPVT);                                                                                           \
+    } while (0)
+                if (e8) MORB_TILE_T(true); else MORB_TILE_T(false);
+#undef MORB_TILE_T
+                return check_launch();
+            }
             if (e8) MORB_TILE_SCAN(true); else MORB_TILE_SCAN(false);
 #undef MORB_TILE_SCAN
             return check_launch();
@@ -1486,8 +1561,19 @@ int launch_finalize(const ScalingArgs& a, const long long* ext_nnz, int32_t* met
     return check_launch();
 }
 
+int launch_fallback_transpose(const ScalingArgs& a, cudaStream_t st) {
+    if (!a.out_t) return kOk;
+    const int64_t n_tiles = (a.rows / 32) * (a.cols / 32);
+    int64_t grid = n_tiles;
+    const int64_t cap = (int64_t)sm_count() * 8;
+    if (grid > cap) grid = cap;
+    if (a.is_fp32) fallback_transpose_kernel<uint32_t><<<(unsigned)grid, 256, 0, st>>>(static_cast<const uint32_t*>(a.in), static_cast<uint32_t*>(a.out_t), a.rows, a.cols, a.ws);
+    else fallback_transpose_kernel<uint16_t><<<(unsigned)grid, 256, 0, st>>>(static_cast<const uint16_t*>(a.in), static_cast<uint16_t*>(a.out_t), a.rows, a.cols, a.ws);
+    return check_launch();
+}
+
 int launch_fallback_copy(const ScalingArgs& a, cudaStream_t st) {
-    if (a.in == a.out) return kOk;
+    if (a.in == a.out || !a.out) return kOk;
     const int64_t nvec = a.rows * a.cols * (a.is_fp32 ? 4 : 2) / 16;
     int64_t grid = (nvec + 255) / 256;
     const int64_t cap = (int64_t)sm_count() * 8;

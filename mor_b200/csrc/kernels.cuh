@@ -87,6 +87,7 @@ struct ScalingArgs {
     int err_slot_stride;        // the reference stores entry i at slot i * stride of its array
     ScalarsWs* ws;
     const float* ext_gamax;     // optional device pointer: amax of the whole (sharded) tensor
+    void* out_t;                // optional: the output transposed, [cols, rows] (single-pass 128 x 128 tile kernel only)
     int scan_blocks;            // 1: single pass -- the cast kernel takes each block's amax from the tile it
                                 // has staged and publishes the tensor's amax / non-zero count itself
                                 // (ext_gamax then is the amax of an earlier step: delayed scaling)
@@ -97,6 +98,7 @@ int launch_colgroup_err_cast(const ScalingArgs& a, bool store, bool only_if_not_
 int launch_finalize(const ScalingArgs& a, const long long* ext_nnz, int32_t* meta, float* gamax, void* gnnz,
                     int nnz_is_i64, float* gerr, cudaStream_t st);
 int launch_fallback_copy(const ScalingArgs& a, cudaStream_t st);
+int launch_fallback_transpose(const ScalingArgs& a, cudaStream_t st);   // out_t := in transposed, if the tensor stays BF16
 
 // ---- fq_resident.cu: block scaling on 128 x 128 blocks as one cooperative kernel, for tensors
 // that fit in the shared memories of the device (kErrUnsupportedShape otherwise: use the phases above)

@@ -249,6 +249,38 @@ std::vector<at::Tensor> fake_quantize_block_scaling_delayed(const at::Tensor& in
     return {out, meta, gamax, gnnz, gerr};
 }
 
+// the same, and the result transposed as well: returns [out, out_t [dim_y, dim_x], meta, amax, non-zero count, error]
+std::vector<at::Tensor> fake_quantize_block_scaling_delayed_t(const at::Tensor& input, int64_t rows, int64_t cols,
+                                                              int64_t br, int64_t bc, double thr, int64_t ss,
+                                                              const at::Tensor& amax_in) {
+    const char* name = "fake_quantize_block_scaling_delayed_t";
+    const c10::cuda::CUDAGuard guard(input.device());
+    at::Tensor in = checked_input(input, rows, cols, name);
+    const int dt = dtype_code(in, true, name);
+    TORCH_CHECK(ss >= 1 && ss <= 4, "mor::", name, ": ss_mode must be 1..4");
+    TORCH_CHECK(br == 128 && bc == 128 && rows % 128 == 0 && cols % 128 == 0, "mor::", name,
+                ": 128 x 128 blocks that divide the tensor only");
+    TORCH_CHECK(amax_in.is_cuda() && amax_in.scalar_type() == at::kFloat && amax_in.numel() == 1, "mor::", name,
+                ": amax_in must be a float32 CUDA tensor with one element");
+    TORCH_CHECK(dt == MOR_B200_FP32 || rows * cols < (int64_t(1) << 31), "mor::", name,
+                ": bfloat16 tensors report an int32 non-zero count; use float32 for 2^31 elements and more");
+    const size_t wsb = mor_b200_workspace_bytes(MOR_B200_OP_BLOCK_SCALING, rows, cols, 128, 128);
+    at::Tensor ws = workspace(in, wsb);
+    at::Tensor out = torch::empty_like(in);
+    at::Tensor out_t = torch::empty({cols, rows}, in.options());
+    auto iopt = in.options().dtype(torch::kInt32);
+    auto fopt = in.options().dtype(torch::kFloat);
+    at::Tensor meta = torch::empty({1}, iopt), gamax = torch::empty({1}, fopt), gerr = torch::empty({1}, fopt);
+    const bool nnz64 = dt == MOR_B200_FP32;
+    at::Tensor gnnz = torch::empty({1}, nnz64 ? in.options().dtype(torch::kInt64) : iopt);
+    check_status(mor_b200_block_scaling_delayed_t(in.data_ptr(), out.data_ptr(), out_t.data_ptr(), dt, rows, cols, 128, 128,
+                                                  thr, (int)ss, amax_in.data_ptr<float>(), meta.data_ptr<int32_t>(),
+                                                  gamax.data_ptr<float>(), gnnz.data_ptr(), nnz64 ? 1 : 0,
+                                                  gerr.data_ptr<float>(), ws.data_ptr(), wsb, cur_stream()),
+                 name);
+    return {out, out_t, meta, gamax, gnnz, gerr};
+}
+
 // ---- extension: real quantized output (codes + E8M0 scale bytes) -----------------------
 // returns [payload uint8 [dim_x, dim_y], scales uint8 [dim_x, dim_y / block_y]]
 std::vector<at::Tensor> quantize_mx(const at::Tensor& input, int64_t rows, int64_t cols, int64_t bc, int64_t elem_format) {
@@ -328,6 +360,7 @@ TORCH_LIBRARY(mor, m) {
   m.def("quantize_mx_fp6(Tensor input, int dim_x, int dim_y, int block_y) -> Tensor[]");
   m.def("quantize_scaled(Tensor input, int dim_x, int dim_y, int block_x, int block_y, int ss_mode) -> Tensor[]");
   m.def("fake_quantize_block_scaling_delayed(Tensor input, int dim_x, int dim_y, int block_x, int block_y, float e4m3_threshold, int ss_mode, Tensor amax_in) -> Tensor[]");
+  m.def("fake_quantize_block_scaling_delayed_t(Tensor input, int dim_x, int dim_y, int block_x, int block_y, float e4m3_threshold, int ss_mode, Tensor amax_in) -> Tensor[]");
 }
 
 TORCH_LIBRARY_IMPL(mor, CUDA, m) {
@@ -350,6 +383,7 @@ TORCH_LIBRARY_IMPL(mor, CUDA, m) {
   m.impl("quantize_mx_fp6", &quantize_mx_fp6);
   m.impl("quantize_scaled", &quantize_scaled);
   m.impl("fake_quantize_block_scaling_delayed", &fake_quantize_block_scaling_delayed);
+  m.impl("fake_quantize_block_scaling_delayed_t", &fake_quantize_block_scaling_delayed_t);
 }
 
 }  // namespace mor

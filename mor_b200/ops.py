@@ -28,6 +28,7 @@ __all__ = [
     "quantize_mx_fp6",
     "quantize_scaled",
     "fake_quantize_block_scaling_delayed",
+    "fake_quantize_block_scaling_delayed_t",
 ]
 
 
@@ -143,6 +144,14 @@ def fake_quantize_block_scaling_delayed(a: Tensor, dim_x: int, dim_y: int, block
     return _ops.fake_quantize_block_scaling_delayed.default(a, dim_x, dim_y, block_x, block_y, e4m3_threshold, ss_mode, amax_in)
 
 
+def fake_quantize_block_scaling_delayed_t(a: Tensor, dim_x: int, dim_y: int, block_x: int, block_y: int,
+                                          e4m3_threshold: float, ss_mode: int, amax_in: Tensor) -> List[Tensor]:
+    """:func:`fake_quantize_block_scaling_delayed` that also returns the result transposed (``[dim_y, dim_x]``, the
+    layout a weight-gradient GEMM reads), written from the tile while it is on chip: returns
+    ``[out, out_t, meta, amax, non_zero, error]``."""
+    return _ops.fake_quantize_block_scaling_delayed_t.default(a, dim_x, dim_y, block_x, block_y, e4m3_threshold, ss_mode, amax_in)
+
+
 def quantize_mx(a: Tensor, dim_x: int, dim_y: int, block_y: int, elem_format: int) -> List[Tensor]:
     """The real quantized form of :func:`fake_quantize_mx` with a power-of-two scale: returns
     ``[payload, scales]``, both ``uint8``: one narrow-float code per element (fp8 byte for E4M3 / E5M2, the
@@ -189,6 +198,7 @@ for _name, _n in {
     "e4m3_with_e8_scale_rne": 5, "e4m3_with_e8_scale_rz": 5,
     "fake_quantize_mx": 6,
     "fake_quantize_block_scaling_delayed": 8,
+    "fake_quantize_block_scaling_delayed_t": 8,
 }.items():
     torch.library.register_autograd(f"mor::{_name}", _straight_through(_n), setup_context=_no_context)
 del _name, _n

@@ -136,6 +136,27 @@ def block_scaling_delayed(x, thr, ss, amax_in):
             "gerr": float(gerr.item())}
 
 
+def block_scaling_delayed_t(x, thr, ss, amax_in, want_out=True):
+    rows, cols = x.shape
+    d = to_dev(x)
+    out = torch.empty_like(d) if want_out else None
+    out_t = torch.empty(cols, rows, dtype=d.dtype, device="cuda")
+    wsb = cabi.workspace_bytes(cabi.OP_BLOCK_SCALING, rows, cols, 128, 128)
+    ws = torch.empty(wsb, dtype=torch.uint8, device="cuda")
+    f32 = x.dtype == np.float32
+    meta = torch.zeros(1, dtype=torch.int32, device="cuda")
+    gamax = torch.zeros(1, dtype=torch.float32, device="cuda")
+    gerr = torch.zeros(1, dtype=torch.float32, device="cuda")
+    gnnz = torch.zeros(1, dtype=torch.int64 if f32 else torch.int32, device="cuda")
+    ain = torch.tensor([amax_in], dtype=torch.float32, device="cuda")
+    cabi.call("mor_b200_block_scaling_delayed_t", d.data_ptr(), out.data_ptr() if want_out else None, out_t.data_ptr(),
+              dtype_of(x), rows, cols, 128, 128, float(thr), ss, ain.data_ptr(), meta.data_ptr(), gamax.data_ptr(),
+              gnnz.data_ptr(), 1 if f32 else 0, gerr.data_ptr(), ws.data_ptr(), wsb, stream())
+    torch.cuda.synchronize()
+    return {"out": to_np(out) if want_out else None, "out_t": to_np(out_t), "meta": to_np(meta), "gamax": float(gamax.item()),
+            "gnnz": int(gnnz.item()), "gerr": float(gerr.item())}
+
+
 def quantize_mx(x, by, fmt):
     rows, cols = x.shape
     d = to_dev(x)

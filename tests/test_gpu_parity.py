@@ -608,6 +608,30 @@ def test_block_scaling_delayed_amax(dtype, ss, kind):
     assert np.float32(got["gamax"]) == np.float32(true_amax)
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+@pytest.mark.parametrize("ss", [1, 2, 3, 4])
+@pytest.mark.parametrize("thr,want_out", [(0.045, True), (1e-6, True), (0.045, False)])
+def test_block_scaling_delayed_transposed(dtype, ss, thr, want_out):
+    """the single-pass operator's transposed output equals the oracle's result transposed (or the transposed
+    input when the tensor stays BF16), with and without the regular output, on a non-square tensor"""
+    import gpu_harness as H
+    g = torch.Generator().manual_seed(ss * 11 + 3)
+    t = torch.randn(384, 640, generator=g) * 3.0
+    t = torch.where(torch.rand(384, 640, generator=g) < 0.1, 0.0, t)
+    x = t.numpy().copy() if dtype == "f32" else oracle.bf16_bits(t.to(torch.bfloat16))
+    amax, _ = oracle.amax_nnz(x)
+    amax_in = float(np.float32(amax) * np.float32(0.75))
+    out, meta, _, nnz, err = oracle.block_scaling(x, 128, 128, thr, ss, global_amax=amax_in)
+    assert meta == (3 if thr < 1e-3 else 1)
+    got = H.block_scaling_delayed_t(x, thr, ss, amax_in, want_out)
+    assert np.array_equal(got["out_t"].view(np.uint8), np.ascontiguousarray(out.T).view(np.uint8)), "transposed output"
+    if want_out:
+        assert np.array_equal(got["out"].view(np.uint8), np.ascontiguousarray(out).view(np.uint8))
+    assert int(got["meta"][0]) == meta and got["gnnz"] == nnz
+    assert np.float32(got["gerr"]).view(np.uint32) == np.float32(err).view(np.uint32)
+    assert np.float32(got["gamax"]) == np.float32(amax)
+
+
 def test_peer_exchange_wait_runs_out():
     """A rank whose peer never shows up: the exchange kernels give up after their bounded wait, flag the
     workspace, and the ordered sum then reports meta = -1.  The absent peer is a second local buffer that

@@ -175,6 +175,10 @@ def test_additional_operators():
     fq = mor.ops.fake_quantize_block_scaling(xd, R, C, 128, 128, 3e38, 1)[0]
     deq = pq.view(torch.float8_e4m3fn).float() / sq.repeat_interleave(128, 0).repeat_interleave(128, 1)
     assert torch.equal(deq.to(torch.bfloat16).view(torch.int16)[xd != 0], fq.view(torch.int16)[xd != 0])
+    amax_in = xd.float().abs().max().reshape(1)
+    o, ot, m, am, nz, er = mor.ops.fake_quantize_block_scaling_delayed_t(xd, R, C, 128, 128, 3e38, 1, amax_in)
+    assert ot.shape == (C, R) and torch.equal(ot.view(torch.int16), o.t().contiguous().view(torch.int16))
+    same(o, oracle.block_scaling(xb, 128, 128, 3e38, 1)[0], "delayed_t regular output")
     p6, sb6 = mor.ops.quantize_mx_fp6(xd, R, C, 32)
     c6, e6 = oracle.quantize_mx(xb, 32, 3)
     same(p6, oracle.pack_fp6(c6), "quantize_mx_fp6 payload")
@@ -190,6 +194,8 @@ GRAD_OPS = [
     ("fake_quantize_mx", lambda m, x: m.fake_quantize_mx(x, R, C, 32, 0, 2)[0]),
     ("fake_quantize_block_scaling_delayed",
      lambda m, x: m.fake_quantize_block_scaling_delayed(x, R, C, 128, 128, 0.045, 1, torch.ones(1, device="cuda"))[0]),
+    ("fake_quantize_block_scaling_delayed_t",
+     lambda m, x: m.fake_quantize_block_scaling_delayed_t(x, R, C, 128, 128, 0.045, 1, torch.ones(1, device="cuda"))[0]),
 ]
 
 
