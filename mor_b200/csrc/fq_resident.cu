@@ -414,8 +414,12 @@ int launch_resident_t(const ScalingArgs& a, int32_t* meta, float* gamax, void* g
                     &nnz_is_i64, &gerr, &limit};
     if (cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), dim3((unsigned)grid), dim3(R::kThreads), args,
                                     (size_t)R::kSmem, st) != cudaSuccess) {
+        // e.g. fewer SMs than the device reports are available to this process: the grid cannot be resident.
+        // Nothing has run yet (the scalars were zeroed, which the launch sequence does again): take that one,
+        // now and from here on.
         cudaGetLastError();
-        return kErrLaunch;
+        c.checked = -1;
+        return kErrUnsupportedShape;
     }
     return kOk;
 }

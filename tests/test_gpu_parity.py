@@ -676,6 +676,63 @@ def test_peer_exchange_wait_runs_out():
             L.mor_b200_p2p_free(0, b)
 
 
+def test_peer_exchange_recovers_with_new_buffers():
+    """After a wait ran out (meta = -1) the documented recovery is to drop the exchange buffers and set new ones up,
+    with the call counter back at 1.  The absent peer is played by the host here: no second kernel waits on this
+    GPU -- the peer's slot (amax, count, epoch flag) is written with a plain copy before the exchange kernel starts."""
+    import ctypes
+    import struct
+    from mor_b200 import cabi
+    L = cabi.lib()
+    rt = ctypes.CDLL("libcudart.so.12")
+    rt.cudaMemcpy.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]
+    n_err, world = 64, 2
+    nbytes = int(L.mor_b200_p2p_bytes(world, n_err))
+    wsb = cabi.workspace_bytes(cabi.OP_AMAX_NNZ, 1, 1, 1, 1)
+    st = torch.cuda.current_stream().cuda_stream
+    x = torch.randn(4096, device="cuda")
+    amax = torch.zeros(1, dtype=torch.float32, device="cuda")
+    nnz = torch.zeros(1, dtype=torch.int64, device="cuda")
+
+    def fresh_buffers():
+        bufs, handle = [], (ctypes.c_ubyte * 64)()
+        for _ in range(world):
+            p = ctypes.c_void_p()
+            cabi.call("mor_b200_p2p_alloc", 0, nbytes, ctypes.byref(p), handle)
+            bufs.append(int(p.value))
+        return bufs
+
+    def one_call(bufs, epoch, peer_present):
+        ws = torch.zeros(wsb, dtype=torch.uint8, device="cuda")
+        cabi.call("mor_b200_amax_nnz", x.data_ptr(), cabi.FP32, x.numel(), amax.data_ptr(), nnz.data_ptr(), ws.data_ptr(), wsb, st)
+        torch.cuda.synchronize()
+        if peer_present:   # rank 1's slot in rank 0's buffer: 32 bytes at ((epoch & 1) * 16 + 1) * 32
+            slot = struct.pack("<IIQI12x", int(np.float32(7.5).view(np.uint32)), 0, 1000, epoch)
+            assert rt.cudaMemcpy(bufs[0] + ((epoch & 1) * 16 + 1) * 32, slot, len(slot), 1) == 0
+        peers = (ctypes.c_void_p * world)(*bufs)
+        cabi.call("mor_b200_p2p_exchange_scalars", ws.data_ptr(), bufs[0], peers, 0, world, epoch, amax.data_ptr(), nnz.data_ptr(), st)
+        torch.cuda.synchronize()
+        return ws[28:32].view(torch.int32).item(), amax.item(), nnz.item()
+
+    L.mor_b200_p2p_set_wait_limit(1 << 12)
+    bufs = fresh_buffers()
+    try:
+        timed_out, _, _ = one_call(bufs, 1, peer_present=False)
+        assert timed_out == 1                                    # the call that would report meta = -1
+        for b in bufs:
+            L.mor_b200_p2p_free(0, b)
+        bufs = fresh_buffers()                                   # recovery: new buffers, epoch back to 1
+        for epoch in (1, 2, 3):
+            timed_out, a, n = one_call(bufs, epoch, peer_present=True)
+            assert timed_out == 0
+            assert a == max(7.5, float(x.abs().max().item())) and n == 1000 + int((x != 0).sum().item())
+    finally:
+        L.mor_b200_p2p_set_wait_limit(1 << 25)
+        torch.cuda.synchronize()
+        for b in bufs:
+            L.mor_b200_p2p_free(0, b)
+
+
 def test_host_pipeline_matches_device_call():
     """HostScaling (pinned host in/out, double-buffered copies) gives the bits of the device-side call,
     call after call, with a different tensor in every call"""
