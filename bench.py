@@ -522,6 +522,9 @@ def main():
                          "amax_kernel": {"ms_per_launch": amax_ms,
                                          "achieved": rows_local * COLS * 4 / (amax_ms * 1e-3) / 1e9}},
             "phases_us": {k: round(v * 1e3, 2) for k, v in phases_ms.items()},
+            "phases_note": "CUDA events around each phase in back-to-back steps; with pipelined steps exchange2, sum and "
+                           "fallback run on the second stream under the next step's amax pass, so their figures include "
+                           "waiting for free SMs and are not part of the step's critical path",
             "result": result, "verified": verified,
             "clocks": clocks.summary(),
             "gpu_launches": launches * n_gpus,

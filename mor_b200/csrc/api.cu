@@ -72,6 +72,7 @@ Geometry geometry(int kind, int64_t rows, int64_t cols, int br, int bc, int dtyp
 size_t ws_bytes_for(const Geometry& g) { return kHead + round256(4 * (size_t)g.n_amax) + round256(4 * (size_t)g.n_err); }
 
 __global__ void export_scalars_kernel(const ScalarsWs* ws, float* amax_out, long long* nnz_out) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // a cast kernel launched behind this one may start
     if (amax_out) *amax_out = u2f(ws->gamax_bits);
     if (nnz_out) *nnz_out = (long long)ws->gnnz;
 }
@@ -450,6 +451,7 @@ int mor_b200_scaling_cast(int kind, const void* in, void* out, int dtype, int64_
     a.block_amax = reinterpret_cast<float*>(static_cast<char*>(wsp) + kHead);
     a.block_err = block_err_out;
     a.n_err = g.n_err; a.err_slot_stride = g.stride; a.ws = static_cast<ScalarsWs*>(wsp); a.ext_gamax = global_amax;
+    a.early_launch = 1;   // behind the kernel (or collective) that delivers the global amax
     return phase_cast(kind, a, /*store=*/true, false, static_cast<cudaStream_t>(stream));
 }
 

@@ -130,7 +130,9 @@ block_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename T::vec_t
     constexpr int VW = T::kWordsPerVec, LPW = 32 / VW, NT = Tile128<T>::kThreads, NS = Tile128<T>::kStrips;
     constexpr int EPS = 128 / T::kBytesPerElem;  // elements per strip
     constexpr int CI = 2;                        // vectors per lane and row: 128 columns / (LPW lanes x 16 bytes)
-    if (skip_if_fallback && ws->fallback) return;
+    if (skip_if_fallback) {                      // reads what an earlier kernel decided: never launched ahead of it
+        if (ws->fallback) return;
+    }
     extern __shared__ __align__(128) uint8_t s_tile[];
     __shared__ __align__(8) uint64_t s_bar[4];
     __shared__ float wsum[32];
@@ -152,6 +154,11 @@ block_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename T::vec_t
                 tma_load_2d(s_tile + (j * NS + sidx) * 4096, &tmap, bx * 128 + sidx * EPS, by * 128 + j * 32, &s_bar[j]);
         }
     }
+    // When launched as a programmatic dependent (the row-sharded pipeline does, behind the kernel that exchanges
+    // the amax), this CTA may be running before that kernel has finished: the tile is input data and was requested
+    // above, everything the earlier kernels produce (block amax, scalars, the gathered amax) is read below.
+    // Without such a launch the instruction returns at once.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int p = tid % LPW, ty = tid / LPW;
     const typename T::vec_t* tile = reinterpret_cast<const typename T::vec_t*>(s_tile);
     bool arrived = true;
@@ -1333,8 +1340,24 @@ int launch_block_t(const ScalingArgs& a, bool store, bool skip, cudaStream_t st)
     do {                                                                                                             \
         static SmemOptIn opt;                                                                                        \
         if (!opt(block_tile128_kernel<T, E, S>, Tile128<T>::kBytes)) return kErrLaunch;                              \
-        block_tile128_kernel<T, E, S><<<(unsigned)nb, TH, Tile128<T>::kBytes, st>>>(                                  \
-            map, out, cols_vec, (int)bx, a.ss_mode, a.block_amax, a.block_err, a.ws, a.ext_gamax, skip ? 1 : 0);     \
+        if (a.early_launch && !skip) {                                                                               \
+            /* programmatic dependent launch: the CTAs may start, and request their tiles, while the kernel */      \
+            /* before this one in the stream is still running; they wait for it before they read its results */     \
+            cudaLaunchConfig_t cfg = {};                                                                             \
+            cfg.gridDim = dim3((unsigned)nb); cfg.blockDim = dim3(TH);                                               \
+            cfg.dynamicSmemBytes = Tile128<T>::kBytes; cfg.stream = st;                                              \
+            cudaLaunchAttribute attr[1];                                                                             \
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                                         \
+            attr[0].val.programmaticStreamSerializationAllowed = 1;                                                  \
+            cfg.attrs = attr; cfg.numAttrs = 1;                                                                      \
+            typename T::vec_t* no_t = nullptr;                                                                       \
+            if (cudaLaunchKernelEx(&cfg, block_tile128_kernel<T, E, S>, map, out, cols_vec, (int)bx, a.ss_mode,      \
+                                   (const float*)a.block_amax, a.block_err, a.ws, a.ext_gamax, 0, no_t,              \
+                                   (int64_t)0) != cudaSuccess) { cudaGetLastError(); return kErrLaunch; }            \
+        } else {                                                                                                     \
+            block_tile128_kernel<T, E, S><<<(unsigned)nb, TH, Tile128<T>::kBytes, st>>>(                              \
+                map, out, cols_vec, (int)bx, a.ss_mode, a.block_amax, a.block_err, a.ws, a.ext_gamax, skip ? 1 : 0); \
+        }                                                                                                            \
     } while (0)
         if (a.scan_blocks) {
 #define MORB_TILE_SCAN(E)                                                                                            \

@@ -87,6 +87,8 @@ struct ScalingArgs {
     int err_slot_stride;        // the reference stores entry i at slot i * stride of its array
     ScalarsWs* ws;
     const float* ext_gamax;     // optional device pointer: amax of the whole (sharded) tensor
+    int early_launch;           // 1: the 128 x 128 tile kernel may start before the previous kernel of the stream has
+                                // finished (it waits for it before reading anything that kernel writes)
     void* out_t;                // optional: the output transposed, [cols, rows] (single-pass 128 x 128 tile kernel only)
     int scan_blocks;            // 1: single pass -- the cast kernel takes each block's amax from the tile it
                                 // has staged and publishes the tensor's amax / non-zero count itself

@@ -61,6 +61,8 @@ __device__ __forceinline__ bool wait_epoch(const uint32_t* flag, uint32_t epoch,
 __global__ void p2p_exchange_scalars_kernel(ScalarsWs* __restrict__ ws, unsigned char* __restrict__ mine, PeerPtrs peers,
                                             int rank, int world, uint32_t epoch, float* __restrict__ gamax_out,
                                             long long* __restrict__ gnnz_out, uint32_t limit) {
+    // the cast kernel behind this one may start now: it requests its tiles and then waits for this kernel to finish
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int p = threadIdx.x;
     const uint32_t par = epoch & 1u;
     uint32_t amax_bits = 0u;
