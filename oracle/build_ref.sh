@@ -6,10 +6,11 @@
 # only tests/golden/make_gpu_golden.py loads it, in a process of its own, to record
 # the reference's outputs on a GPU.  Nothing in the product imports it.
 #
-# usage: oracle/build_ref.sh [reference_root]     (default: the reference checkout beside this repository's parent)
+# usage: oracle/build_ref.sh [reference_root]
+#        (default: $MOR_REFERENCE_ROOT, else the folder "reference" beside this repository)
 set -euo pipefail
-REF="${1:-/root/reference}"
 HERE="$(cd "$(dirname "$0")" && pwd)"
+REF="${1:-${MOR_REFERENCE_ROOT:-$(dirname "$(dirname "$HERE")")/reference}}"
 OUT="$HERE/_ref"
 mkdir -p "$OUT"
 TI="$(python -c 'import torch,os;print(os.path.dirname(torch.__file__))')"

@@ -1,7 +1,7 @@
 """Record golden vectors from the UNMODIFIED reference extension on a CUDA GPU.
 
     oracle/build_ref.sh                      # builds oracle/_ref/mor_ref_C.so (needs the reference sources)
-    python tests/golden/make_gpu_golden.py   # on a machine with a GPU
+    python tests/golden/make_gpu_golden.py [--out-dir DIR]   # on a machine with a GPU
 
 Loads ``oracle/_ref/mor_ref_C.so`` -- the reference's two translation units compiled
 as they are -- in this process only (it registers ``torch.ops.mor.*``, so the
@@ -10,7 +10,7 @@ repository's own extension must not be imported here), runs every case of
 
     tests/golden/reference_b200.json   per case: sha256 of the output bits, the meta
                                        matrix and the scalar outputs (as bit patterns)
-    <run-output folder>/golden_report.txt   case-by-case comparison with the CPU oracle
+    <out-dir>/golden_report.txt            case-by-case comparison with the CPU oracle
 
 Before a case runs on the GPU the CPU oracle evaluates it: a case on which a
 device-side assert() of the reference would fire (the reference is built with asserts
@@ -80,6 +80,11 @@ def canon(out: np.ndarray) -> np.ndarray:
 
 
 def main() -> int:
+    import argparse
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--out-dir", default=os.path.join(ROOT, "golden_out"),
+                    help="folder for the report, mismatch dumps and a copy of the golden file")
+    out_dir = ap.parse_args().out_dir
     ref_so = os.path.join(ROOT, "oracle", "_ref", "mor_ref_C.so")
     if not os.path.exists(ref_so):
         print(f"{ref_so} missing: run oracle/build_ref.sh where the reference sources are", file=sys.stderr)
@@ -88,8 +93,8 @@ def main() -> int:
         print("no CUDA device", file=sys.stderr)
         return 2
     torch.ops.load_library(ref_so)
-    os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
-    report = open(os.path.join(ROOT, "gpurun_out", "golden_report.txt"), "w")
+    os.makedirs(out_dir, exist_ok=True)
+    report = open(os.path.join(out_dir, "golden_report.txt"), "w")
     golden = {"device": torch.cuda.get_device_name(0), "torch": torch.__version__, "cases": {}}
     n_bad = 0
     for name, op, fn, kw in cases():
@@ -124,7 +129,7 @@ def main() -> int:
             bad = np.nonzero(a != b)[0]
             msgs.append(f"out differs at {bad.size} of {a.size}; first idx {bad[:5].tolist()} "
                         f"ref {a[bad[:5]].tolist()} oracle {b[bad[:5]].tolist()} in {x.reshape(-1)[bad[:5]].tolist()}")
-            np.savez_compressed(os.path.join(ROOT, "gpurun_out", f"golden_mismatch_{name}.npz"), x=x,
+            np.savez_compressed(os.path.join(out_dir, f"golden_mismatch_{name}.npz"), x=x,
                                 ref=got["out"], oracle=exp["out"])
         if "meta" in got and not np.array_equal(got["meta"].reshape(-1), np.asarray(exp["meta"]).reshape(-1)):
             msgs.append(f"meta ref {got['meta'].reshape(-1).tolist()} oracle {np.asarray(exp['meta']).reshape(-1).tolist()}")
@@ -139,7 +144,7 @@ def main() -> int:
     with open(os.path.join(HERE, "reference_b200.json"), "w") as f:
         json.dump(golden, f, indent=1, sort_keys=True)
     # a copy in the folder that travels back from a remote GPU run
-    with open(os.path.join(ROOT, "gpurun_out", "reference_b200.json"), "w") as f:
+    with open(os.path.join(out_dir, "reference_b200.json"), "w") as f:
         json.dump(golden, f, indent=1, sort_keys=True)
     report.write(f"cases {len(golden['cases'])}, oracle mismatches {n_bad}\n")
     report.close()
