@@ -177,7 +177,7 @@ template <> __device__ __forceinline__ uint4 tile_pack<4>(const uint32_t (&w)[4]
 template <> __device__ __forceinline__ uint2 tile_pack<2>(const uint32_t (&w)[2]) { return make_uint2(w[0], w[1]); }
 
 template <int SF, int VW>
-__global__ void __launch_bounds__(512 / VW)
+__global__ void __launch_bounds__(512 / VW, VW == 2 ? 4 : 7)
 fq_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename TileVec<VW>::type* __restrict__ out, int32_t* __restrict__ meta,
                   int64_t cols_vec, int blocks_x, float clamp, int qmode, int dyn_mode, int table_entries) {
     extern __shared__ __align__(128) uint8_t s_tile[];  // [4 strips][128 rows][64 B], then the error table
@@ -217,16 +217,32 @@ fq_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename TileVec<VW>
     // (a zero becomes 0x7FFF, the largest; a magnitude m becomes 0x8000 + m - 1, ordered by
     // m).  NaN patterns, which the reference's fmaxf/fminf ignore, sort above infinity: a
     // tile that holds one is scanned again with the per-element form.
+    //
+    // RT (the 256-thread variant): the thread's 64 elements are read from shared memory once and stay in
+    // registers for the passes that follow; the error pass then reuses the first half of the tile's space.
+    constexpr bool RT = VW == 2;
+    uint32_t tw[RT ? 16 : 1][VW];
     uint32_t pmx = 0u, pmn = 0x7FFF7FFFu;
-#pragma unroll 4
-    for (int n = 0; n < 16; ++n) {
-        uint32_t w[VW];
-        tile_unpack<VW>(chunk(n >> 2, n & 3), w);
+    if constexpr (RT) {
 #pragma unroll
-        for (int q = 0; q < VW; q += 2) {
-            const uint32_t m0 = mag2(w[q]), m1 = mag2(w[q + 1]);
+        for (int n = 0; n < 16; ++n) tile_unpack<VW>(chunk(n >> 2, n & 3), tw[n]);
+#pragma unroll
+        for (int n = 0; n < 16; ++n) {
+            const uint32_t m0 = mag2(tw[n][0]), m1 = mag2(tw[n][1]);
             pmx = umax16x2_3(pmx, m0, m1);
             pmn = smin16x2_3(pmn, m0 + 0x7FFF7FFFu, m1 + 0x7FFF7FFFu);
+        }
+    } else {
+#pragma unroll 4
+        for (int n = 0; n < 16; ++n) {
+            uint32_t w[VW];
+            tile_unpack<VW>(chunk(n >> 2, n & 3), w);
+#pragma unroll
+            for (int q = 0; q < VW; q += 2) {
+                const uint32_t m0 = mag2(w[q]), m1 = mag2(w[q + 1]);
+                pmx = umax16x2_3(pmx, m0, m1);
+                pmn = smin16x2_3(pmn, m0 + 0x7FFF7FFFu, m1 + 0x7FFF7FFFu);
+            }
         }
     }
 #pragma unroll
@@ -310,7 +326,9 @@ fq_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename TileVec<VW>
             const int n_pat = (int)(amax_pat - amin_pat) + 1;
             const int q_fold = max((n_pat >> 7) - 11, 1);
             const int n_tab = 128 * (q_fold + 1);          // entries 0 .. n_tab - 1
-            if (!has_nan && n_tab <= table_entries) {
+            // (the periodicity needs normal numbers throughout: a block whose amax is below 2^-96 could
+            // meet denormal quotients q / scale in the folded rows, and takes the per-element form)
+            if (!has_nan && n_tab <= table_entries && amax_pat >= 0x0F80u) {
                 float2* tab = reinterpret_cast<float2*>(s_tile + kTileBytes);
                 if (tid == 0) tab[0] = make_float2(0.0f, 0.0f);
                 for (int i = 1 + 2 * tid; i < n_tab; i += 2 * NT) {  // two consecutive patterns per step
@@ -324,18 +342,45 @@ fq_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename TileVec<VW>
                 }
                 __syncthreads();
                 const int base = (int)amin_pat - 1, fold = q_fold << 7;
-#pragma unroll 2
-                for (int n = 0; n < 16; ++n) {  // rows outer (j = n / 4), words inner (i = n % 4)
-                    uint32_t w[VW];
-                    tile_unpack<VW>(chunk(n >> 2, n & 3), w);
+                if constexpr (RT) {
+                    // Nearly every element of real data lies in the folded rows, whose 128 entries are indexed
+                    // by the seven mantissa bits alone.  Sixteen copies of that row, interleaved so that lane r
+                    // of a half-warp reads only bank pair r, make those lookups free of bank conflicts; they
+                    // take the place of the tile's first 16 KiB (every thread holds its elements in registers).
+                    // The few elements below the folded rows (and zeros) read the full table instead.
+                    float2* rep = reinterpret_cast<float2*>(s_tile);
+                    for (int i = tid; i < 2048; i += NT) rep[i] = tab[fold + (((i >> 4) - base) & 127)];
+                    __syncthreads();
+                    const uint32_t thr = (uint32_t)(base + fold);   // magnitude patterns from here up are folded
+                    const uint8_t* repl = s_tile + (tid & 15) * 8;
 #pragma unroll
-                    for (int k = 0; k < VW; ++k) {
-                        int il = max((int)(w[k] & 0x7FFFu) - base, 0), ih = max((int)((w[k] >> 16) & 0x7FFFu) - base, 0);
-                        il = min(il, (il & 127) | fold);
-                        ih = min(ih, (ih & 127) | fold);
-                        const float2 el = tab[il], eh = tab[ih];
-                        a4[k] = __fadd_rn(a4[k], __fadd_rn(eh.x, el.x));
-                        a5[k] = __fadd_rn(a5[k], __fadd_rn(eh.y, el.y));
+                    for (int n = 0; n < 16; ++n) {  // rows outer (j = n / 4), words inner (i = n % 4)
+#pragma unroll
+                        for (int k = 0; k < VW; ++k) {
+                            const uint32_t w = tw[n][k];
+                            const uint32_t ml = w & 0x7FFFu, mh = (w >> 16) & 0x7FFFu;
+                            float2 el = *reinterpret_cast<const float2*>(repl + ((w & 0x7Fu) << 7));
+                            float2 eh = *reinterpret_cast<const float2*>(repl + ((w >> 9) & 0x3F80u));
+                            if (ml < thr) el = tab[max((int)ml - base, 0)];
+                            if (mh < thr) eh = tab[max((int)mh - base, 0)];
+                            a4[k] = __fadd_rn(a4[k], __fadd_rn(eh.x, el.x));
+                            a5[k] = __fadd_rn(a5[k], __fadd_rn(eh.y, el.y));
+                        }
+                    }
+                } else {
+#pragma unroll 2
+                    for (int n = 0; n < 16; ++n) {  // rows outer (j = n / 4), words inner (i = n % 4)
+                        uint32_t w[VW];
+                        tile_unpack<VW>(chunk(n >> 2, n & 3), w);
+#pragma unroll
+                        for (int k = 0; k < VW; ++k) {
+                            int il = max((int)(w[k] & 0x7FFFu) - base, 0), ih = max((int)((w[k] >> 16) & 0x7FFFu) - base, 0);
+                            il = min(il, (il & 127) | fold);
+                            ih = min(ih, (ih & 127) | fold);
+                            const float2 el = tab[il], eh = tab[ih];
+                            a4[k] = __fadd_rn(a4[k], __fadd_rn(eh.x, el.x));
+                            a5[k] = __fadd_rn(a5[k], __fadd_rn(eh.y, el.y));
+                        }
                     }
                 }
             } else {
@@ -374,8 +419,13 @@ fq_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename TileVec<VW>
     V* dst = out + ((int64_t)by * 128) * cols_vec + (int64_t)bx * (4 * LPR);   // cols_vec in units of V
     auto store = [&](int n, const V& v) { st_stream(dst + (int64_t)(ty + 32 * (n >> 2)) * cols_vec + LPR * (n & 3) + a, v); };
     if (fmt < 0) {
+        if constexpr (RT) {
+#pragma unroll
+            for (int n = 0; n < 16; ++n) store(n, tile_pack<VW>(tw[n]));
+        } else {
 #pragma unroll 4
-        for (int n = 0; n < 16; ++n) store(n, chunk(n >> 2, n & 3));
+            for (int n = 0; n < 16; ++n) store(n, chunk(n >> 2, n & 3));
+        }
         return;
     }
     const float s = __fdiv_rn(fmt == kE2M3 ? 7.5f : (fmt == kE4M3 ? 448.0f : 57344.0f), amax);
@@ -386,13 +436,23 @@ fq_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename TileVec<VW>
         __syncthreads();
         auto cast_all = [&](auto fmt_tag) {
             constexpr int F = decltype(fmt_tag)::value;
-#pragma unroll 2
-            for (int n = 0; n < 16; ++n) {
-                uint32_t w[VW];
-                tile_unpack<VW>(chunk(n >> 2, n & 3), w);
+            if constexpr (RT) {
 #pragma unroll
-                for (int q = 0; q < VW; ++q) w[q] = lut_word<F>(s_lut16, w[q], s);
-                store(n, tile_pack<VW>(w));
+                for (int n = 0; n < 16; ++n) {
+                    uint32_t w[VW];
+#pragma unroll
+                    for (int q = 0; q < VW; ++q) w[q] = lut_word<F>(s_lut16, tw[n][q], s);
+                    store(n, tile_pack<VW>(w));
+                }
+            } else {
+#pragma unroll 2
+                for (int n = 0; n < 16; ++n) {
+                    uint32_t w[VW];
+                    tile_unpack<VW>(chunk(n >> 2, n & 3), w);
+#pragma unroll
+                    for (int q = 0; q < VW; ++q) w[q] = lut_word<F>(s_lut16, w[q], s);
+                    store(n, tile_pack<VW>(w));
+                }
             }
         };
         if (fmt == kE4M3) cast_all(std::integral_constant<int, kE4M3>{});
@@ -402,13 +462,23 @@ fq_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename TileVec<VW>
         const E8Consts c = e8_consts(s);
         auto cast_all = [&](auto fmt_tag) {
             constexpr int F = decltype(fmt_tag)::value;
-#pragma unroll 2
-            for (int n = 0; n < 16; ++n) {
-                uint32_t w[VW];
-                tile_unpack<VW>(chunk(n >> 2, n & 3), w);
+            if constexpr (RT) {
 #pragma unroll
-                for (int q = 0; q < VW; ++q) w[q] = e8_word<F>(w[q], c);
-                store(n, tile_pack<VW>(w));
+                for (int n = 0; n < 16; ++n) {
+                    uint32_t w[VW];
+#pragma unroll
+                    for (int q = 0; q < VW; ++q) w[q] = e8_word<F>(tw[n][q], c);
+                    store(n, tile_pack<VW>(w));
+                }
+            } else {
+#pragma unroll 2
+                for (int n = 0; n < 16; ++n) {
+                    uint32_t w[VW];
+                    tile_unpack<VW>(chunk(n >> 2, n & 3), w);
+#pragma unroll
+                    for (int q = 0; q < VW; ++q) w[q] = e8_word<F>(w[q], c);
+                    store(n, tile_pack<VW>(w));
+                }
             }
         };
         if (fmt == kE4M3) cast_all(std::integral_constant<int, kE4M3>{});

@@ -227,10 +227,11 @@ def test_fake_quantize_ragged_and_odd_blocks(rows, cols, bx, by, mode):
         assert_same(H.fake_quantize(x, bx, by, 1e-15, mode, sf), exp, f"{rows}x{cols} block {bx}x{by} mode {mode} sf {sf}")
 
 
-@pytest.mark.parametrize("shift", [-96, 90])
+@pytest.mark.parametrize("shift", [-118, -112, -104, -96, 90])
 @pytest.mark.parametrize("sf", [1, 2])
 def test_mor_error_pass_with_extreme_magnitudes(shift, sf):
-    """blocks scaled by 2^-96 / 2^90 leave the range of the short exact quotient: the IEEE division takes over"""
+    """blocks scaled by 2^-96 / 2^90 leave the range of the short exact quotient: the IEEE division takes over;
+    below that the quotients q / scale turn denormal, where the error table's binade folding does not hold"""
     import gpu_harness as H
     from cases import mixed_blocks_bf16
     from ref_fixtures import bits_to_bf16, bf16_bits
