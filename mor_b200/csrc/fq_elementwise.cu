@@ -244,41 +244,71 @@ __global__ void __launch_bounds__(kThreads) block_scales_kernel(const float* __r
     if (i < n_blocks) scales[i] = payload_scale(ss, gamax, fabsf(block_amax[i]));   // the sign bit of a stored amax is a flag
     if (i == 0 && gamax_out) *gamax_out = gamax;
 }
-// One 16-byte vector of input per thread and step: E4M3 bytes of RN(x * scale), a zero element -> code 0.
-// The scale of an element is scales[(row / brows) * blocks_x + col / bcols]; a vector never straddles two
-// blocks unless bcols == 1 (one scale per column), where every element looks its own scale up.
+// E4M3 bytes of RN(x * scale), a zero element -> code 0.  A thread owns one 16-byte vector column and walks
+// `rows_per_cta` consecutive rows, four loads in flight; its scale(s) change only when the walk enters the next
+// row of blocks, so no index arithmetic is left per element.  The scale of an element is
+// scales[(row / brows) * blocks_x + col / bcols]; a vector never straddles two blocks unless bcols == 1 (one
+// scale per column), where the thread keeps one scale per element.
 template <typename T>
 __global__ void __launch_bounds__(kThreads) quantize_scaled_kernel(const typename T::vec_t* __restrict__ in,
                                                                    uint8_t* __restrict__ payload,
-                                                                   const float* __restrict__ scales, int64_t nvec,
-                                                                   int64_t cols_vec, int brows, int bcols, int64_t blocks_x) {
+                                                                   const float* __restrict__ scales, int64_t rows,
+                                                                   int cols_vec, int brows, int bcols, int blocks_x,
+                                                                   int rows_per_cta) {
     constexpr int EPV = 16 / T::kBytesPerElem;
-    const int64_t stride = (int64_t)gridDim.x * kThreads;
-    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < nvec; i += stride) {
-        const typename T::vec_t v = ld_stream(in + i);
-        const int64_t r = i / cols_vec, c0 = (i - r * cols_vec) * EPV;
-        const int64_t brow = (r / brows) * blocks_x;
-        uint32_t codes[EPV / 2];
-        const float s_all = bcols == 1 ? 0.0f : __ldg(scales + brow + c0 / bcols);
+    const int cv = blockIdx.x * kThreads + threadIdx.x;
+    if (cv >= cols_vec) return;
+    const bool per_col = bcols == 1;
+    const int bc = per_col ? cv * EPV : cv * EPV / bcols;
+    int64_t r = (int64_t)blockIdx.y * rows_per_cta;
+    const int64_t r_end = r + rows_per_cta < rows ? r + rows_per_cta : rows;
+    int64_t br = r / brows;
+    int rem = (int)(r - br * brows);
+    float s[EPV];
+    auto load_scales = [&]() {
+        const float* p = scales + br * blocks_x + bc;
+        const float first = __ldg(p);
 #pragma unroll
-        for (int k = 0; k < T::kWordsPerVec; ++k) {
-            float hi, lo;
-            T::unpack(v, k, hi, lo);
-            const float sl = bcols == 1 ? __ldg(scales + brow + c0 + 2 * k) : s_all;
-            const float sh = bcols == 1 ? __ldg(scales + brow + c0 + 2 * k + 1) : s_all;
-            uint32_t c = cvt_codes<kE4M3>(__fmul_rn(hi, sh), __fmul_rn(lo, sl));
-            if (hi == 0.0f) c &= 0x00FFu;     // zeros (of either sign) are stored as +0
-            if (lo == 0.0f) c &= 0xFF00u;
-            codes[k] = c;                     // low byte: element 2k, high byte: element 2k + 1
+        for (int j = 0; j < EPV; ++j) s[j] = per_col ? __ldg(p + j) : first;
+    };
+    load_scales();
+    const typename T::vec_t* src = in + r * cols_vec + cv;
+    uint8_t* dst = payload + (r * cols_vec + cv) * EPV;
+    for (; r < r_end; r += 4) {
+        typename T::vec_t v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (r + u < r_end) v[u] = ld_stream(src + (int64_t)u * cols_vec);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (r + u >= r_end) break;
+            uint32_t codes[EPV / 2];
+#pragma unroll
+            for (int k = 0; k < T::kWordsPerVec; ++k) {
+                float hi, lo;
+                T::unpack(v[u], k, hi, lo);
+                uint32_t c = cvt_codes<kE4M3>(__fmul_rn(hi, s[2 * k + 1]), __fmul_rn(lo, s[2 * k]));
+                if (hi == 0.0f) c &= 0x00FFu;     // zeros (of either sign) are stored as +0
+                if (lo == 0.0f) c &= 0xFF00u;
+                codes[k] = c;                     // low byte: element 2k, high byte: element 2k + 1
+            }
+            uint8_t* d = dst + (int64_t)u * cols_vec * EPV;
+            if constexpr (EPV == 8) {
+                uint2 o;
+                o.x = codes[0] | (codes[1] << 16);
+                o.y = codes[2] | (codes[3] << 16);
+                *reinterpret_cast<uint2*>(d) = o;
+            } else {
+                *reinterpret_cast<uint32_t*>(d) = codes[0] | (codes[1] << 16);
+            }
+            if (++rem == brows) {   // the next row belongs to the next row of blocks
+                rem = 0;
+                ++br;
+                if (r + u + 1 < r_end) load_scales();
+            }
         }
-        if constexpr (EPV == 8) {
-            uint2 o;
-            o.x = codes[0] | (codes[1] << 16);
-            o.y = codes[2] | (codes[3] << 16);
-            *reinterpret_cast<uint2*>(payload + i * 8) = o;
-        } else {
-            *reinterpret_cast<uint32_t*>(payload + i * 4) = codes[0] | (codes[1] << 16);
-        }
+        src += (int64_t)4 * cols_vec;
+        dst += (int64_t)4 * cols_vec * EPV;
     }
 }
 
@@ -347,10 +377,14 @@ int launch_quantize_scaled(const void* in, int is_fp32, uint8_t* payload, float*
     int rc = check_launch();
     if (rc) return rc;
     const int epv = is_fp32 ? 4 : 8;
-    const int64_t nvec = rows * cols / epv, cols_vec = cols / epv, blocks_x = cols / bcols;
-    const int g = grid_for(nvec);
-    if (is_fp32) quantize_scaled_kernel<Fp32><<<g, kThreads, 0, st>>>(static_cast<const float4*>(in), payload, scales, nvec, cols_vec, brows, bcols, blocks_x);
-    else quantize_scaled_kernel<Bf16><<<g, kThreads, 0, st>>>(static_cast<const uint4*>(in), payload, scales, nvec, cols_vec, brows, bcols, blocks_x);
+    const int64_t cols_vec = cols / epv, blocks_x = cols / bcols;
+    if (cols_vec >= (int64_t(1) << 31) || blocks_x >= (int64_t(1) << 31)) return kErrTooLarge;
+    int64_t rpc = 16;                                     // rows per CTA; grid.y is limited to 65535
+    if ((rows + rpc - 1) / rpc > 65535) rpc = (rows + 65534) / 65535;
+    if (rpc >= (int64_t(1) << 31)) return kErrTooLarge;
+    const dim3 grid((unsigned)((cols_vec + kThreads - 1) / kThreads), (unsigned)((rows + rpc - 1) / rpc));
+    if (is_fp32) quantize_scaled_kernel<Fp32><<<grid, kThreads, 0, st>>>(static_cast<const float4*>(in), payload, scales, rows, (int)cols_vec, brows, bcols, (int)blocks_x, (int)rpc);
+    else quantize_scaled_kernel<Bf16><<<grid, kThreads, 0, st>>>(static_cast<const uint4*>(in), payload, scales, rows, (int)cols_vec, brows, bcols, (int)blocks_x, (int)rpc);
     return check_launch();
 }
 

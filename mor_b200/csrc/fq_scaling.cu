@@ -118,8 +118,9 @@ template <typename T> struct Tile128 {
 
 // TRANS (single pass only): the results also go out transposed (out_t is [cols, rows], the layout a
 // weight-gradient GEMM reads), from the tile itself: every thread puts its result vectors back where it
-// read the inputs, and after a barrier each warp walks 32 consecutive columns -- one lane per column, 2- or
-// 4-byte shared loads down the rows, conflict-free -- and stores 16 or 32 bytes of a transposed row per lane.
+// read the inputs (in the same strip row, at a chunk position rotated by the row), and after a barrier eight
+// lanes per column gather 8 or 4 consecutive rows each -- 2- or 4-byte shared loads, conflict-free thanks to
+// the rotation -- and store 128 contiguous bytes of a transposed row.
 // `out` may then be NULL (transposed output only).
 template <typename T, bool E8, bool STORE, bool SCAN = false, bool TRANS = false>
 __global__ void __launch_bounds__(Tile128<T>::kThreads, Tile128<T>::kCtasPerSm)
@@ -272,7 +273,9 @@ block_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename T::vec_t
     auto run = [&](const auto& path, auto fd_tag, auto nz_tag) {
         constexpr int FD = (T::kBytesPerElem != 2) ? kDivIeee : (decltype(fd_tag)::value ? kDivBf16 : kDivBf16Any);
         for (int j = 0; j < 4; ++j) {
-            if (!mbar_wait_bounded(&s_bar[j], 0)) { arrived = false; return; }
+            bool landed = mbar_wait_bounded(&s_bar[j], 0);
+            if constexpr (TRANS) landed = __all_sync(0xFFFFFFFFu, landed);   // the warp stays together: it synchronises below
+            if (!landed) { arrived = false; return; }
 #pragma unroll
             for (int i = 0; i < CI; ++i) {
                 const int vc = p + LPW * i;
@@ -280,7 +283,12 @@ block_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename T::vec_t
                 typename T::vec_t o;
                 err_vec<T, std::decay_t<decltype(path)>, STORE, FD, decltype(nz_tag)::value>(path, v, o, acc);
                 if constexpr (TRANS) {
-                    const_cast<typename T::vec_t*>(tile)[((j * NS + (vc >> 3)) * 32 + ty) * 8 + (vc & 7)] = o;
+                    // parked in the strip row it came from, at chunk (vc & 7) ^ f(row): the eight lanes that read
+                    // this strip row are lanes of this warp and have their inputs by now
+                    __syncwarp();
+                    constexpr int EPVT = 16 / T::kBytesPerElem;
+                    const int f = ((32 * j + ty) / EPVT) & 7;
+                    const_cast<typename T::vec_t*>(tile)[((j * NS + (vc >> 3)) * 32 + ty) * 8 + ((vc & 7) ^ f)] = o;
                     if (out) st_stream(dst + (int64_t)(32 * j) * cols_vec + LPW * i, o);
                 } else if constexpr (STORE) {
                     st_stream(dst + (int64_t)(32 * j) * cols_vec + LPW * i, o);
@@ -319,24 +327,27 @@ block_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename T::vec_t
         if (tid == 0) block_err[b] = t;
     }
     if constexpr (TRANS) {
-        // element (r, c) of the tile sits at [r / 32][strip of c][r % 32][byte of c in the strip]
+        // Element (r, c) of the tile sits at [r / 32][strip of c][r % 32][chunk of c ^ f(r)][byte of c in its chunk],
+        // f(r) = (r / EPV) & 7.  Eight lanes share a column: lane `sub` takes EPV consecutive rows (one 16-byte
+        // piece of the transposed row) and the eight pieces are 128 contiguous bytes; a warp stores four such
+        // lines per instruction.  The eight lanes of a column read eight different chunks (f = sub), the four
+        // columns of an instruction are the words of one chunk: no bank conflicts.
         using E = std::conditional_t<T::kBytesPerElem == 2, uint16_t, uint32_t>;
         constexpr int EPV = 16 / T::kBytesPerElem;          // elements of a 16-byte store: 8 / 4 rows of one column
-        constexpr int NW = NT / 32;                          // 8 / 16 warps: four column groups x 2 / 4 row ranges
-        constexpr int ROWS_PER_WARP = 128 / (NW / 4);        // 64 / 32
-        const int lane = tid & 31, w = tid >> 5;
-        const int c = (w & 3) * 32 + lane;                   // this lane's column of the tile
-        const int r_begin = (w >> 2) * ROWS_PER_WARP;
-        const uint8_t* col = s_tile + ((c * T::kBytesPerElem) >> 7) * 4096 + ((c * T::kBytesPerElem) & 127);
-        typename T::vec_t* trow = out_t + ((int64_t)bx * 128 + c) * rows_vec + (int64_t)by * (128 / EPV);
+        constexpr int NW = NT / 32;                          // 8 / 16 warps
+        constexpr int RPI = 8 * EPV;                         // rows per warp instruction: 64 / 32
+        constexpr int STEPS = (128 / 4) * (128 / RPI);       // (groups of four columns) x (row ranges): 64 / 128
+        const int lane = tid & 31, w = tid >> 5, sub = lane & 7, colsel = lane >> 3;
 #pragma unroll 2
-        for (int r0 = r_begin; r0 < r_begin + ROWS_PER_WARP; r0 += EPV) {
+        for (int t = w; t < STEPS; t += NW) {
+            const int c = 4 * (t / (128 / RPI)) + colsel;
+            const int r0 = RPI * (t % (128 / RPI)) + EPV * sub;
+            const int cb = c * T::kBytesPerElem;             // byte of the column in a tile row
+            const uint8_t* src = s_tile + (r0 >> 5) * (NS * 4096) + (cb >> 7) * 4096 + (r0 & 31) * 128 +
+                                 ((((cb & 127) >> 4) ^ sub) << 4) + (cb & 15);
             E e[EPV];
 #pragma unroll
-            for (int k = 0; k < EPV; ++k) {
-                const int r = r0 + k;
-                e[k] = *reinterpret_cast<const E*>(col + (r >> 5) * (NS * 4096) + (r & 31) * 128);
-            }
+            for (int k = 0; k < EPV; ++k) e[k] = *reinterpret_cast<const E*>(src + k * 128);
             typename T::vec_t o;
             if constexpr (T::kBytesPerElem == 2) {
                 o.x = (uint32_t)e[0] | ((uint32_t)e[1] << 16); o.y = (uint32_t)e[2] | ((uint32_t)e[3] << 16);
@@ -344,7 +355,7 @@ block_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename T::vec_t
             } else {
                 o.x = __uint_as_float(e[0]); o.y = __uint_as_float(e[1]); o.z = __uint_as_float(e[2]); o.w = __uint_as_float(e[3]);
             }
-            st_stream(trow + r0 / EPV, o);
+            st_stream(out_t + ((int64_t)bx * 128 + c) * rows_vec + (int64_t)by * (128 / EPV) + r0 / EPV, o);
         }
     }
 }
@@ -1053,22 +1064,24 @@ colgroup_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::v
 }
 
 // The same CTA as real threads, fed by TMA: thread (tx, ty) of 32 x 16 owns word tx (columns 2 tx and 2 tx + 1,
-// each with its own scale) of rows ty, ty + 16, ... of a strip of 64 columns.  Boxes of 64 columns x 64 (or 16)
-// rows travel through a ring of four shared-memory stages: one mbarrier per stage says "full" (the copy has
-// landed), one says "empty" (all sixteen warps are done with it) and lets thread 0 request the box four ahead.
+// each with its own scale) of rows ty, ty + 16, ... of a strip of 64 columns.  Boxes of 64 columns x 16 KiB worth
+// of rows (or 64, or 16 rows, whichever divides the group) travel through a ring of up to eight shared-memory
+// stages -- a strip is one CTA, one SM, and it takes that many bytes in flight to keep the SM's share of the
+// memory system busy: one mbarrier per stage says "full" (the copy has landed), one says "empty" (all sixteen
+// warps are done with it) and lets thread 0 request the box `stages` ahead.
 // Binary32 scales use one table of quotients per column (64 x 256 entries, filled once per CTA).
-constexpr int kColStages = 4, kColThreads = 512;
+constexpr int kColStages = 8, kColThreads = 512;
 template <typename T> struct ColStrip {
     static constexpr int kRowBytes = 64 * T::kBytesPerElem;           // 128 / 256
-    static constexpr int kMaxBoxRows = 64;
-    static constexpr int kRingBytes = kColStages * kMaxBoxRows * kRowBytes;
+    static constexpr int kMaxBoxRows = 16384 / kRowBytes;             // 128 / 64
+    static constexpr int kStageBytes = kMaxBoxRows * kRowBytes;       // 16 KiB
     static constexpr int kLutBytes = 64 * 256 * 4;
 };
 
 template <typename T, bool E8, bool STORE>
 __global__ void __launch_bounds__(kColThreads)
 colstrip_tma_kernel(const __grid_constant__ CUtensorMap tmap, void* __restrict__ out_raw, int64_t cols, int brows,
-                    int box_rows, int ss, const float* __restrict__ block_amax, float* __restrict__ block_err,
+                    int box_rows, int stages, int ss, const float* __restrict__ block_amax, float* __restrict__ block_err,
                     ScalarsWs* __restrict__ ws, const float* __restrict__ ext_gamax, int skip_if_fallback) {
     using W = typename PairWord<T>::type;
     using CS = ColStrip<T>;
@@ -1078,7 +1091,7 @@ colstrip_tma_kernel(const __grid_constant__ CUtensorMap tmap, void* __restrict__
     __shared__ __align__(8) uint64_t s_full[kColStages], s_empty[kColStages];
     __shared__ float s_sf[64];
     __shared__ float s_wsum[32];
-    float* s_lut = reinterpret_cast<float*>(s_col + CS::kRingBytes);
+    float* s_lut = reinterpret_cast<float*>(s_col + stages * CS::kStageBytes);
     const int tid = threadIdx.x, tx = tid & 31, ty = tid >> 5;
     const int64_t ctas_x = cols / 64;
     const int64_t rb = blockIdx.x / ctas_x, cx = blockIdx.x % ctas_x;
@@ -1090,9 +1103,9 @@ colstrip_tma_kernel(const __grid_constant__ CUtensorMap tmap, void* __restrict__
     }
     __syncthreads();
     if (tid == 0) {
-        for (int b = 0; b < kColStages && b < n_boxes; ++b) {
+        for (int b = 0; b < stages && b < n_boxes; ++b) {
             mbar_expect_tx(&s_full[b], box_bytes);
-            tma_load_2d(s_col + b * (CS::kMaxBoxRows * CS::kRowBytes), &tmap, (int)(cx * 64), (int)(rb * brows + (int64_t)b * box_rows), &s_full[b]);
+            tma_load_2d(s_col + b * CS::kStageBytes, &tmap, (int)(cx * 64), (int)(rb * brows + (int64_t)b * box_rows), &s_full[b]);
         }
     }
     // the scales of the strip's 64 columns (and their tables), while the first boxes travel
@@ -1114,10 +1127,10 @@ colstrip_tma_kernel(const __grid_constant__ CUtensorMap tmap, void* __restrict__
     float eh = 0.0f, el = 0.0f;
     bool ok = true;
     for (int b = 0; b < n_boxes; ++b) {
-        const int s = b % kColStages;
-        const uint32_t parity = (uint32_t)(b / kColStages) & 1u;
+        const int s = b % stages;
+        const uint32_t parity = (uint32_t)(b / stages) & 1u;
         if (!__all_sync(0xFFFFFFFFu, mbar_wait_bounded(&s_full[s], parity))) { ok = false; break; }
-        const W* stage = reinterpret_cast<const W*>(s_col + s * (CS::kMaxBoxRows * CS::kRowBytes));
+        const W* stage = reinterpret_cast<const W*>(s_col + s * CS::kStageBytes);
         for (int r = 0; r < rounds; ++r) {
             float hi, lo, dh, dl;
             PairWord<T>::unpack(stage[(ty + 16 * r) * 32 + tx], hi, lo);
@@ -1160,12 +1173,12 @@ colstrip_tma_kernel(const __grid_constant__ CUtensorMap tmap, void* __restrict__
         }
         __syncwarp();
         if (tx == 0) mbar_arrive(&s_empty[s]);
-        if (tid == 0 && b + kColStages < n_boxes) {
+        if (tid == 0 && b + stages < n_boxes) {
             if (!mbar_wait_bounded(&s_empty[s], parity)) { ok = false; }
             else {
                 mbar_expect_tx(&s_full[s], box_bytes);
-                tma_load_2d(s_col + s * (CS::kMaxBoxRows * CS::kRowBytes), &tmap, (int)(cx * 64),
-                            (int)(rb * brows + (int64_t)(b + kColStages) * box_rows), &s_full[s]);
+                tma_load_2d(s_col + s * CS::kStageBytes, &tmap, (int)(cx * 64),
+                            (int)(rb * brows + (int64_t)(b + stages) * box_rows), &s_full[s]);
             }
         }
         ok = __shfl_sync(0xFFFFFFFFu, (int)ok, 0) != 0 || ty != 0 ? ok : false;
@@ -1174,7 +1187,7 @@ colstrip_tma_kernel(const __grid_constant__ CUtensorMap tmap, void* __restrict__
         // a copy (or the other warps) did not show up within the bounded wait: flag the call -- the decision kernel
         // reports meta = -1 -- and give copies still in flight a last bounded chance before the shared memory goes
         if (tid == 0) atomicOr(&ws->load_timeout, 1u);
-        for (int s = 0; s < kColStages; ++s) { mbar_wait_bounded(&s_full[s], 0); mbar_wait_bounded(&s_full[s], 1); }
+        for (int s = 0; s < stages; ++s) { mbar_wait_bounded(&s_full[s], 0); mbar_wait_bounded(&s_full[s], 1); }
         return;
     }
     const float sum = warp_sum_ordered(__fadd_rn(eh, el));
@@ -1516,17 +1529,19 @@ int launch_colgroup_t(const ScalingArgs& a, bool store, bool skip, cudaStream_t 
     if (n_cta > 0x7FFFFFFF) return kErrTooLarge;
     const bool e8 = a.ss_mode == 2;
     CUtensorMap map;
-    const int box_rows = a.brows % 64 == 0 ? 64 : 16;
+    using CS = ColStrip<T>;
+    const int box_rows = a.brows % CS::kMaxBoxRows == 0 ? CS::kMaxBoxRows : (a.brows % 64 == 0 ? 64 : 16);
     if (!force_generic() && a.rows < (int64_t(1) << 31) && a.cols < (int64_t(1) << 31) &&
         make_tile_map(&map, a.in, a.rows, a.cols, T::kBytesPerElem, 64, box_rows)) {
-        using CS = ColStrip<T>;
-        const int smem = CS::kRingBytes + (e8 ? 0 : CS::kLutBytes);
+        const int n_boxes = a.brows / box_rows;
+        const int stages = n_boxes < kColStages ? n_boxes : kColStages;
+        const int smem = stages * CS::kStageBytes + (e8 ? 0 : CS::kLutBytes);
 #define MORB_COL(E, S)                                                                                              \
     do {                                                                                                            \
         static SmemOptIn opt;                                                                                       \
-        if (!opt(colstrip_tma_kernel<T, E, S>, CS::kRingBytes + CS::kLutBytes)) return kErrLaunch;                   \
+        if (!opt(colstrip_tma_kernel<T, E, S>, kColStages * CS::kStageBytes + CS::kLutBytes)) return kErrLaunch;     \
         colstrip_tma_kernel<T, E, S><<<(unsigned)n_cta, kColThreads, smem, st>>>(                                   \
-            map, a.out, a.cols, a.brows, box_rows, a.ss_mode, a.block_amax, a.block_err, a.ws, a.ext_gamax, skip ? 1 : 0); \
+            map, a.out, a.cols, a.brows, box_rows, stages, a.ss_mode, a.block_amax, a.block_err, a.ws, a.ext_gamax, skip ? 1 : 0); \
     } while (0)
         if (e8 && store) MORB_COL(true, true);
         else if (e8) MORB_COL(true, false);
