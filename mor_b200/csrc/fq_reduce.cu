@@ -369,15 +369,50 @@ __global__ void __launch_bounds__(kThreads) amax_nnz_colgroups_kernel(const type
                          !(al == 0.0f || (al >= 8.0779357e-28f && al < 1.2379400e27f));
             }
         };
-        int64_t r = r_begin + wid;
-        for (; r + 24 < r_end; r += 32) {
-            typename T::vec_t v[4];
+        auto scan = [&](auto&& per_vector) {
+            int64_t r = r_begin + wid;
+            for (; r + 24 < r_end; r += 32) {
+                typename T::vec_t v[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) v[u] = ld_keep(in + (r + 8 * u) * cols_vec + cv);
+                for (int u = 0; u < 4; ++u) v[u] = ld_keep(in + (r + 8 * u) * cols_vec + cv);
 #pragma unroll
-            for (int u = 0; u < 4; ++u) take(v[u]);
+                for (int u = 0; u < 4; ++u) per_vector(v[u]);
+            }
+            for (; r < r_end; r += 8) per_vector(ld_keep(in + r * cols_vec + cv));
+        };
+        if constexpr (T::kBytesPerElem == 2) {
+            // packed form, both columns of a word at once: unsigned 16-bit maxima of the magnitudes per word
+            // position, one signed minimum of magnitude + 0x7FFF over everything (a zero becomes 0x7FFF, the
+            // largest; bit 15 of a half says "non-zero"), the non-zero count from those bits.  A NaN pattern sorts
+            // above infinity, where fmaxf would skip it: a thread that met one repeats its rows element by element.
+            uint32_t cm[4] = {0u, 0u, 0u, 0u}, pmn = 0x7FFF7FFFu;
+            int n2 = 0;
+            scan([&](const uint4& v) {
+                const uint32_t m0 = mag2(v.x), m1 = mag2(v.y), m2 = mag2(v.z), m3 = mag2(v.w);
+                cm[0] = umax16x2(cm[0], m0); cm[1] = umax16x2(cm[1], m1);
+                cm[2] = umax16x2(cm[2], m2); cm[3] = umax16x2(cm[3], m3);
+                const uint32_t t0 = m0 + 0x7FFF7FFFu, t1 = m1 + 0x7FFF7FFFu, t2 = m2 + 0x7FFF7FFFu, t3 = m3 + 0x7FFF7FFFu;
+                pmn = smin16x2_3(pmn, t0, t1);
+                pmn = smin16x2_3(pmn, t2, t3);
+                n2 += __popc(((t0 & 0x80008000u) >> 1) | (t1 & 0x80008000u)) + __popc(((t2 & 0x80008000u) >> 1) | (t3 & 0x80008000u));
+            });
+            const uint32_t mx = hmax_halves(umax16x2(umax16x2_3(cm[0], cm[1], cm[2]), cm[3]));
+            if (mx > 0x7F80u) {
+                scan(take);
+            } else {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) { cmax[2 * k] = u2f(cm[k] << 16); cmax[2 * k + 1] = u2f(cm[k] & 0xFFFF0000u); }
+                nnz = n2;
+                // smallest non-zero magnitude: a half with bit 15 set holds it, less one, in its low 15 bits
+                const uint32_t h0 = pmn & 0xFFFFu, h1 = pmn >> 16;
+                uint32_t mn = 0x7FFFu;
+                if (h0 & 0x8000u) mn = min(mn, (h0 & 0x7FFFu) + 1u);
+                if (h1 & 0x8000u) mn = min(mn, (h1 & 0x7FFFu) + 1u);
+                unsafe = mx >= 0x6C80u || mn < 0x1280u;   // outside [2^-90, 2^90)
+            }
+        } else {
+            scan(take);
         }
-        for (; r < r_end; r += 8) take(ld_keep(in + r * cols_vec + cv));
     }
 #pragma unroll
     for (int e = 0; e < EPV; ++e) s_cmax[wid][lane][e] = cmax[e];

@@ -1114,14 +1114,19 @@ colstrip_tma_kernel(const __grid_constant__ CUtensorMap tmap, void* __restrict__
     if (tid < 32) s_wsum[tid] = 0.0f;
     __syncthreads();
     if constexpr (!E8) {
-        for (int i = tid; i < 64 * 256; i += kColThreads)
-            s_lut[i] = canon_nan(__fdiv_rn(h_lo_to_f32(codes_to_h2<kE4M3>((uint32_t)(i & 255))), s_sf[i >> 8]));
+        // entry (code, column) at [column & 1][code][column / 2]: lane tx finds both of its columns' quotients
+        // in bank tx, whatever the codes of the other lanes
+        for (int i = tid; i < 64 * 256; i += kColThreads) {
+            const int col = i & 63, code = i >> 6;
+            s_lut[(col & 1) * 8192 + code * 32 + (col >> 1)] =
+                canon_nan(__fdiv_rn(h_lo_to_f32(codes_to_h2<kE4M3>((uint32_t)code)), s_sf[col]));
+        }
         __syncthreads();
     }
     const float sfl = s_sf[2 * tx], sfh = s_sf[2 * tx + 1];
     const E8Consts cl = e8_consts(sfl), ch = e8_consts(sfh);
-    const float* lut_l = s_lut + (2 * tx) * 256;
-    const float* lut_h = lut_l + 256;
+    const float* lut_l = s_lut + tx;
+    const float* lut_h = lut_l + 8192;
     W* out = static_cast<W*>(out_raw) + (rb * brows + ty) * (cols / 2) + cx * 32 + tx;
     const int64_t out_step = 16 * (cols / 2);
     float eh = 0.0f, el = 0.0f;
@@ -1131,7 +1136,7 @@ colstrip_tma_kernel(const __grid_constant__ CUtensorMap tmap, void* __restrict__
         const uint32_t parity = (uint32_t)(b / stages) & 1u;
         if (!__all_sync(0xFFFFFFFFu, mbar_wait_bounded(&s_full[s], parity))) { ok = false; break; }
         const W* stage = reinterpret_cast<const W*>(s_col + s * CS::kStageBytes);
-        for (int r = 0; r < rounds; ++r) {
+        auto one_row = [&](int r, auto fd) {   // fd: the short quotient is valid for the whole tensor
             float hi, lo, dh, dl;
             PairWord<T>::unpack(stage[(ty + 16 * r) * 32 + tx], hi, lo);
             if constexpr (E8) {
@@ -1142,13 +1147,13 @@ colstrip_tma_kernel(const __grid_constant__ CUtensorMap tmap, void* __restrict__
                 (void)th; (void)tl; (void)uh; (void)ul;
             } else {
                 const uint32_t c = cvt_codes<kE4M3>(__fmul_rn(hi, sfh), __fmul_rn(lo, sfl));
-                dh = lut_h[c >> 8];
-                dl = lut_l[c & 0xFFu];
+                dh = lut_h[(c >> 8) * 32];
+                dl = lut_l[(c & 0xFFu) * 32];
             }
             const bool zh = hi == 0.0f, zl = lo == 0.0f;
             float e_h, e_l;
             if constexpr (T::kBytesPerElem == 2) {
-                if (fastdiv) {   // warp-uniform
+                if constexpr (decltype(fd)::value) {
                     e_h = fabsf(div_by_bf16(__fsub_rn(dh, hi), hi, rcp_fast(hi)));
                     e_l = fabsf(div_by_bf16(__fsub_rn(dl, lo), lo, rcp_fast(lo)));
                 } else {
@@ -1170,7 +1175,20 @@ colstrip_tma_kernel(const __grid_constant__ CUtensorMap tmap, void* __restrict__
                 __stcs(out, w);
             }
             out += out_step;
-        }
+        };
+        // four rows at a time: their loads, casts and quotients overlap, the additions keep their order
+        auto rows_of_box = [&](auto fd) {
+            if (rounds >= 4) {
+                for (int r = 0; r < rounds; r += 4) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) one_row(r + u, fd);
+                }
+            } else {
+                for (int r = 0; r < rounds; ++r) one_row(r, fd);
+            }
+        };
+        if (fastdiv) rows_of_box(std::true_type{});
+        else rows_of_box(std::false_type{});
         __syncwarp();
         if (tx == 0) mbar_arrive(&s_empty[s]);
         if (tid == 0 && b + stages < n_boxes) {
