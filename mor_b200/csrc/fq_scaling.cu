@@ -1304,7 +1304,9 @@ finalize_kernel(const float* __restrict__ block_err, int64_t n_err, int stride, 
 constexpr int kChainsPerCta = 8, kChainRows = 1024, kChainThreads = 1024;
 __global__ void __launch_bounds__(kChainThreads) chain_sum_kernel(const float* __restrict__ block_err, int64_t n_err, int period,
                                                         float* __restrict__ chain_sums) {
-    __shared__ float s_rows[kChainRows][kChainsPerCta];
+    // [chain][row], rows padded by four floats: the eight adding lanes read 16 bytes each from eight different
+    // bank groups, the 32 lanes of a staging warp (8 chains x 4 rows) write 32 different banks
+    __shared__ __align__(16) float s_rows[kChainsPerCta][kChainRows + 4];
     const int ch = threadIdx.x & 7, ry = threadIdx.x >> 3;
     const int j = blockIdx.x * kChainsPerCta + ch;
     const int64_t rows = (n_err + period - 1) / period;
@@ -1320,27 +1322,29 @@ __global__ void __launch_bounds__(kChainThreads) chain_sum_kernel(const float* _
     float acc = 0.0f;
     for (int64_t c0 = 0; c0 < rows; c0 += kChainRows) {
 #pragma unroll
-        for (int u = 0; u < 8; ++u) s_rows[ry + (kChainThreads / 8) * u][ch] = v[u];
+        for (int u = 0; u < 8; ++u) s_rows[ch][ry + (kChainThreads / 8) * u] = v[u];
         __syncthreads();
         if (c0 + kChainRows < rows) load(c0 + kChainRows);
         if (threadIdx.x < kChainsPerCta) {
-            // the additions form one dependent chain; the shared-memory loads of the next 16 rows
-            // are issued before the current 16 are added, so only the adds' own latency remains
-            float x[16], y[16];
+            // the additions form one dependent chain; the next 16 rows are read (four 16-byte loads) before the
+            // current 16 are added, so only the adds' own latency remains
+            const float4* mine = reinterpret_cast<const float4*>(s_rows[threadIdx.x]);
+            float4 x[4], y[4];
 #pragma unroll
-            for (int u = 0; u < 16; ++u) x[u] = s_rows[u][threadIdx.x];
-            for (int r = 0; r < kChainRows; r += 32) {
+            for (int u = 0; u < 4; ++u) x[u] = mine[u];
+            for (int r = 0; r < kChainRows / 4; r += 4) {
+                const int rn = r + 4 < kChainRows / 4 ? r + 4 : 0;   // the last reload is not used
 #pragma unroll
-                for (int u = 0; u < 16; ++u) {
-                    y[u] = s_rows[r + 16 + u][threadIdx.x];
-                    acc = __fadd_rn(acc, x[u]);
+                for (int u = 0; u < 4; ++u) y[u] = mine[rn + u];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    acc = __fadd_rn(acc, x[u].x);
+                    acc = __fadd_rn(acc, x[u].y);
+                    acc = __fadd_rn(acc, x[u].z);
+                    acc = __fadd_rn(acc, x[u].w);
                 }
-                const int rn = r + 32 < kChainRows ? r + 32 : 0;   // the last reload is not used
 #pragma unroll
-                for (int u = 0; u < 16; ++u) {
-                    x[u] = s_rows[rn + u][threadIdx.x];
-                    acc = __fadd_rn(acc, y[u]);
-                }
+                for (int u = 0; u < 4; ++u) x[u] = y[u];
             }
         }
         __syncthreads();
