@@ -81,15 +81,36 @@ def gpu_numa_node(index: int):
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while running."""
+    """SM clock and throttle reasons while the timed region runs: NVML queries (read-only) from a thread every few
+    milliseconds, so that a region of some tens of milliseconds still gets samples; `nvidia-smi -lms` otherwise.
+    Only samples taken between `mark_start()` and `mark_end()` count, if there are any."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
 
     def __init__(self, gpu_index: int):
-        self.gpu, self.rows, self.proc = gpu_index, [], None
+        self.gpu, self.rows, self.proc, self.nvml, self.stop = gpu_index, [], None, None, False
+        self.t0 = self.t1 = None
+
+    def mark_start(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
 
     def __enter__(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.gpu)
+            self.max_sm = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.nvml = pynvml
+            self.t = threading.Thread(target=self._poll, daemon=True)
+            self.t.start()
+            return self
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
                                           "-lms", "200", "-i", str(self.gpu)], stdout=subprocess.PIPE,
@@ -100,12 +121,37 @@ class ClockSampler:
             self.proc = None
         return self
 
+    def _poll(self):
+        n = self.nvml
+        get_reasons = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or n.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self.stop:
+            try:
+                sm = float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM))
+                mask = int(get_reasons(self.handle))
+                self.rows.append((time.time(), sm, self.max_sm, [name for name, bit in self.REASONS if mask & bit]))
+            except Exception:
+                pass
+            time.sleep(0.003)
+
     def _read(self):
+        names = [name for name, _ in self.REASONS]
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            r = [c.strip() for c in line.split(",")]
+            try:
+                self.rows.append((time.time(), float(r[1]), float(r[2]),
+                                  [n for n, v in zip(names, r[5:9]) if v.lower().startswith("active")]))
+            except Exception:
+                continue
 
     def __exit__(self, *a):
-        if self.proc:
+        if self.nvml:
+            self.stop = True
+            self.t.join(timeout=2)
+            try:
+                self.nvml.nvmlShutdown()
+            except Exception:
+                pass
+        elif self.proc:
             time.sleep(0.25)
             self.proc.terminate()
             try:
@@ -114,19 +160,17 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self):
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
-            try:
-                sm.append(float(r[1])); mx.append(float(r[2]))
-                for n, v in zip(names, r[5:9]):
-                    if v.lower().startswith("active"):
-                        reasons.add(n)
-            except Exception:
-                continue
-        if not sm:
+        rows = self.rows
+        if self.t0 is not None and self.t1 is not None:
+            inside = [r for r in rows if self.t0 <= r[0] <= self.t1]
+            rows = inside or rows
+        if not rows:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        reasons = set()
+        for r in rows:
+            reasons.update(r[3])
+        return {"sm_mhz": statistics.median(r[1] for r in rows), "sm_max_mhz": max(r[2] for r in rows),
+                "reasons": sorted(reasons), "samples": len(rows), "source": "nvml" if self.nvml else "nvidia-smi"}
 
 
 # --------------------------------------------------------------------------------------
@@ -342,11 +386,13 @@ def main():
     with ClockSampler(local_rank) as clocks:
         barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        clocks.mark_start()
         ev0.record()
         for _ in range(args.steps):
             res = op(x, out, SS_MODE, THRESHOLD)
         ev1.record()
         barrier()
+        clocks.mark_end()
     step_ms = ev0.elapsed_time(ev1) / args.steps
     launches = sum(b.launches for b in op.backends) - launches0
 
@@ -435,7 +481,7 @@ def main():
         oh = torch.empty(rows_local, COLS, dtype=torch.float32, pin_memory=True)
         xh.copy_(x)
         scal_h = torch.empty(2, dtype=torch.float32, pin_memory=True)
-        e2e_steps = max(2, min(args.steps, 10))
+        e2e_steps = max(4, min(args.steps, 16))
         out = None
         torch.cuda.empty_cache()
         from mor_b200.sharded import HostScaling
@@ -449,8 +495,10 @@ def main():
         host_op.synchronize()
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(e2e_steps)]
         e0.record()
-        for _ in range(e2e_steps):
+        for i in range(e2e_steps):
+            starts[i].record(host_op.s_in)      # on the upload stream: when this step's upload could begin
             e2e_step()
         host_op.s_out.wait_stream(torch.cuda.current_stream())
         torch.cuda.current_stream().wait_stream(host_op.s_out)   # the last read-back ends the timed region
@@ -458,6 +506,11 @@ def main():
         host_op.synchronize()
         barrier()
         e2e_ms = e0.elapsed_time(e1) / e2e_steps
+        # the timed region starts with an empty pipeline and ends when it has drained: one upload and one read-back
+        # of its K steps overlap nothing.  The period between the uploads of consecutive steps, once both
+        # directions are busy, is what a long run sees per step.
+        first = min(2, e2e_steps - 2)
+        steady_ms = starts[first].elapsed_time(starts[-1]) / (e2e_steps - 1 - first)
         # the same buffers, the same two copy streams, no kernels: what the host links give on their own
         c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         cur = torch.cuda.current_stream()
@@ -473,10 +526,10 @@ def main():
         c1.record()
         barrier()
         copy_ms = c0.elapsed_time(c1) / e2e_steps
-        tt = torch.tensor([e2e_ms, copy_ms], dtype=torch.float64, device=dev)
+        tt = torch.tensor([e2e_ms, copy_ms, steady_ms], dtype=torch.float64, device=dev)
         if world > 1:
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        e2e_ms, copy_ms = tt.tolist()
+        e2e_ms, copy_ms, steady_ms = tt.tolist()
         job_bytes = total_elems * BYTES_PER_ELEM_TWO_PASS
         numa = gpu_numa_node(local_rank)
         e2e = {"value": job_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
@@ -484,6 +537,10 @@ def main():
                "ms_per_step": e2e_ms, "steps": e2e_steps,
                "copy_only_GBs": job_bytes / (copy_ms * 1e-3) / 1e9, "copy_only_ms_per_step": copy_ms,
                "frac_of_copy": copy_ms / e2e_ms,
+               "steady_state": {"ms_per_step": steady_ms, "GB/s": job_bytes / (steady_ms * 1e-3) / 1e9,
+                                "frac_of_copy": copy_ms / steady_ms,
+                                "note": "period between the uploads of consecutive steps after the first two; "
+                                        "value above is the whole timed region, pipeline fill and drain included"},
                "host_link_GBs_per_direction_per_gpu": nbytes / (copy_ms * 1e-3) / 1e9,
                "host": {"cpu_affinity_cores": host_threads(), "gpu_numa_node": numa},
                "note": "mor_b200.sharded.HostScaling: pinned host float32 in and out, every step uploads its input and "
