@@ -320,6 +320,32 @@ def test_channel_scaling_small_groups_power_of_two(by, kind, rows, cols, channel
         assert_same(H.channel_scaling(x, 1, by, thr, 2), exp, f"{kind} {rows}x{cols} 1x{by} thr {thr}")
 
 
+@pytest.mark.parametrize("by", [4096, 8192])
+def test_channel_rows_with_mixed_magnitudes(by):
+    """Long rows under their own binary32 scale: rows whose elements are all normal E4M3 numbers under the row's
+    scale, rows that mix them with E4M3 denormals and zeros, rows at both ends of the bf16 exponent range, an
+    all-zero row, a row with a single non-zero element"""
+    import gpu_harness as H
+    from ref_fixtures import bf16_bits
+    g = torch.Generator().manual_seed(by)
+    x = torch.randn(32, 8192, generator=g)
+    x[1] *= 2.0 ** -112                      # amax below 2^-100
+    x[2] *= 2.0 ** 100                       # a large scale exponent the other way
+    x[3, ::64] *= 2.0 ** -16                 # one element of every step below the normal range
+    x[4, 100:164] = 0.0                      # a step of zeros, and a step that straddles them
+    x[5] = 0.0                               # nothing but zeros
+    x[6] = 0.0; x[6, 77] = -3.0              # a single non-zero element
+    x[7, :4096] *= 2.0 ** -20                # half a row of E4M3 denormals and zeros after the cast
+    x[8] = x[8].abs() * 2.0 ** -126          # bf16 denormals and the smallest normals
+    x[9, 5] = 3.0e38                         # the largest finite magnitudes
+    bits = bf16_bits(x.to(torch.bfloat16))
+    oracle.clear_assert_flags()
+    exp = dict(zip(("out", "meta", "gamax", "gnnz", "gerr"), oracle.channel_scaling(bits, 1, by, 3e38, 3)))
+    assert not oracle.assert_flags()
+    exp["meta"] = np.array([exp["meta"]])
+    assert_same(H.channel_scaling(bits, 1, by, 3e38, 3), exp, f"1x{by} rows with mixed magnitudes")
+
+
 @pytest.mark.parametrize("by", [2048, 4096, 8192])
 @pytest.mark.parametrize("ss", [1, 2, 3, 4])
 @pytest.mark.parametrize("kind", ["normal", "wide", "nan"])
