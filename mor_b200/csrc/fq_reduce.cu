@@ -125,6 +125,8 @@ __device__ __forceinline__ void publish(ScalarsWs* ws, float amax, int nnz) {
     if (nnz) atomicAdd(&ws->gnnz, (unsigned long long)nnz);
 }
 __global__ void zero_scalars_kernel(ScalarsWs* ws) {
+    // the amax kernel behind this one may start reading the tensor now; it waits for this kernel before its first atomic
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     ws->gamax_bits = 0u; ws->fallback = 0; ws->gnnz = 0ull; ws->gerr = 0.0f; ws->meta = 0;
     ws->div_unsafe = 0u; ws->load_timeout = 0u; ws->bar[0] = 0u; ws->bar[1] = 0u;
 }
@@ -208,6 +210,11 @@ __global__ void __launch_bounds__(kThreads, 8) amax_nnz_blocks_kernel(const type
                                                                    int64_t blocks_x, int w_shift,
                                                                    float* __restrict__ block_amax,
                                                                    ScalarsWs* __restrict__ ws) {
+    // Launched as a programmatic dependent of the kernel that clears the scalars: the loads below may run before
+    // that kernel has finished (the tensor was complete before it started), the results are published after
+    // griddepcontrol.wait.  The kernel behind this one (the exchange of the amax between ranks, or the cast) may in
+    // turn become resident while this kernel's last CTAs run; it waits for this kernel before it reads anything.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int64_t b = blockIdx.x;
     const int64_t r0 = (b / blocks_x) * brows, c0 = (b % blocks_x) * bcols_vec;
     const int W = 1 << w_shift, RPS = kThreads >> w_shift;
@@ -255,6 +262,7 @@ __global__ void __launch_bounds__(kThreads, 8) amax_nnz_blocks_kernel(const type
         // not counted), so it may leave out the selects that keep zero elements out of the sums
         const bool zero_free = nnz == brows * bcols_vec * (16 / T::kBytesPerElem);
         block_amax[b] = zero_free ? -amax : amax;
+        asm volatile("griddepcontrol.wait;" ::: "memory");   // the scalars have been cleared
         publish(ws, amax, nnz);
         if (flags) atomicOr(&ws->div_unsafe, 1u);
     }
@@ -496,8 +504,16 @@ int launch_amax_nnz_blocks(const void* in, int is_fp32, int64_t rows, int64_t co
     }
     int w_shift = 0;
     while ((2 << w_shift) <= bcols_vec && (2 << w_shift) <= kThreads) ++w_shift;  // largest power of two <= min(bcols_vec, 256)
-    if (is_fp32) amax_nnz_blocks_kernel<Fp32><<<(unsigned)nb, kThreads, 0, st>>>(static_cast<const float4*>(in), cols_vec, brows, bcols_vec, bx, w_shift, block_amax, ws);
-    else amax_nnz_blocks_kernel<Bf16><<<(unsigned)nb, kThreads, 0, st>>>(static_cast<const uint4*>(in), cols_vec, brows, bcols_vec, bx, w_shift, block_amax, ws);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)nb); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = 0; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    const cudaError_t e = is_fp32
+        ? cudaLaunchKernelEx(&cfg, amax_nnz_blocks_kernel<Fp32>, static_cast<const float4*>(in), cols_vec, brows, bcols_vec, bx, w_shift, block_amax, ws)
+        : cudaLaunchKernelEx(&cfg, amax_nnz_blocks_kernel<Bf16>, static_cast<const uint4*>(in), cols_vec, brows, bcols_vec, bx, w_shift, block_amax, ws);
+    if (e != cudaSuccess) { cudaGetLastError(); return kErrLaunch; }
     return check_launch();
 }
 

@@ -63,6 +63,8 @@ __global__ void p2p_exchange_scalars_kernel(ScalarsWs* __restrict__ ws, unsigned
                                             long long* __restrict__ gnnz_out, uint32_t limit) {
     // the cast kernel behind this one may start now: it requests its tiles and then waits for this kernel to finish
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // this kernel itself may have been launched ahead of the end of the amax kernel: wait for its scalars
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int p = threadIdx.x;
     const uint32_t par = epoch & 1u;
     uint32_t amax_bits = 0u;
@@ -142,8 +144,14 @@ int launch_p2p_exchange_scalars(ScalarsWs* ws, void* mine, void* const* peer_buf
     PeerPtrs pp;
     if (!ws || !mine || !gamax_out || !gnnz_out || !fill_peers(pp, peer_bufs, world) || rank < 0 || rank >= world)
         return kErrInvalidArgument;
-    p2p_exchange_scalars_kernel<<<1, 32, 0, st>>>(ws, static_cast<unsigned char*>(mine), pp, rank, world, epoch,
-                                                  gamax_out, gnnz_out, g_spin_limit);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1); cfg.blockDim = dim3(32); cfg.dynamicSmemBytes = 0; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, p2p_exchange_scalars_kernel, ws, static_cast<unsigned char*>(mine), pp, rank, world, epoch,
+                           gamax_out, gnnz_out, g_spin_limit) != cudaSuccess) { cudaGetLastError(); return kErrLaunch; }
     return check_launch();
 }
 int launch_p2p_exchange_errors(const float* local_err, int64_t n_err, const void* mine, void* const* peer_bufs, int rank,
