@@ -160,7 +160,9 @@ int scaling_op(int kind, const void* in, void* out, int dtype, int64_t rows, int
     if (rc) return rc;
     // In place the input must survive until the tensor-level decision is known: sum the
     // errors without storing, decide, then cast only if the tensor is kept in E4M3.
+    a.early_launch = 1;   // the tile kernel may become resident, and request its tiles, during the amax kernel's last wave
     rc = phase_cast(kind, a, /*store=*/!inplace, false, st);
+    a.early_launch = 0;
     if (rc) return rc;
     rc = launch_finalize(a, nullptr, meta, gamax, gnnz, nnz64, gerr, st);
     if (rc) return rc;
