@@ -138,6 +138,13 @@ __device__ __forceinline__ void word_errors_fast(const ErrCtx<SF>& e, float hi, 
     e5 = __fadd_rn(e5h, e5l);
 }
 
+// (a.x + b.x, a.y + b.y), each sum rounded to nearest even as a single addition would be
+__device__ __forceinline__ float2 add_f32x2(float2 a, float2 b) {
+    unsigned long long r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(*reinterpret_cast<const unsigned long long*>(&a)),
+                                                "l"(*reinterpret_cast<const unsigned long long*>(&b)));
+    return *reinterpret_cast<float2*>(&r);
+}
 template <int FMT>
 __device__ __forceinline__ void fill_lut16(uint16_t* lut, float s, int tid, int nthreads) {
     constexpr int NCODES = (FMT == kE2M3) ? 64 : 256;
@@ -353,6 +360,9 @@ fq_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename TileVec<VW>
                     __syncthreads();
                     const uint32_t thr = (uint32_t)(base + fold);   // magnitude patterns from here up are folded
                     const uint8_t* repl = s_tile + (tid & 15) * 8;
+                    float2 acc2[VW];
+#pragma unroll
+                    for (int k = 0; k < VW; ++k) acc2[k] = make_float2(0.0f, 0.0f);
 #pragma unroll
                     for (int n = 0; n < 16; ++n) {  // rows outer (j = n / 4), words inner (i = n % 4)
 #pragma unroll
@@ -363,10 +373,12 @@ fq_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename TileVec<VW>
                             float2 eh = *reinterpret_cast<const float2*>(repl + ((w >> 9) & 0x3F80u));
                             if (ml < thr) el = tab[max((int)ml - base, 0)];
                             if (mh < thr) eh = tab[max((int)mh - base, 0)];
-                            a4[k] = __fadd_rn(a4[k], __fadd_rn(eh.x, el.x));
-                            a5[k] = __fadd_rn(a5[k], __fadd_rn(eh.y, el.y));
+                            // both formats' sums at once: packed binary32 additions, each half rounded on its own
+                            acc2[k] = add_f32x2(acc2[k], add_f32x2(eh, el));
                         }
                     }
+#pragma unroll
+                    for (int k = 0; k < VW; ++k) { a4[k] = acc2[k].x; a5[k] = acc2[k].y; }
                 } else {
 #pragma unroll 2
                     for (int n = 0; n < 16; ++n) {  // rows outer (j = n / 4), words inner (i = n % 4)
