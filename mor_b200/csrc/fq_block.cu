@@ -359,6 +359,7 @@ fq_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename TileVec<VW>
                     for (int i = tid; i < 2048; i += NT) rep[i] = tab[fold + (((i >> 4) - base) & 127)];
                     __syncthreads();
                     const uint32_t thr = (uint32_t)(base + fold);   // magnitude patterns from here up are folded
+                    const uint32_t thr2 = thr * 0x00010001u;
                     const uint8_t* repl = s_tile + (tid & 15) * 8;
                     float2 acc2[VW];
 #pragma unroll
@@ -368,11 +369,13 @@ fq_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename TileVec<VW>
 #pragma unroll
                         for (int k = 0; k < VW; ++k) {
                             const uint32_t w = tw[n][k];
-                            const uint32_t ml = w & 0x7FFFu, mh = (w >> 16) & 0x7FFFu;
                             float2 el = *reinterpret_cast<const float2*>(repl + ((w & 0x7Fu) << 7));
                             float2 eh = *reinterpret_cast<const float2*>(repl + ((w >> 9) & 0x3F80u));
-                            if (ml < thr) el = tab[max((int)ml - base, 0)];
-                            if (mh < thr) eh = tab[max((int)mh - base, 0)];
+                            if (umin16x2(mag2(w), thr2) != thr2) {   // rare: a half below the folded rows, or zero
+                                const uint32_t ml = w & 0x7FFFu, mh = (w >> 16) & 0x7FFFu;
+                                if (ml < thr) el = tab[max((int)ml - base, 0)];
+                                if (mh < thr) eh = tab[max((int)mh - base, 0)];
+                            }
                             // both formats' sums at once: packed binary32 additions, each half rounded on its own
                             acc2[k] = add_f32x2(acc2[k], add_f32x2(eh, el));
                         }
