@@ -308,7 +308,10 @@ int mor_b200_e8mx(const void* in, void* out, int64_t rows, int64_t cols, int qty
     if (!wsp || wsb < kHead || !aligned16(wsp)) return kErrWorkspace;
     auto st = static_cast<cudaStream_t>(stream);
     auto* ws = static_cast<ScalarsWs*>(wsp);
-    int rc = launch_zero_scalars(ws, st);
+    // small tensors: one cooperative launch that keeps the tensor in shared memory between the amax and the cast
+    int rc = launch_e8mx_resident(in, out, rows * cols, qtype, strategy, ws, st);
+    if (rc != kErrUnsupportedShape) return rc;
+    rc = launch_zero_scalars(ws, st);
     if (rc) return rc;
     rc = launch_amax_nnz_flat(in, 0, rows * cols, ws, st);
     if (rc) return rc;

@@ -3,6 +3,7 @@
 // the binary32 test operators.  One HBM read and one HBM write per element,
 // 16-byte accesses, persistent grid-stride loops sized to the SM count.
 #include "kernels.cuh"
+#include "e8mx_math.cuh"
 
 namespace morb {
 
@@ -129,78 +130,16 @@ __global__ void __launch_bounds__(kThreads) e4m3_e8_scale_kernel(const float* __
     }
 }
 
-// ref: 1243-1327: keep the exponent, round the mantissa to M bits.  The reference's
-// threshold ladder is round-to-nearest-even on the top seven mantissa bits: index j
-// is kept while man <= j*step + step/2 (even j) or that minus 65536 (odd j).
-template <int M>
-__device__ __forceinline__ float e8m_round(float v) {
-    const uint32_t b = f2u(v);
-    uint32_t e = (b >> 23) & 0xFFu, man = b & 0x7FFFFFu;
-    if (e == 0) man = 0;
-    else if (e != 255) {
-        constexpr uint32_t step = 0x800000u >> M;
-        constexpr uint32_t steps = 1u << M;
-        uint32_t k = steps;
-#pragma unroll
-        for (int j = (int)steps - 1; j >= 0; --j) {
-            const uint32_t lim = (uint32_t)j * step + step / 2 - ((j & 1) ? 65536u : 0u);
-            if (man <= lim) k = (uint32_t)j;
-        }
-        if (k < steps) man = k * step;
-        else {
-            man = 0;
-            e += 1;
-            if (e == 255) { e = 254; man = (steps - 1) * step; }
-        }
-    }
-    return u2f((b & 0x80000000u) | (e << 23) | man);
-}
-
-// ref: 1335-1359
-template <int M>
-__device__ __forceinline__ float e8mx_scale(float gamax, int strategy) {
-    if (strategy != 1) return 1.0f;
-    const uint32_t e = (f2u(gamax) >> 23) + 1;
-    const float fp_max = u2f((e << 23) | (((1u << M) - 1u) << (23 - M)));
-    float s = __fdiv_rn(fp_max, gamax);
-    if (s >= 2.0f) s = __fdiv_rn(s, 2.0f);
-    return s;
-}
-
 template <int M>
 __global__ void __launch_bounds__(kThreads) e8mx_cast_kernel(const uint4* __restrict__ in, uint4* __restrict__ out,
                                                              int64_t nvec, int64_t n_tail_words, int strategy,
                                                              const uint32_t* __restrict__ gamax_bits) {
-    const float s = e8mx_scale<M>(u2f(*gamax_bits), strategy);
+    __shared__ uint32_t s_off[128];
+    E8mxCast<M> cast;
+    cast.init(s_off, e8mx_scale<M>(u2f(*gamax_bits), strategy), threadIdx.x);
+    __syncthreads();
     const int64_t stride = (int64_t)gridDim.x * kThreads;
     const int64_t gtid = (int64_t)blockIdx.x * kThreads + threadIdx.x;
-    auto one = [&](float x) -> float {
-        const float v = __fmul_rn(x, s);
-        float d = 0.0f;
-        if (v != 0.0f) d = e8m_round<M>(v);
-        return __fdiv_rn(d, s);
-    };
-    auto slow_word = [&](uint32_t w) -> uint32_t { return pack_bf16(one(bf16_hi(w)), one(bf16_lo(w))); };
-    // Every step of `one` commutes with a power of two as long as nothing leaves the normal range (the product
-    // and the quotient are correctly rounded, the mantissa rounding keeps the exponent or raises it by one), and
-    // the result has the sign of the input: for an exponent field in [2, 251] the output pattern is the input
-    // pattern plus a small offset that depends on the seven mantissa bits only.  The 128 offsets are tabulated
-    // per CTA with the literal arithmetic; zeros give +0 as in the reference; anything else (subnormals, the top
-    // binades, Inf, NaN) takes the literal path.
-    __shared__ uint32_t s_off[128];   // offset + 256, so that the packed sum below never borrows
-    if (threadIdx.x < 128) {
-        const uint32_t pat = (127u << 7) | threadIdx.x;
-        s_off[threadIdx.x] = f32_to_bf16_bits(one(u2f(pat << 16))) + 256u - pat;
-    }
-    __syncthreads();
-    auto word = [&](uint32_t w) -> uint32_t {
-        const uint32_t m = mag2(w);
-        const uint32_t nz = (((m + 0x7FFF7FFFu) & 0x80008000u) >> 15) * 0xFFFFu;   // 0xFFFF in every non-zero half
-        const uint32_t mp = m | (~nz & 0x3F803F80u);                               // a zero half stands in as 1.0
-        if (umax16x2(mp, 0x01000100u) != mp || umin16x2(mp, 0x7DFF7DFFu) != mp) return slow_word(w);
-        const uint32_t off = s_off[mp & 0x7Fu] + (s_off[(mp >> 16) & 0x7Fu] << 16);
-        return ((mp + off - 0x01000100u) | (w & 0x80008000u)) & nz;
-    };
     for (int64_t i = gtid; i < nvec; i += stride * kUnroll) {
         uint4 v[kUnroll];
 #pragma unroll
@@ -210,14 +149,14 @@ __global__ void __launch_bounds__(kThreads) e8mx_cast_kernel(const uint4* __rest
         for (int u = 0; u < kUnroll; ++u)
             if (i + u * stride < nvec) {
                 uint4 r;
-                r.x = word(v[u].x); r.y = word(v[u].y); r.z = word(v[u].z); r.w = word(v[u].w);
+                r.x = cast.word(v[u].x); r.y = cast.word(v[u].y); r.z = cast.word(v[u].z); r.w = cast.word(v[u].w);
                 st_stream(out + i + u * stride, r);
             }
     }
     if (gtid < n_tail_words) {
         const uint32_t* tin = reinterpret_cast<const uint32_t*>(in + nvec);
         uint32_t* tout = reinterpret_cast<uint32_t*>(out + nvec);
-        tout[gtid] = word(tin[gtid]);
+        tout[gtid] = cast.word(tin[gtid]);
     }
 }
 

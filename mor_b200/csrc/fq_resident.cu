@@ -35,6 +35,7 @@
 #include <type_traits>
 
 #include "kernels.cuh"
+#include "e8mx_math.cuh"
 #include "scaling_math.cuh"
 #include "tma.cuh"
 
@@ -424,6 +425,147 @@ int launch_resident_t(const ScalingArgs& a, int32_t* meta, float* gamax, void* g
     return kOk;
 }
 
+// ---------------------------------------------------------------------------------
+// quantize_e8mx in one launch (ref: 1361-1428: amax kernel, then the element kernel)
+// ---------------------------------------------------------------------------------
+// The same idea on a flat tensor: CTA b requests chunks b, b + grid, ... (32 KiB each, up to seven) with bulk
+// copies as it starts, takes the largest magnitude from shared memory as they land (NaNs skipped, as the
+// reference's fmaxf does), meets the other CTAs at one grid barrier, and casts from shared memory with the
+// tensor's scale.  HBM is read once.  A chunk whose copy does not land within the bounded wait is read with
+// ordinary loads instead.
+constexpr int kE8Chunk = 32 * 1024, kE8Slots = 7, kE8Threads = 1024;
+constexpr int kE8Smem = kE8Slots * kE8Chunk + 64 + 512;   // chunks, mbarriers, the 128 offsets of the cast
+
+template <int M>
+__global__ void __launch_bounds__(kE8Threads, 1)
+e8mx_resident_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int64_t n_bytes, int strategy,
+                     ScalarsWs* __restrict__ ws, uint32_t limit) {
+    extern __shared__ __align__(128) uint8_t s_data[];
+    uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_data + kE8Slots * kE8Chunk);
+    uint32_t* s_off = reinterpret_cast<uint32_t*>(s_data + kE8Slots * kE8Chunk + 64);
+    __shared__ uint32_t s_red[kE8Threads / 32];
+    const int tid = threadIdx.x;
+    const int64_t n_chunks = (n_bytes + kE8Chunk - 1) / kE8Chunk;
+    auto chunk_of = [&](int k) { return (int64_t)blockIdx.x + (int64_t)k * gridDim.x; };
+    auto bytes_of = [&](int64_t c) { const int64_t r = n_bytes - c * kE8Chunk; return (uint32_t)(r < kE8Chunk ? r : kE8Chunk); };
+    if (tid == 0) {
+#pragma unroll
+        for (int k = 0; k < kE8Slots; ++k) mbar_init(&s_bar[k], 1);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        for (int k = 0; k < kE8Slots; ++k) {
+            const int64_t c = chunk_of(k);
+            if (c >= n_chunks) break;
+            mbar_expect_tx(&s_bar[k], bytes_of(c));
+            bulk_load(s_data + k * kE8Chunk, in + c * kE8Chunk, bytes_of(c), &s_bar[k]);
+        }
+    }
+    // pass 1: the largest magnitude, two halves of a word at a time; a NaN pattern sorts above infinity and is dropped
+    uint32_t pmx = 0u;
+    bool all_landed = true;
+    for (int k = 0; k < kE8Slots; ++k) {
+        const int64_t c = chunk_of(k);
+        if (c >= n_chunks) break;
+        const bool landed = mbar_wait_bounded(&s_bar[k], 0);
+        all_landed = all_landed && landed;
+        uint4* v = reinterpret_cast<uint4*>(s_data + k * kE8Chunk);
+        const uint4* g = reinterpret_cast<const uint4*>(in + c * kE8Chunk);
+        const int nv = (int)(bytes_of(c) / 16);
+        for (int i = tid; i < nv; i += kE8Threads) {
+            uint4 x;
+            if (landed) x = v[i];
+            else { x = ld_stream(g + i); v[i] = x; }   // this thread reads the same vectors again in pass 2
+            uint32_t m[4] = {mag2(x.x), mag2(x.y), mag2(x.z), mag2(x.w)};
+            uint32_t mx = umax16x2_3(umax16x2_3(m[0], m[0], m[1]), m[2], m[3]);
+            if (umin16x2(mx, 0x7F807F80u) != mx) {
+                mx = 0u;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint32_t lo = m[q] & 0xFFFFu, hi = m[q] >> 16;
+                    lo = lo > 0x7F80u ? 0u : lo;
+                    hi = hi > 0x7F80u ? 0u : hi;
+                    mx = umax16x2(mx, lo | (hi << 16));
+                }
+            }
+            pmx = umax16x2(pmx, mx);
+        }
+    }
+    const uint32_t top = __reduce_max_sync(0xFFFFFFFFu, hmax_halves(pmx));
+    if ((tid & 31) == 0) s_red[tid >> 5] = top;
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t a = 0u;
+#pragma unroll
+        for (int w = 0; w < kE8Threads / 32; ++w) a = max(a, s_red[w]);
+        atomicMax(&ws->gamax_bits, a << 16);
+    }
+    const bool met = grid_barrier(&ws->bar[0], gridDim.x, limit);
+    if (met) {
+        // pass 2: the cast, from shared memory
+        E8mxCast<M> cast;
+        cast.init(s_off, e8mx_scale<M>(u2f(ld_acquire_gpu(&ws->gamax_bits)), strategy), tid);
+        __syncthreads();
+        for (int k = 0; k < kE8Slots; ++k) {
+            const int64_t c = chunk_of(k);
+            if (c >= n_chunks) break;
+            const uint4* v = reinterpret_cast<const uint4*>(s_data + k * kE8Chunk);
+            uint4* o = reinterpret_cast<uint4*>(out + c * kE8Chunk);
+            const int nv = (int)(bytes_of(c) / 16);
+            for (int i = tid; i < nv; i += kE8Threads) {
+                const uint4 x = v[i];
+                uint4 r;
+                r.x = cast.word(x.x); r.y = cast.word(x.y); r.z = cast.word(x.z); r.w = cast.word(x.w);
+                st_stream(o + i, r);
+            }
+        }
+    } else if (tid == 0) {
+        atomicOr(&ws->load_timeout, 1u);   // the other CTAs did not show up: nothing is written
+    }
+    if (!all_landed) {
+        // a copy may still be in flight: one more bounded chance to land before the shared memory is handed on
+        for (int k = 0; k < kE8Slots; ++k)
+            if (chunk_of(k) < n_chunks) mbar_wait_bounded(&s_bar[k], 0);
+    }
+}
+
+template <int M>
+int launch_e8mx_resident_t(const void* in, void* out, int64_t n_bytes, int strategy, ScalarsWs* ws, cudaStream_t st) {
+    static DeviceCaps caps[64];
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return kErrUnsupportedShape;
+    DeviceCaps& c = caps[dev];
+    auto kernel = e8mx_resident_kernel<M>;
+    if (c.checked == 0) {
+        int coop = 0, per_sm = 0;
+        static SmemOptIn opt;
+        if (cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev) == cudaSuccess && coop && opt(kernel, kE8Smem) &&
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kE8Threads, kE8Smem) == cudaSuccess && per_sm >= 1) {
+            c.ctas = sm_count();
+            c.checked = 1;
+        } else {
+            cudaGetLastError();
+            c.checked = -1;
+        }
+    }
+    const int64_t n_chunks = (n_bytes + kE8Chunk - 1) / kE8Chunk;
+    if (c.checked < 0 || n_chunks > (int64_t)c.ctas * kE8Slots) return kErrUnsupportedShape;
+    const int rc = launch_zero_scalars(ws, st);
+    if (rc) return rc;
+    const int grid = (int)(n_chunks < c.ctas ? n_chunks : c.ctas);
+    const uint8_t* in8 = static_cast<const uint8_t*>(in);
+    uint8_t* out8 = static_cast<uint8_t*>(out);
+    uint32_t limit = kSpinLimit;
+    void* args[] = {&in8, &out8, &n_bytes, &strategy, &ws, &limit};
+    if (cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), dim3((unsigned)grid), dim3(kE8Threads), args,
+                                    (size_t)kE8Smem, st) != cudaSuccess) {
+        cudaGetLastError();   // the grid cannot be resident: the launch sequence takes over, now and from here on
+        c.checked = -1;
+        return kErrUnsupportedShape;
+    }
+    return kOk;
+}
+
 }  // namespace
 
 // kErrUnsupportedShape: the tensor is not one this kernel takes (too large, other blocks, ss_mode 3, a
@@ -437,6 +579,20 @@ int launch_block_resident(const ScalingArgs& a, int32_t* meta, float* gamax, voi
                              : launch_resident_t<Fp32, false>(a, meta, gamax, gnnz, nnz_is_i64, gerr, st);
     return e8 ? launch_resident_t<Bf16, true>(a, meta, gamax, gnnz, nnz_is_i64, gerr, st)
               : launch_resident_t<Bf16, false>(a, meta, gamax, gnnz, nnz_is_i64, gerr, st);
+}
+
+// kErrUnsupportedShape: not a tensor for the single launch (too large, a length that is no multiple of 16 bytes,
+// no cooperative launch): the caller runs the amax kernel and the element kernel instead.
+int launch_e8mx_resident(const void* in, void* out, int64_t n_elems, int qtype, int strategy, ScalarsWs* ws,
+                         cudaStream_t st) {
+    const int64_t n_bytes = n_elems * 2;
+    if (n_bytes % 16 || resident_disabled() || force_generic()) return kErrUnsupportedShape;
+    switch (qtype) {
+        case 1: return launch_e8mx_resident_t<1>(in, out, n_bytes, strategy, ws, st);
+        case 2: return launch_e8mx_resident_t<2>(in, out, n_bytes, strategy, ws, st);
+        case 3: return launch_e8mx_resident_t<3>(in, out, n_bytes, strategy, ws, st);
+        default: return kErrInvalidArgument;
+    }
 }
 
 }  // namespace morb

@@ -106,6 +106,8 @@ int launch_fallback_transpose(const ScalingArgs& a, cudaStream_t st);   // out_t
 // that fit in the shared memories of the device (kErrUnsupportedShape otherwise: use the phases above)
 int launch_block_resident(const ScalingArgs& a, int32_t* meta, float* gamax, void* gnnz, int nnz_is_i64, float* gerr,
                           cudaStream_t st);
+int launch_e8mx_resident(const void* in, void* out, int64_t n_elems, int qtype, int strategy, ScalarsWs* ws,
+                         cudaStream_t st);
 
 // ---- fq_block.cu: fake_quantize per-block modes (MoR, block E4M3 / E5M2) ----------
 int launch_fq_block(const void* in, void* out, int is_fp32, int32_t* meta, int64_t rows, int64_t cols, int brows,

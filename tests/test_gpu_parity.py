@@ -146,9 +146,10 @@ def test_group_scaled_with_nan_and_inf_elements(by):
 @pytest.mark.parametrize("qtype", [1, 2, 3])
 @pytest.mark.parametrize("strategy", [0, 1])
 @pytest.mark.parametrize("top", [0x7F7F, 0x4680, 0x3F80, 0x0200])
-def test_e8mx_every_bf16_pattern(qtype, strategy, top):
+def test_e8mx_every_bf16_pattern(qtype, strategy, top, selection):
     """E8Mx on every finite bf16 pattern up to a largest magnitude `top` (which sets the tensor scale under strategy 1):
-    the tabulated offsets of the fast path, the literal path at both ends of the exponent range, zeros of both signs"""
+    the tabulated offsets of the fast path, the literal path at both ends of the exponent range, zeros of both signs;
+    through the single launch that small tensors take and through the amax kernel + element kernel"""
     import gpu_harness as H
     mags = np.arange(0, top + 1, dtype=np.uint32)
     pats = np.concatenate([mags, mags | 0x8000]).astype(np.uint16)
@@ -161,6 +162,20 @@ def test_e8mx_every_bf16_pattern(qtype, strategy, top):
     got = H.e8mx(x, qtype, strategy)["out"]
     bad = np.nonzero(got.reshape(-1) != exp.reshape(-1))[0]
     assert bad.size == 0, f"e8m{qtype} strategy {strategy}: {bad.size} differ, e.g. in {x.reshape(-1)[bad[:5]]} got {got.reshape(-1)[bad[:5]]} want {exp.reshape(-1)[bad[:5]]}"
+
+
+@pytest.mark.parametrize("rows,cols", [(1000, 520), (148 * 7 * 4, 4096), (148 * 7 * 4 + 1, 4096), (3, 8)])
+def test_e8mx_single_launch_sizes(rows, cols, selection):
+    """the single-launch E8Mx kernel keeps up to 148 x 7 chunks of 32 KiB in shared memory: a ragged last chunk,
+    exactly the capacity, one row more (the launch sequence takes over), a tensor smaller than one chunk"""
+    import gpu_harness as H
+    from ref_fixtures import bf16_bits
+    g = torch.Generator().manual_seed(rows)
+    x = bf16_bits((torch.randn(rows, cols, generator=g) * 3.0).to(torch.bfloat16))
+    x[0, 0] = 0x0000; x[0, 1] = 0x8000; x[rows - 1, cols - 1] = 0x4680   # zeros of both signs; the largest magnitude last
+    exp, _ = oracle.e8mx(x, 3, 1)
+    got = H.e8mx(x, 3, 1)["out"]
+    assert np.array_equal(got, exp), f"e8m3 {rows}x{cols}"
 
 
 def test_unscaled_casts_every_bf16_pattern_and_neighbours():
