@@ -1399,8 +1399,18 @@ int launch_block_t(const ScalingArgs& a, bool store, bool skip, cudaStream_t st)
     do {                                                                                                             \
         static SmemOptIn opt;                                                                                        \
         if (!opt(block_tile128_kernel<T, E, true, true>, Tile128<T>::kBytes)) return kErrLaunch;                     \
-        block_tile128_kernel<T, E, true, true><<<(unsigned)nb, TH, Tile128<T>::kBytes, st>>>(                         \
-            map, out, cols_vec, (int)bx, a.ss_mode, a.block_amax, a.block_err, a.ws, a.ext_gamax, 0);                \
+        /* behind the one-thread kernel that clears the scalars: the tiles are requested while it runs */             \
+        cudaLaunchConfig_t cfg = {};                                                                                 \
+        cfg.gridDim = dim3((unsigned)nb); cfg.blockDim = dim3(TH);                                                   \
+        cfg.dynamicSmemBytes = Tile128<T>::kBytes; cfg.stream = st;                                                  \
+        cudaLaunchAttribute attr[1];                                                                                 \
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                                             \
+        attr[0].val.programmaticStreamSerializationAllowed = 1;                                                      \
+        cfg.attrs = attr; cfg.numAttrs = 1;                                                                          \
+        typename T::vec_t* no_t = nullptr;                                                                           \
+        if (cudaLaunchKernelEx(&cfg, block_tile128_kernel<T, E, true, true>, map, out, cols_vec, (int)bx, a.ss_mode, \
+                               (const float*)a.block_amax, a.block_err, a.ws, a.ext_gamax, 0, no_t,                  \
+                               (int64_t)0) != cudaSuccess) { cudaGetLastError(); return kErrLaunch; }                \
     } while (0)
             if (!store || skip) return kErrInvalidArgument;
             if (a.out_t) {
@@ -1410,9 +1420,16 @@ int launch_block_t(const ScalingArgs& a, bool store, bool skip, cudaStream_t st)
     do {                                                                                                             \
         static SmemOptIn opt;                                                                                        \
         if (!opt(block_tile128_kernel<T, E, true, true, true>, Tile128<T>::kBytes)) return kErrLaunch;               \
-        block_tile128_kernel<T, E, true, true, true><<<(unsigned)nb, TH, Tile128<T>::kBytes, st>>>(                   \
-            map, out, cols_vec, (int)bx, a.ss_mode, a.block_amax, a.block_err, a.ws, a.ext_gamax, 0, out_t,           \
-            a.rows / EPVT);                                                                                           \
+        cudaLaunchConfig_t cfg = {};                                                                                 \
+        cfg.gridDim = dim3((unsigned)nb); cfg.blockDim = dim3(TH);                                                   \
+        cfg.dynamicSmemBytes = Tile128<T>::kBytes; cfg.stream = st;                                                  \
+        cudaLaunchAttribute attr[1];                                                                                 \
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                                             \
+        attr[0].val.programmaticStreamSerializationAllowed = 1;                                                      \
+        cfg.attrs = attr; cfg.numAttrs = 1;                                                                          \
+        if (cudaLaunchKernelEx(&cfg, block_tile128_kernel<T, E, true, true, true>, map, out, cols_vec, (int)bx,      \
+                               a.ss_mode, (const float*)a.block_amax, a.block_err, a.ws, a.ext_gamax, 0, out_t,      \
+                               (int64_t)(a.rows / EPVT)) != cudaSuccess) { cudaGetLastError(); return kErrLaunch; }  \
     } while (0)
                 if (e8) MORB_TILE_T(true); else MORB_TILE_T(false);
 #undef MORB_TILE_T
