@@ -155,6 +155,7 @@ block_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename T::vec_t
                 tma_load_2d(s_tile + (j * NS + sidx) * 4096, &tmap, bx * 128 + sidx * EPS, by * 128 + j * 32, &s_bar[j]);
         }
     }
+    pdl_launch_dependents();   // the kernel behind this one (the ordered sum of the block errors) may become resident
     // When launched as a programmatic dependent (the row-sharded pipeline does, behind the kernel that exchanges
     // the amax), this CTA may be running before that kernel has finished: the tile is input data and was requested
     // above, everything the earlier kernels produce (block amax, scalars, the gathered amax) is read below.
@@ -1231,6 +1232,8 @@ finalize_kernel(const float* __restrict__ block_err, int64_t n_err, int stride, 
                 float* gamax_out, void* gnnz_out, int nnz_is_i64, float* gerr_out) {
     __shared__ float wsum[32];
     extern __shared__ float s_chunk[];  // chunk_elems floats
+    pdl_launch_dependents();   // the conditional copy behind this kernel may become resident; it waits for the decision
+    pdl_wait();                // the error sums come from the kernel before this one
     const int t = threadIdx.x;
     float acc = 0.0f;
     // The additions of a thread are sequential by definition; what can be hidden is the
@@ -1307,6 +1310,8 @@ __global__ void __launch_bounds__(kChainThreads) chain_sum_kernel(const float* _
     // [chain][row], rows padded by four floats: the eight adding lanes read 16 bytes each from eight different
     // bank groups, the 32 lanes of a staging warp (8 chains x 4 rows) write 32 different banks
     __shared__ __align__(16) float s_rows[kChainsPerCta][kChainRows + 4];
+    pdl_launch_dependents();
+    pdl_wait();                // the error sums come from the kernel before this one
     const int ch = threadIdx.x & 7, ry = threadIdx.x >> 3;
     const int j = blockIdx.x * kChainsPerCta + ch;
     const int64_t rows = (n_err + period - 1) / period;
@@ -1354,6 +1359,7 @@ __global__ void __launch_bounds__(kChainThreads) chain_sum_kernel(const float* _
 
 __global__ void __launch_bounds__(256) fallback_copy_kernel(const uint4* __restrict__ in, uint4* __restrict__ out,
                                                             int64_t nvec, const ScalarsWs* __restrict__ ws) {
+    pdl_wait();                // the decision comes from the kernel before this one
     if (!ws->fallback) return;
     const int64_t stride = (int64_t)gridDim.x * 256;
     for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < nvec; i += stride) st_stream(out + i, ld_stream(in + i));
@@ -1621,9 +1627,10 @@ int launch_finalize(const ScalingArgs& a, const long long* ext_nnz, int32_t* met
     if (n > 2 * kMaxChunk) {  // spread the independent sequential sums over CTAs first
         const int period = 1024 / a.err_slot_stride;
         float* chains = reinterpret_cast<float*>(reinterpret_cast<char*>(a.ws) + kChainSumsOffset);
-        chain_sum_kernel<<<period / kChainsPerCta, kChainThreads, 0, st>>>(err, n, period, chains);
-        const int rc = check_launch();
-        if (rc) return rc;
+        if (launch_pdl(chain_sum_kernel, dim3(period / kChainsPerCta), dim3(kChainThreads), 0, st, err, n, period, chains) != cudaSuccess) {
+            cudaGetLastError();
+            return kErrLaunch;
+        }
         err = chains;
         n = period;
     }
@@ -1633,8 +1640,11 @@ int launch_finalize(const ScalingArgs& a, const long long* ext_nnz, int32_t* met
     if (smem > 48 * 1024 &&
         cudaFuncSetAttribute(finalize_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxChunk * (int)sizeof(float)) != cudaSuccess)
         return kErrLaunch;
-    finalize_kernel<<<1, 1024, smem, st>>>(err, n, a.err_slot_stride, chunk, a.threshold, a.ws,
-                                           a.ext_gamax, ext_nnz, meta, gamax, gnnz, nnz_is_i64, gerr);
+    if (launch_pdl(finalize_kernel, dim3(1), dim3(1024), smem, st, err, n, a.err_slot_stride, chunk, a.threshold, a.ws,
+                   a.ext_gamax, ext_nnz, meta, gamax, gnnz, nnz_is_i64, gerr) != cudaSuccess) {
+        cudaGetLastError();
+        return kErrLaunch;
+    }
     return check_launch();
 }
 
@@ -1655,7 +1665,11 @@ int launch_fallback_copy(const ScalingArgs& a, cudaStream_t st) {
     int64_t grid = (nvec + 255) / 256;
     const int64_t cap = (int64_t)sm_count() * 8;
     if (grid > cap) grid = cap;
-    fallback_copy_kernel<<<(unsigned)grid, 256, 0, st>>>(static_cast<const uint4*>(a.in), static_cast<uint4*>(a.out), nvec, a.ws);
+    if (launch_pdl(fallback_copy_kernel, dim3((unsigned)grid), dim3(256), 0, st, static_cast<const uint4*>(a.in),
+                   static_cast<uint4*>(a.out), nvec, static_cast<const ScalarsWs*>(a.ws)) != cudaSuccess) {
+        cudaGetLastError();
+        return kErrLaunch;
+    }
     return check_launch();
 }
 

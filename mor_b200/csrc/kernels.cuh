@@ -11,7 +11,23 @@
 namespace morb {
 
 int sm_count();                 // SMs of the current device (cached per device)
-int check_launch();             // cudaGetLastError() -> status code
+int check_launch();
+
+// Launch as a programmatic dependent of the kernel before it in the stream: the grid may become resident once every
+// CTA of that kernel has executed griddepcontrol.launch_dependents (or exited); what it reads from earlier kernels it
+// reads after its own griddepcontrol.wait, which returns when the kernel before it has completed.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }             // cudaGetLastError() -> status code
 // test switches (mor_b200_debug_kernel_selection)
 bool force_generic();           // skip the TMA-staged tile kernels and the single-pass group kernels
 bool resident_disabled();       // skip the single-launch kernel for tensors that fit in shared memory
