@@ -398,7 +398,7 @@ def main():
 
     # ---- where a step's time goes: CUDA events around every phase, in a loop of its own (outside the timed region)
     phase_events = {}
-    names = {"amax_nnz": "amax", "amax_nnz_local": "amax", "exchange_scalars": "exchange1", "cast": "cast",
+    names = {"amax_nnz": "amax", "amax_nnz_local": "amax", "amax_nnz_exchange": "amax", "exchange_scalars": "exchange1", "cast": "cast",
              "exchange_errors": "exchange2", "finalize": "sum", "finalize_ptr": "sum", "fallback": "fallback"}
     originals = []
     for bk in op.backends:
@@ -408,8 +408,10 @@ def main():
 
             def timed(*a, _inner=inner, _label=label):
                 s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                s.record(); _inner(*a); e.record()   # on the stream the phase is enqueued on
-                phase_events.setdefault(_label, []).append((s, e))
+                s.record(); r = _inner(*a); e.record()   # on the stream the phase is enqueued on
+                if r is not False:                       # False: nothing was launched, the caller takes another way
+                    phase_events.setdefault(_label, []).append((s, e))
+                return r
             setattr(bk, meth, timed)
     barrier()
     n_phase_steps = 8
@@ -420,6 +422,7 @@ def main():
         setattr(bk, meth, inner)
     # the first two steps start on an idle device (their events also see the host's launch latency): left out
     phases_ms = {k: statistics.mean(s.elapsed_time(e) for s, e in v[2 * len(v) // n_phase_steps:]) for k, v in phase_events.items()}
+    # with the exchange of the amax built into the amax kernel there is no "exchange1" of its own: it is part of "amax"
     order = ["amax", "exchange1", "cast", "exchange2", "sum", "fallback"]
     t = torch.tensor([step_ms] + [phases_ms.get(k, 0.0) for k in order], dtype=torch.float64, device=dev)
     if world > 1:

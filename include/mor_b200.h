@@ -267,6 +267,16 @@ MOR_B200_API void mor_b200_p2p_set_wait_limit(uint32_t polls);
 MOR_B200_API size_t mor_b200_p2p_error_offset(int world, int64_t n_err, uint32_t epoch);
 MOR_B200_API int mor_b200_p2p_exchange_scalars(void* workspace, void* my_buf, void* const* peer_bufs, int rank, int world,
                                   uint32_t epoch, float* global_amax, int64_t* global_nnz, void* stream);
+/* Phase 1 and the exchange of its scalars in one kernel (no reference counterpart): as mor_b200_scaling_amax,
+ * and the CTA that finishes last stores the slab's amax and count into every peer's buffer, flags, waits
+ * (bounded) for the peers' and writes the tensor's amax and count to global_amax / global_nnz -- what
+ * mor_b200_p2p_exchange_scalars does in a launch of its own.  MOR_B200_ERR_UNSUPPORTED_SHAPE, with nothing
+ * launched, for block shapes whose amax kernel has no built-in exchange (k x 1 and long 1 x k groups, flat
+ * tensors): call the two separately then. */
+MOR_B200_API int mor_b200_scaling_amax_p2p(int kind, const void* input, int dtype, int64_t rows, int64_t cols,
+                              int block_rows, int block_cols, void* workspace, size_t workspace_bytes, void* my_buf,
+                              void* const* peer_bufs, int rank, int world, uint32_t epoch, float* global_amax,
+                              int64_t* global_nnz, void* stream);
 MOR_B200_API int mor_b200_p2p_exchange_errors(const float* local_err, int64_t n_err, const void* my_buf,
                                  void* const* peer_bufs, int rank, int world, uint32_t epoch, void* workspace,
                                  void* stream);

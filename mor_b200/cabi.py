@@ -53,8 +53,12 @@ SIGNATURES = {
     "mor_b200_p2p_set_wait_limit": (None, [C.c_uint32]),
     "mor_b200_p2p_error_offset": (_sz, [_i, _i64, C.c_uint32]),
     "mor_b200_p2p_exchange_scalars": (_i, [_vp, _vp, _vp, _i, _i, C.c_uint32, _vp, _vp, _vp]),
+    "mor_b200_scaling_amax_p2p": (_i, [_i, _vp, _i, _i64, _i64, _i, _i, _vp, _sz, _vp, _vp, _i, _i, C.c_uint32, _vp, _vp, _vp]),
     "mor_b200_p2p_exchange_errors": (_i, [_vp, _i64, _vp, _vp, _i, _i, C.c_uint32, _vp, _vp]),
 }
+
+
+ERR_UNSUPPORTED_SHAPE = -2   # MOR_B200_ERR_UNSUPPORTED_SHAPE
 
 
 class MorB200Error(RuntimeError):

@@ -7,6 +7,7 @@
 #include <cstring>
 
 #include "kernels.cuh"
+#include "p2p.cuh"
 
 using namespace morb;
 
@@ -88,12 +89,16 @@ __global__ void __launch_bounds__(256) copy_if_meta3_kernel(const uint4* __restr
 }
 
 int phase_amax(int kind, const void* in, int dtype, int64_t rows, int64_t cols, int br, int bc, const Geometry& g,
-               ScalarsWs* ws, float* block_amax, cudaStream_t st) {
+               ScalarsWs* ws, float* block_amax, cudaStream_t st, const PeerFuse* fuse = nullptr) {
+    const int is_f32 = dtype == MOR_B200_FP32;
+    const bool flat = kind == MOR_B200_OP_CHANNEL_SCALING && g.n_amax == 0;
+    // the exchange between ranks is built into the kernel of tall-enough blocks only; checked before anything is launched
+    if (fuse && fuse->enabled && (flat || bc == 1 || (br == 1 && (int64_t)bc * (is_f32 ? 4 : 2) % 4096 == 0)))
+        return kErrUnsupportedShape;
     int rc = launch_zero_scalars(ws, st);
     if (rc) return rc;
-    const int is_f32 = dtype == MOR_B200_FP32;
-    if (kind == MOR_B200_OP_CHANNEL_SCALING && g.n_amax == 0) return launch_amax_nnz_flat(in, is_f32, rows * cols, ws, st);
-    return launch_amax_nnz_blocks(in, is_f32, rows, cols, br, bc, block_amax, ws, st);
+    if (flat) return launch_amax_nnz_flat(in, is_f32, rows * cols, ws, st);
+    return launch_amax_nnz_blocks(in, is_f32, rows, cols, br, bc, block_amax, ws, st, fuse);
 }
 
 int phase_cast(int kind, const ScalingArgs& a, bool store, bool skip_if_fallback, cudaStream_t st) {
@@ -438,6 +443,25 @@ int mor_b200_scaling_amax(int kind, const void* in, int dtype, int64_t rows, int
     if (!amax_out && !nnz_out) return kOk;   // the caller takes them from the workspace head (peer exchange)
     export_scalars_kernel<<<1, 1, 0, st>>>(ws, amax_out, reinterpret_cast<long long*>(nnz_out));
     return check_launch();
+}
+
+int mor_b200_scaling_amax_p2p(int kind, const void* in, int dtype, int64_t rows, int64_t cols, int br, int bc,
+                              void* wsp, size_t wsb, void* my_buf, void* const* peer_bufs, int rank, int world,
+                              uint32_t epoch, float* global_amax, int64_t* global_nnz, void* stream) {
+    if (!in || !my_buf || !global_amax || !global_nnz || (dtype != MOR_B200_BF16 && dtype != MOR_B200_FP32))
+        return kErrInvalidArgument;
+    const Geometry g = geometry(kind, rows, cols, br, bc, dtype);
+    if (g.status) return g.status;
+    if (!aligned16(in)) return kErrUnsupportedShape;
+    if (!wsp || wsb < ws_bytes_for(g) || !aligned16(wsp)) return kErrWorkspace;
+    PeerFuse pf{};
+    if (!p2p_fill_peers(pf.peers, peer_bufs, world) || rank < 0 || rank >= world) return kErrInvalidArgument;
+    pf.mine = static_cast<unsigned char*>(my_buf);
+    pf.gamax_out = global_amax;
+    pf.gnnz_out = reinterpret_cast<long long*>(global_nnz);
+    pf.rank = rank; pf.world = world; pf.epoch = epoch; pf.limit = p2p_wait_limit(); pf.enabled = 1;
+    return phase_amax(kind, in, dtype, rows, cols, br, bc, g, static_cast<ScalarsWs*>(wsp),
+                      reinterpret_cast<float*>(static_cast<char*>(wsp) + kHead), static_cast<cudaStream_t>(stream), &pf);
 }
 
 int mor_b200_scaling_cast(int kind, const void* in, void* out, int dtype, int64_t rows, int64_t cols, int br, int bc,

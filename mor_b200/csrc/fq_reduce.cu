@@ -11,6 +11,7 @@
 // reference's fmaxf ignores and never counts, show up as a packed maximum above
 // 0x7F80; a CTA that sees one redoes its part with float compares.
 #include "kernels.cuh"
+#include "p2p.cuh"
 #include "tma.cuh"
 
 namespace morb {
@@ -202,6 +203,27 @@ __global__ void __launch_bounds__(kThreads) amax_nnz_flat_kernel(const typename 
     }
 }
 
+// The warp that exchanges the slab's scalars with the other ranks from inside the amax kernel: waits (bounded) until
+// every CTA of the grid has counted itself in, then publishes and gathers.  Not inlined: its registers are not the
+// amax loop's business.
+__device__ __noinline__ void last_cta_exchange(ScalarsWs* ws, const PeerFuse* fusep) {
+    const PeerFuse& fuse = *fusep;
+    bool all_in = false;
+    if ((threadIdx.x & 31) == 0) {
+        for (uint32_t i = 0; i < kSpinLimit; ++i) {
+            uint32_t seen;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(&ws->bar[0]) : "memory");
+            if (seen >= gridDim.x) { all_in = true; break; }
+            __nanosleep(100);
+        }
+        if (!all_in) atomicOr(&ws->load_timeout, 1u);   // reported as meta = -1 by the decision kernel
+    }
+    all_in = __shfl_sync(0xFFFFFFFFu, (int)all_in, 0) != 0;
+    if (all_in)
+        exchange_scalars_warp(ws, fuse.mine, fuse.peers, fuse.rank, fuse.world, fuse.epoch, fuse.gamax_out, fuse.gnnz_out,
+                              fuse.limit);
+}
+
 // One CTA per (brows x bcols) block.  W lanes (a power of two) span a block row in
 // 16-byte vectors, 256 / W rows are in flight per step; no division in the loops.
 template <typename T>
@@ -209,7 +231,7 @@ __global__ void __launch_bounds__(kThreads, 8) amax_nnz_blocks_kernel(const type
                                                                    int64_t cols_vec, int brows, int bcols_vec,
                                                                    int64_t blocks_x, int w_shift,
                                                                    float* __restrict__ block_amax,
-                                                                   ScalarsWs* __restrict__ ws) {
+                                                                   ScalarsWs* __restrict__ ws, const __grid_constant__ PeerFuse fuse) {
     // Launched as a programmatic dependent of the kernel that clears the scalars: the loads below may run before
     // that kernel has finished (the tensor was complete before it started), the results are published after
     // griddepcontrol.wait.  The kernel behind this one (the exchange of the amax between ranks, or the cast) may in
@@ -265,6 +287,17 @@ __global__ void __launch_bounds__(kThreads, 8) amax_nnz_blocks_kernel(const type
         asm volatile("griddepcontrol.wait;" ::: "memory");   // the scalars have been cleared
         publish(ws, amax, nnz);
         if (flags) atomicOr(&ws->div_unsafe, 1u);
+    }
+    if (fuse.enabled) {
+        // Row-sharded tensors: the CTA with the highest index -- scheduled last, so little is left to wait for --
+        // exchanges the slab's amax and count with the other ranks over NVLink itself (stores into every peer's
+        // buffer, epoch flags, a bounded wait for theirs), so that the collective needs no launch of its own.  Every
+        // CTA counts itself in with a release (its results are visible before the count); the exchanging warp waits,
+        // bounded, for the full count.  The counter is the first grid-barrier word of the workspace, cleared with the
+        // scalars.
+        if (threadIdx.x == 0)
+            asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(&ws->bar[0]) : "memory");
+        if (blockIdx.x == gridDim.x - 1 && threadIdx.x < 32) last_cta_exchange(ws, &fuse);
     }
 }
 
@@ -472,11 +505,12 @@ int launch_amax_nnz_flat(const void* in, int is_fp32, int64_t n_elems, ScalarsWs
 }
 
 int launch_amax_nnz_blocks(const void* in, int is_fp32, int64_t rows, int64_t cols, int brows, int bcols,
-                           float* block_amax, ScalarsWs* ws, cudaStream_t st) {
+                           float* block_amax, ScalarsWs* ws, cudaStream_t st, const PeerFuse* fuse) {
     const int epv = is_fp32 ? 4 : 8;
     if (cols % epv) return kErrUnsupportedShape;
     const int64_t cols_vec = cols / epv;
     if (bcols == 1) {
+        if (fuse && fuse->enabled) return kErrUnsupportedShape;   // the exchange is built into the block kernel only
         // column groups: block index = row_block * cols + column
         const int64_t n_amax = (rows / brows) * cols;
         zero_floats_kernel<<<(int)((n_amax + 255) / 256 < 1024 ? (n_amax + 255) / 256 : 1024), 256, 0, st>>>(block_amax, n_amax);
@@ -493,6 +527,7 @@ int launch_amax_nnz_blocks(const void* in, int is_fp32, int64_t rows, int64_t co
     const int64_t bx = cols / bcols, nb = bx * (rows / brows);
     if (nb > 0x7FFFFFFF) return kErrTooLarge;
     if (brows == 1 && bcols_vec % kFlatChunkVec == 0 && bcols_vec / kFlatChunkVec <= 4096) {
+        if (fuse && fuse->enabled) return kErrUnsupportedShape;
         constexpr int kRing = kFlatWarps * kFlatStages * kFlatChunkVec * 16;
         static SmemOptIn opt32, opt16;
         if (!(is_fp32 ? opt32(amax_nnz_runs_kernel<Fp32>, kRing) : opt16(amax_nnz_runs_kernel<Bf16>, kRing))) return kErrLaunch;
@@ -504,6 +539,8 @@ int launch_amax_nnz_blocks(const void* in, int is_fp32, int64_t rows, int64_t co
     }
     int w_shift = 0;
     while ((2 << w_shift) <= bcols_vec && (2 << w_shift) <= kThreads) ++w_shift;  // largest power of two <= min(bcols_vec, 256)
+    PeerFuse pf{};
+    if (fuse) pf = *fuse;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)nb); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = 0; cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -511,8 +548,8 @@ int launch_amax_nnz_blocks(const void* in, int is_fp32, int64_t rows, int64_t co
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
     const cudaError_t e = is_fp32
-        ? cudaLaunchKernelEx(&cfg, amax_nnz_blocks_kernel<Fp32>, static_cast<const float4*>(in), cols_vec, brows, bcols_vec, bx, w_shift, block_amax, ws)
-        : cudaLaunchKernelEx(&cfg, amax_nnz_blocks_kernel<Bf16>, static_cast<const uint4*>(in), cols_vec, brows, bcols_vec, bx, w_shift, block_amax, ws);
+        ? cudaLaunchKernelEx(&cfg, amax_nnz_blocks_kernel<Fp32>, static_cast<const float4*>(in), cols_vec, brows, bcols_vec, bx, w_shift, block_amax, ws, pf)
+        : cudaLaunchKernelEx(&cfg, amax_nnz_blocks_kernel<Bf16>, static_cast<const uint4*>(in), cols_vec, brows, bcols_vec, bx, w_shift, block_amax, ws, pf);
     if (e != cudaSuccess) { cudaGetLastError(); return kErrLaunch; }
     return check_launch();
 }

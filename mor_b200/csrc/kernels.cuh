@@ -85,8 +85,11 @@ int launch_zero_scalars(ScalarsWs* ws, cudaStream_t st);
 // amax and nnz of a flat tensor (phase 1 of e8mx and of the row-sharded pipeline)
 int launch_amax_nnz_flat(const void* in, int is_fp32, int64_t n_elems, ScalarsWs* ws, cudaStream_t st);
 // per-block amax (brows x bcols blocks, natural row-major block index) + tensor amax/nnz
+// `fuse` (may be null): the last CTA also exchanges the slab's amax and count with the other ranks (p2p.cuh);
+// kErrUnsupportedShape, with nothing launched, for block shapes whose kernel has no such exchange
+struct PeerFuse;
 int launch_amax_nnz_blocks(const void* in, int is_fp32, int64_t rows, int64_t cols, int brows, int bcols,
-                           float* block_amax, ScalarsWs* ws, cudaStream_t st);
+                           float* block_amax, ScalarsWs* ws, cudaStream_t st, const PeerFuse* fuse = nullptr);
 
 // ---- fq_scaling.cu: the amax -> error+cast -> ordered error sum -> fallback pipeline
 struct ScalingArgs {

@@ -16,48 +16,16 @@
 // kernel records the time-out in the workspace head (the call then reports meta = -1) and
 // returns, so a lost peer cannot hang the GPU.
 #include "kernels.cuh"
+#include "p2p.cuh"
 
 namespace morb {
 
 namespace {
 
-constexpr int kMaxWorld = 16;
-constexpr size_t kScalOffset = 0, kScalBytes = 2 * kMaxWorld * 32;
-constexpr size_t kFlagOffset = kScalBytes, kErrOffset = 2048;
 // polls of a wait, x 200 ns of back-off: several seconds by default (ranks start a first call unevenly)
 uint32_t g_spin_limit = 1u << 25;
 
-struct ScalSlot {
-    uint32_t amax_bits;
-    uint32_t pad0;
-    unsigned long long nnz;
-    uint32_t flag;
-    uint32_t pad1[3];
-};
-static_assert(sizeof(ScalSlot) == 32, "slot size");
-
-struct PeerPtrs {
-    unsigned char* p[kMaxWorld];
-};
-
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ bool wait_epoch(const uint32_t* flag, uint32_t epoch, uint32_t limit) {
-    for (uint32_t i = 0; i < limit; ++i) {
-        if (ld_acquire_sys(flag) == epoch) return true;
-        __nanosleep(200);
-    }
-    return false;
-}
-
-// publish, then gather: one warp, lane p talks to rank p.  Every rank stores before it waits, so
-// the waits cannot form a cycle.
+// the same exchange as a kernel of its own
 __global__ void p2p_exchange_scalars_kernel(ScalarsWs* __restrict__ ws, unsigned char* __restrict__ mine, PeerPtrs peers,
                                             int rank, int world, uint32_t epoch, float* __restrict__ gamax_out,
                                             long long* __restrict__ gnnz_out, uint32_t limit) {
@@ -65,32 +33,7 @@ __global__ void p2p_exchange_scalars_kernel(ScalarsWs* __restrict__ ws, unsigned
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // this kernel itself may have been launched ahead of the end of the amax kernel: wait for its scalars
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int p = threadIdx.x;
-    const uint32_t par = epoch & 1u;
-    uint32_t amax_bits = 0u;
-    unsigned long long nnz = 0ull;
-    bool ok = true;
-    if (p < world) {
-        ScalSlot* out = reinterpret_cast<ScalSlot*>(peers.p[p] + kScalOffset) + par * kMaxWorld + rank;
-        out->amax_bits = ws->gamax_bits;
-        out->nnz = ws->gnnz;
-        __threadfence_system();
-        st_release_sys(&out->flag, epoch);
-        const ScalSlot* in = reinterpret_cast<const ScalSlot*>(mine + kScalOffset) + par * kMaxWorld + p;
-        ok = wait_epoch(&in->flag, epoch, limit);
-        if (ok) {
-            amax_bits = *reinterpret_cast<const volatile uint32_t*>(&in->amax_bits);
-            nnz = *reinterpret_cast<const volatile unsigned long long*>(&in->nnz);
-        }
-    }
-    if (!__all_sync(0xFFFFFFFFu, ok) && p == 0) atomicOr(&ws->load_timeout, 1u);
-    amax_bits = __reduce_max_sync(0xFFFFFFFFu, amax_bits);   // non-negative floats order like their bit patterns
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) nnz += __shfl_xor_sync(0xFFFFFFFFu, nnz, o);
-    if (p == 0) {
-        *gamax_out = u2f(amax_bits);
-        *gnnz_out = (long long)nnz;
-    }
+    exchange_scalars_warp(ws, mine, peers, rank, world, epoch, gamax_out, gnnz_out, limit);
 }
 
 __global__ void __launch_bounds__(256) p2p_push_errors_kernel(const float* __restrict__ local_err, int64_t n_err,
@@ -117,7 +60,7 @@ __global__ void p2p_flag_wait_errors_kernel(const unsigned char* __restrict__ mi
     if (!__all_sync(0xFFFFFFFFu, ok) && p == 0) atomicOr(&ws->load_timeout, 1u);
 }
 
-bool fill_peers(PeerPtrs& pp, void* const* peer_bufs, int world) {
+bool fill_peers_impl(PeerPtrs& pp, void* const* peer_bufs, int world) {
     if (!peer_bufs || world < 1 || world > kMaxWorld) return false;
     for (int i = 0; i < kMaxWorld; ++i) pp.p[i] = nullptr;
     for (int i = 0; i < world; ++i) {
@@ -130,6 +73,8 @@ bool fill_peers(PeerPtrs& pp, void* const* peer_bufs, int world) {
 }  // namespace
 
 void p2p_set_wait_limit(uint32_t polls) { g_spin_limit = polls ? polls : 1u; }
+uint32_t p2p_wait_limit() { return g_spin_limit; }
+bool p2p_fill_peers(PeerPtrs& pp, void* const* peer_bufs, int world) { return fill_peers_impl(pp, peer_bufs, world); }
 
 size_t p2p_buffer_bytes(int world, int64_t n_err) {
     if (world < 1 || world > kMaxWorld || n_err < 1) return 0;
@@ -142,7 +87,7 @@ size_t p2p_error_offset(int world, int64_t n_err, uint32_t epoch) {
 int launch_p2p_exchange_scalars(ScalarsWs* ws, void* mine, void* const* peer_bufs, int rank, int world, uint32_t epoch,
                                 float* gamax_out, long long* gnnz_out, cudaStream_t st) {
     PeerPtrs pp;
-    if (!ws || !mine || !gamax_out || !gnnz_out || !fill_peers(pp, peer_bufs, world) || rank < 0 || rank >= world)
+    if (!ws || !mine || !gamax_out || !gnnz_out || !fill_peers_impl(pp, peer_bufs, world) || rank < 0 || rank >= world)
         return kErrInvalidArgument;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(1); cfg.blockDim = dim3(32); cfg.dynamicSmemBytes = 0; cfg.stream = st;
@@ -157,7 +102,7 @@ int launch_p2p_exchange_scalars(ScalarsWs* ws, void* mine, void* const* peer_buf
 int launch_p2p_exchange_errors(const float* local_err, int64_t n_err, const void* mine, void* const* peer_bufs, int rank,
                                int world, uint32_t epoch, ScalarsWs* ws, cudaStream_t st) {
     PeerPtrs pp;
-    if (!local_err || n_err < 1 || !mine || !ws || !fill_peers(pp, peer_bufs, world) || rank < 0 || rank >= world)
+    if (!local_err || n_err < 1 || !mine || !ws || !fill_peers_impl(pp, peer_bufs, world) || rank < 0 || rank >= world)
         return kErrInvalidArgument;
     int64_t grid = (n_err + 255) / 256;
     const int64_t cap = (int64_t)sm_count() * 4;

@@ -110,6 +110,20 @@ class CudaBackend:
                   self.bcols, None, None, self.ws.data_ptr(), self.ws_bytes, self._stream())
         self.launches += 2
 
+    def amax_nnz_exchange(self, x, ex: "PeerExchange", epoch: int, amax_out, nnz_out) -> bool:
+        """phase 1 with the exchange of the slab's amax and count built into the amax kernel (its last CTA stores
+        to the peers and waits for theirs); False, with nothing launched, for block shapes whose kernel has none"""
+        try:
+            cabi.call("mor_b200_scaling_amax_p2p", self.kind, x.data_ptr(), self.dt, self.rows, self.cols, self.brows,
+                      self.bcols, self.ws.data_ptr(), self.ws_bytes, ex.mine, ex.peer_array, ex.rank, ex.world, epoch,
+                      amax_out.data_ptr(), nnz_out.data_ptr(), self._stream())
+        except cabi.MorB200Error as e:
+            if e.status == cabi.ERR_UNSUPPORTED_SHAPE:
+                return False
+            raise
+        self.launches += 2
+        return True
+
     def exchange_scalars(self, ex: "PeerExchange", epoch: int, amax_out, nnz_out):
         cabi.call("mor_b200_p2p_exchange_scalars", self.ws.data_ptr(), ex.mine, ex.peer_array, ex.rank, ex.world, epoch,
                   amax_out.data_ptr(), nnz_out.data_ptr(), self._stream())
@@ -238,11 +252,15 @@ class ShardedScaling:
 
     def __init__(self, rows_local: int, cols: int, brows: int, bcols: int, dtype: torch.dtype,
                  device: torch.device, kind: int = KIND_BLOCK, group: Optional[dist.ProcessGroup] = None,
-                 backend=None, exchange: str = "auto", overlap: bool = False):
+                 backend=None, exchange: str = "auto", overlap: bool = False, fused_exchange: bool = False):
         """``exchange``: "nccl" (two all-reduces and an all-gather), "p2p" (stores into peer-mapped
         buffers, :class:`PeerExchange`), or "auto": p2p with the CUDA backend on more than one rank when
         the peer buffers can be set up, NCCL otherwise.  The choice is made once, here, by all ranks
-        together; both give the same bits."""
+        together; both give the same bits.  ``fused_exchange``: with p2p, let the amax kernel's last CTA do
+        the exchange of the amax and the count itself where its block shape allows (no launch in between).
+        Off by default: every CTA then has to count itself in with a release, which keeps it resident a
+        microsecond longer, and on slabs of a GiB and more that costs more than the launch it saves."""
+        self.fused_exchange = fused_exchange
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.device = device
@@ -323,8 +341,9 @@ class ShardedScaling:
             ex = self.peer
             ex.epoch += 1
             ep = ex.epoch
-            b.amax_nnz_local(x)
-            b.exchange_scalars(ex, ep, s["amax"], s["nnz"])
+            if not (self.fused_exchange and b.amax_nnz_exchange(x, ex, ep, s["amax"], s["nnz"])):
+                b.amax_nnz_local(x)
+                b.exchange_scalars(ex, ep, s["amax"], s["nnz"])
         else:
             b.amax_nnz(x, s["amax"], s["nnz"])
             if self.world > 1:

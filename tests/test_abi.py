@@ -21,7 +21,7 @@ def declared_functions():
 
 def test_header_declares_the_expected_surface():
     names = declared_functions()
-    assert len(names) == 33
+    assert len(names) == 34
     for n in ("mor_b200_fake_quantize", "mor_b200_block_scaling", "mor_b200_channel_scaling", "mor_b200_e8mx",
               "mor_b200_quant_dequant", "mor_b200_e4m3_with_e8_scale", "mor_b200_fake_quantize_group",
               "mor_b200_workspace_bytes"):

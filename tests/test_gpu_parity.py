@@ -718,6 +718,57 @@ def test_peer_exchange_wait_runs_out():
             L.mor_b200_p2p_free(0, b)
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_amax_kernel_with_built_in_exchange(dtype):
+    """mor_b200_scaling_amax_p2p: the last CTA of the amax kernel exchanges the slab's amax and count itself.  One GPU:
+    the rank's own slot travels through its own buffer, the second rank is played by the host (its slot is written
+    with a plain copy before the kernel starts, so nothing on this GPU waits for another kernel).  Shapes without a
+    built-in exchange answer MOR_B200_ERR_UNSUPPORTED_SHAPE and launch nothing."""
+    import ctypes
+    import struct
+    from mor_b200 import cabi
+    L = cabi.lib()
+    rt = ctypes.CDLL("libcudart.so.12")
+    rt.cudaMemcpy.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]
+    rows, cols, world = 512, 768, 2
+    dt = getattr(torch, dtype)
+    x = (torch.randn(rows, cols, generator=torch.Generator().manual_seed(3)) * 2.0).to(dt).cuda()
+    x[7, 9] = 0.0
+    code = cabi.BF16 if dt == torch.bfloat16 else cabi.FP32
+    wsb = cabi.workspace_bytes(cabi.OP_BLOCK_SCALING, rows, cols, 128, 128)
+    n_err = 24
+    nbytes = int(L.mor_b200_p2p_bytes(world, n_err))
+    bufs, handle = [], (ctypes.c_ubyte * 64)()
+    for _ in range(world):
+        p = ctypes.c_void_p()
+        cabi.call("mor_b200_p2p_alloc", 0, nbytes, ctypes.byref(p), handle)
+        bufs.append(int(p.value))
+    peers = (ctypes.c_void_p * world)(*bufs)
+    st = torch.cuda.current_stream().cuda_stream
+    amax = torch.zeros(1, dtype=torch.float32, device="cuda")
+    nnz = torch.zeros(1, dtype=torch.int64, device="cuda")
+    try:
+        for epoch, (peer_amax, peer_nnz) in enumerate([(1.0, 10), (1000.0, 7), (0.5, 0)], start=1):
+            ws = torch.zeros(wsb, dtype=torch.uint8, device="cuda")
+            slot = struct.pack("<IIQI12x", int(np.float32(peer_amax).view(np.uint32)), 0, peer_nnz, epoch)
+            assert rt.cudaMemcpy(bufs[0] + ((epoch & 1) * 16 + 1) * 32, slot, len(slot), 1) == 0
+            cabi.call("mor_b200_scaling_amax_p2p", cabi.OP_BLOCK_SCALING, x.data_ptr(), code, rows, cols, 128, 128,
+                      ws.data_ptr(), wsb, bufs[0], peers, 0, world, epoch, amax.data_ptr(), nnz.data_ptr(), st)
+            torch.cuda.synchronize()
+            assert ws[28:32].view(torch.int32).item() == 0, "no wait ran out"
+            assert amax.item() == max(x.float().abs().max().item(), peer_amax)
+            assert nnz.item() == int((x != 0).sum().item()) + peer_nnz
+        ws = torch.zeros(wsb, dtype=torch.uint8, device="cuda")
+        rc = L.mor_b200_scaling_amax_p2p(cabi.OP_CHANNEL_SCALING, x.data_ptr(), code, rows, cols, rows, 1, ws.data_ptr(),
+                                         cabi.workspace_bytes(cabi.OP_CHANNEL_SCALING, rows, cols, rows, 1), bufs[0], peers,
+                                         0, world, 4, amax.data_ptr(), nnz.data_ptr(), st)
+        assert rc == cabi.ERR_UNSUPPORTED_SHAPE
+    finally:
+        torch.cuda.synchronize()
+        for b in bufs:
+            L.mor_b200_p2p_free(0, b)
+
+
 def test_peer_exchange_recovers_with_new_buffers():
     """After a wait ran out (meta = -1) the documented recovery is to drop the exchange buffers and set new ones up,
     with the call counter back at 1.  The absent peer is played by the host here: no second kernel waits on this

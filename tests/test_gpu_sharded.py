@@ -38,7 +38,9 @@ def _worker(rank, world, port, dtype_name, ss_mode, thr, q, exchange, calls, ove
     try:
         dtype = getattr(torch, dtype_name)
         r0, r1 = shard_rows(ROWS, world, rank, 128)
-        op = ShardedScaling(r1 - r0, COLS, 128, 128, dtype, dev, KIND_BLOCK, exchange=exchange, overlap=overlap)
+        # odd numbers of calls: the amax kernel exchanges the scalars itself; even: the exchange kernel of its own
+        op = ShardedScaling(r1 - r0, COLS, 128, 128, dtype, dev, KIND_BLOCK, exchange=exchange, overlap=overlap,
+                            fused_exchange=calls % 2 == 1)
         assert (op.peer is not None) == (exchange == "p2p")
         xs = [make_input(dtype_name, c)[r0:r1].contiguous().to(dev) for c in range(calls)]
         outs = [torch.empty_like(x) for x in xs]
