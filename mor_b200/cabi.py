@@ -78,7 +78,7 @@ def lib() -> C.CDLL:
     if _lib is None:
         if not os.path.exists(LIB_PATH):
             raise ImportError(
-                f"{LIB_PATH} is missing: build it with `python -m mor_b200.build` "
+                f"{LIB_PATH} is missing: build it with `python mor_b200/build.py` "
                 "(nvcc, sm_100a).  mor_b200 has no CPU or PyTorch fallback.")
         L = C.CDLL(LIB_PATH)
         for name, (res, args) in SIGNATURES.items():
