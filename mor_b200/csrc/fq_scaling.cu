@@ -108,7 +108,8 @@ block_err_cast_kernel(const typename T::vec_t* __restrict__ in, typename T::vec_
 // flips.  Shared-memory layout [row group j][strip][32 rows][128 B]: the eight lanes
 // that cover 128 consecutive bytes of a row read eight consecutive 16-byte chunks, so
 // every 16-byte shared load is conflict-free.  No registers hold data in flight, which
-// leaves room for three (binary32) or six (bf16) CTAs per SM.
+// leaves room for three (binary32) or six (bf16) CTAs per SM (five for the bf16 variant that also writes the
+// transposed result: it is faster with the registers of a sixth).
 template <typename T> struct Tile128 {
     static constexpr int kStrips = T::kBytesPerElem;          // 128-byte strips per block row
     static constexpr int kBytes = 128 * 128 * T::kBytesPerElem;
@@ -123,7 +124,7 @@ template <typename T> struct Tile128 {
 // the rotation -- and store 128 contiguous bytes of a transposed row.
 // `out` may then be NULL (transposed output only).
 template <typename T, bool E8, bool STORE, bool SCAN = false, bool TRANS = false>
-__global__ void __launch_bounds__(Tile128<T>::kThreads, Tile128<T>::kCtasPerSm)
+__global__ void __launch_bounds__(Tile128<T>::kThreads, (TRANS && T::kBytesPerElem == 2) ? 5 : Tile128<T>::kCtasPerSm)
 block_tile128_kernel(const __grid_constant__ CUtensorMap tmap, typename T::vec_t* __restrict__ out, int64_t cols_vec,
                      int blocks_x, int ss, const float* __restrict__ block_amax, float* __restrict__ block_err,
                      ScalarsWs* __restrict__ ws, const float* __restrict__ ext_gamax, int skip_if_fallback,
